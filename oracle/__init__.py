@@ -1,0 +1,317 @@
+"""TEST INFRASTRUCTURE - not part of the product.
+
+ctypes access to the two CPU checkers:
+
+* ``liboracle.so``  - the plain-C restatement in ``tc_oracle.c`` (always available after
+  ``make -C oracle``);
+* ``_ref/libtensorcore_ref.so`` - the reference's own portable-CPU backend compiled from its
+  sources (available when it was built where a reference checkout exists; the built file
+  travels with the repository tree, the sources do not).
+
+Only the test suite, ``__graft_entry__.smoke()`` and the CPU-baseline legs of ``bench.py`` may
+import this module.  The product package never does.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from ctypes import POINTER, c_float, c_int, c_size_t, c_void_p
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(_HERE, "liboracle.so")
+REF_SO = os.path.join(_HERE, "_ref", "libtensorcore_ref.so")
+
+Q4_0, Q8_0 = 0, 1
+BLOCK_BYTES = {Q4_0: 18, Q8_0: 34}
+
+
+def build(ref_root: str | None = None) -> None:
+    """Compile liboracle.so and, when a reference checkout is present, _ref/."""
+    args = ["make", "-C", _HERE, "all"]
+    if ref_root:
+        args.append(f"REF={ref_root}")
+    subprocess.run(args, check=True, stdout=subprocess.DEVNULL)
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(ORACLE_SO):
+            build()
+        L = ctypes.CDLL(ORACLE_SO)
+        L.orc_f16_to_f32.argtypes = [ctypes.c_uint16]
+        L.orc_f16_to_f32.restype = c_float
+        L.orc_f32_to_f16.argtypes = [c_float]
+        L.orc_f32_to_f16.restype = ctypes.c_uint16
+        L.orc_quantized_size.argtypes = [c_int, c_int, c_int]
+        L.orc_quantized_size.restype = c_size_t
+        for name in ("orc_f32_to_f16_array", "orc_f16_to_f32_array"):
+            getattr(L, name).argtypes = [c_void_p, c_void_p, c_size_t]
+            getattr(L, name).restype = None
+        _lib = L
+    return _lib
+
+
+def _p(a: np.ndarray) -> c_void_p:
+    assert a.flags["C_CONTIGUOUS"]
+    return c_void_p(a.ctypes.data)
+
+
+def _call(fn, *args):
+    fn.restype = c_int
+    rc = fn(*args)
+    if rc != 0:
+        raise ValueError(f"oracle rejected the arguments (rc={rc})")
+
+
+def f32_to_f16_bits(a: np.ndarray) -> np.ndarray:
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    out = np.empty(a.shape, dtype=np.uint16)
+    lib().orc_f32_to_f16_array(_p(a), _p(out), a.size)
+    return out
+
+
+def f16_bits_to_f32(a: np.ndarray) -> np.ndarray:
+    a = np.ascontiguousarray(a, dtype=np.uint16)
+    out = np.empty(a.shape, dtype=np.float32)
+    lib().orc_f16_to_f32_array(_p(a), _p(out), a.size)
+    return out
+
+
+def quantized_size(fmt: int, N: int, K: int) -> int:
+    return int(lib().orc_quantized_size(fmt, N, K))
+
+
+def quantize_weights(W_f16: np.ndarray, fmt: int) -> np.ndarray:
+    """W_f16: [N,K] float16 (or uint16 bit patterns) -> packed blocks as uint8."""
+    W = np.ascontiguousarray(W_f16).view(np.uint16)
+    N, K = W.shape
+    out = np.empty(quantized_size(fmt, N, K), dtype=np.uint8)
+    _call(lib().orc_quantize_weights, _p(W), _p(out), c_int(fmt), c_int(N), c_int(K))
+    return out
+
+
+def gemv_quantized(X_f16: np.ndarray, Wq: np.ndarray, fmt: int, N: int) -> np.ndarray:
+    X = np.ascontiguousarray(X_f16).view(np.uint16)
+    M, K = X.shape
+    Y = np.empty((M, N), dtype=np.uint16)
+    _call(lib().orc_gemv_quantized, _p(X), _p(Wq), _p(Y), c_int(fmt), c_int(M), c_int(N), c_int(K))
+    return Y.view(np.float16)
+
+
+def gemv_quantized_rows(X_f16, Wq, Y_bits, fmt, N, n_begin, n_end) -> None:
+    """Rows [n_begin, n_end) of gemv_quantized, written into Y_bits ([M,N] uint16)."""
+    X = np.ascontiguousarray(X_f16).view(np.uint16)
+    M, K = X.shape
+    _call(lib().orc_gemv_quantized_rows, _p(X), _p(Wq), _p(Y_bits), c_int(fmt), c_int(M),
+          c_int(N), c_int(K), c_int(n_begin), c_int(n_end))
+
+
+def gemv_quantized_f32(X: np.ndarray, Wq: np.ndarray, fmt: int, N: int) -> np.ndarray:
+    X = np.ascontiguousarray(X, dtype=np.float32)
+    M, K = X.shape
+    Y = np.empty((M, N), dtype=np.float32)
+    _call(lib().orc_gemv_quantized_f32, _p(X), _p(Wq), _p(Y), c_int(fmt), c_int(M), c_int(N),
+          c_int(K))
+    return Y
+
+
+def fused_rmsnorm_gemv_quantized(X_f16, gamma_f16, Wq, fmt, N, eps=1e-5) -> np.ndarray:
+    X = np.ascontiguousarray(X_f16).view(np.uint16)
+    g = np.ascontiguousarray(gamma_f16).view(np.uint16)
+    M, K = X.shape
+    Y = np.empty((M, N), dtype=np.uint16)
+    _call(lib().orc_fused_rmsnorm_gemv_quantized, _p(X), _p(g), _p(Wq), _p(Y), c_int(fmt),
+          c_int(M), c_int(N), c_int(K), c_float(eps))
+    return Y.view(np.float16)
+
+
+def fused_rmsnorm_gemv_quantized_f32(X, gamma, Wq, fmt, N, eps=1e-5) -> np.ndarray:
+    X = np.ascontiguousarray(X, dtype=np.float32)
+    g = np.ascontiguousarray(gamma, dtype=np.float32)
+    M, K = X.shape
+    Y = np.empty((M, N), dtype=np.float32)
+    _call(lib().orc_fused_rmsnorm_gemv_quantized_f32, _p(X), _p(g), _p(Wq), _p(Y), c_int(fmt),
+          c_int(M), c_int(N), c_int(K), c_float(eps))
+    return Y
+
+
+def fused_rmsnorm_gemv(X_f16, gamma_f16, W_f16, eps=1e-5) -> np.ndarray:
+    X = np.ascontiguousarray(X_f16).view(np.uint16)
+    g = np.ascontiguousarray(gamma_f16).view(np.uint16)
+    W = np.ascontiguousarray(W_f16).view(np.uint16)
+    M, K = X.shape
+    N = W.shape[1]
+    Y = np.empty((M, N), dtype=np.uint16)
+    _call(lib().orc_fused_rmsnorm_gemv, _p(X), _p(g), _p(W), _p(Y), c_int(M), c_int(N), c_int(K),
+          c_float(eps))
+    return Y.view(np.float16)
+
+
+def fused_layernorm_gemv(X_f16, gamma_f16, beta_f16, W_f16, eps=1e-5) -> np.ndarray:
+    X = np.ascontiguousarray(X_f16).view(np.uint16)
+    g = np.ascontiguousarray(gamma_f16).view(np.uint16)
+    b = np.ascontiguousarray(beta_f16).view(np.uint16)
+    W = np.ascontiguousarray(W_f16).view(np.uint16)
+    M, K = X.shape
+    N = W.shape[1]
+    Y = np.empty((M, N), dtype=np.uint16)
+    _call(lib().orc_fused_layernorm_gemv, _p(X), _p(g), _p(b), _p(W), _p(Y), c_int(M), c_int(N),
+          c_int(K), c_float(eps))
+    return Y.view(np.float16)
+
+
+def dequant_dot_f64(X: np.ndarray, Wq: np.ndarray, fmt: int, N: int) -> np.ndarray:
+    X = np.ascontiguousarray(X, dtype=np.float64)
+    M, K = X.shape
+    Y = np.empty((M, N), dtype=np.float64)
+    _call(lib().orc_dequant_dot_f64, _p(X), _p(Wq), _p(Y), c_int(fmt), c_int(M), c_int(N),
+          c_int(K))
+    return Y
+
+
+def dequantize(Wq: np.ndarray, fmt: int, N: int, K: int) -> np.ndarray:
+    out = np.empty((N, K), dtype=np.float32)
+    _call(lib().orc_dequantize, _p(Wq), _p(out), c_int(fmt), c_int(N), c_int(K))
+    return out
+
+
+def scaled_rms(got: np.ndarray, want: np.ndarray) -> float:
+    """rms(got - want) / rms(want), the reference's error measure (docs/numerics.md:10-28)."""
+    g = np.asarray(got, dtype=np.float64).ravel()
+    w = np.asarray(want, dtype=np.float64).ravel()
+    den = np.sqrt(np.mean(w * w))
+    num = np.sqrt(np.mean((g - w) ** 2))
+    return float(num / den) if den > 0 else float(num)
+
+
+# --------------------------------------------------------------------------------------
+# The reference's own CPU backend (oracle/_ref), driven through its public tc_* C ABI.
+# --------------------------------------------------------------------------------------
+class RefLib:
+    """Minimal ctypes driver for a libtensorcore-compatible shared library, used on the
+    reference's CPU build.  Buffers are filled and read through tc_buffer_map exactly as the
+    reference's tests do (tests/test_quantized.c:114-138)."""
+
+    def __init__(self, path: str = REF_SO):
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        L = ctypes.CDLL(path)
+        self.L = L
+        vp = c_void_p
+        L.tc_init.argtypes = [POINTER(vp)]
+        L.tc_buffer_alloc.argtypes = [vp, c_size_t, POINTER(vp)]
+        L.tc_buffer_free.argtypes = [vp, vp]
+        L.tc_buffer_map.argtypes = [vp, POINTER(vp)]
+        L.tc_quantized_size.argtypes = [c_int, c_int, c_int]
+        L.tc_quantized_size.restype = c_size_t
+        L.tc_quantize_weights.argtypes = [vp, vp, vp, c_int, c_int, c_int]
+        L.tc_gemv_quantized.argtypes = [vp, vp, vp, vp, c_int, c_int, c_int, c_int]
+        L.tc_fused_rmsnorm_gemv_quantized.argtypes = [vp, vp, vp, vp, vp, c_int, c_int, c_int,
+                                                      c_int, c_float]
+        L.tc_fused_rmsnorm_gemv.argtypes = [vp, vp, vp, vp, vp, c_int, c_int, c_int, c_float]
+        L.tc_fused_layernorm_gemv.argtypes = [vp, vp, vp, vp, vp, vp, c_int, c_int, c_int,
+                                              c_float]
+        ctx = vp()
+        st = L.tc_init(ctypes.byref(ctx))
+        if st not in (0, -2):
+            raise RuntimeError(f"tc_init -> {st}")
+        self.ctx = ctx
+
+    def _buf(self, data: np.ndarray | int):
+        nbytes = data if isinstance(data, int) else data.nbytes
+        h = c_void_p()
+        st = self.L.tc_buffer_alloc(self.ctx, nbytes, ctypes.byref(h))
+        assert st == 0, st
+        p = c_void_p()
+        assert self.L.tc_buffer_map(h, ctypes.byref(p)) == 0
+        if not isinstance(data, int):
+            ctypes.memmove(p, data.ctypes.data, nbytes)
+        return h, p, nbytes
+
+    def _read(self, p, nbytes, dtype):
+        out = np.empty(nbytes // np.dtype(dtype).itemsize, dtype=dtype)
+        ctypes.memmove(out.ctypes.data, p, nbytes)
+        return out
+
+    def _free(self, *hs):
+        for h in hs:
+            self.L.tc_buffer_free(self.ctx, h)
+
+    def quantize_weights(self, W_f16: np.ndarray, fmt: int) -> np.ndarray:
+        W = np.ascontiguousarray(W_f16).view(np.uint16)
+        N, K = W.shape
+        hw, _, _ = self._buf(W)
+        hq, pq, nq = self._buf(int(self.L.tc_quantized_size(fmt, N, K)))
+        st = self.L.tc_quantize_weights(self.ctx, hw, hq, fmt, N, K)
+        assert st == 0, st
+        out = self._read(pq, nq, np.uint8)
+        self._free(hw, hq)
+        return out
+
+    def gemv_quantized(self, X_f16, Wq, fmt, N) -> np.ndarray:
+        X = np.ascontiguousarray(X_f16).view(np.uint16)
+        M, K = X.shape
+        hx, _, _ = self._buf(X)
+        hw, _, _ = self._buf(np.ascontiguousarray(Wq))
+        hy, py, ny = self._buf(M * N * 2)
+        st = self.L.tc_gemv_quantized(self.ctx, hx, hw, hy, fmt, M, N, K)
+        assert st == 0, st
+        out = self._read(py, ny, np.uint16).reshape(M, N).view(np.float16)
+        self._free(hx, hw, hy)
+        return out
+
+    def fused_rmsnorm_gemv_quantized(self, X_f16, gamma_f16, Wq, fmt, N, eps=1e-5):
+        X = np.ascontiguousarray(X_f16).view(np.uint16)
+        M, K = X.shape
+        hx, _, _ = self._buf(X)
+        hg, _, _ = self._buf(np.ascontiguousarray(gamma_f16).view(np.uint16))
+        hw, _, _ = self._buf(np.ascontiguousarray(Wq))
+        hy, py, ny = self._buf(M * N * 2)
+        st = self.L.tc_fused_rmsnorm_gemv_quantized(self.ctx, hx, hg, hw, hy, fmt, M, N, K,
+                                                    c_float(eps))
+        assert st == 0, st
+        out = self._read(py, ny, np.uint16).reshape(M, N).view(np.float16)
+        self._free(hx, hg, hw, hy)
+        return out
+
+    def fused_rmsnorm_gemv(self, X_f16, gamma_f16, W_f16, eps=1e-5):
+        X = np.ascontiguousarray(X_f16).view(np.uint16)
+        W = np.ascontiguousarray(W_f16).view(np.uint16)
+        M, K = X.shape
+        N = W.shape[1]
+        hx, _, _ = self._buf(X)
+        hg, _, _ = self._buf(np.ascontiguousarray(gamma_f16).view(np.uint16))
+        hw, _, _ = self._buf(W)
+        hy, py, ny = self._buf(M * N * 2)
+        st = self.L.tc_fused_rmsnorm_gemv(self.ctx, hx, hg, hw, hy, M, N, K, c_float(eps))
+        assert st == 0, st
+        out = self._read(py, ny, np.uint16).reshape(M, N).view(np.float16)
+        self._free(hx, hg, hw, hy)
+        return out
+
+    def fused_layernorm_gemv(self, X_f16, gamma_f16, beta_f16, W_f16, eps=1e-5):
+        X = np.ascontiguousarray(X_f16).view(np.uint16)
+        W = np.ascontiguousarray(W_f16).view(np.uint16)
+        M, K = X.shape
+        N = W.shape[1]
+        hx, _, _ = self._buf(X)
+        hg, _, _ = self._buf(np.ascontiguousarray(gamma_f16).view(np.uint16))
+        hb, _, _ = self._buf(np.ascontiguousarray(beta_f16).view(np.uint16))
+        hw, _, _ = self._buf(W)
+        hy, py, ny = self._buf(M * N * 2)
+        st = self.L.tc_fused_layernorm_gemv(self.ctx, hx, hg, hb, hw, hy, M, N, K, c_float(eps))
+        assert st == 0, st
+        out = self._read(py, ny, np.uint16).reshape(M, N).view(np.float16)
+        self._free(hx, hg, hb, hw, hy)
+        return out
+
+
+def ref_available() -> bool:
+    return os.path.exists(REF_SO)

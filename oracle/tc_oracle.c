@@ -1,0 +1,364 @@
+/*
+ * TEST INFRASTRUCTURE - not part of the product.  See tc_oracle.h.
+ *
+ * Plain-C restatement of the reference's portable-CPU arithmetic for the quantized-decode
+ * path.  Written from the reference's behaviour, with the same operation order wherever the
+ * order changes a rounding, so that results are bit-identical to the reference's CPU backend.
+ * Build with -ffp-contract=off (no fused multiply-add may replace a multiply and an add).
+ */
+#include "tc_oracle.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define Q4_BLOCK_BYTES 18u
+#define Q8_BLOCK_BYTES 34u
+
+static inline uint32_t bits_of(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+static inline float float_of(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+
+/* lib/core/cpu_float.h:20-43 - exact widening, including subnormals, infinities and NaN
+ * payloads.  A binary16 subnormal is mant * 2^-24, which binary32 represents exactly. */
+float orc_f16_to_f32(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    const uint32_t e = (h >> 10) & 0x1fu;
+    const uint32_t m = h & 0x3ffu;
+    if (e == 0x1fu) return float_of(sign | 0x7f800000u | (m << 13));
+    if (e != 0) return float_of(sign | ((e + 112u) << 23) | (m << 13));
+    /* zero or subnormal */
+    float mag = ldexpf((float)m, -24);
+    return float_of(sign | bits_of(mag));
+}
+
+/* lib/core/cpu_float.h:45-74 - round to nearest, ties to even; overflow gives infinity;
+ * every NaN becomes the quiet pattern 0x7e00 with the input's sign; results below half of the
+ * smallest subnormal flush to signed zero. */
+uint16_t orc_f32_to_f16(float f) {
+    const uint32_t b = bits_of(f);
+    const uint16_t sign = (uint16_t)((b >> 16) & 0x8000u);
+    const uint32_t a = b & 0x7fffffffu;
+
+    if (a >= 0x7f800000u) return (uint16_t)(sign | (a > 0x7f800000u ? 0x7e00u : 0x7c00u));
+    if (a >= 0x47800000u) return (uint16_t)(sign | 0x7c00u);          /* >= 65536 */
+    if (a < 0x33000000u) return sign;                                  /* < 2^-25   */
+    if (a < 0x38800000u) {                                             /* subnormal result */
+        const uint32_t e = a >> 23;                                    /* 102..112 */
+        const uint32_t m = (a & 0x7fffffu) | 0x800000u;
+        const uint32_t sh = 126u - e;                                  /* 14..24 */
+        const uint32_t r = m + ((1u << (sh - 1)) - 1u) + ((m >> sh) & 1u);
+        return (uint16_t)(sign | (r >> sh));
+    }
+    /* normal result: add the rounding increment to the whole word so that a mantissa carry
+     * moves into the exponent by itself, then re-bias. */
+    const uint32_t r = a + 0xfffu + ((a >> 13) & 1u);
+    const uint32_t h = (r - 0x38000000u) >> 13;
+    return (uint16_t)(sign | (h >= 0x7c00u ? 0x7c00u : h));
+}
+
+void orc_f32_to_f16_array(const float* src, uint16_t* dst, size_t n) {
+    for (size_t i = 0; i < n; ++i) dst[i] = orc_f32_to_f16(src[i]);
+}
+void orc_f16_to_f32_array(const uint16_t* src, float* dst, size_t n) {
+    for (size_t i = 0; i < n; ++i) dst[i] = orc_f16_to_f32(src[i]);
+}
+
+static unsigned block_bytes(int fmt) {
+    return fmt == 0 ? Q4_BLOCK_BYTES : (fmt == 1 ? Q8_BLOCK_BYTES : 0u);
+}
+
+/* lib/ops/quantized_cpu.cpp:90-100 */
+size_t orc_quantized_size(int fmt, int N, int K) {
+    const unsigned bb = block_bytes(fmt);
+    if (N <= 0 || K <= 0 || (K % 32) != 0 || bb == 0) return 0;
+    return (size_t)N * (size_t)(K / 32) * bb;
+}
+
+static inline uint16_t load_u16(const uint8_t* p) { uint16_t v; memcpy(&v, p, 2); return v; }
+static inline void store_u16(uint8_t* p, uint16_t v) { memcpy(p, &v, 2); }
+
+/* lib/ops/quantized_cpu.cpp:102-162.
+ * Per 32-weight block: a = max |w| taken in fp32 (a NaN never wins the comparison); the stored
+ * scale is fp16(a / d0) with d0 = 8 (Q4_0) or 127 (Q8_0); codes are lround(w * (d0 / a)),
+ * biased by +8 and clamped to [0,15] for Q4_0, clamped to [-128,127] for Q8_0.  An all-zero
+ * block has scale 0 and inverse 0, hence codes 8 (bytes 0x88) / 0.  Q4_0 byte i carries weight
+ * i in its low nibble and weight i+16 in its high nibble. */
+int orc_quantize_weights(const uint16_t* W, uint8_t* out, int fmt, int N, int K) {
+    const unsigned bb = block_bytes(fmt);
+    if (!W || !out || N <= 0 || K <= 0 || (K % 32) != 0 || bb == 0) return -1;
+    const int nb = K / 32;
+    const float d0 = (fmt == 0) ? 8.0f : 127.0f;
+    for (int n = 0; n < N; ++n) {
+        for (int b = 0; b < nb; ++b) {
+            const uint16_t* src = W + (size_t)n * K + (size_t)b * 32;
+            uint8_t* dst = out + ((size_t)n * nb + b) * bb;
+            float w[32];
+            float amax = 0.0f;
+            for (int i = 0; i < 32; ++i) {
+                w[i] = orc_f16_to_f32(src[i]);
+                const float av = fabsf(w[i]);
+                if (amax < av) amax = av;
+            }
+            const float scale = amax / d0;
+            const float inv = (scale > 0.0f) ? d0 / amax : 0.0f;
+            store_u16(dst, orc_f32_to_f16(scale));
+            if (fmt == 0) {
+                for (int i = 0; i < 16; ++i) {
+                    int lo = (int)lroundf(w[i] * inv) + 8;
+                    int hi = (int)lroundf(w[i + 16] * inv) + 8;
+                    if (lo < 0) lo = 0; else if (lo > 15) lo = 15;
+                    if (hi < 0) hi = 0; else if (hi > 15) hi = 15;
+                    dst[2 + i] = (uint8_t)((hi << 4) | lo);
+                }
+            } else {
+                for (int i = 0; i < 32; ++i) {
+                    int q = (int)lroundf(w[i] * inv);
+                    if (q < -128) q = -128; else if (q > 127) q = 127;
+                    dst[2 + i] = (uint8_t)(int8_t)q;
+                }
+            }
+        }
+    }
+    return 0;
+}
+
+/* The dot product of one activation row (already widened to fp32) with one quantized weight
+ * row, in the reference's order: blocks ascending; inside a Q4_0 block byte i contributes
+ * x[i]*d*(lo-8) then x[i+16]*d*(hi-8); every product is (x*d)*q with two roundings and is then
+ * added to a single fp32 accumulator (lib/ops/quantized_cpu.cpp:193-225, 286-314). */
+static float row_dot(const float* x, const uint8_t* row, int fmt, int nb) {
+    float acc = 0.0f;
+    if (fmt == 0) {
+        for (int b = 0; b < nb; ++b) {
+            const uint8_t* blk = row + (size_t)b * Q4_BLOCK_BYTES;
+            const float d = orc_f16_to_f32(load_u16(blk));
+            const float* xb = x + (size_t)b * 32;
+            for (int i = 0; i < 16; ++i) {
+                const uint8_t p = blk[2 + i];
+                acc += xb[i] * d * (float)((int)(p & 0x0f) - 8);
+                acc += xb[i + 16] * d * (float)((int)(p >> 4) - 8);
+            }
+        }
+    } else {
+        for (int b = 0; b < nb; ++b) {
+            const uint8_t* blk = row + (size_t)b * Q8_BLOCK_BYTES;
+            const float d = orc_f16_to_f32(load_u16(blk));
+            const int8_t* qs = (const int8_t*)(blk + 2);
+            const float* xb = x + (size_t)b * 32;
+            for (int i = 0; i < 32; ++i) acc += xb[i] * d * (float)qs[i];
+        }
+    }
+    return acc;
+}
+
+int orc_gemv_quantized_rows(const uint16_t* X, const uint8_t* Wq, uint16_t* Y,
+                            int fmt, int M, int N, int K, int n_begin, int n_end) {
+    const unsigned bb = block_bytes(fmt);
+    if (!X || !Wq || !Y || M <= 0 || N <= 0 || K <= 0 || (K % 32) != 0 || bb == 0) return -1;
+    if (n_begin < 0 || n_end > N || n_begin > n_end) return -1;
+    const int nb = K / 32;
+    float* x = (float*)malloc((size_t)K * sizeof(float));
+    if (!x) return -1;
+    for (int m = 0; m < M; ++m) {
+        orc_f16_to_f32_array(X + (size_t)m * K, x, (size_t)K);
+        for (int n = n_begin; n < n_end; ++n) {
+            const float acc = row_dot(x, Wq + (size_t)n * nb * bb, fmt, nb);
+            Y[(size_t)m * N + n] = orc_f32_to_f16(acc);
+        }
+    }
+    free(x);
+    return 0;
+}
+
+/* lib/ops/quantized_cpu.cpp:164-230 */
+int orc_gemv_quantized(const uint16_t* X, const uint8_t* Wq, uint16_t* Y,
+                       int fmt, int M, int N, int K) {
+    return orc_gemv_quantized_rows(X, Wq, Y, fmt, M, N, K, 0, N);
+}
+
+int orc_gemv_quantized_f32(const float* X, const uint8_t* Wq, float* Y,
+                           int fmt, int M, int N, int K) {
+    const unsigned bb = block_bytes(fmt);
+    if (!X || !Wq || !Y || M <= 0 || N <= 0 || K <= 0 || (K % 32) != 0 || bb == 0) return -1;
+    const int nb = K / 32;
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n)
+            Y[(size_t)m * N + n] = row_dot(X + (size_t)m * K, Wq + (size_t)n * nb * bb, fmt, nb);
+    return 0;
+}
+
+/* lib/ops/quantized_cpu.cpp:272-284: sum of squares in double, rstd = 1/sqrtf(float(ss/K)+eps),
+ * normalised row = (x * rstd) * gamma kept in fp32. */
+static void rmsnorm_row_f32(const float* x, const float* g, float* out, int K, float eps) {
+    double ss = 0.0;
+    for (int k = 0; k < K; ++k) ss += (double)x[k] * (double)x[k];
+    const float rstd = 1.0f / sqrtf((float)(ss / (double)K) + eps);
+    for (int k = 0; k < K; ++k) out[k] = x[k] * rstd * g[k];
+}
+
+int orc_fused_rmsnorm_gemv_quantized_f32(const float* X, const float* gamma, const uint8_t* Wq,
+                                         float* Y, int fmt, int M, int N, int K, float eps) {
+    const unsigned bb = block_bytes(fmt);
+    if (!X || !gamma || !Wq || !Y || M <= 0 || N <= 0 || K <= 0 || (K % 32) != 0 || bb == 0)
+        return -1;
+    const int nb = K / 32;
+    float* xn = (float*)malloc((size_t)K * sizeof(float));
+    if (!xn) return -1;
+    for (int m = 0; m < M; ++m) {
+        rmsnorm_row_f32(X + (size_t)m * K, gamma, xn, K, eps);
+        for (int n = 0; n < N; ++n)
+            Y[(size_t)m * N + n] = row_dot(xn, Wq + (size_t)n * nb * bb, fmt, nb);
+    }
+    free(xn);
+    return 0;
+}
+
+/* lib/ops/quantized_cpu.cpp:232-320 */
+int orc_fused_rmsnorm_gemv_quantized(const uint16_t* X, const uint16_t* gamma,
+                                     const uint8_t* Wq, uint16_t* Y,
+                                     int fmt, int M, int N, int K, float eps) {
+    const unsigned bb = block_bytes(fmt);
+    if (!X || !gamma || !Wq || !Y || M <= 0 || N <= 0 || K <= 0 || (K % 32) != 0 || bb == 0)
+        return -1;
+    const int nb = K / 32;
+    float* buf = (float*)malloc((size_t)K * 3 * sizeof(float));
+    if (!buf) return -1;
+    float* x = buf; float* g = buf + K; float* xn = buf + 2 * (size_t)K;
+    orc_f16_to_f32_array(gamma, g, (size_t)K);
+    for (int m = 0; m < M; ++m) {
+        orc_f16_to_f32_array(X + (size_t)m * K, x, (size_t)K);
+        rmsnorm_row_f32(x, g, xn, K, eps);
+        for (int n = 0; n < N; ++n)
+            Y[(size_t)m * N + n] =
+                orc_f32_to_f16(row_dot(xn, Wq + (size_t)n * nb * bb, fmt, nb));
+    }
+    free(buf);
+    return 0;
+}
+
+/* Dense product of the reference's portable GEMM for fp16 in / fp16 out / fp32 accumulate,
+ * alpha = 1, beta = 0 (lib/ops/gemm_cpu.cpp:544-568): k ascending, one fp32 accumulator,
+ * stored value = 1*sum + 0*0. */
+static void dense_rows_times_w(const uint16_t* xn, const uint16_t* W, uint16_t* Y,
+                               int M, int N, int K) {
+    float* wcol = (float*)malloc((size_t)K * sizeof(float));
+    float* xr = (float*)malloc((size_t)M * K * sizeof(float));
+    orc_f16_to_f32_array(xn, xr, (size_t)M * K);
+    for (int n = 0; n < N; ++n) {
+        for (int k = 0; k < K; ++k) wcol[k] = orc_f16_to_f32(W[(size_t)k * N + n]);
+        for (int m = 0; m < M; ++m) {
+            const float* x = xr + (size_t)m * K;
+            float sum = 0.0f;
+            for (int k = 0; k < K; ++k) sum += x[k] * wcol[k];
+            const float out = 1.0f * sum + 0.0f * 0.0f;
+            Y[(size_t)m * N + n] = orc_f32_to_f16(out);
+        }
+    }
+    free(wcol);
+    free(xr);
+}
+
+/* lib/ops/training_cpu.cpp:799-856: RMSNorm as above, but the normalised row is rounded to
+ * fp16 before the product. */
+int orc_fused_rmsnorm_gemv(const uint16_t* X, const uint16_t* gamma, const uint16_t* W,
+                           uint16_t* Y, int M, int N, int K, float eps) {
+    if (!X || !gamma || !W || !Y || M <= 0 || N <= 0 || K <= 0) return -1;
+    uint16_t* xn = (uint16_t*)malloc((size_t)M * K * sizeof(uint16_t));
+    if (!xn) return -1;
+    for (int m = 0; m < M; ++m) {
+        const uint16_t* xr = X + (size_t)m * K;
+        double ss = 0.0;
+        for (int k = 0; k < K; ++k) {
+            const float xv = orc_f16_to_f32(xr[k]);
+            ss += (double)xv * (double)xv;
+        }
+        const float rstd = 1.0f / sqrtf((float)(ss / K) + eps);
+        for (int k = 0; k < K; ++k)
+            xn[(size_t)m * K + k] =
+                orc_f32_to_f16(orc_f16_to_f32(xr[k]) * rstd * orc_f16_to_f32(gamma[k]));
+    }
+    dense_rows_times_w(xn, W, Y, M, N, K);
+    free(xn);
+    return 0;
+}
+
+/* lib/ops/training_cpu.cpp:858-935: mean in double then narrowed to fp32; centred second
+ * moment in double; rstd = 1/sqrtf(float(var)+eps); row = fp16(((x-mean)*rstd)*gamma + beta). */
+int orc_fused_layernorm_gemv(const uint16_t* X, const uint16_t* gamma, const uint16_t* beta,
+                             const uint16_t* W, uint16_t* Y, int M, int N, int K, float eps) {
+    if (!X || !gamma || !beta || !W || !Y || M <= 0 || N <= 0 || K <= 0) return -1;
+    uint16_t* xn = (uint16_t*)malloc((size_t)M * K * sizeof(uint16_t));
+    if (!xn) return -1;
+    for (int m = 0; m < M; ++m) {
+        const uint16_t* xr = X + (size_t)m * K;
+        double sum = 0.0;
+        for (int k = 0; k < K; ++k) sum += orc_f16_to_f32(xr[k]);
+        const float mean = (float)(sum / K);
+        double ss = 0.0;
+        for (int k = 0; k < K; ++k) {
+            const float c = orc_f16_to_f32(xr[k]) - mean;
+            ss += (double)c * (double)c;
+        }
+        const float rstd = 1.0f / sqrtf((float)(ss / K) + eps);
+        for (int k = 0; k < K; ++k) {
+            const float xv = orc_f16_to_f32(xr[k]);
+            const float gv = orc_f16_to_f32(gamma[k]);
+            const float bv = orc_f16_to_f32(beta[k]);
+            xn[(size_t)m * K + k] = orc_f32_to_f16((xv - mean) * rstd * gv + bv);
+        }
+    }
+    dense_rows_times_w(xn, W, Y, M, N, K);
+    free(xn);
+    return 0;
+}
+
+int orc_dequantize(const uint8_t* Wq, float* out, int fmt, int N, int K) {
+    const unsigned bb = block_bytes(fmt);
+    if (!Wq || !out || N <= 0 || K <= 0 || (K % 32) != 0 || bb == 0) return -1;
+    const size_t nblk = (size_t)N * (size_t)(K / 32);
+    for (size_t t = 0; t < nblk; ++t) {
+        const uint8_t* blk = Wq + t * bb;
+        const float d = orc_f16_to_f32(load_u16(blk));
+        float* o = out + t * 32;
+        if (fmt == 0) {
+            for (int i = 0; i < 16; ++i) {
+                o[i] = d * (float)((int)(blk[2 + i] & 0x0f) - 8);
+                o[i + 16] = d * (float)((int)(blk[2 + i] >> 4) - 8);
+            }
+        } else {
+            for (int i = 0; i < 32; ++i) o[i] = d * (float)(int8_t)blk[2 + i];
+        }
+    }
+    return 0;
+}
+
+/* tests/test_quantized.c:48-94 - the fp64 yardstick: dequantise each stored block in double
+ * and dot it with the activations in double. */
+int orc_dequant_dot_f64(const double* X, const uint8_t* Wq, double* Y,
+                        int fmt, int M, int N, int K) {
+    const unsigned bb = block_bytes(fmt);
+    if (!X || !Wq || !Y || M <= 0 || N <= 0 || K <= 0 || (K % 32) != 0 || bb == 0) return -1;
+    const int nb = K / 32;
+    for (int n = 0; n < N; ++n) {
+        const uint8_t* row = Wq + (size_t)n * nb * bb;
+        for (int m = 0; m < M; ++m) {
+            const double* x = X + (size_t)m * K;
+            double acc = 0.0;
+            for (int b = 0; b < nb; ++b) {
+                const uint8_t* blk = row + (size_t)b * bb;
+                const double d = (double)orc_f16_to_f32(load_u16(blk));
+                const double* xb = x + (size_t)b * 32;
+                if (fmt == 0) {
+                    for (int i = 0; i < 16; ++i) {
+                        acc += xb[i] * d * (double)((int)(blk[2 + i] & 0x0f) - 8);
+                        acc += xb[i + 16] * d * (double)((int)(blk[2 + i] >> 4) - 8);
+                    }
+                } else {
+                    for (int i = 0; i < 32; ++i) acc += xb[i] * d * (double)(int8_t)blk[2 + i];
+                }
+            }
+            Y[(size_t)m * N + n] = acc;
+        }
+    }
+    return 0;
+}

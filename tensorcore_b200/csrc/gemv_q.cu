@@ -1,0 +1,759 @@
+// Quantized GEMV for sm_100a: Y[M,N] = X[M,K] . dequant(W)^T with W in GGUF Q4_0 / Q8_0 blocks.
+//
+// The weight matrix is one contiguous byte array ([N] rows of K/32 blocks).  Each CTA owns a
+// contiguous range of rows, i.e. one contiguous byte range, and streams it exactly once from
+// HBM with 1-D bulk async copies (cp.async.bulk, the TMA engine) into per-warp shared-memory
+// rings guarded by mbarriers.  The unit of work is a "group" of 8 consecutive blocks:
+// 8*18 = 144 bytes (Q4_0) or 8*34 = 272 bytes (Q8_0) are the smallest runs of whole blocks
+// whose size is a multiple of 16 bytes, so a lane can pull its group out of shared memory
+// with conflict-free 128-bit loads (9 resp. 17 of them; the 16-byte stride count is odd) and
+// pick scales and codes out of registers at compile-time-known positions.
+//
+// Codes become fp16 operands without an integer->float conversion: a 4-bit (8-bit) code c
+// placed in the low mantissa bits of a binary16 is the subnormal c * 2^-24, so masking the
+// packed word yields two ready fp16 values.  Products are taken with the sm_100 mixed
+// precision FMA (fp16 x fp16 + fp32 -> fp32), which is exact in the product and rounds once
+// in fp32; the zero point (-8 resp. the +128 bias used to make Q8_0 codes unsigned) is removed
+// per block with a precomputed sum of the block's activations.
+//
+// Activations (M <= 4 rows per pass) live in shared memory in a chunk-transposed layout so that
+// the 32 lanes of a warp, which work on 32 consecutive groups, read consecutive 16-byte
+// chunks.  Per-lane partial sums are combined with a segmented warp-shuffle reduction (a warp's
+// 32 groups may span several weight rows) and added to per-row accumulators in shared memory.
+//
+// With programmatic dependent launch the kernel starts its weight stream before waiting for
+// the previous kernel in the stream, so consecutive GEMVs of a decode step overlap their
+// fill/drain phases.  Every mbarrier wait is bounded; on expiry the kernel records
+// ERR_WAIT_TIMEOUT, drains its outstanding copies (again bounded) and exits.
+#include "kernels.h"
+
+#include <cuda_fp16.h>
+
+namespace tcb {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kGroupBlocks = 8;
+constexpr int kMaxMB = 4;
+
+template <int FMT> struct Fmt;
+template <> struct Fmt<FMT_Q4_0> {
+    static constexpr int kBlockBytes = 18;
+    static constexpr int kGroupBytes = 144;
+    static constexpr int kGroupV4 = 9;
+    static constexpr float kZeroPoint = 8.0f;
+};
+template <> struct Fmt<FMT_Q8_0> {
+    static constexpr int kBlockBytes = 34;
+    static constexpr int kGroupBytes = 272;
+    static constexpr int kGroupV4 = 17;
+    static constexpr float kZeroPoint = 128.0f;
+};
+
+struct StreamParams {
+    const uint8_t* W;
+    const void* X;
+    void* Y;
+    const void* gamma;
+    uint32_t* err;
+    int M, N, K;
+    int nb;        // blocks per row
+    int gpr;       // groups per row
+    int ns;        // ring stages per warp
+    int y_f32;
+    int x_src_f16; // activations (and gamma) are fp16 in global memory
+    float eps;
+    // shared-memory offsets (bytes)
+    int off_rowacc, off_sx, off_x, off_ring;
+    int max_rows;  // rows per CTA upper bound
+};
+
+// ---------------------------------------------------------------------------------------
+// PTX helpers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ~2e9 clocks (about a second) and reports false.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > 2000000000LL) return false;
+    }
+    return true;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes,
+                                         uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// fp16 x fp16 + fp32 -> fp32, exact product, one rounding (PTX ISA 8.6, sm_100).
+__device__ __forceinline__ float fma_h(uint16_t a, uint16_t b, float c) {
+    float d;
+    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ uint16_t lo16(uint32_t v) { return static_cast<uint16_t>(v); }
+__device__ __forceinline__ uint16_t hi16(uint32_t v) { return static_cast<uint16_t>(v >> 16); }
+__device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+__device__ __forceinline__ uint32_t get4(const uint4& v, int i) {
+    return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
+}
+
+// ---------------------------------------------------------------------------------------
+// Activation staging.  Element k of row m sits at
+//   fp16: ((c*gpr + kg)*16 + (k&7)*2)   with kg = k>>8, c = (k&255)>>3   (32 chunks / group)
+//   fp32: ((c*gpr + kg)*16 + (k&3)*4)   with kg = k>>8, c = (k&255)>>2   (64 chunks / group)
+// so lanes holding consecutive groups kg read consecutive 16-byte chunks.
+// ---------------------------------------------------------------------------------------
+template <bool XF32>
+__device__ __forceinline__ int x_chunk_index(int k_chunk, int gpr) {
+    // k_chunk = index of a 16-byte chunk in natural order (8 halves or 4 floats)
+    constexpr int per_group = XF32 ? 64 : 32;
+    const int kg = k_chunk / per_group;
+    const int c = k_chunk % per_group;
+    return c * gpr + kg;
+}
+
+// Sum over a thread block of one double per thread (result broadcast to all threads).
+__device__ double block_sum_f64(double v, double* scratch /* >= kWarps doubles */) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __syncthreads();
+    if (l == 0) scratch[w] = v;
+    __syncthreads();
+    double t = 0.0;
+#pragma unroll
+    for (int i = 0; i < kWarps; ++i) t += scratch[i];
+    return t;
+}
+
+// Loads MB activation rows into shared memory and fills
+// sx[m][j*gpr+kg] = zero_point * (sum of the 32 staged activations of block kg*8+j).
+// Without gamma the rows are copied as they are (staging type == source type).  With gamma the
+// RMSNorm prologue runs first: sum of squares in double, rstd = 1/sqrtf(float(ss/K)+eps),
+// row = (x*rstd)*gamma, kept in fp32 (XF32 staging) whether the source is fp16 or fp32.
+template <bool XF32, int MB>
+__device__ void stage_activations(const StreamParams& p, uint8_t* smem, float zero_point,
+                                  double* red_scratch) {
+    const int K = p.K, gpr = p.gpr, nb = p.nb;
+    uint8_t* xs = smem + p.off_x;
+    float* sx = reinterpret_cast<float*>(smem + p.off_sx);
+    const int tid = threadIdx.x;
+    const size_t row_bytes = static_cast<size_t>(K) * (XF32 ? 4 : 2);
+
+    for (int m = 0; m < MB; ++m) {
+        uint4* dst = reinterpret_cast<uint4*>(xs + m * row_bytes);
+        if (p.gamma == nullptr) {
+            const int nchunks = K / (XF32 ? 4 : 8);
+            const uint4* src = reinterpret_cast<const uint4*>(
+                static_cast<const uint8_t*>(p.X) + m * row_bytes);
+            for (int i = tid; i < nchunks; i += kThreads)
+                dst[x_chunk_index<XF32>(i, gpr)] = __ldg(src + i);
+        } else if (XF32) {
+            const int nquads = K / 4;
+            double ss = 0.0;
+            if (p.x_src_f16) {
+                const uint2* xr = reinterpret_cast<const uint2*>(
+                    static_cast<const __half*>(p.X) + static_cast<size_t>(m) * K);
+                for (int i = tid; i < nquads; i += kThreads) {
+                    const uint2 v = __ldg(xr + i);
+                    const double a = h2f(lo16(v.x)), b = h2f(hi16(v.x));
+                    const double c = h2f(lo16(v.y)), d = h2f(hi16(v.y));
+                    ss += a * a + b * b + c * c + d * d;
+                }
+            } else {
+                const float4* xr = reinterpret_cast<const float4*>(
+                    static_cast<const float*>(p.X) + static_cast<size_t>(m) * K);
+                for (int i = tid; i < nquads; i += kThreads) {
+                    const float4 v = __ldg(xr + i);
+                    const double a = v.x, b = v.y, c = v.z, d = v.w;
+                    ss += a * a + b * b + c * c + d * d;
+                }
+            }
+            ss = block_sum_f64(ss, red_scratch);
+            const float rstd =
+                1.0f / sqrtf(static_cast<float>(ss / static_cast<double>(K)) + p.eps);
+            float4* dstf = reinterpret_cast<float4*>(dst);
+            for (int i = tid; i < nquads; i += kThreads) {
+                float4 xv, gv;
+                if (p.x_src_f16) {
+                    const uint2 xb = __ldg(reinterpret_cast<const uint2*>(
+                        static_cast<const __half*>(p.X) + static_cast<size_t>(m) * K) + i);
+                    const uint2 gb = __ldg(reinterpret_cast<const uint2*>(p.gamma) + i);
+                    xv = make_float4(h2f(lo16(xb.x)), h2f(hi16(xb.x)), h2f(lo16(xb.y)), h2f(hi16(xb.y)));
+                    gv = make_float4(h2f(lo16(gb.x)), h2f(hi16(gb.x)), h2f(lo16(gb.y)), h2f(hi16(gb.y)));
+                } else {
+                    xv = __ldg(reinterpret_cast<const float4*>(
+                        static_cast<const float*>(p.X) + static_cast<size_t>(m) * K) + i);
+                    gv = __ldg(reinterpret_cast<const float4*>(p.gamma) + i);
+                }
+                float4 o;
+                o.x = __fmul_rn(__fmul_rn(xv.x, rstd), gv.x);
+                o.y = __fmul_rn(__fmul_rn(xv.y, rstd), gv.y);
+                o.z = __fmul_rn(__fmul_rn(xv.z, rstd), gv.z);
+                o.w = __fmul_rn(__fmul_rn(xv.w, rstd), gv.w);
+                dstf[x_chunk_index<true>(i, gpr)] = o;
+            }
+        }
+    }
+    __syncthreads();
+    for (int t = tid; t < MB * nb; t += kThreads) {
+        const int m = t / nb, b = t % nb;
+        const int kg = b >> 3, j = b & 7;
+        const uint4* xrow = reinterpret_cast<const uint4*>(xs + m * row_bytes);
+        float s = 0.f;
+        if (XF32) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const uint4 v = xrow[(8 * j + q) * gpr + kg];
+                s += __uint_as_float(v.x);
+                s += __uint_as_float(v.y);
+                s += __uint_as_float(v.z);
+                s += __uint_as_float(v.w);
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint4 v = xrow[(4 * j + q) * gpr + kg];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const uint32_t w = get4(v, e);
+                    s += h2f(lo16(w));
+                    s += h2f(hi16(w));
+                }
+            }
+        }
+        sx[m * nb + j * gpr + kg] = zero_point * s;
+    }
+    __syncthreads();
+}
+
+// ---------------------------------------------------------------------------------------
+// One group (8 blocks, 256 weights) against MB activation rows.
+// w[] holds the group's bytes as 32-bit words; all indexing below is compile-time.
+// ---------------------------------------------------------------------------------------
+template <int FMT, bool XF32, int MB>
+__device__ __forceinline__ void group_dot(const uint32_t (&w)[Fmt<FMT>::kGroupV4 * 4],
+                                          const uint8_t* xs, const float* sx, int kg, int gpr,
+                                          int K, int nb, float (&out)[MB]) {
+    const size_t row_bytes = static_cast<size_t>(K) * (XF32 ? 4 : 2);
+#pragma unroll
+    for (int j = 0; j < kGroupBlocks; ++j) {
+        constexpr int kHwPerBlock = Fmt<FMT>::kBlockBytes / 2;  // 9 or 17 halfwords
+        const int hw = kHwPerBlock * j;                          // halfword index of the scale
+        const uint32_t sw = w[hw >> 1];
+        const float d = h2f((hw & 1) ? hi16(sw) : lo16(sw));
+        const int qhw = hw + 1;                                  // first halfword of the codes
+        constexpr int kQWords = (Fmt<FMT>::kBlockBytes - 2) / 4; // 4 or 8 code words
+        uint32_t q[kQWords];
+#pragma unroll
+        for (int t = 0; t < kQWords; ++t) {
+            if (qhw & 1) q[t] = __funnelshift_r(w[(qhw >> 1) + t], w[(qhw >> 1) + t + 1], 16);
+            else q[t] = w[(qhw >> 1) + t];
+        }
+#pragma unroll
+        for (int m = 0; m < MB; ++m) {
+            const uint4* xrow = reinterpret_cast<const uint4*>(xs + m * row_bytes);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            if (FMT == FMT_Q4_0) {
+                // byte i of the block: low nibble <-> x[i], high nibble <-> x[i+16].
+                // Word t covers bytes 4t..4t+3.  (q & 0x000f000f) = codes of bytes 4t, 4t+2 as
+                // two fp16 subnormals (c * 2^-24); ((q>>8) & ...) = bytes 4t+1, 4t+3.  The high
+                // nibbles masked in place carry an extra factor 16 (c * 2^-20).
+                if (!XF32) {
+                    uint4 xv[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) xv[c] = xrow[(4 * j + c) * gpr + kg];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const uint32_t l01 = get4(xv[t >> 1], (t & 1) * 2);
+                        const uint32_t l23 = get4(xv[t >> 1], (t & 1) * 2 + 1);
+                        const uint32_t h01 = get4(xv[2 + (t >> 1)], (t & 1) * 2);
+                        const uint32_t h23 = get4(xv[2 + (t >> 1)], (t & 1) * 2 + 1);
+                        const uint32_t v0 = q[t] & 0x000f000fu;
+                        const uint32_t v1 = q[t] & 0x00f000f0u;
+                        const uint32_t s8 = q[t] >> 8;
+                        const uint32_t v2 = s8 & 0x000f000fu;
+                        const uint32_t v3 = s8 & 0x00f000f0u;
+                        a0 = fma_h(lo16(v0), lo16(l01), a0);
+                        a1 = fma_h(lo16(v2), hi16(l01), a1);
+                        a0 = fma_h(hi16(v0), lo16(l23), a0);
+                        a1 = fma_h(hi16(v2), hi16(l23), a1);
+                        a2 = fma_h(lo16(v1), lo16(h01), a2);
+                        a3 = fma_h(lo16(v3), hi16(h01), a3);
+                        a2 = fma_h(hi16(v1), lo16(h23), a2);
+                        a3 = fma_h(hi16(v3), hi16(h23), a3);
+                    }
+                } else {
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const uint4 xl = xrow[(8 * j + t) * gpr + kg];       // x[4t..4t+3]
+                        const uint4 xh = xrow[(8 * j + 4 + t) * gpr + kg];   // x[16+4t..]
+                        const uint32_t v0 = q[t] & 0x000f000fu;
+                        const uint32_t v1 = q[t] & 0x00f000f0u;
+                        const uint32_t s8 = q[t] >> 8;
+                        const uint32_t v2 = s8 & 0x000f000fu;
+                        const uint32_t v3 = s8 & 0x00f000f0u;
+                        a0 = fmaf(h2f(lo16(v0)), __uint_as_float(xl.x), a0);
+                        a1 = fmaf(h2f(lo16(v2)), __uint_as_float(xl.y), a1);
+                        a0 = fmaf(h2f(hi16(v0)), __uint_as_float(xl.z), a0);
+                        a1 = fmaf(h2f(hi16(v2)), __uint_as_float(xl.w), a1);
+                        a2 = fmaf(h2f(lo16(v1)), __uint_as_float(xh.x), a2);
+                        a3 = fmaf(h2f(lo16(v3)), __uint_as_float(xh.y), a3);
+                        a2 = fmaf(h2f(hi16(v1)), __uint_as_float(xh.z), a2);
+                        a3 = fmaf(h2f(hi16(v3)), __uint_as_float(xh.w), a3);
+                    }
+                }
+                const float s = sx[m * nb + j * gpr + kg];
+                // undo 2^-24 / 2^-20, remove the zero point, apply the block scale
+                const float blk = fmaf(a0 + a1, 16777216.0f, fmaf(a2 + a3, 1048576.0f, -s));
+                out[m] = fmaf(d, blk, out[m]);
+            } else {
+                // Q8_0: flip the sign bit of every code byte (c + 128, unsigned), widen byte
+                // pairs to fp16 subnormals with a byte permute.
+                if (!XF32) {
+                    uint4 xv[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) xv[c] = xrow[(4 * j + c) * gpr + kg];
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) {
+                        const uint32_t u = q[t] ^ 0x80808080u;
+                        const uint32_t p01 = __byte_perm(u, 0u, 0x4140);
+                        const uint32_t p23 = __byte_perm(u, 0u, 0x4342);
+                        const uint32_t x01 = get4(xv[t >> 1], (t & 1) * 2);
+                        const uint32_t x23 = get4(xv[t >> 1], (t & 1) * 2 + 1);
+                        a0 = fma_h(lo16(p01), lo16(x01), a0);
+                        a1 = fma_h(hi16(p01), hi16(x01), a1);
+                        a2 = fma_h(lo16(p23), lo16(x23), a2);
+                        a3 = fma_h(hi16(p23), hi16(x23), a3);
+                    }
+                } else {
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) {
+                        const uint4 xq = xrow[(8 * j + t) * gpr + kg];
+                        const uint32_t u = q[t] ^ 0x80808080u;
+                        const uint32_t p01 = __byte_perm(u, 0u, 0x4140);
+                        const uint32_t p23 = __byte_perm(u, 0u, 0x4342);
+                        a0 = fmaf(h2f(lo16(p01)), __uint_as_float(xq.x), a0);
+                        a1 = fmaf(h2f(hi16(p01)), __uint_as_float(xq.y), a1);
+                        a2 = fmaf(h2f(lo16(p23)), __uint_as_float(xq.z), a2);
+                        a3 = fmaf(h2f(hi16(p23)), __uint_as_float(xq.w), a3);
+                    }
+                }
+                const float s = sx[m * nb + j * gpr + kg];
+                const float blk = fmaf((a0 + a1) + (a2 + a3), 16777216.0f, -s);
+                out[m] = fmaf(d, blk, out[m]);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// The streaming kernel.
+// ---------------------------------------------------------------------------------------
+template <int FMT, bool XF32, int MB>
+__global__ void __launch_bounds__(kThreads, 2) gemv_q_stream_kernel(const StreamParams p) {
+    using F = Fmt<FMT>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                  // [kWarps*ns]
+    double* red_scratch = reinterpret_cast<double*>(smem + 8 * kWarps * 4);  // after <=32 bars
+    float* rowacc = reinterpret_cast<float*>(smem + p.off_rowacc);
+    uint8_t* ring = smem + p.off_ring;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int ns = p.ns, gpr = p.gpr;
+    constexpr int kChunkBytes = 32 * F::kGroupBytes;
+
+    // Row range of this CTA and the corresponding run of groups.
+    const int r0 = static_cast<int>(static_cast<long long>(p.N) * blockIdx.x / gridDim.x);
+    const int r1 = static_cast<int>(static_cast<long long>(p.N) * (blockIdx.x + 1) / gridDim.x);
+    const int rows = r1 - r0;
+    const long long g_base = static_cast<long long>(r0) * gpr;
+    const int g_count = rows * gpr;
+    const int nchunks = (g_count + 31) >> 5;
+    const int my_n = nchunks > warp ? (nchunks - warp + kWarps - 1) / kWarps : 0;
+
+    pdl_launch_dependents();
+
+    if (tid == 0) {
+        for (int i = 0; i < kWarps * ns; ++i) mbar_init(&bars[i], 1);
+        fence_barrier_init();
+    }
+    for (int i = tid; i < rows * MB; i += kThreads) rowacc[i] = 0.f;
+    __syncthreads();
+
+    auto issue = [&](int i) {  // lane 0 only: start the copy of this warp's i-th chunk
+        const int c = warp + kWarps * i;
+        const int first = c << 5;
+        const int ng = min(32, g_count - first);
+        const uint32_t bytes = static_cast<uint32_t>(ng) * F::kGroupBytes;
+        const int s = i % ns;
+        uint64_t* bar = &bars[warp * ns + s];
+        mbar_expect_tx(bar, bytes);
+        bulk_g2s(ring + static_cast<size_t>(warp * ns + s) * kChunkBytes,
+                 p.W + (g_base + first) * F::kGroupBytes, bytes, bar);
+    };
+    // Weights do not depend on the previous kernel in the stream: start streaming now.
+    if (lane == 0) {
+        const int pre = min(ns, my_n);
+        for (int i = 0; i < pre; ++i) issue(i);
+    }
+
+    // Activations may be the previous kernel's output: wait for it, then stage them.
+    pdl_wait();
+    stage_activations<XF32, MB>(p, smem, F::kZeroPoint, red_scratch);
+
+    const uint8_t* xs = smem + p.off_x;
+    const float* sx = reinterpret_cast<const float*>(smem + p.off_sx);
+    bool failed = false;
+    int waited = 0;  // number of this warp's chunks whose barrier has been consumed
+
+    for (int i = 0; i < my_n; ++i) {
+        const int s = i % ns;
+        uint64_t* bar = &bars[warp * ns + s];
+        if (!mbar_wait_bounded(bar, static_cast<uint32_t>((i / ns) & 1))) {
+            failed = true;
+            break;
+        }
+        waited = i + 1;
+        const int c = warp + kWarps * i;
+        const int gl = (c << 5) + lane;           // group index local to the CTA
+        const bool valid = gl < g_count;
+
+        uint32_t w[F::kGroupV4 * 4];
+        if (valid) {
+            const uint4* src = reinterpret_cast<const uint4*>(
+                ring + static_cast<size_t>(warp * ns + s) * kChunkBytes +
+                static_cast<size_t>(lane) * F::kGroupBytes);
+#pragma unroll
+            for (int v = 0; v < F::kGroupV4; ++v) {
+                const uint4 t = src[v];
+                w[4 * v + 0] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
+            }
+        } else {
+#pragma unroll
+            for (int v = 0; v < F::kGroupV4 * 4; ++v) w[v] = 0u;
+        }
+        __syncwarp();
+        if (lane == 0 && i + ns < my_n) {
+            fence_proxy_async();
+            issue(i + ns);
+        }
+
+        float out[MB];
+#pragma unroll
+        for (int m = 0; m < MB; ++m) out[m] = 0.f;
+        int row = -1 - lane;  // distinct negatives for idle lanes
+        if (valid) {
+            row = gl / gpr;
+            const int kg = gl - row * gpr;
+            group_dot<FMT, XF32, MB>(w, xs, sx, kg, gpr, p.K, p.nb, out);
+        }
+        // Segmented reduction over lanes that hold groups of the same row (contiguous runs).
+#pragma unroll
+        for (int dlt = 1; dlt < 32; dlt <<= 1) {
+            const int r2 = __shfl_down_sync(0xffffffffu, row, dlt);
+            const bool take = (lane + dlt < 32) && (r2 == row);
+#pragma unroll
+            for (int m = 0; m < MB; ++m) {
+                const float v2 = __shfl_down_sync(0xffffffffu, out[m], dlt);
+                if (take) out[m] += v2;
+            }
+        }
+        const int rprev = __shfl_up_sync(0xffffffffu, row, 1);
+        if (valid && (lane == 0 || rprev != row)) {
+#pragma unroll
+            for (int m = 0; m < MB; ++m) atomicAdd(&rowacc[row * MB + m], out[m]);
+        }
+    }
+
+    if (failed) {
+        if (lane == 0) atomicOr(p.err, ERR_WAIT_TIMEOUT);
+        // Drain copies this warp still has in flight (bounded), so that none lands after exit.
+        const int issued = min(my_n, waited + ns);
+        for (int i = waited; i < issued; ++i)
+            (void)mbar_wait_bounded(&bars[warp * ns + (i % ns)], static_cast<uint32_t>((i / ns) & 1));
+    }
+    __syncthreads();
+
+    for (int i = tid; i < rows * MB; i += kThreads) {
+        const int r = i / MB, m = i - r * MB;
+        const size_t o = static_cast<size_t>(m) * p.N + (r0 + r);
+        const float v = rowacc[i];
+        if (p.y_f32) static_cast<float*>(p.Y)[o] = v;
+        else static_cast<__half*>(p.Y)[o] = __float2half_rn(v);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Generic kernel: any K % 32 == 0, any alignment, any N.  One warp per output row, lanes over
+// blocks, byte-granular loads.  Correctness path for shapes the streaming kernel rejects.
+// ---------------------------------------------------------------------------------------
+struct GenericParams {
+    const uint8_t* W;
+    const void* X;
+    void* Y;
+    const void* gamma;
+    int M, N, K, nb;
+    int fmt, x_f32, y_f32;
+    float eps;
+};
+
+__device__ __forceinline__ float load_x(const void* X, size_t idx, int x_f32) {
+    return x_f32 ? static_cast<const float*>(X)[idx]
+                 : __half2float(static_cast<const __half*>(X)[idx]);
+}
+
+__global__ void __launch_bounds__(kThreads) gemv_q_generic_kernel(const GenericParams p) {
+    __shared__ double red[kWarps];
+    __shared__ float rstd_s;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int bb = p.fmt == FMT_Q4_0 ? 18 : 34;
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int m = 0; m < p.M; ++m) {
+        float rstd = 1.f;
+        if (p.gamma != nullptr) {
+            double ss = 0.0;
+            for (int k = tid; k < p.K; k += kThreads) {
+                const double v = static_cast<double>(load_x(p.X, static_cast<size_t>(m) * p.K + k, p.x_f32));
+                ss += v * v;
+            }
+            ss = block_sum_f64(ss, red);
+            if (tid == 0)
+                rstd_s = 1.0f / sqrtf(static_cast<float>(ss / static_cast<double>(p.K)) + p.eps);
+            __syncthreads();
+            rstd = rstd_s;
+        }
+        for (int n = blockIdx.x * kWarps + warp; n < p.N; n += gridDim.x * kWarps) {
+            const uint8_t* row = p.W + static_cast<size_t>(n) * p.nb * bb;
+            float acc = 0.f;
+            for (int b = lane; b < p.nb; b += 32) {
+                const uint8_t* blk = row + static_cast<size_t>(b) * bb;
+                const float d = h2f(static_cast<uint16_t>(blk[0] | (blk[1] << 8)));
+                float part = 0.f;
+                for (int i = 0; i < 32; ++i) {
+                    const size_t xi = static_cast<size_t>(m) * p.K + static_cast<size_t>(b) * 32 + i;
+                    float xv = load_x(p.X, xi, p.x_f32);
+                    if (p.gamma != nullptr)
+                        xv = __fmul_rn(__fmul_rn(xv, rstd), load_x(p.gamma, b * 32 + i, p.x_f32));
+                    int q;
+                    if (p.fmt == FMT_Q4_0) {
+                        const uint8_t byte = blk[2 + (i & 15)];
+                        q = static_cast<int>((i < 16) ? (byte & 0x0f) : (byte >> 4)) - 8;
+                    } else {
+                        q = static_cast<int>(static_cast<int8_t>(blk[2 + i]));
+                    }
+                    part = fmaf(xv, static_cast<float>(q), part);
+                }
+                acc = fmaf(d, part, acc);
+            }
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) {
+                const size_t o = static_cast<size_t>(m) * p.N + n;
+                if (p.y_f32) static_cast<float*>(p.Y)[o] = acc;
+                else static_cast<__half*>(p.Y)[o] = __float2half_rn(acc);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+template <typename KernelT, typename ParamT>
+cudaError_t launch_with_attrs(KernelT kernel, dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, bool pdl, const ParamT& params) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, params);
+}
+
+inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
+
+struct StreamPlan {
+    bool ok = false;
+    int ns = 0;
+    int grid = 0;
+    int smem = 0;
+    StreamParams p{};
+};
+
+// Decides whether the streaming kernel can take (fmt, K, alignment, MB rows of activations
+// staged as fp16/fp32) and lays out its shared memory.
+StreamPlan plan_stream(const GemvQArgs& a, int mb, bool stage_f32, const LaunchEnv& env) {
+    StreamPlan pl;
+    if (a.K % 256 != 0) return pl;
+    if ((reinterpret_cast<uintptr_t>(a.W) & 15u) != 0) return pl;
+    if ((reinterpret_cast<uintptr_t>(a.X) & 15u) != 0) return pl;
+    if (a.gamma && (reinterpret_cast<uintptr_t>(a.gamma) & 15u) != 0) return pl;
+    const int nb = a.K / 32, gpr = nb / 8;
+    const int group_bytes = a.fmt == FMT_Q4_0 ? 144 : 272;
+    const int chunk_bytes = 32 * group_bytes;
+    const int grid = a.N < env.sm_count ? a.N : env.sm_count;
+    const int max_rows = (a.N + grid - 1) / grid + 1;
+
+    int off = 8 * kWarps * 4 + 8 * kWarps;  // barriers (up to 4 stages) + reduction scratch
+    off = align_up(off, 16);
+    const int off_rowacc = off;
+    off += align_up(max_rows * mb * 4, 16);
+    const int off_sx = off;
+    off += align_up(mb * nb * 4, 16);
+    const int off_x = off;
+    off += align_up(mb * a.K * (stage_f32 ? 4 : 2), 128);
+    const int off_ring = off;
+
+    const int half_budget = (env.smem_optin > 0 ? env.smem_optin : 232448) / 2 - 1024;
+    const int full_budget = (env.smem_optin > 0 ? env.smem_optin : 232448);
+    int ns = 0;
+    for (int cand = 4; cand >= 2; --cand) {
+        if (off_ring + kWarps * cand * chunk_bytes <= half_budget) { ns = cand; break; }
+    }
+    if (ns == 0) {
+        for (int cand = 3; cand >= 1; --cand) {
+            if (off_ring + kWarps * cand * chunk_bytes <= full_budget) { ns = cand; break; }
+        }
+    }
+    if (ns == 0) return pl;
+
+    pl.ok = true;
+    pl.ns = ns;
+    pl.grid = grid;
+    pl.smem = off_ring + kWarps * ns * chunk_bytes;
+    StreamParams& p = pl.p;
+    p.W = a.W; p.X = a.X; p.Y = a.Y; p.gamma = a.gamma; p.err = env.err_word;
+    p.M = mb; p.N = a.N; p.K = a.K; p.nb = nb; p.gpr = gpr; p.ns = ns;
+    p.y_f32 = a.y_f32 ? 1 : 0; p.eps = a.eps;
+    p.off_rowacc = off_rowacc; p.off_sx = off_sx; p.off_x = off_x; p.off_ring = off_ring;
+    p.max_rows = max_rows;
+    return pl;
+}
+
+template <int FMT, bool XF32>
+cudaError_t launch_stream_mb(int mb, const StreamPlan& pl, cudaStream_t st, bool pdl) {
+    const dim3 grid(pl.grid), block(kThreads);
+    switch (mb) {
+        case 1: return launch_with_attrs(gemv_q_stream_kernel<FMT, XF32, 1>, grid, block, pl.smem, st, pdl, pl.p);
+        case 2: return launch_with_attrs(gemv_q_stream_kernel<FMT, XF32, 2>, grid, block, pl.smem, st, pdl, pl.p);
+        case 3: return launch_with_attrs(gemv_q_stream_kernel<FMT, XF32, 3>, grid, block, pl.smem, st, pdl, pl.p);
+        default: return launch_with_attrs(gemv_q_stream_kernel<FMT, XF32, 4>, grid, block, pl.smem, st, pdl, pl.p);
+    }
+}
+
+template <typename K>
+cudaError_t set_smem(K kernel, int bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+}  // namespace
+
+cudaError_t init_gemv_kernels(int smem_optin) {
+    cudaError_t e = cudaSuccess;
+#define TCB_SET(FMT, XF, MB)                                                      \
+    e = set_smem(gemv_q_stream_kernel<FMT, XF, MB>, smem_optin);                  \
+    if (e != cudaSuccess) return e;
+    TCB_SET(FMT_Q4_0, false, 1) TCB_SET(FMT_Q4_0, false, 2) TCB_SET(FMT_Q4_0, false, 3) TCB_SET(FMT_Q4_0, false, 4)
+    TCB_SET(FMT_Q4_0, true, 1) TCB_SET(FMT_Q4_0, true, 2) TCB_SET(FMT_Q4_0, true, 3) TCB_SET(FMT_Q4_0, true, 4)
+    TCB_SET(FMT_Q8_0, false, 1) TCB_SET(FMT_Q8_0, false, 2) TCB_SET(FMT_Q8_0, false, 3) TCB_SET(FMT_Q8_0, false, 4)
+    TCB_SET(FMT_Q8_0, true, 1) TCB_SET(FMT_Q8_0, true, 2) TCB_SET(FMT_Q8_0, true, 3) TCB_SET(FMT_Q8_0, true, 4)
+#undef TCB_SET
+    return e;
+}
+
+cudaError_t launch_gemv_q(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t stream,
+                          int* launches, const char** name) {
+    int count = 0;
+    cudaError_t err = cudaSuccess;
+    const char* used = "none";
+    const size_t xsz = a.x_f32 ? 4 : 2, ysz = a.y_f32 ? 4 : 2;
+    const bool fuse = a.gamma != nullptr;
+    // The RMSNorm prologue keeps the normalised row in fp32, whatever the activation type.
+    const bool stage_f32 = a.x_f32 || fuse;
+
+    for (int m0 = 0; m0 < a.M && err == cudaSuccess; m0 += kMaxMB) {
+        const int mb = (a.M - m0) < kMaxMB ? (a.M - m0) : kMaxMB;
+        GemvQArgs s = a;
+        s.X = static_cast<const uint8_t*>(a.X) + static_cast<size_t>(m0) * a.K * xsz;
+        s.Y = static_cast<uint8_t*>(a.Y) + static_cast<size_t>(m0) * a.N * ysz;
+        s.M = mb;
+        StreamPlan pl;
+        if (env.variant != VARIANT_GENERIC) pl = plan_stream(s, mb, stage_f32, env);
+        if (pl.ok) {
+            pl.p.x_src_f16 = a.x_f32 ? 0 : 1;
+            if (a.fmt == FMT_Q4_0) {
+                err = stage_f32 ? launch_stream_mb<FMT_Q4_0, true>(mb, pl, stream, env.pdl)
+                                : launch_stream_mb<FMT_Q4_0, false>(mb, pl, stream, env.pdl);
+                used = stage_f32 ? "q4_0_gemv_stream_f32x_sm100" : "q4_0_gemv_stream_sm100";
+            } else {
+                err = stage_f32 ? launch_stream_mb<FMT_Q8_0, true>(mb, pl, stream, env.pdl)
+                                : launch_stream_mb<FMT_Q8_0, false>(mb, pl, stream, env.pdl);
+                used = stage_f32 ? "q8_0_gemv_stream_f32x_sm100" : "q8_0_gemv_stream_sm100";
+            }
+        } else {
+            GenericParams g;
+            g.W = s.W; g.X = s.X; g.Y = s.Y; g.gamma = s.gamma;
+            g.M = mb; g.N = s.N; g.K = s.K; g.nb = s.K / 32;
+            g.fmt = s.fmt; g.x_f32 = s.x_f32; g.y_f32 = s.y_f32; g.eps = s.eps;
+            int grid = (s.N + kWarps - 1) / kWarps;
+            const int cap = env.sm_count > 0 ? env.sm_count * 8 : 1024;
+            if (grid > cap) grid = cap;
+            err = launch_with_attrs(gemv_q_generic_kernel, dim3(grid), dim3(kThreads), 0, stream,
+                                    env.pdl, g);
+            used = a.fmt == FMT_Q4_0 ? "q4_0_gemv_generic_sm100" : "q8_0_gemv_generic_sm100";
+        }
+        ++count;
+    }
+    if (launches) *launches += count;
+    if (name) *name = used;
+    return err;
+}
+
+}  // namespace tcb

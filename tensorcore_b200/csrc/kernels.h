@@ -1,0 +1,65 @@
+// Launch interface between the host layer (runtime.cu) and the sm_100a kernels.
+// Everything here works on raw device pointers; handle validation happens above.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tcb {
+
+enum QuantFmt : int { FMT_Q4_0 = 0, FMT_Q8_0 = 1 };
+
+// Kernel families for the quantized GEMV (see gemv_q.cu).
+enum GemvVariant : int {
+    VARIANT_AUTO = 0,
+    VARIANT_SIMT = 1,     // CUDA-core dequant-dot, streamed through shared memory
+    VARIANT_MMA = 2,      // warp-level tensor-core dot for 1 <= M <= 8
+    VARIANT_TC = 3,       // tcgen05 path for batched decode
+    VARIANT_GENERIC = 4,  // any K % 32 == 0, any alignment; correctness path for odd shapes
+};
+
+struct LaunchEnv {
+    int sm_count = 0;
+    int smem_optin = 0;        // max dynamic shared memory per block (opt-in), bytes
+    bool pdl = false;          // launch with programmatic stream serialization
+    int variant = VARIANT_AUTO;
+    uint32_t* err_word = nullptr;  // device-visible word a kernel ORs an error bit into
+};
+
+struct GemvQArgs {
+    const uint8_t* W = nullptr;   // [N][K/32] blocks
+    const void* X = nullptr;      // [M,K] fp16 or fp32
+    void* Y = nullptr;            // [M,N] fp16 or fp32
+    const void* gamma = nullptr;  // [K], activation dtype; non-null => RMSNorm prologue
+    int fmt = 0, M = 0, N = 0, K = 0;
+    bool x_f32 = false, y_f32 = false;
+    float eps = 0.f;
+};
+
+struct DenseNormGemvArgs {
+    const void* X = nullptr;      // [M,K] fp16
+    const void* gamma = nullptr;  // [K] fp16
+    const void* beta = nullptr;   // [K] fp16 or null (null => RMSNorm, else LayerNorm)
+    const void* W = nullptr;      // [K,N] fp16, N contiguous
+    void* Y = nullptr;            // [M,N] fp16
+    int M = 0, N = 0, K = 0;
+    float eps = 0.f;
+};
+
+// Error bits ORed into LaunchEnv::err_word by kernels.
+enum : uint32_t { ERR_WAIT_TIMEOUT = 1u, ERR_BAD_SHAPE = 2u };
+
+// Each launcher enqueues on `stream`, adds the number of kernels it launched to *launches (may
+// be null) and stores a static string naming the kernel variant in *name (may be null).
+cudaError_t launch_quantize(const void* W_f16, void* W_quant, int fmt, int N, int K,
+                            const LaunchEnv& env, cudaStream_t stream, int* launches,
+                            const char** name);
+cudaError_t launch_gemv_q(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t stream,
+                          int* launches, const char** name);
+cudaError_t launch_dense_norm_gemv(const DenseNormGemvArgs& a, const LaunchEnv& env,
+                                   cudaStream_t stream, int* launches, const char** name);
+
+// One-time per-device kernel attribute setup (max dynamic shared memory).
+cudaError_t init_kernels_for_device(int smem_optin);
+
+}  // namespace tcb

@@ -1,0 +1,1115 @@
+// Host layer of the B200 tensorcore library: context, device buffers, streams and the
+// operation entry points of the quantized-decode path.  Thin by design - argument checks in
+// the reference's order, pointer resolution, then a kernel launch from kernels.h.
+//
+// There is no CPU fallback anywhere in this file: if the device or a launch is unavailable the
+// call fails with a status code.
+#include "../../include/tensorcore_b200.h"
+#include "kernels.h"
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <limits>
+#include <mutex>
+#include <new>
+#include <unordered_map>
+#include <vector>
+
+using tcb::LaunchEnv;
+
+namespace tcb {
+cudaError_t init_gemv_kernels(int smem_optin);
+}
+
+// ---------------------------------------------------------------------------------------
+// Handle definitions
+// ---------------------------------------------------------------------------------------
+enum BufKind : int {
+    BUF_DEVICE = 0,        // cudaMalloc, owned; never seen by the host
+    BUF_MANAGED = 1,       // cudaMallocManaged, owned; host-visible after tc_buffer_map
+    BUF_WRAP_DEVICE = 2,   // caller's device memory
+    BUF_WRAP_MANAGED = 3,  // caller's managed memory
+    BUF_WRAP_HOST = 4,     // caller's host memory + owned device mirror, staged per operation
+    BUF_HOST_SHADOW = 5,   // owned pinned host shadow + device memory (when managed memory is
+                           // unavailable), staged per operation
+};
+
+struct tc_context {
+    tc_device_info info;
+    std::atomic<int> ref;
+    int device;
+    int sm_count;
+    int smem_optin;
+    bool managed_ok;
+    bool pdl;
+    bool graphs;
+    cudaStream_t stream0;
+    uint32_t* err_host;   // pinned, mapped
+    uint32_t* err_dev;
+};
+
+struct tc_buffer {
+    void* dptr;
+    void* hptr;
+    size_t bytes;
+    tc_context* owner;
+    BufKind kind;
+    bool prefetch_hint;   // host may have touched a managed buffer since its last device use
+};
+
+namespace {
+
+enum OpKind : int { OP_GEMV_Q = 1 };
+
+struct RecordedOp {
+    int kind;
+    tcb::GemvQArgs a;
+    tc_buffer* X;
+    tc_buffer* W;
+    tc_buffer* Y;
+    tc_buffer* gamma;
+    size_t x_bytes, w_bytes, y_bytes, g_bytes;
+};
+
+struct CachedGraph {
+    cudaGraphExec_t exec = nullptr;
+    int kernels = 0;
+    int seen = 0;
+};
+
+}  // namespace
+
+struct tc_stream {
+    tc_context* owner;
+    cudaStream_t s;
+    std::vector<RecordedOp> pending;
+    std::unordered_map<uint64_t, CachedGraph> cache;
+};
+
+namespace {
+
+tc_context* g_ctx = nullptr;
+std::mutex g_ctx_mutex;
+thread_local tc_backend_t t_last_backend = TC_BACKEND_NONE;
+thread_local const char* t_last_kernel = "none";
+std::atomic<uint64_t> g_launches{0};
+std::atomic<int> g_variant{tcb::VARIANT_AUTO};
+
+bool env_flag(const char* name, bool dflt) {
+    const char* v = std::getenv(name);
+    if (!v || !v[0]) return dflt;
+    return v[0] != '0';
+}
+
+bool trace_enabled() {
+    static const bool on = env_flag("TC_TRACE", false);
+    return on;
+}
+
+// lib/core/trace.cpp:22-37 - remember the backend on success, optional one-line trace.
+tc_status_t record(const char* op, tc_status_t st) {
+    if (st == TC_OK) t_last_backend = TC_BACKEND_CUDA;
+    if (trace_enabled()) {
+        std::fprintf(stderr, "[tensorcore] trace op=%s status=%s backend=%s\n", op ? op : "?",
+                     tc_status_string(st), tc_backend_name(tc_last_backend()));
+    }
+    return st;
+}
+
+tc_status_t from_cuda(cudaError_t e, tc_status_t fallback) {
+    if (e == cudaSuccess) return TC_OK;
+    if (e == cudaErrorMemoryAllocation) return TC_ERR_ALLOC;
+    if (trace_enabled())
+        std::fprintf(stderr, "[tensorcore] cuda error: %s\n", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return fallback;
+}
+
+bool checked_mul(size_t a, size_t b, size_t* out) {
+    if (a != 0 && b > std::numeric_limits<size_t>::max() / a) return false;
+    *out = a * b;
+    return true;
+}
+
+bool matrix_bytes(int rows, int cols, size_t elem, size_t* out) {
+    size_t n = 0;
+    if (rows <= 0 || cols <= 0) return false;
+    if (!checked_mul(static_cast<size_t>(rows), static_cast<size_t>(cols), &n)) return false;
+    return checked_mul(n, elem, out);
+}
+
+// lib/core/device_cpu.cpp:236-243
+tc_status_t validate(tc_context* ctx, const tc_buffer* b, size_t min_bytes) {
+    if (!ctx || !b || !b->dptr) return TC_ERR_INVALID_ARG;
+    if (b->owner != ctx) return TC_ERR_INVALID_ARG;
+    if (min_bytes > b->bytes) return TC_ERR_INVALID_SHAPE;
+    return TC_OK;
+}
+
+bool staged(const tc_buffer* b) { return b->kind == BUF_WRAP_HOST || b->kind == BUF_HOST_SHADOW; }
+bool managed(const tc_buffer* b) { return b->kind == BUF_MANAGED || b->kind == BUF_WRAP_MANAGED; }
+
+LaunchEnv make_env(tc_context* ctx, bool allow_pdl) {
+    LaunchEnv e;
+    e.sm_count = ctx->sm_count;
+    e.smem_optin = ctx->smem_optin;
+    e.pdl = allow_pdl && ctx->pdl;
+    e.variant = g_variant.load();
+    e.err_word = ctx->err_dev;
+    return e;
+}
+
+// Makes `bytes` of an input buffer current on the device before a kernel reads it.
+cudaError_t prepare_input(tc_context* ctx, tc_buffer* b, size_t bytes, cudaStream_t st) {
+    if (staged(b)) return cudaMemcpyAsync(b->dptr, b->hptr, bytes, cudaMemcpyHostToDevice, st);
+    if (managed(b) && b->prefetch_hint) {
+        b->prefetch_hint = false;
+        if (ctx->managed_ok) (void)cudaMemPrefetchAsync(b->dptr, b->bytes, ctx->device, st);
+        (void)cudaGetLastError();  // a refused hint is not an error: pages fault in on demand
+    }
+    return cudaSuccess;
+}
+cudaError_t prepare_output(tc_context* ctx, tc_buffer* b, cudaStream_t st) {
+    if (managed(b) && b->prefetch_hint) {
+        b->prefetch_hint = false;
+        if (ctx->managed_ok) (void)cudaMemPrefetchAsync(b->dptr, b->bytes, ctx->device, st);
+        (void)cudaGetLastError();
+    }
+    return cudaSuccess;
+}
+cudaError_t finish_output(tc_buffer* b, size_t bytes, cudaStream_t st) {
+    if (staged(b)) return cudaMemcpyAsync(b->hptr, b->dptr, bytes, cudaMemcpyDeviceToHost, st);
+    return cudaSuccess;
+}
+
+tc_status_t check_device_error(tc_context* ctx) {
+    if (ctx->err_host && *reinterpret_cast<volatile uint32_t*>(ctx->err_host) != 0) {
+        return TC_ERR_INTERNAL;  // left set; tcx_take_device_error reads and clears it
+    }
+    return TC_OK;
+}
+
+cudaError_t bind_device(tc_context* ctx) { return cudaSetDevice(ctx->device); }
+
+tc_status_t setup_device(tc_context* ctx, int device) {
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return TC_ERR_NO_DEVICE;
+    if (prop.major != 10) return TC_ERR_NO_DEVICE;  // kernels are built for sm_100a only
+    if (cudaSetDevice(device) != cudaSuccess) return TC_ERR_NO_DEVICE;
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    int optin = 0;
+    cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+    ctx->smem_optin = optin;
+    int mm = 0, cma = 0;
+    cudaDeviceGetAttribute(&mm, cudaDevAttrManagedMemory, device);
+    cudaDeviceGetAttribute(&cma, cudaDevAttrConcurrentManagedAccess, device);
+    ctx->managed_ok = (mm != 0) && (cma != 0) && env_flag("TC_MANAGED_MAP", true);
+
+    std::memset(&ctx->info, 0, sizeof(ctx->info));
+    ctx->info.family = TC_FAMILY_UNKNOWN;
+    std::strncpy(ctx->info.name, "cuda", sizeof(ctx->info.name) - 1);
+    ctx->info.max_buffer_bytes = prop.totalGlobalMem;
+    ctx->info.recommended_working_set_bytes = prop.totalGlobalMem;
+    ctx->info.max_threadgroup_memory = static_cast<uint32_t>(optin);
+    ctx->info.max_threads_per_threadgroup = static_cast<uint32_t>(prop.maxThreadsPerBlock);
+    ctx->info.thread_execution_width = static_cast<uint32_t>(prop.warpSize);
+    ctx->info.unified_memory = false;
+    ctx->info.supports_fp64_native = true;
+
+    if (cudaStreamCreateWithFlags(&ctx->stream0, cudaStreamNonBlocking) != cudaSuccess)
+        return TC_ERR_INTERNAL;
+    if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->err_host), sizeof(uint32_t),
+                      cudaHostAllocMapped) != cudaSuccess)
+        return TC_ERR_ALLOC;
+    *ctx->err_host = 0;
+    if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->err_dev), ctx->err_host, 0) !=
+        cudaSuccess)
+        return TC_ERR_INTERNAL;
+    if (tcb::init_gemv_kernels(optin) != cudaSuccess) return TC_ERR_INTERNAL;
+    return TC_OK;
+}
+
+void teardown_device(tc_context* ctx) {
+    if (ctx->stream0) cudaStreamDestroy(ctx->stream0);
+    if (ctx->err_host) cudaFreeHost(ctx->err_host);
+    ctx->stream0 = nullptr;
+    ctx->err_host = nullptr;
+    ctx->err_dev = nullptr;
+}
+
+uint64_t fnv1a(uint64_t h, const void* data, size_t n) {
+    const uint8_t* p = static_cast<const uint8_t*>(data);
+    for (size_t i = 0; i < n; ++i) { h ^= p[i]; h *= 1099511628211ull; }
+    return h;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// Strings
+// ---------------------------------------------------------------------------------------
+extern "C" const int tensorcore_abi_version = 1;
+
+extern "C" const char* tc_version(void) { return "tensorcore 0.1.22"; }
+
+extern "C" const char* tc_status_string(tc_status_t s) {
+    switch (s) {
+        case TC_OK: return "ok";
+        case TC_ERR_NOT_INITIALIZED: return "context not initialized";
+        case TC_ERR_ALREADY_INITIALIZED: return "context already initialized";
+        case TC_ERR_NO_DEVICE: return "no Metal device available";
+        case TC_ERR_UNSUPPORTED_FAMILY: return "operation unsupported on this GPU family";
+        case TC_ERR_UNSUPPORTED_DTYPE: return "dtype unsupported on this GPU family";
+        case TC_ERR_INVALID_SHAPE: return "invalid tensor shape";
+        case TC_ERR_INVALID_ARG: return "invalid argument";
+        case TC_ERR_ALLOC: return "allocation failure";
+        case TC_ERR_KERNEL_NOT_FOUND: return "kernel not in metallib";
+        case TC_ERR_PIPELINE: return "MTLComputePipelineState creation failed";
+        case TC_ERR_DISPATCH: return "command-buffer dispatch failed";
+        case TC_ERR_INTERNAL: return "internal error";
+    }
+    return "unknown status";
+}
+
+extern "C" const char* tc_dtype_name(tc_dtype_t d) {
+    static const char* const names[] = {"f16", "bf16", "f32", "i8", "i32",
+                                        "f64", "sf64", "df64", "fp24", "fp53"};
+    const int i = static_cast<int>(d);
+    return (i >= 0 && i < 10) ? names[i] : "?";
+}
+
+extern "C" const char* tc_backend_name(tc_backend_t b) {
+    static const char* const names[] = {"none", "simdgroup_matrix", "tensorops_m5", "mps",
+                                        "accelerate_cpu", "sf64_emulated", "ozaki_ii",
+                                        "portable_cpu", "metal_compute", "cuda", "hip"};
+    const int i = static_cast<int>(b);
+    return (i >= 0 && i <= 10) ? names[i] : "?";
+}
+
+extern "C" tc_backend_t tc_last_backend(void) { return t_last_backend; }
+extern "C" const char* tc_cuda_last_kernel_name(void) { return t_last_kernel; }
+
+// ---------------------------------------------------------------------------------------
+// Context
+// ---------------------------------------------------------------------------------------
+extern "C" tc_status_t tc_init(tc_context** out_ctx) {
+    if (!out_ctx) return TC_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    if (g_ctx) {
+        g_ctx->ref.fetch_add(1);
+        *out_ctx = g_ctx;
+        return TC_ERR_ALREADY_INITIALIZED;
+    }
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+        (void)cudaGetLastError();
+        return TC_ERR_NO_DEVICE;
+    }
+    int device = 0;
+    if (const char* v = std::getenv("TC_CUDA_DEVICE")) device = std::atoi(v);
+    else if (cudaGetDevice(&device) != cudaSuccess) device = 0;
+    if (device < 0 || device >= count) return TC_ERR_NO_DEVICE;
+
+    tc_context* ctx = new (std::nothrow) tc_context();
+    if (!ctx) return TC_ERR_ALLOC;
+    ctx->ref.store(1);
+    ctx->stream0 = nullptr;
+    ctx->err_host = nullptr;
+    ctx->err_dev = nullptr;
+    ctx->pdl = env_flag("TC_PDL", true);
+    ctx->graphs = env_flag("TC_STREAM_GRAPH", true);
+    const tc_status_t st = setup_device(ctx, device);
+    if (st != TC_OK) {
+        teardown_device(ctx);
+        delete ctx;
+        return st;
+    }
+    g_ctx = ctx;
+    *out_ctx = ctx;
+    return TC_OK;
+}
+
+extern "C" tc_status_t tc_shutdown(tc_context* ctx) {
+    if (!ctx) return TC_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    if (ctx != g_ctx) return TC_ERR_INVALID_ARG;
+    if (ctx->ref.fetch_sub(1) > 1) return TC_OK;
+    g_ctx = nullptr;
+    bind_device(ctx);
+    cudaDeviceSynchronize();
+    teardown_device(ctx);
+    delete ctx;
+    return TC_OK;
+}
+
+extern "C" tc_status_t tc_device_info_get(tc_context* ctx, tc_device_info* out_info) {
+    if (!ctx || !out_info) return TC_ERR_INVALID_ARG;
+    *out_info = ctx->info;
+    return TC_OK;
+}
+
+// --- tc_cuda_* ---------------------------------------------------------------------------
+static bool fill_cuda_info(int index, tc_cuda_device_info* out) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || index >= count) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, index) != cudaSuccess) return false;
+    std::memset(out, 0, sizeof(*out));
+    std::strncpy(out->device_name, prop.name, sizeof(out->device_name) - 1);
+    std::snprintf(out->compute_capability, sizeof(out->compute_capability), "%d.%d", prop.major,
+                  prop.minor);
+    out->major = prop.major;
+    out->minor = prop.minor;
+    out->global_memory_bytes = prop.totalGlobalMem;
+    out->shared_memory_per_block = prop.sharedMemPerBlock;
+    out->multiprocessor_count = static_cast<uint32_t>(prop.multiProcessorCount);
+    out->max_threads_per_block = static_cast<uint32_t>(prop.maxThreadsPerBlock);
+    out->warp_size = static_cast<uint32_t>(prop.warpSize);
+    out->supports_fp16 = (prop.major > 5) || (prop.major == 5 && prop.minor >= 3);
+    out->supports_bf16 = prop.major >= 8;
+    out->supports_int8_tensor_core = (prop.major > 7) || (prop.major == 7 && prop.minor >= 2);
+    out->supports_tf32 = prop.major >= 8;
+    out->unified_memory = prop.integrated != 0;
+    return true;
+}
+
+extern "C" tc_status_t tc_cuda_init(tc_context* ctx) {
+    if (!ctx) return TC_ERR_NOT_INITIALIZED;
+    return TC_OK;  // tc_init already bound the device
+}
+
+extern "C" int tc_cuda_device_count(void) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+    return count;
+}
+
+extern "C" tc_status_t tc_cuda_device_at(int index, tc_cuda_device_info* out_info) {
+    if (index < 0 || !out_info) return TC_ERR_INVALID_ARG;
+    return fill_cuda_info(index, out_info) ? TC_OK : TC_ERR_INVALID_ARG;
+}
+
+extern "C" tc_status_t tc_cuda_select_device(tc_context* ctx, int index) {
+    if (!ctx) return TC_ERR_NOT_INITIALIZED;
+    if (index < 0 || index >= tc_cuda_device_count()) return TC_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    if (index == ctx->device) return from_cuda(bind_device(ctx), TC_ERR_INTERNAL);
+    // Buffers and streams created on the old device keep working only there; like the
+    // reference, switching is meant to happen before any allocation.
+    bind_device(ctx);
+    cudaDeviceSynchronize();
+    teardown_device(ctx);
+    return setup_device(ctx, index);
+}
+
+// ---------------------------------------------------------------------------------------
+// Buffers
+// ---------------------------------------------------------------------------------------
+extern "C" tc_status_t tc_buffer_alloc(tc_context* ctx, size_t bytes, tc_buffer** out) {
+    if (!ctx || !out || bytes == 0) return TC_ERR_INVALID_ARG;
+    tc_buffer* b = new (std::nothrow) tc_buffer();
+    if (!b) return TC_ERR_ALLOC;
+    bind_device(ctx);
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess || !p) {
+        (void)cudaGetLastError();
+        delete b;
+        return TC_ERR_ALLOC;
+    }
+    b->dptr = p;
+    b->hptr = nullptr;
+    b->bytes = bytes;
+    b->owner = ctx;
+    b->kind = BUF_DEVICE;
+    b->prefetch_hint = false;
+    *out = b;
+    return TC_OK;
+}
+
+extern "C" tc_status_t tc_buffer_from_ptr(tc_context* ctx, void* ptr, size_t bytes,
+                                          tc_buffer** out) {
+    if (!ctx || !ptr || !out || bytes == 0) return TC_ERR_INVALID_ARG;
+    tc_buffer* b = new (std::nothrow) tc_buffer();
+    if (!b) return TC_ERR_ALLOC;
+    bind_device(ctx);
+    cudaPointerAttributes at;
+    std::memset(&at, 0, sizeof(at));
+    cudaMemoryType type = cudaMemoryTypeUnregistered;
+    if (cudaPointerGetAttributes(&at, ptr) == cudaSuccess) type = at.type;
+    else (void)cudaGetLastError();
+    b->bytes = bytes;
+    b->owner = ctx;
+    b->prefetch_hint = false;
+    b->hptr = nullptr;
+    if (type == cudaMemoryTypeDevice) {
+        b->kind = BUF_WRAP_DEVICE;
+        b->dptr = ptr;
+    } else if (type == cudaMemoryTypeManaged) {
+        b->kind = BUF_WRAP_MANAGED;
+        b->dptr = ptr;
+        b->prefetch_hint = true;
+    } else {
+        void* mirror = nullptr;
+        if (cudaMalloc(&mirror, bytes) != cudaSuccess || !mirror) {
+            (void)cudaGetLastError();
+            delete b;
+            return TC_ERR_ALLOC;
+        }
+        b->kind = BUF_WRAP_HOST;
+        b->dptr = mirror;
+        b->hptr = ptr;
+    }
+    *out = b;
+    return TC_OK;
+}
+
+extern "C" tc_status_t tc_buffer_free(tc_context* ctx, tc_buffer* buf) {
+    if (!ctx || !buf || buf->owner != ctx) return TC_ERR_INVALID_ARG;
+    bind_device(ctx);
+    switch (buf->kind) {
+        case BUF_DEVICE:
+        case BUF_MANAGED:
+        case BUF_WRAP_HOST:
+            if (buf->dptr) cudaFree(buf->dptr);  // cudaFree waits for work that uses the memory
+            break;
+        case BUF_HOST_SHADOW:
+            if (buf->dptr) cudaFree(buf->dptr);
+            if (buf->hptr) cudaFreeHost(buf->hptr);
+            break;
+        default:
+            break;
+    }
+    buf->dptr = nullptr;
+    buf->owner = nullptr;
+    delete buf;
+    return TC_OK;
+}
+
+// The reference contract: the pointer is stable for the buffer's life and there is no unmap
+// (include/tensorcore/device.h:59-62).  A device buffer is converted once, on its first map,
+// to managed memory, which the driver keeps coherent page by page; its contents are carried
+// over.  Later maps only note that the host may have written, so that the next operation can
+// move the pages back in one prefetch instead of by demand faults.
+extern "C" tc_status_t tc_buffer_map(tc_buffer* buf, void** out_ptr) {
+    if (!buf || !buf->dptr || !out_ptr) return TC_ERR_INVALID_ARG;
+    tc_context* ctx = buf->owner;
+    if (!ctx) return TC_ERR_INVALID_ARG;
+    switch (buf->kind) {
+        case BUF_MANAGED:
+        case BUF_WRAP_MANAGED:
+            buf->prefetch_hint = true;
+            *out_ptr = buf->dptr;
+            return TC_OK;
+        case BUF_WRAP_HOST:
+        case BUF_HOST_SHADOW:
+            *out_ptr = buf->hptr;
+            return TC_OK;
+        case BUF_WRAP_DEVICE:
+            return TC_ERR_INVALID_ARG;
+        case BUF_DEVICE:
+            break;
+    }
+    bind_device(ctx);
+    if (cudaDeviceSynchronize() != cudaSuccess) return TC_ERR_INTERNAL;
+    if (ctx->managed_ok) {
+        void* m = nullptr;
+        if (cudaMallocManaged(&m, buf->bytes, cudaMemAttachGlobal) != cudaSuccess || !m) {
+            (void)cudaGetLastError();
+            return TC_ERR_ALLOC;
+        }
+        if (cudaMemcpy(m, buf->dptr, buf->bytes, cudaMemcpyDeviceToDevice) != cudaSuccess) {
+            cudaFree(m);
+            return TC_ERR_INTERNAL;
+        }
+        (void)cudaMemAdvise(m, buf->bytes, cudaMemAdviseSetPreferredLocation, ctx->device);
+        (void)cudaGetLastError();
+        cudaFree(buf->dptr);
+        buf->dptr = m;
+        buf->kind = BUF_MANAGED;
+        buf->prefetch_hint = true;
+        *out_ptr = m;
+        return TC_OK;
+    }
+    void* h = nullptr;
+    if (cudaHostAlloc(&h, buf->bytes, cudaHostAllocDefault) != cudaSuccess || !h) {
+        (void)cudaGetLastError();
+        return TC_ERR_ALLOC;
+    }
+    if (cudaMemcpy(h, buf->dptr, buf->bytes, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaFreeHost(h);
+        return TC_ERR_INTERNAL;
+    }
+    buf->hptr = h;
+    buf->kind = BUF_HOST_SHADOW;
+    *out_ptr = h;
+    return TC_OK;
+}
+
+extern "C" size_t tc_buffer_size(const tc_buffer* buf) { return buf ? buf->bytes : 0; }
+
+extern "C" tc_status_t tcx_buffer_upload(tc_buffer* buf, size_t offset, const void* src,
+                                         size_t bytes) {
+    if (!buf || !buf->dptr || !src || !buf->owner) return TC_ERR_INVALID_ARG;
+    if (offset > buf->bytes || bytes > buf->bytes - offset) return TC_ERR_INVALID_SHAPE;
+    bind_device(buf->owner);
+    if (staged(buf)) std::memcpy(static_cast<uint8_t*>(buf->hptr) + offset, src, bytes);
+    return from_cuda(cudaMemcpy(static_cast<uint8_t*>(buf->dptr) + offset, src, bytes,
+                                cudaMemcpyHostToDevice), TC_ERR_INTERNAL);
+}
+
+extern "C" tc_status_t tcx_buffer_download(const tc_buffer* buf, size_t offset, void* dst,
+                                           size_t bytes) {
+    if (!buf || !buf->dptr || !dst || !buf->owner) return TC_ERR_INVALID_ARG;
+    if (offset > buf->bytes || bytes > buf->bytes - offset) return TC_ERR_INVALID_SHAPE;
+    bind_device(buf->owner);
+    return from_cuda(cudaMemcpy(dst, static_cast<const uint8_t*>(buf->dptr) + offset, bytes,
+                                cudaMemcpyDeviceToHost), TC_ERR_INTERNAL);
+}
+
+extern "C" tc_status_t tcx_buffer_device_ptr(const tc_buffer* buf, void** out_dptr) {
+    if (!buf || !out_dptr) return TC_ERR_INVALID_ARG;
+    *out_dptr = buf->dptr;
+    return TC_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Streams
+// ---------------------------------------------------------------------------------------
+extern "C" tc_status_t tc_stream_create(tc_context* ctx, tc_stream** out) {
+    if (!ctx || !out) return TC_ERR_INVALID_ARG;
+    tc_stream* s = new (std::nothrow) tc_stream();
+    if (!s) return TC_ERR_ALLOC;
+    bind_device(ctx);
+    if (cudaStreamCreateWithFlags(&s->s, cudaStreamNonBlocking) != cudaSuccess) {
+        (void)cudaGetLastError();
+        delete s;
+        return TC_ERR_INTERNAL;
+    }
+    s->owner = ctx;
+    *out = s;
+    return TC_OK;
+}
+
+static void drop_graphs(tc_stream* s) {
+    for (auto& kv : s->cache)
+        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    s->cache.clear();
+}
+
+extern "C" tc_status_t tc_stream_destroy(tc_context* ctx, tc_stream* s) {
+    if (!ctx || !s || s->owner != ctx) return TC_ERR_INVALID_ARG;
+    bind_device(ctx);
+    cudaStreamSynchronize(s->s);
+    drop_graphs(s);
+    cudaStreamDestroy(s->s);
+    delete s;
+    return TC_OK;
+}
+
+namespace {
+
+cudaError_t launch_recorded(tc_context* ctx, const RecordedOp& op, cudaStream_t st, bool pdl,
+                            int* launches, const char** name) {
+    LaunchEnv env = make_env(ctx, pdl);
+    return tcb::launch_gemv_q(op.a, env, st, launches, name);
+}
+
+// Submits the recorded operations.  Lists without host-staged buffers are replayed as a CUDA
+// graph from the second time the identical list (same kernels, pointers and shapes) is seen;
+// the first submission of a list, and lists that need staging copies, launch directly.
+tc_status_t submit_pending(tc_stream* s) {
+    tc_context* ctx = s->owner;
+    if (s->pending.empty()) return TC_OK;
+    bind_device(ctx);
+    bool any_staged = false;
+    uint64_t sig = 1469598103934665603ull;
+    for (RecordedOp& op : s->pending) {
+        tc_buffer* bufs[4] = {op.X, op.W, op.Y, op.gamma};
+        for (tc_buffer* b : bufs)
+            if (b && staged(b)) any_staged = true;
+        sig = fnv1a(sig, &op.kind, sizeof(op.kind));
+        sig = fnv1a(sig, &op.a, sizeof(op.a));
+    }
+    const int variant = g_variant.load();
+    sig = fnv1a(sig, &variant, sizeof(variant));
+
+    cudaError_t e = cudaSuccess;
+    // Host-visible inputs first (staging copies or prefetch hints), outside any graph.
+    for (RecordedOp& op : s->pending) {
+        if (e == cudaSuccess) e = prepare_input(ctx, op.X, op.x_bytes, s->s);
+        if (e == cudaSuccess) e = prepare_input(ctx, op.W, op.w_bytes, s->s);
+        if (e == cudaSuccess && op.gamma) e = prepare_input(ctx, op.gamma, op.g_bytes, s->s);
+        if (e == cudaSuccess) e = prepare_output(ctx, op.Y, s->s);
+    }
+    if (e != cudaSuccess) { s->pending.clear(); return from_cuda(e, TC_ERR_DISPATCH); }
+
+    const char* name = t_last_kernel;
+    int launches = 0;
+    bool done = false;
+    if (ctx->graphs && !any_staged && s->pending.size() > 1) {
+        CachedGraph& cg = s->cache[sig];
+        if (cg.exec) {
+            e = cudaGraphLaunch(cg.exec, s->s);
+            launches = cg.kernels;
+            done = true;
+        } else if (cg.seen >= 1) {
+            cudaGraph_t graph = nullptr;
+            e = cudaStreamBeginCapture(s->s, cudaStreamCaptureModeThreadLocal);
+            if (e == cudaSuccess) {
+                cudaError_t le = cudaSuccess;
+                int k = 0;
+                for (size_t i = 0; i < s->pending.size() && le == cudaSuccess; ++i)
+                    le = launch_recorded(ctx, s->pending[i], s->s, i > 0, &k, &name);
+                e = cudaStreamEndCapture(s->s, &graph);
+                if (le != cudaSuccess) e = le;
+                if (e == cudaSuccess && graph) {
+                    e = cudaGraphInstantiate(&cg.exec, graph, 0);
+                    if (e == cudaSuccess) {
+                        cg.kernels = k;
+                        e = cudaGraphLaunch(cg.exec, s->s);
+                        launches = k;
+                        done = true;
+                    } else {
+                        cg.exec = nullptr;
+                    }
+                }
+                if (graph) cudaGraphDestroy(graph);
+            }
+            if (!done) {  // capture or instantiation refused: fall through to direct launches
+                (void)cudaGetLastError();
+                e = cudaSuccess;
+                cg.seen = -1000000;  // do not try again for this list
+            }
+        }
+        if (!done) cg.seen += 1;
+        if (s->cache.size() > 64) {  // bound the cache: drop everything but keep working
+            if (!done) { drop_graphs(s); }
+        }
+    }
+    if (!done) {
+        for (size_t i = 0; i < s->pending.size() && e == cudaSuccess; ++i)
+            e = launch_recorded(ctx, s->pending[i], s->s, i > 0, &launches, &name);
+    }
+    if (e == cudaSuccess && any_staged) {
+        for (RecordedOp& op : s->pending)
+            if (e == cudaSuccess) e = finish_output(op.Y, op.y_bytes, s->s);
+    }
+    g_launches.fetch_add(static_cast<uint64_t>(launches));
+    t_last_kernel = name;
+    s->pending.clear();
+    return from_cuda(e, TC_ERR_DISPATCH);
+}
+
+}  // namespace
+
+extern "C" tc_status_t tcx_stream_flush(tc_stream* s) {
+    if (!s) return TC_ERR_INVALID_ARG;
+    return submit_pending(s);
+}
+
+extern "C" tc_status_t tc_stream_sync(tc_stream* s) {
+    if (!s) return TC_ERR_INVALID_ARG;
+    tc_status_t st = submit_pending(s);
+    const cudaError_t e = cudaStreamSynchronize(s->s);
+    if (st == TC_OK) st = from_cuda(e, TC_ERR_DISPATCH);
+    if (st == TC_OK) st = check_device_error(s->owner);
+    return st;
+}
+
+extern "C" tc_status_t tcx_stream_cuda_handle(const tc_stream* s, void** out) {
+    if (!s || !out) return TC_ERR_INVALID_ARG;
+    *out = static_cast<void*>(s->s);
+    return TC_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Quantized operations
+// ---------------------------------------------------------------------------------------
+extern "C" size_t tc_quantized_size(tc_quant_t fmt, int N, int K) {
+    if (N <= 0 || K <= 0 || K % 32 != 0) return 0;
+    const size_t nblocks = static_cast<size_t>(K / 32);
+    if (fmt == TC_QUANT_Q4_0) return static_cast<size_t>(N) * nblocks * 18u;
+    if (fmt == TC_QUANT_Q8_0) return static_cast<size_t>(N) * nblocks * 34u;
+    return 0;
+}
+
+extern "C" tc_status_t tc_quantize_weights(tc_context* ctx, const tc_buffer* W_fp16,
+                                           tc_buffer* W_quant, tc_quant_t fmt, int N, int K) {
+    if (!ctx) return TC_ERR_NOT_INITIALIZED;
+    if (!W_fp16 || !W_quant || N <= 0 || K <= 0 || K % 32 != 0) return TC_ERR_INVALID_ARG;
+    size_t in_bytes = 0;
+    if (!matrix_bytes(N, K, 2, &in_bytes)) return TC_ERR_INVALID_ARG;
+    const size_t out_bytes = tc_quantized_size(fmt, N, K);
+    if (out_bytes == 0) return TC_ERR_INVALID_ARG;
+    tc_status_t st = validate(ctx, W_fp16, in_bytes);
+    if (st != TC_OK) return st;
+    st = validate(ctx, W_quant, out_bytes);
+    if (st != TC_OK) return st;
+    if ((reinterpret_cast<uintptr_t>(W_fp16->dptr) & 15u) != 0) return TC_ERR_INVALID_ARG;
+
+    bind_device(ctx);
+    tc_buffer* in = const_cast<tc_buffer*>(W_fp16);
+    cudaStream_t s0 = ctx->stream0;
+    cudaError_t e = prepare_input(ctx, in, in_bytes, s0);
+    if (e == cudaSuccess) e = prepare_output(ctx, W_quant, s0);
+    int launches = 0;
+    const char* name = "none";
+    if (e == cudaSuccess)
+        e = tcb::launch_quantize(in->dptr, W_quant->dptr, static_cast<int>(fmt), N, K,
+                                 make_env(ctx, false), s0, &launches, &name);
+    if (e == cudaSuccess) e = finish_output(W_quant, out_bytes, s0);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s0);
+    g_launches.fetch_add(static_cast<uint64_t>(launches));
+    t_last_kernel = name;
+    return record("tc_quantize_weights", from_cuda(e, TC_ERR_DISPATCH));
+}
+
+namespace {
+
+struct GemvCall {
+    tc_context* ctx;
+    const tc_buffer* X;
+    const tc_buffer* gamma;  // null unless fused
+    const tc_buffer* W;
+    tc_buffer* Y;
+    tc_quant_t fmt;
+    int M, N, K;
+    float eps;
+    tc_dtype_t xd, yd;
+    bool fused;
+};
+
+// Argument checks in the reference's order (lib/ops/quantized_cpu.cpp:171-177, 243-250),
+// then either a direct launch + wait (stream == null) or a recording on the stream.
+tc_status_t gemv_common(const GemvCall& c, tc_stream* stream, const char* opname) {
+    if (!c.ctx) return TC_ERR_NOT_INITIALIZED;
+    if (!c.X || !c.W || !c.Y || (c.fused && !c.gamma) || c.M <= 0 || c.N <= 0 || c.K <= 0 ||
+        c.K % 32 != 0)
+        return TC_ERR_INVALID_ARG;
+    if ((c.xd != TC_DTYPE_F16 && c.xd != TC_DTYPE_F32) ||
+        (c.yd != TC_DTYPE_F16 && c.yd != TC_DTYPE_F32))
+        return TC_ERR_UNSUPPORTED_DTYPE;
+    const size_t xs = c.xd == TC_DTYPE_F32 ? 4 : 2, ys = c.yd == TC_DTYPE_F32 ? 4 : 2;
+    size_t xb = 0, yb = 0, gb = 0;
+    if (!matrix_bytes(c.M, c.K, xs, &xb) || !matrix_bytes(c.M, c.N, ys, &yb))
+        return TC_ERR_INVALID_ARG;
+    const size_t wb = tc_quantized_size(c.fmt, c.N, c.K);
+    if (wb == 0) return TC_ERR_INVALID_ARG;
+    tc_status_t st = validate(c.ctx, c.X, xb);
+    if (st != TC_OK) return st;
+    st = validate(c.ctx, c.W, wb);
+    if (st != TC_OK) return st;
+    st = validate(c.ctx, c.Y, yb);
+    if (st != TC_OK) return st;
+    if (c.fused) {
+        if (!matrix_bytes(1, c.K, xs, &gb)) return TC_ERR_INVALID_ARG;
+        st = validate(c.ctx, c.gamma, gb);
+        if (st != TC_OK) return st;
+    }
+    if (stream && stream->owner != c.ctx) return TC_ERR_INVALID_ARG;
+
+    RecordedOp op;
+    op.kind = OP_GEMV_Q;
+    op.X = const_cast<tc_buffer*>(c.X);
+    op.W = const_cast<tc_buffer*>(c.W);
+    op.Y = c.Y;
+    op.gamma = c.fused ? const_cast<tc_buffer*>(c.gamma) : nullptr;
+    op.x_bytes = xb; op.w_bytes = wb; op.y_bytes = yb; op.g_bytes = gb;
+    std::memset(&op.a, 0, sizeof(op.a));  // padding bytes take part in the list signature
+    op.a.W = static_cast<const uint8_t*>(c.W->dptr);
+    op.a.X = c.X->dptr;
+    op.a.Y = c.Y->dptr;
+    op.a.gamma = c.fused ? c.gamma->dptr : nullptr;
+    op.a.fmt = static_cast<int>(c.fmt);
+    op.a.M = c.M; op.a.N = c.N; op.a.K = c.K;
+    op.a.x_f32 = c.xd == TC_DTYPE_F32;
+    op.a.y_f32 = c.yd == TC_DTYPE_F32;
+    op.a.eps = c.eps;
+
+    if (stream) {
+        stream->pending.push_back(op);
+        return record(opname, TC_OK);
+    }
+    tc_context* ctx = c.ctx;
+    bind_device(ctx);
+    cudaStream_t s0 = ctx->stream0;
+    cudaError_t e = prepare_input(ctx, op.X, xb, s0);
+    if (e == cudaSuccess) e = prepare_input(ctx, op.W, wb, s0);
+    if (e == cudaSuccess && op.gamma) e = prepare_input(ctx, op.gamma, gb, s0);
+    if (e == cudaSuccess) e = prepare_output(ctx, op.Y, s0);
+    int launches = 0;
+    const char* name = "none";
+    if (e == cudaSuccess) e = launch_recorded(ctx, op, s0, false, &launches, &name);
+    if (e == cudaSuccess) e = finish_output(op.Y, yb, s0);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s0);
+    g_launches.fetch_add(static_cast<uint64_t>(launches));
+    t_last_kernel = name;
+    tc_status_t out = from_cuda(e, TC_ERR_DISPATCH);
+    if (out == TC_OK) out = check_device_error(ctx);
+    return record(opname, out);
+}
+
+}  // namespace
+
+extern "C" tc_status_t tc_gemv_quantized(tc_context* ctx, const tc_buffer* X,
+                                         const tc_buffer* W_quant, tc_buffer* Y, tc_quant_t fmt,
+                                         int M, int N, int K) {
+    GemvCall c{ctx, X, nullptr, W_quant, Y, fmt, M, N, K, 0.f, TC_DTYPE_F16, TC_DTYPE_F16, false};
+    return gemv_common(c, nullptr, "tc_gemv_quantized");
+}
+
+extern "C" tc_status_t tc_gemv_quantized_async(tc_context* ctx, const tc_buffer* X,
+                                               const tc_buffer* W_quant, tc_buffer* Y,
+                                               tc_quant_t fmt, int M, int N, int K,
+                                               tc_stream* stream) {
+    if (!stream) return TC_ERR_INVALID_ARG;
+    GemvCall c{ctx, X, nullptr, W_quant, Y, fmt, M, N, K, 0.f, TC_DTYPE_F16, TC_DTYPE_F16, false};
+    return gemv_common(c, stream, "tc_gemv_quantized_async");
+}
+
+extern "C" tc_status_t tc_fused_rmsnorm_gemv_quantized(tc_context* ctx, const tc_buffer* X,
+                                                       const tc_buffer* gamma,
+                                                       const tc_buffer* W_quant, tc_buffer* Y,
+                                                       tc_quant_t fmt, int M, int N, int K,
+                                                       float eps) {
+    GemvCall c{ctx, X, gamma, W_quant, Y, fmt, M, N, K, eps, TC_DTYPE_F16, TC_DTYPE_F16, true};
+    return gemv_common(c, nullptr, "tc_fused_rmsnorm_gemv_quantized");
+}
+
+extern "C" tc_status_t tcx_gemv_quantized_ex(tc_context* ctx, const tc_buffer* X,
+                                             const tc_buffer* W_quant, tc_buffer* Y,
+                                             tc_quant_t fmt, int M, int N, int K,
+                                             tc_dtype_t x_dtype, tc_dtype_t y_dtype,
+                                             tc_stream* stream) {
+    GemvCall c{ctx, X, nullptr, W_quant, Y, fmt, M, N, K, 0.f, x_dtype, y_dtype, false};
+    return gemv_common(c, stream, "tcx_gemv_quantized_ex");
+}
+
+extern "C" tc_status_t tcx_fused_rmsnorm_gemv_quantized_ex(
+    tc_context* ctx, const tc_buffer* X, const tc_buffer* gamma, const tc_buffer* W_quant,
+    tc_buffer* Y, tc_quant_t fmt, int M, int N, int K, float eps, tc_dtype_t x_dtype,
+    tc_dtype_t y_dtype, tc_stream* stream) {
+    GemvCall c{ctx, X, gamma, W_quant, Y, fmt, M, N, K, eps, x_dtype, y_dtype, true};
+    return gemv_common(c, stream, "tcx_fused_rmsnorm_gemv_quantized_ex");
+}
+
+// ---------------------------------------------------------------------------------------
+// Fused norm + dense fp16 GEMV
+// ---------------------------------------------------------------------------------------
+static tc_status_t dense_common(tc_context* ctx, const tc_buffer* X, const tc_buffer* gamma,
+                                const tc_buffer* beta, bool layernorm, const tc_buffer* W,
+                                tc_buffer* Y, int M, int N, int K, float eps, const char* opname) {
+    if (!ctx) return TC_ERR_NOT_INITIALIZED;
+    if (!X || !gamma || (layernorm && !beta) || !W || !Y || M <= 0 || N <= 0 || K <= 0)
+        return TC_ERR_INVALID_ARG;
+    size_t xb = 0, gb = 0, wb = 0, yb = 0;
+    if (!matrix_bytes(M, K, 2, &xb) || !matrix_bytes(1, K, 2, &gb) ||
+        !matrix_bytes(K, N, 2, &wb) || !matrix_bytes(M, N, 2, &yb))
+        return TC_ERR_INVALID_ARG;
+    tc_status_t st = validate(ctx, X, xb);
+    if (st != TC_OK) return st;
+    st = validate(ctx, gamma, gb);
+    if (st != TC_OK) return st;
+    if (layernorm) {
+        st = validate(ctx, beta, gb);
+        if (st != TC_OK) return st;
+    }
+    st = validate(ctx, W, wb);
+    if (st != TC_OK) return st;
+    st = validate(ctx, Y, yb);
+    if (st != TC_OK) return st;
+
+    bind_device(ctx);
+    cudaStream_t s0 = ctx->stream0;
+    tc_buffer* bx = const_cast<tc_buffer*>(X);
+    tc_buffer* bg = const_cast<tc_buffer*>(gamma);
+    tc_buffer* bb = layernorm ? const_cast<tc_buffer*>(beta) : nullptr;
+    tc_buffer* bw = const_cast<tc_buffer*>(W);
+    cudaError_t e = prepare_input(ctx, bx, xb, s0);
+    if (e == cudaSuccess) e = prepare_input(ctx, bg, gb, s0);
+    if (e == cudaSuccess && bb) e = prepare_input(ctx, bb, gb, s0);
+    if (e == cudaSuccess) e = prepare_input(ctx, bw, wb, s0);
+    if (e == cudaSuccess) e = prepare_output(ctx, Y, s0);
+    tcb::DenseNormGemvArgs a;
+    a.X = bx->dptr; a.gamma = bg->dptr; a.beta = bb ? bb->dptr : nullptr; a.W = bw->dptr;
+    a.Y = Y->dptr; a.M = M; a.N = N; a.K = K; a.eps = eps;
+    int launches = 0;
+    const char* name = "none";
+    if (e == cudaSuccess)
+        e = tcb::launch_dense_norm_gemv(a, make_env(ctx, false), s0, &launches, &name);
+    if (e == cudaSuccess) e = finish_output(Y, yb, s0);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s0);
+    g_launches.fetch_add(static_cast<uint64_t>(launches));
+    t_last_kernel = name;
+    return record(opname, from_cuda(e, TC_ERR_DISPATCH));
+}
+
+extern "C" tc_status_t tc_fused_rmsnorm_gemv(tc_context* ctx, const tc_buffer* X,
+                                             const tc_buffer* gamma, const tc_buffer* W,
+                                             tc_buffer* Y, int M, int N, int K, float eps) {
+    return dense_common(ctx, X, gamma, nullptr, false, W, Y, M, N, K, eps, "tc_fused_rmsnorm_gemv");
+}
+
+extern "C" tc_status_t tc_fused_layernorm_gemv(tc_context* ctx, const tc_buffer* X,
+                                               const tc_buffer* gamma, const tc_buffer* beta,
+                                               const tc_buffer* W, tc_buffer* Y, int M, int N,
+                                               int K, float eps) {
+    return dense_common(ctx, X, gamma, beta, true, W, Y, M, N, K, eps, "tc_fused_layernorm_gemv");
+}
+
+// ---------------------------------------------------------------------------------------
+// Raw device-pointer launches
+// ---------------------------------------------------------------------------------------
+extern "C" tc_status_t tcx_raw_quantize_weights(tc_context* ctx, const void* W_fp16,
+                                                void* W_quant, tc_quant_t fmt, int N, int K,
+                                                void* cuda_stream) {
+    if (!ctx) return TC_ERR_NOT_INITIALIZED;
+    if (!W_fp16 || !W_quant || tc_quantized_size(fmt, N, K) == 0) return TC_ERR_INVALID_ARG;
+    if ((reinterpret_cast<uintptr_t>(W_fp16) & 15u) != 0) return TC_ERR_INVALID_ARG;
+    int launches = 0;
+    const char* name = "none";
+    const cudaError_t e = tcb::launch_quantize(W_fp16, W_quant, static_cast<int>(fmt), N, K,
+                                               make_env(ctx, false),
+                                               static_cast<cudaStream_t>(cuda_stream), &launches,
+                                               &name);
+    g_launches.fetch_add(static_cast<uint64_t>(launches));
+    t_last_kernel = name;
+    return record("tcx_raw_quantize_weights", from_cuda(e, TC_ERR_DISPATCH));
+}
+
+static tc_status_t raw_gemv(tc_context* ctx, const void* X, const void* gamma, bool fused,
+                            const void* W, void* Y, tc_quant_t fmt, int M, int N, int K, float eps,
+                            tc_dtype_t xd, tc_dtype_t yd, void* cuda_stream, const char* opname) {
+    if (!ctx) return TC_ERR_NOT_INITIALIZED;
+    if (!X || !W || !Y || (fused && !gamma) || M <= 0 || tc_quantized_size(fmt, N, K) == 0)
+        return TC_ERR_INVALID_ARG;
+    if ((xd != TC_DTYPE_F16 && xd != TC_DTYPE_F32) || (yd != TC_DTYPE_F16 && yd != TC_DTYPE_F32))
+        return TC_ERR_UNSUPPORTED_DTYPE;
+    tcb::GemvQArgs a;
+    a.W = static_cast<const uint8_t*>(W);
+    a.X = X; a.Y = Y; a.gamma = fused ? gamma : nullptr;
+    a.fmt = static_cast<int>(fmt); a.M = M; a.N = N; a.K = K;
+    a.x_f32 = xd == TC_DTYPE_F32; a.y_f32 = yd == TC_DTYPE_F32; a.eps = eps;
+    int launches = 0;
+    const char* name = "none";
+    const cudaError_t e = tcb::launch_gemv_q(a, make_env(ctx, true),
+                                             static_cast<cudaStream_t>(cuda_stream), &launches,
+                                             &name);
+    g_launches.fetch_add(static_cast<uint64_t>(launches));
+    t_last_kernel = name;
+    return record(opname, from_cuda(e, TC_ERR_DISPATCH));
+}
+
+extern "C" tc_status_t tcx_raw_gemv_quantized(tc_context* ctx, const void* X, const void* W_quant,
+                                              void* Y, tc_quant_t fmt, int M, int N, int K,
+                                              tc_dtype_t x_dtype, tc_dtype_t y_dtype,
+                                              void* cuda_stream) {
+    return raw_gemv(ctx, X, nullptr, false, W_quant, Y, fmt, M, N, K, 0.f, x_dtype, y_dtype,
+                    cuda_stream, "tcx_raw_gemv_quantized");
+}
+
+extern "C" tc_status_t tcx_raw_fused_rmsnorm_gemv_quantized(
+    tc_context* ctx, const void* X, const void* gamma, const void* W_quant, void* Y,
+    tc_quant_t fmt, int M, int N, int K, float eps, tc_dtype_t x_dtype, tc_dtype_t y_dtype,
+    void* cuda_stream) {
+    return raw_gemv(ctx, X, gamma, true, W_quant, Y, fmt, M, N, K, eps, x_dtype, y_dtype,
+                    cuda_stream, "tcx_raw_fused_rmsnorm_gemv_quantized");
+}
+
+extern "C" tc_status_t tcx_raw_fused_norm_gemv_f16(tc_context* ctx, const void* X,
+                                                   const void* gamma, const void* beta,
+                                                   const void* W, void* Y, int M, int N, int K,
+                                                   float eps, void* cuda_stream) {
+    if (!ctx) return TC_ERR_NOT_INITIALIZED;
+    if (!X || !gamma || !W || !Y || M <= 0 || N <= 0 || K <= 0) return TC_ERR_INVALID_ARG;
+    tcb::DenseNormGemvArgs a;
+    a.X = X; a.gamma = gamma; a.beta = beta; a.W = W; a.Y = Y;
+    a.M = M; a.N = N; a.K = K; a.eps = eps;
+    int launches = 0;
+    const char* name = "none";
+    const cudaError_t e = tcb::launch_dense_norm_gemv(a, make_env(ctx, true),
+                                                      static_cast<cudaStream_t>(cuda_stream),
+                                                      &launches, &name);
+    g_launches.fetch_add(static_cast<uint64_t>(launches));
+    t_last_kernel = name;
+    return record("tcx_raw_fused_norm_gemv_f16", from_cuda(e, TC_ERR_DISPATCH));
+}
+
+// ---------------------------------------------------------------------------------------
+// Diagnostics
+// ---------------------------------------------------------------------------------------
+extern "C" tc_status_t tcx_set_gemv_variant(const char* name) {
+    if (!name) return TC_ERR_INVALID_ARG;
+    int v = -1;
+    if (!std::strcmp(name, "auto")) v = tcb::VARIANT_AUTO;
+    else if (!std::strcmp(name, "simt")) v = tcb::VARIANT_SIMT;
+    else if (!std::strcmp(name, "mma")) v = tcb::VARIANT_MMA;
+    else if (!std::strcmp(name, "tc")) v = tcb::VARIANT_TC;
+    else if (!std::strcmp(name, "generic")) v = tcb::VARIANT_GENERIC;
+    if (v < 0) return TC_ERR_INVALID_ARG;
+    g_variant.store(v);
+    return TC_OK;
+}
+
+extern "C" uint32_t tcx_take_device_error(tc_context* ctx) {
+    if (!ctx || !ctx->err_host) return 0;
+    const uint32_t v = *reinterpret_cast<volatile uint32_t*>(ctx->err_host);
+    *reinterpret_cast<volatile uint32_t*>(ctx->err_host) = 0;
+    return v;
+}
+
+extern "C" uint64_t tcx_launch_count(void) { return g_launches.load(); }
+
+// Used by gguf.cpp: a device buffer filled from host memory through a pinned staging ring.
+extern "C" tc_status_t tcb_buffer_from_host_bytes(tc_context* ctx, const void* src, size_t bytes,
+                                                  tc_buffer** out) {
+    if (!ctx || !src || !out || bytes == 0) return TC_ERR_INVALID_ARG;
+    tc_buffer* b = nullptr;
+    tc_status_t st = tc_buffer_alloc(ctx, bytes, &b);
+    if (st != TC_OK) return st;
+    // Two pinned slots: the CPU fills one while the copy engine drains the other.
+    static std::mutex ring_mutex;
+    static void* slots[2] = {nullptr, nullptr};
+    static cudaEvent_t done[2] = {nullptr, nullptr};
+    static const size_t kSlot = 32u << 20;
+    std::lock_guard<std::mutex> lock(ring_mutex);
+    for (int i = 0; i < 2; ++i) {
+        if (!slots[i]) {
+            if (cudaHostAlloc(&slots[i], kSlot, cudaHostAllocDefault) != cudaSuccess ||
+                cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming) != cudaSuccess) {
+                (void)cudaGetLastError();
+                tc_buffer_free(ctx, b);
+                return TC_ERR_ALLOC;
+            }
+        }
+    }
+    cudaError_t e = cudaSuccess;
+    size_t off = 0;
+    int slot = 0;
+    while (off < bytes && e == cudaSuccess) {
+        const size_t n = (bytes - off) < kSlot ? (bytes - off) : kSlot;
+        e = cudaEventSynchronize(done[slot]);  // slot free again (no-op before first use)
+        if (e != cudaSuccess) break;
+        std::memcpy(slots[slot], static_cast<const uint8_t*>(src) + off, n);
+        e = cudaMemcpyAsync(static_cast<uint8_t*>(b->dptr) + off, slots[slot], n,
+                            cudaMemcpyHostToDevice, ctx->stream0);
+        if (e == cudaSuccess) e = cudaEventRecord(done[slot], ctx->stream0);
+        off += n;
+        slot ^= 1;
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream0);
+    if (e != cudaSuccess) {
+        tc_buffer_free(ctx, b);
+        return from_cuda(e, TC_ERR_INTERNAL);
+    }
+    *out = b;
+    return TC_OK;
+}

@@ -1,0 +1,70 @@
+"""Generates tests/golden/*.npz by running the reference's own portable-CPU backend
+(oracle/_ref/libtensorcore_ref.so, compiled from the reference sources by oracle/Makefile).
+
+Run where a reference checkout is present:  python tests/golden/make_golden.py
+The fixtures are small (a few hundred KB in total) and are committed; the GPU box has no
+reference checkout and reads only these files.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+import oracle as O  # noqa: E402
+
+OUT = os.path.dirname(os.path.abspath(__file__))
+
+
+def weights(rng, N, K):
+    """fp32 N(0, 0.02^2) rounded to fp16, with the edge blocks the quantiser must get right."""
+    W = (rng.standard_normal((N, K)) * 0.02).astype(np.float32).astype(np.float16)
+    W[0, :32] = 0                       # all-zero block: scale 0, codes 8 / 0
+    W[1, 32:64] = np.float16(-0.5)      # constant negative block: codes clamp at 0 / -127
+    W[2, :32] = np.float16(6.1e-5)      # smallest normal fp16: subnormal scale
+    W[3, 5] = np.float16(3.0)           # one large value: the rest of the block rounds to zero
+    W[4, :32] = np.linspace(-1, 1, 32).astype(np.float16)   # exact .5 ties after scaling
+    return W
+
+
+def main() -> None:
+    R = O.RefLib()
+    rng = np.random.default_rng(0x7C0DE)
+    cases = {}
+    for fmt, tag in ((O.Q4_0, "q4_0"), (O.Q8_0, "q8_0")):
+        for (N, K, M) in ((8, 32, 1), (130, 256, 1), (97, 512, 3), (64, 1024, 4), (33, 4096, 2)):
+            W = weights(rng, N, K)
+            X = rng.standard_normal((M, K)).astype(np.float32).astype(np.float16)
+            g = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32).astype(np.float16)
+            Wq = R.quantize_weights(W, fmt)
+            key = f"{tag}_N{N}_K{K}_M{M}"
+            cases[key + "_W"] = W.view(np.uint16)
+            cases[key + "_X"] = X.view(np.uint16)
+            cases[key + "_gamma"] = g.view(np.uint16)
+            cases[key + "_Wq"] = Wq
+            cases[key + "_Y"] = R.gemv_quantized(X, Wq, fmt, N).view(np.uint16)
+            cases[key + "_Yfused"] = R.fused_rmsnorm_gemv_quantized(X, g, Wq, fmt, N, 1e-5).view(np.uint16)
+    np.savez_compressed(os.path.join(OUT, "quantized_path.npz"), **cases)
+
+    dense = {}
+    for (M, N, K) in ((1, 128, 256), (2, 96, 512), (4, 40, 1024), (1, 33, 64)):
+        X = rng.standard_normal((M, K)).astype(np.float32).astype(np.float16)
+        g = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32).astype(np.float16)
+        b = (0.1 * rng.standard_normal(K)).astype(np.float32).astype(np.float16)
+        W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32).astype(np.float16)
+        key = f"M{M}_N{N}_K{K}"
+        dense[key + "_X"] = X.view(np.uint16)
+        dense[key + "_gamma"] = g.view(np.uint16)
+        dense[key + "_beta"] = b.view(np.uint16)
+        dense[key + "_W"] = W.view(np.uint16)
+        dense[key + "_Yrms"] = R.fused_rmsnorm_gemv(X, g, W, 1e-5).view(np.uint16)
+        dense[key + "_Yln"] = R.fused_layernorm_gemv(X, g, b, W, 1e-5).view(np.uint16)
+    np.savez_compressed(os.path.join(OUT, "dense_fused.npz"), **dense)
+    print("wrote", sorted(os.listdir(OUT)))
+
+
+if __name__ == "__main__":
+    main()

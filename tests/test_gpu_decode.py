@@ -1,0 +1,64 @@
+"""GPU: the recorded decode step (compiled harness over the C ABI) on a small Llama-shaped
+model loaded from a synthetic GGUF file, checked projection by projection against the oracle."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_token(oracle, shape, fmt, W, norms, x, fused):
+    """Mirror of csrc/harness/decode_harness.cpp:record_token on the CPU."""
+    def proj(xin, gamma, name, which):
+        N, _ = shape.proj_shape(which)
+        if fused and gamma is not None:
+            return oracle.fused_rmsnorm_gemv_quantized(xin, gamma, W[name], fmt, N, 1e-5)
+        return oracle.gemv_quantized(xin, W[name], fmt, N)
+    cur = x
+    for l in range(shape.n_layers):
+        an, fn = norms[f"blk.{l}.attn_norm.weight"], norms[f"blk.{l}.ffn_norm.weight"]
+        q = proj(cur, an, f"blk.{l}.attn_q.weight", "attn_q")
+        o = proj(q, None, f"blk.{l}.attn_output.weight", "attn_output")
+        gate = proj(o, fn, f"blk.{l}.ffn_gate.weight", "ffn_gate")
+        cur = proj(gate, None, f"blk.{l}.ffn_down.weight", "ffn_down")
+    return proj(cur, norms["output_norm.weight"], "output.weight", "output")
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+@pytest.mark.parametrize("M", [1, 3])
+def test_decode_session_matches_oracle_chain(tc, ctx, oracle, tmp_path, fmt, M):
+    from tensorcore_b200 import decode as D
+    shape = D.tiny_shape()
+    path = str(tmp_path / "tiny.gguf")
+    nbytes = D.build_synthetic_gguf(path, shape, ctx, fmt)
+    assert nbytes == shape.weight_bytes(fmt)
+    model = D.model_from_gguf(ctx, path, shape, fmt)
+    assert model.owner.tensor_count() == shape.n_layers * 9 + 2
+    # host copies of what was loaded, for the oracle
+    W, norms = {}, {}
+    for i in range(model.owner.tensor_count()):
+        t = model.owner.tensor_at(i)
+        buf = tc.Buffer(ctx, handle=__import__("ctypes").c_void_p(t["buffer"]), owned=False)
+        if t["type"] in (tc.TC_GGUF_TYPE_Q4_0, tc.TC_GGUF_TYPE_Q8_0):
+            W[t["name"]] = buf.to_numpy((t["n_bytes"],), np.uint8)
+        else:
+            norms[t["name"]] = buf.to_numpy((t["dims"][0],), np.float16)
+    # the device quantiser produced exactly what the oracle would from the same fp16 weights
+    w16 = D.device_weights_fp16(*shape.proj_shape("attn_q"), D.tensor_seed(0, 0)).cpu().numpy()
+    assert np.array_equal(W["blk.0.attn_q.weight"], oracle.quantize_weights(w16, fmt))
+
+    rng = np.random.default_rng(D.X_SEED)
+    x = rng.standard_normal((M, shape.d_model)).astype(np.float16)
+    sess = D.DecodeSession(ctx, model, M)
+    for fused in (False, True):
+        want = oracle_token(oracle, shape, fmt, W, norms, x, fused)
+        for rep in range(3):          # direct launch, graph build, graph replay
+            sess.x.upload(x)
+            sess.run(1, fused_norms=fused)
+            got = sess.logits.to_numpy((M, shape.vocab), np.float16)
+            # four to nine dependent GEMVs: rounding flips of one feed the next
+            assert oracle.scaled_rms(got, want) <= 5e-4, (fused, rep)
+    gpu_ms, wall_ms = sess.run(4, fused_norms=True)
+    assert gpu_ms > 0 and wall_ms > 0
+    assert tc.take_device_error(ctx) == 0
+    sess.close()
+    model.owner.close()

@@ -1,0 +1,299 @@
+"""GPU: parity of the CUDA path, called through the C ABI, against the oracle.
+
+Bars: quantiser bytes identical; fp16-ABI GEMV / fused outputs within scaled-RMS 1e-4 of the
+oracle's fp16 outputs (both sides rounded to fp16; only rounding flips may differ) and within
+2.5e-4 of an fp64 dequantise-and-dot (the fp16 output rounding floor is 2.1e-4); fp32-output
+entry points within 1e-4 of fp64 (observed ~1e-6); fp16 activations within 2e-3.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import GOLDEN
+
+pytestmark = pytest.mark.gpu
+
+Q = {"q4_0": 0, "q8_0": 1}
+TOL_VS_ORACLE_F16 = 1e-4
+TOL_VS_F64_F16OUT = 2.5e-4
+TOL_F32 = 1e-4
+TOL_F16_ACT = 2e-3
+
+
+def make_weights(rng, N, K):
+    return (rng.standard_normal((N, K)) * 0.02).astype(np.float32).astype(np.float16)
+
+
+def dev(ctx, arr):
+    return ctx.buffer_from_array(np.ascontiguousarray(arr))
+
+
+def gpu_quantize(tc, ctx, W16, fmt):
+    N, K = W16.shape
+    with dev(ctx, W16.view(np.uint16)) as bw, ctx.buffer(tc.quantized_size(fmt, N, K)) as bq:
+        ctx.quantize_weights(bw, bq, fmt, N, K)
+        return bq.to_numpy((tc.quantized_size(fmt, N, K),), np.uint8)
+
+
+def gpu_gemv(tc, ctx, X, Wq, fmt, N, y_f32=False, gamma=None, eps=1e-5, stream=None):
+    """X: float16 or float32 [M,K].  Uses the reference entry points when both types are
+    fp16 and no stream is given, else the additive *_ex forms."""
+    M, K = X.shape
+    x_f32 = X.dtype == np.float32
+    ydt = np.float32 if y_f32 else np.float16
+    bx, bw = dev(ctx, X), dev(ctx, Wq)
+    by = ctx.buffer(M * N * np.dtype(ydt).itemsize)
+    bg = dev(ctx, gamma) if gamma is not None else None
+    try:
+        plain = not x_f32 and not y_f32 and stream is None
+        if gamma is None:
+            if plain:
+                ctx.gemv_quantized(bx, bw, by, fmt, M, N, K)
+            else:
+                tc.gemv_quantized_ex(ctx, bx, bw, by, fmt, M, N, K, "f32" if x_f32 else "f16",
+                                     "f32" if y_f32 else "f16", stream)
+        else:
+            if plain:
+                ctx.fused_rmsnorm_gemv_quantized(bx, bg, bw, by, fmt, M, N, K, eps)
+            else:
+                tc.fused_rmsnorm_gemv_quantized_ex(ctx, bx, bg, bw, by, fmt, M, N, K, eps,
+                                                   "f32" if x_f32 else "f16",
+                                                   "f32" if y_f32 else "f16", stream)
+        if stream is not None:
+            stream.sync()
+        return by.to_numpy((M, N), ydt)
+    finally:
+        for b in (bx, bw, by, bg):
+            if b is not None:
+                b.close()
+
+
+# ---------------------------------------------------------------------------------------
+# Quantiser: bit-exact
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("tag", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("shape", [(1, 32), (8, 32), (130, 256), (97, 512), (33, 4096),
+                                   (1024, 4096)])
+def test_quantiser_bytes_match_oracle(tc, ctx, oracle, tag, shape):
+    rng = np.random.default_rng(Q[tag] * 100003 + shape[0] * 31 + shape[1])
+    W = make_weights(rng, *shape)
+    W[0, :32] = 0
+    if shape[0] > 1:
+        W[1, :32] = np.float16(-0.25)
+    got = gpu_quantize(tc, ctx, W, Q[tag])
+    assert np.array_equal(got, oracle.quantize_weights(W, Q[tag]))
+    assert tc.last_backend() == tc.TC_BACKEND_CUDA
+    assert "quantize" in tc.cuda_last_kernel_name()
+
+
+@pytest.mark.parametrize("tag", ["q4_0", "q8_0"])
+def test_quantiser_matches_reference_golden_bytes(tc, ctx, tag):
+    g = np.load(os.path.join(GOLDEN, "quantized_path.npz"))
+    for key in sorted({k.rsplit("_", 1)[0] for k in g.files if k.startswith(tag)}):
+        W = g[key + "_W"].view(np.float16)
+        assert np.array_equal(gpu_quantize(tc, ctx, W, Q[tag]), g[key + "_Wq"]), key
+
+
+def test_quantiser_extreme_values(tc, ctx, oracle):
+    """Subnormal inputs, the largest finite fp16, mixed signs, exact ties."""
+    rng = np.random.default_rng(77)
+    W = np.zeros((8, 64), dtype=np.float16)
+    W[0, :32] = np.float16(65504)
+    W[1, :32] = np.array([5.96e-8 * (i + 1) for i in range(32)], dtype=np.float16)
+    W[2, :32] = np.linspace(-8, 8, 32).astype(np.float16)           # ties at .5 after scaling
+    W[3, :32] = (np.arange(32) - 16).astype(np.float16) * np.float16(0.5)
+    W[4] = (rng.standard_normal(64) * 1e-4).astype(np.float16)
+    W[5] = (rng.standard_normal(64) * 100).astype(np.float16)
+    W[6, ::2] = np.float16(-1.0)
+    W[7, 33] = np.float16(-6.1e-5)
+    for fmt in (0, 1):
+        assert np.array_equal(gpu_quantize(tc, ctx, W, fmt), oracle.quantize_weights(W, fmt))
+
+
+# ---------------------------------------------------------------------------------------
+# GEMV, fp16 ABI
+# ---------------------------------------------------------------------------------------
+SHAPES = [
+    # (N, K, M) - streaming kernel (K % 256 == 0) and the generic path (other K)
+    (128, 256, 1), (130, 256, 1), (129, 256, 2), (1, 256, 1), (97, 512, 3), (64, 1024, 4),
+    (33, 4096, 2), (500, 2816, 1), (300, 768, 5), (64, 512, 9),
+    (3, 32, 1), (8, 64, 2), (77, 96, 1), (40, 1376, 1),
+]
+
+
+@pytest.mark.parametrize("tag", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_gemv_fp16_abi(tc, ctx, oracle, tag, shape):
+    N, K, M = shape
+    fmt = Q[tag]
+    rng = np.random.default_rng(N * 7919 + K + M)
+    Wq = oracle.quantize_weights(make_weights(rng, N, K), fmt)
+    X = rng.standard_normal((M, K)).astype(np.float32).astype(np.float16)
+    got = gpu_gemv(tc, ctx, X, Wq, fmt, N)
+    want16 = oracle.gemv_quantized(X, Wq, fmt, N)
+    want64 = oracle.dequant_dot_f64(X.astype(np.float64), Wq, fmt, N)
+    assert oracle.scaled_rms(got, want16) <= TOL_VS_ORACLE_F16
+    assert oracle.scaled_rms(got, want64) <= TOL_VS_F64_F16OUT
+    assert tc.last_backend() == tc.TC_BACKEND_CUDA
+    name = tc.cuda_last_kernel_name()
+    assert ("stream" in name) == (K % 256 == 0), name
+
+
+@pytest.mark.parametrize("tag", ["q4_0", "q8_0"])
+def test_gemv_matches_reference_golden_outputs(tc, ctx, oracle, tag):
+    g = np.load(os.path.join(GOLDEN, "quantized_path.npz"))
+    for key in sorted({k.rsplit("_", 1)[0] for k in g.files if k.startswith(tag)}):
+        N = int(key.split("_N")[1].split("_")[0])
+        X = g[key + "_X"].view(np.float16)
+        gam = g[key + "_gamma"].view(np.float16)
+        Wq = g[key + "_Wq"]
+        got = gpu_gemv(tc, ctx, X, Wq, Q[tag], N)
+        assert oracle.scaled_rms(got, g[key + "_Y"].view(np.float16)) <= TOL_VS_ORACLE_F16, key
+        gotf = gpu_gemv(tc, ctx, X, Wq, Q[tag], N, gamma=gam)
+        assert oracle.scaled_rms(gotf, g[key + "_Yfused"].view(np.float16)) <= TOL_VS_ORACLE_F16, key
+
+
+def test_gguf_known_answer_is_bit_exact(tc, ctx):
+    # tests/test_gguf.c:119-122,267-279 -> 0x5100
+    blk = np.array([0x00, 0x38] + [0xAB] * 16, dtype=np.uint8)
+    x = np.full((1, 32), 0x3C00, dtype=np.uint16).view(np.float16)
+    y = gpu_gemv(tc, ctx, x, blk, 0, 1)
+    assert y.view(np.uint16)[0, 0] == 0x5100
+
+
+# ---------------------------------------------------------------------------------------
+# fp32 activations / outputs (additive entry points)
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("tag", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("shape", [(130, 256, 1), (97, 512, 3), (256, 4096, 1), (8, 64, 2)])
+def test_gemv_fp32(tc, ctx, oracle, tag, shape):
+    N, K, M = shape
+    fmt = Q[tag]
+    rng = np.random.default_rng(N + K * 31 + M)
+    Wq = oracle.quantize_weights(make_weights(rng, N, K), fmt)
+    X = rng.standard_normal((M, K)).astype(np.float32)
+    want64 = oracle.dequant_dot_f64(X.astype(np.float64), Wq, fmt, N)
+    got = gpu_gemv(tc, ctx, X, Wq, fmt, N, y_f32=True)
+    assert oracle.scaled_rms(got, want64) <= TOL_F32
+    assert oracle.scaled_rms(got, oracle.gemv_quantized_f32(X, Wq, fmt, N)) <= 1e-5
+    # fp16 activations, fp32 output
+    X16 = X.astype(np.float16)
+    got16 = gpu_gemv(tc, ctx, X16, Wq, fmt, N, y_f32=True)
+    assert oracle.scaled_rms(got16, want64) <= TOL_F16_ACT
+    assert oracle.scaled_rms(
+        got16, oracle.dequant_dot_f64(X16.astype(np.float64), Wq, fmt, N)) <= 1e-5
+
+
+# ---------------------------------------------------------------------------------------
+# Fused RMSNorm + quantized GEMV
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("tag", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("shape", [(97, 256, 1), (96, 256, 2), (130, 1024, 4), (64, 4096, 1),
+                                   (12, 64, 1), (300, 768, 5)])
+def test_fused_rmsnorm_gemv_quantized(tc, ctx, oracle, tag, shape):
+    N, K, M = shape
+    fmt = Q[tag]
+    rng = np.random.default_rng(N * 3 + K * 5 + M)
+    Wq = oracle.quantize_weights(make_weights(rng, N, K), fmt)
+    X = rng.standard_normal((M, K)).astype(np.float32).astype(np.float16)
+    gam = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32).astype(np.float16)
+    got = gpu_gemv(tc, ctx, X, Wq, fmt, N, gamma=gam)
+    want = oracle.fused_rmsnorm_gemv_quantized(X, gam, Wq, fmt, N, 1e-5)
+    assert oracle.scaled_rms(got, want) <= TOL_VS_ORACLE_F16
+    # fp32 form
+    Xf = rng.standard_normal((M, K)).astype(np.float32)
+    gf = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    gotf = gpu_gemv(tc, ctx, Xf, Wq, fmt, N, y_f32=True, gamma=gf)
+    wantf = oracle.fused_rmsnorm_gemv_quantized_f32(Xf, gf, Wq, fmt, N, 1e-5)
+    assert oracle.scaled_rms(gotf, wantf) <= 1e-5
+
+
+# ---------------------------------------------------------------------------------------
+# Fused norm + dense fp16 GEMV
+# ---------------------------------------------------------------------------------------
+def gpu_dense(tc, ctx, X, gam, bet, W):
+    M, K = X.shape
+    N = W.shape[1]
+    bufs = [dev(ctx, a.view(np.uint16)) for a in (X, gam, W)]
+    bb = dev(ctx, bet.view(np.uint16)) if bet is not None else None
+    by = ctx.buffer(M * N * 2)
+    try:
+        if bet is None:
+            ctx.fused_rmsnorm_gemv(bufs[0], bufs[1], bufs[2], by, M, N, K, 1e-5)
+        else:
+            ctx.fused_layernorm_gemv(bufs[0], bufs[1], bb, bufs[2], by, M, N, K, 1e-5)
+        return by.to_numpy((M, N), np.float16)
+    finally:
+        for b in bufs + [by] + ([bb] if bb else []):
+            b.close()
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 256), (2, 96, 512), (4, 40, 1024), (1, 33, 64),
+                                   (5, 1024, 4096), (1, 11008, 4096), (3, 77, 100)])
+def test_dense_fused_norm_gemv(tc, ctx, oracle, shape):
+    M, N, K = shape
+    rng = np.random.default_rng(M + N * 3 + K * 7)
+    X = rng.standard_normal((M, K)).astype(np.float16)
+    gam = (1 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    bet = (0.1 * rng.standard_normal(K)).astype(np.float16)
+    W = (rng.standard_normal((K, N)) * 0.02).astype(np.float16)
+    if N * K <= 1 << 22:
+        want_r = oracle.fused_rmsnorm_gemv(X, gam, W, 1e-5)
+        want_l = oracle.fused_layernorm_gemv(X, gam, bet, W, 1e-5)
+        cols = slice(None)
+    else:  # big case: check a slice of the columns against the oracle
+        cols = slice(0, N, 37)
+        Ws = np.ascontiguousarray(W[:, cols])
+        want_r = oracle.fused_rmsnorm_gemv(X, gam, Ws, 1e-5)
+        want_l = oracle.fused_layernorm_gemv(X, gam, bet, Ws, 1e-5)
+    got_r = gpu_dense(tc, ctx, X, gam, None, W)[:, cols]
+    got_l = gpu_dense(tc, ctx, X, gam, bet, W)[:, cols]
+    assert oracle.scaled_rms(got_r, want_r) <= TOL_VS_ORACLE_F16
+    assert oracle.scaled_rms(got_l, want_l) <= TOL_VS_ORACLE_F16
+
+
+def test_dense_fused_matches_reference_golden(tc, ctx, oracle):
+    g = np.load(os.path.join(GOLDEN, "dense_fused.npz"))
+    for key in sorted({k.rsplit("_", 1)[0] for k in g.files}):
+        X, gam, bet, W = (g[key + s].view(np.float16) for s in ("_X", "_gamma", "_beta", "_W"))
+        assert oracle.scaled_rms(gpu_dense(tc, ctx, X, gam, None, W),
+                                 g[key + "_Yrms"].view(np.float16)) <= TOL_VS_ORACLE_F16, key
+        assert oracle.scaled_rms(gpu_dense(tc, ctx, X, gam, bet, W),
+                                 g[key + "_Yln"].view(np.float16)) <= TOL_VS_ORACLE_F16, key
+
+
+# ---------------------------------------------------------------------------------------
+# Full BASELINE shapes
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("case", [("q4_0", 4096, 4096, 1), ("q8_0", 11008, 4096, 1),
+                                  ("q4_0", 32000, 4096, 1), ("q4_0", 4096, 11008, 1),
+                                  ("q4_0", 14336, 4096, 4), ("q4_0", 14336, 4096, 8),
+                                  ("q4_0", 1024, 8192, 1), ("q4_0", 8192, 28672, 1)])
+def test_full_size_shapes(tc, ctx, oracle, case):
+    tag, N, K, M = case
+    fmt = Q[tag]
+    rng = np.random.default_rng(N ^ K ^ M)
+    W = make_weights(rng, N, K)
+    Wq = gpu_quantize(tc, ctx, W, fmt)
+    # quantiser: sampled rows against the oracle (the whole matrix when it is small)
+    rows = np.unique(np.concatenate([[0, N - 1], rng.integers(0, N, 64)]))
+    bb = 18 if fmt == 0 else 34
+    Wq_rows = Wq.reshape(N, K // 32 * bb)[rows]
+    assert np.array_equal(Wq_rows.ravel(), oracle.quantize_weights(W[rows], fmt))
+    X = rng.standard_normal((M, K)).astype(np.float32).astype(np.float16)
+    got = gpu_gemv(tc, ctx, X, Wq, fmt, N)
+    want = oracle.gemv_quantized(X[:1], Wq, fmt, N)          # oracle on the first row: < 1 s
+    assert oracle.scaled_rms(got[:1], want) <= TOL_VS_ORACLE_F16
+    if M > 1:  # remaining rows: sampled output columns
+        cols = rng.integers(0, N, 256)
+        sub = np.ascontiguousarray(Wq.reshape(N, -1)[cols]).ravel()
+        want_s = oracle.gemv_quantized(X, sub, fmt, len(cols))
+        assert oracle.scaled_rms(got[:, cols], want_s) <= TOL_VS_ORACLE_F16
+    # size-independent property: linearity in the activations (fp32 entry point)
+    Xa = rng.standard_normal((1, K)).astype(np.float32)
+    Xb = rng.standard_normal((1, K)).astype(np.float32)
+    ya = gpu_gemv(tc, ctx, Xa, Wq, fmt, N, y_f32=True)
+    yb = gpu_gemv(tc, ctx, Xb, Wq, fmt, N, y_f32=True)
+    yab = gpu_gemv(tc, ctx, Xa + 2 * Xb, Wq, fmt, N, y_f32=True)
+    assert oracle.scaled_rms(yab, ya + 2 * yb) <= 1e-5

@@ -29,7 +29,12 @@
 
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 namespace tcb {
+cudaError_t init_mma_kernels(int smem_optin);
+cudaError_t launch_gemv_q4_mma(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t stream,
+                               const char** name);
 namespace {
 
 constexpr int kWarps = 8;
@@ -638,7 +643,13 @@ StreamPlan plan_stream(const GemvQArgs& a, int mb, bool stage_f32, const LaunchE
     const int nb = a.K / 32, gpr = nb / 8;
     const int group_bytes = a.fmt == FMT_Q4_0 ? 144 : 272;
     const int chunk_bytes = 32 * group_bytes;
-    const int grid = a.N < env.sm_count ? a.N : env.sm_count;
+    static const int ctas_per_sm = [] {
+        const char* v = std::getenv("TC_GEMV_CTAS_PER_SM");
+        const int n = v ? std::atoi(v) : 1;
+        return n >= 1 && n <= 4 ? n : 1;
+    }();
+    const int want = env.sm_count * ctas_per_sm;
+    const int grid = a.N < want ? a.N : want;
     const int max_rows = (a.N + grid - 1) / grid + 1;
 
     int off = 8 * kWarps * 4 + 8 * kWarps;  // barriers (up to 4 stages) + reduction scratch
@@ -696,7 +707,8 @@ cudaError_t set_smem(K kernel, int bytes) {
 }  // namespace
 
 cudaError_t init_gemv_kernels(int smem_optin) {
-    cudaError_t e = cudaSuccess;
+    cudaError_t e = init_mma_kernels(smem_optin);
+    if (e != cudaSuccess) return e;
 #define TCB_SET(FMT, XF, MB)                                                      \
     e = set_smem(gemv_q_stream_kernel<FMT, XF, MB>, smem_optin);                  \
     if (e != cudaSuccess) return e;
@@ -718,7 +730,25 @@ cudaError_t launch_gemv_q(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t
     // The RMSNorm prologue keeps the normalised row in fp32, whatever the activation type.
     const bool stage_f32 = a.x_f32 || fuse;
 
-    for (int m0 = 0; m0 < a.M && err == cudaSuccess; m0 += kMaxMB) {
+    // Q4_0 decode shapes go to the tensor-core dot kernel, two activation rows per launch.
+    const bool try_mma = a.fmt == FMT_Q4_0 &&
+                         (env.variant == VARIANT_AUTO || env.variant == VARIANT_MMA);
+    int step = kMaxMB;
+    for (int m0 = 0; m0 < a.M && err == cudaSuccess; m0 += step) {
+        if (try_mma) {
+            GemvQArgs s2 = a;
+            s2.M = (a.M - m0) < 2 ? (a.M - m0) : 2;
+            s2.X = static_cast<const uint8_t*>(a.X) + static_cast<size_t>(m0) * a.K * xsz;
+            s2.Y = static_cast<uint8_t*>(a.Y) + static_cast<size_t>(m0) * a.N * ysz;
+            const cudaError_t me = launch_gemv_q4_mma(s2, env, stream, &used);
+            if (me != cudaErrorNotSupported) {
+                err = me;
+                step = 2;
+                ++count;
+                continue;
+            }
+        }
+        step = kMaxMB;
         const int mb = (a.M - m0) < kMaxMB ? (a.M - m0) : kMaxMB;
         GemvQArgs s = a;
         s.X = static_cast<const uint8_t*>(a.X) + static_cast<size_t>(m0) * a.K * xsz;

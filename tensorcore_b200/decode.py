@@ -66,7 +66,7 @@ LLAMA_7B = LlamaShape("llama-7b", 32, 4096, 11008, 32, 32, 32000)
 LLAMA_70B = LlamaShape("llama-70b", 80, 8192, 28672, 64, 8, 128256)
 
 
-def tiny_shape(n_layers=2, d_model=256, d_ff=512, n_heads=4, n_kv_heads=2, vocab=320):
+def tiny_shape(n_layers=2, d_model=1024, d_ff=2048, n_heads=8, n_kv_heads=4, vocab=1000):
     return LlamaShape("tiny", n_layers, d_model, d_ff, n_heads, n_kv_heads, vocab)
 
 

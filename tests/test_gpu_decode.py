@@ -55,8 +55,12 @@ def test_decode_session_matches_oracle_chain(tc, ctx, oracle, tmp_path, fmt, M):
             sess.x.upload(x)
             sess.run(1, fused_norms=fused)
             got = sess.logits.to_numpy((M, shape.vocab), np.float16)
-            # four to nine dependent GEMVs: rounding flips of one feed the next
-            assert oracle.scaled_rms(got, want) <= 5e-4, (fused, rep)
+            # Nine dependent GEMVs with fp16 hand-offs: an fp16 rounding flip in one output
+            # (a different but equally valid fp32 summation order) perturbs the next one's
+            # input.  The same chain on the CPU (fp64 accumulation vs the reference order)
+            # grows from 1e-5 to 6e-4 over nine stages; the bar is the fp16-activation
+            # tolerance.
+            assert oracle.scaled_rms(got, want) <= 2e-3, (fused, rep)
     gpu_ms, wall_ms = sess.run(4, fused_norms=True)
     assert gpu_ms > 0 and wall_ms > 0
     assert tc.take_device_error(ctx) == 0

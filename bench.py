@@ -1,0 +1,377 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-decode hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N=1): synthetic Llama-7B-shape decode weight stream, batch 1, all Q4_0 - 32 layers of
+q/k/v/o 4096x4096, gate/up 11008x4096, down 4096x11008 plus lm_head 32000x4096, seeded
+N(0, 0.02^2) weights packed into a GGUF v3 file and loaded with tc_gguf_load_supported_tensors.
+A step is one decode token: 225 quantized GEMVs (RMSNorm fused into q/k/v, gate/up and lm_head)
+recorded on a tc_stream and synchronised once.  Metric: tokens per second (whole job).
+
+Prints one JSON line.  `value` is measured with the model and activations resident in HBM;
+`e2e` runs the same steps with the step input copied from pinned host memory and the logits
+copied back every step.  `--impl reference` times the reference's own CPU implementation of
+the same GEMV sequence on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "synthetic 7B Q4_0 decode tok/s"
+UNIT = "tok/s"
+
+
+def measured_peaks() -> tuple[float, str]:
+    """HBM GB/s denominator: the driver-measured copy bandwidth, else the stated fallback."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int = 0):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(np.max(mx)) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def algorithmic_bytes_per_token(shape, fmt: int = 0) -> tuple[int, int]:
+    """(total, weights only).  Per GEMV: N*(K/32)*18 weight bytes + K*2 activation bytes read +
+    N*2 result bytes written (+ K*2 gamma bytes where the RMSNorm prologue is fused)."""
+    from tensorcore_b200.decode import PROJ
+    total = 0
+    fused = {"attn_q", "attn_k", "attn_v", "ffn_gate", "ffn_up", "output"}
+    items = [(p, shape.n_layers) for p in PROJ] + [("output", 1)]
+    for p, count in items:
+        n, k = shape.proj_shape(p)
+        per = n * (k // 32) * (18 if fmt == 0 else 34) + k * 2 + n * 2
+        if p in fused:
+            per += k * 2
+        total += per * count
+    return total, shape.weight_bytes(fmt)
+
+
+# ---------------------------------------------------------------------------------------
+# Reference arm / CPU baseline: the reference's CPU code on the host cores
+# ---------------------------------------------------------------------------------------
+class CpuDecode:
+    """The same GEMV sequence on the host, through the reference's portable-CPU library
+    (oracle/_ref, kind "reference") or, when that was not built, the oracle port (kind "port").
+    Every GEMV is split by output rows over `threads` host threads; the reference code itself
+    is single-threaded scalar C++ (lib/ops/quantized_cpu.cpp has no threading)."""
+
+    def __init__(self, shape, layers: int, threads: int):
+        import oracle as O
+        self.O, self.shape, self.layers, self.threads = O, shape, layers, threads
+        self.kind = "reference" if O.ref_available() else "port"
+        rng = np.random.default_rng(0x7C0000)
+        from tensorcore_b200.decode import PROJ
+        self.w = {}
+        # one set of weights per projection kind, reused for every layer of the sample: the CPU
+        # loops are compute-bound (0.3 GB/s per core), so cache residency does not help them.
+        for p in list(PROJ) + ["output"]:
+            n, k = shape.proj_shape(p)
+            self.w[p] = rng.integers(0, 256, n * (k // 32) * 18, dtype=np.uint8)
+            blocks = self.w[p].reshape(-1, 18)
+            blocks[:, 0:2] = np.frombuffer(np.float16(0.005).tobytes(), dtype=np.uint8)
+        self.x = rng.standard_normal((1, shape.d_model)).astype(np.float16)
+        self.xff = rng.standard_normal((1, shape.d_ff)).astype(np.float16)
+        self.ref = O.RefLib() if self.kind == "reference" else None
+        from concurrent.futures import ThreadPoolExecutor
+        self.pool = ThreadPoolExecutor(max_workers=threads)
+        self._bufs = {}
+        if self.ref is not None:
+            self._prepare_ref()
+
+    def _prepare_ref(self):
+        """Row-sliced tc_buffers over the numpy arrays (tc_buffer_from_ptr, zero copy)."""
+        import ctypes
+        L, ctx = self.ref.L, self.ref.ctx
+        L.tc_buffer_from_ptr.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t,
+                                         ctypes.POINTER(ctypes.c_void_p)]
+
+        def wrap(ptr, nbytes):
+            h = ctypes.c_void_p()
+            assert L.tc_buffer_from_ptr(ctx, ctypes.c_void_p(int(ptr)), int(nbytes), ctypes.byref(h)) == 0
+            return h
+        self.y = {}
+        for p, w in self.w.items():
+            n, k = self.shape.proj_shape(p)
+            row = (k // 32) * 18
+            self.y[p] = np.zeros((1, n), dtype=np.float16)
+            xin = self.xff if k == self.shape.d_ff else self.x
+            xb = wrap(xin.ctypes.data, xin.nbytes)
+            cuts = np.linspace(0, n, self.threads + 1).astype(int)
+            parts = []
+            for a, b in zip(cuts[:-1], cuts[1:]):
+                if b > a:
+                    parts.append((xb, wrap(w.ctypes.data + a * row, (b - a) * row),
+                                  wrap(self.y[p].ctypes.data + a * 2, (b - a) * 2), b - a, k))
+            self._bufs[p] = parts
+
+    def gemv(self, p):
+        n, k = self.shape.proj_shape(p)
+        if self.ref is not None:
+            L, ctx = self.ref.L, self.ref.ctx
+
+            def run(part):
+                xb, wb, yb, rows, kk = part
+                st = L.tc_gemv_quantized(ctx, xb, wb, yb, 0, 1, int(rows), int(kk))
+                assert st == 0, st
+            list(self.pool.map(run, self._bufs[p]))
+        else:
+            O = self.O
+            xin = self.xff if k == self.shape.d_ff else self.x
+            y = np.zeros((1, n), dtype=np.uint16)
+            cuts = np.linspace(0, n, self.threads + 1).astype(int)
+            list(self.pool.map(lambda ab: O.gemv_quantized_rows(xin, self.w[p], y, 0, n, int(ab[0]), int(ab[1])),
+                               [(a, b) for a, b in zip(cuts[:-1], cuts[1:]) if b > a]))
+
+    def step(self, with_lm_head: bool):
+        from tensorcore_b200.decode import PROJ
+        for _ in range(self.layers):
+            for p in PROJ:
+                self.gemv(p)
+        if with_lm_head:
+            self.gemv("output")
+
+    def seconds_per_token(self, steps: int, warmup: int) -> tuple[float, float]:
+        """Times `steps` samples (self.layers layers + lm_head each) and scales to one full token
+        by weight bytes.  Returns (seconds per token, seconds per sample)."""
+        from tensorcore_b200.decode import PROJ
+        for _ in range(warmup):
+            self.step(True)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            self.step(True)
+        dt = (time.perf_counter() - t0) / steps
+        layer_bytes = sum(self.w[p].nbytes for p in PROJ)
+        sample_bytes = self.layers * layer_bytes + self.w["output"].nbytes
+        full_bytes = self.shape.n_layers * layer_bytes + self.w["output"].nbytes
+        return dt * full_bytes / sample_bytes, dt
+
+
+def run_reference_arm(args) -> dict:
+    from tensorcore_b200.decode import LLAMA_7B
+    shape = LLAMA_7B
+    cores = os.cpu_count() or 1
+    # size the sample so that one step is a few seconds of host work at most
+    probe = CpuDecode(shape, layers=1, threads=cores)
+    t0 = time.perf_counter()
+    probe.step(False)
+    t_layer = time.perf_counter() - t0
+    per_step_budget = 120.0 / max(1, args.steps + args.warmup)   # whole run within ~2 minutes
+    layers = int(max(1, min(shape.n_layers, per_step_budget / max(t_layer, 1e-3))))
+    probe.layers = layers
+    spt, per_sample = probe.seconds_per_token(args.steps, args.warmup)
+    value = 1.0 / spt
+    total_b, weight_b = algorithmic_bytes_per_token(shape)
+    sample = (f"{layers} of {shape.n_layers} layers + lm_head per step, scaled to a full token by "
+              f"weight bytes; {probe.kind} CPU code, every GEMV split by rows over {cores} threads")
+    return {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": spt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "llama-7b-shape Q4_0 decode weight stream, batch 1, 225 GEMVs/token",
+                   "weight_bytes_per_token": weight_b},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": probe.kind,
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "weight_gbs": weight_b / spt / 1e9,
+    }
+
+
+def cpu_baseline_leg(shape) -> dict:
+    """The reference CPU code as shipped (one thread) on a bounded sample: 1 layer + lm_head,
+    scaled to a token."""
+    cpu = CpuDecode(shape, layers=1, threads=1)
+    spt, per_sample = cpu.seconds_per_token(steps=1, warmup=0)
+    return {"value": 1.0 / spt, "unit": UNIT, "cores": 1, "kind": cpu.kind,
+            "sample": f"1 of {shape.n_layers} layers + lm_head on one thread ({per_sample:.1f} s), "
+                      "scaled to a full token by weight bytes"}
+
+
+def run_single_gpu(args) -> dict:
+    import torch
+
+    import tensorcore_b200 as tc
+    from tensorcore_b200 import decode as D
+
+    shape = D.LLAMA_7B
+    if not os.path.exists(tc.LIB_PATH):
+        raise SystemExit("libtensorcore.so is not built: run `python -m tensorcore_b200.build`")
+    torch.cuda.set_device(0)
+    ctx = tc.Context()
+    tmpdir = tempfile.mkdtemp(prefix="tcb_bench_", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
+    path = os.path.join(tmpdir, "synthetic-llama-7b-q4_0.gguf")
+    t0 = time.perf_counter()
+    D.build_synthetic_gguf(path, shape, ctx, fmt=0)
+    t_build = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    model = D.model_from_gguf(ctx, path, shape, fmt=0)
+    t_load = time.perf_counter() - t0
+    os.remove(path)
+    os.rmdir(tmpdir)
+
+    sess = D.DecodeSession(ctx, model, M=1)
+    rng = np.random.default_rng(D.X_SEED)
+    x = rng.standard_normal((1, shape.d_model)).astype(np.float32).astype(np.float16)
+    sess.x.upload(x)
+
+    # resident-in-HBM measurement
+    sess.run(max(3, args.warmup), fused_norms=True)
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = tc.launch_count()
+    gpu_ms, wall_ms = sess.run(args.steps, fused_norms=True)
+    launches = tc.launch_count() - launches0
+    clocks = sampler.stop()
+    logits = sess.logits.to_numpy((1, shape.vocab), np.float16)
+    if not np.all(np.isfinite(logits)):
+        raise SystemExit("non-finite logits")
+    if tc.take_device_error(ctx) != 0:
+        raise SystemExit("device-side error word set")
+
+    # end-to-end: step input from pinned host memory in, logits out, every step
+    hx = torch.from_numpy(x.copy()).pin_memory()
+    hl = torch.empty((1, shape.vocab), dtype=torch.float16).pin_memory()
+    sess.run(3, fused_norms=True, host_x=hx.data_ptr(), host_logits=hl.data_ptr())
+    _, e2e_wall_ms = sess.run(args.steps, fused_norms=True, host_x=hx.data_ptr(),
+                              host_logits=hl.data_ptr())
+    if not np.array_equal(hl.numpy().view(np.uint16), logits.view(np.uint16)):
+        # same input, same kernels: the e2e path must reproduce the resident path's logits
+        print("warning: e2e logits differ from resident-run logits", file=sys.stderr)
+
+    total_b, weight_b = algorithmic_bytes_per_token(shape)
+    ms_per_step = gpu_ms / args.steps
+    value = 1e3 / ms_per_step
+    peak, peak_kind = measured_peaks()
+    n_gemv = shape.gemvs_per_token()
+    achieved = total_b / (ms_per_step * 1e-3) / 1e9
+    out = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {
+            "workload": "llama-7b-shape Q4_0 decode weight stream, batch 1: 32 layers x "
+                        "(q,k,v,o 4096x4096; gate,up 11008x4096; down 4096x11008) + lm_head "
+                        "32000x4096, RMSNorm fused into q/k/v, gate/up and lm_head; GGUF v3 file "
+                        "loaded with tc_gguf_load_supported_tensors",
+            "gemvs_per_token": n_gemv, "weight_bytes_per_token": weight_b,
+            "l2": "3.7 GB of weights are streamed per step (126 MB L2): no flush needed",
+            "api": "tc_gemv_quantized_async / tcx_fused_rmsnorm_gemv_quantized_ex on a tc_stream, "
+                   "one tc_stream_sync per token",
+            "gguf_build_s": round(t_build, 2), "gguf_load_s": round(t_load, 2),
+        },
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                     "bytes_per_launch": total_b / n_gemv,
+                     "us_per_launch": ms_per_step * 1e3 / n_gemv,
+                     "weight_gbs": weight_b / (ms_per_step * 1e-3) / 1e9},
+        "e2e": {"value": 1e3 / (e2e_wall_ms / args.steps), "unit": UNIT,
+                "h2d_bytes_per_step": shape.d_model * 2, "d2h_bytes_per_step": shape.vocab * 2,
+                "timing": "host clock around the loop (copies are synchronous calls)"},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "wall_ms_per_step": wall_ms / args.steps,
+        "kernel": tc.cuda_last_kernel_name(),
+    }
+    if not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_baseline_leg(shape)
+    sess.close()
+    model.owner.close()
+    ctx.close()
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps(run_reference_arm(args)), flush=True)
+        return
+    if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        from tensorcore_b200 import tp
+        out = tp.run_bench(args)
+        if rank == 0 and out is not None:
+            print(json.dumps(out), flush=True)
+        return
+    print(json.dumps(run_single_gpu(args)), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -730,9 +730,8 @@ cudaError_t launch_gemv_q(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t
     // The RMSNorm prologue keeps the normalised row in fp32, whatever the activation type.
     const bool stage_f32 = a.x_f32 || fuse;
 
-    // Q4_0 decode shapes go to the tensor-core dot kernel, two activation rows per launch.
-    const bool try_mma = a.fmt == FMT_Q4_0 &&
-                         (env.variant == VARIANT_AUTO || env.variant == VARIANT_MMA);
+    // The tensor-core dot kernel (two activation rows per launch) is selected explicitly.
+    const bool try_mma = a.fmt == FMT_Q4_0 && env.variant == VARIANT_MMA;
     int step = kMaxMB;
     for (int m0 = 0; m0 < a.M && err == cudaSuccess; m0 += step) {
         if (try_mma) {

@@ -55,6 +55,7 @@ struct MmaParams {
     int chunks;        // chunks per panel = ceil(nb / kc)
     int pitch;         // bytes between rows of a stage
     int ns;            // ring stages
+    uint32_t ns_magic; // floor(2^32 / ns) + 1: s / ns == umulhi(s, ns_magic) for small s
     int x_f32;         // activations are fp32 in global memory
     int y_f32;
     int split;         // 1: two-pass hi/lo activations (fp32 x or fused norm)
@@ -110,6 +111,18 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
         "{%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Shared-memory loads by 32-bit window address (constant offsets fold into the instruction).
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
 }
 __device__ __forceinline__ float hbits2f(uint32_t h16) {
     return __half2float(__ushort_as_half(static_cast<uint16_t>(h16)));
@@ -257,7 +270,7 @@ __device__ void stage_x(const MmaParams& p, uint8_t* smem, double* scratch) {
     consumer_sync();
 }
 
-template <int MB>
+template <int MB, int NPASS>
 __global__ void __maxnreg__(112) gemv_q4_mma_kernel(const MmaParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);            // [kMaxStages]
@@ -322,12 +335,19 @@ __global__ void __maxnreg__(112) gemv_q4_mma_kernel(const MmaParams p) {
     stage_x<MB>(p, smem, scratch);
 
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t* xfrag = reinterpret_cast<const uint32_t*>(smem + p.off_xfrag);
     const float* sxs = reinterpret_cast<const float*>(smem + p.off_sx);
-    const uint8_t* zero = smem + p.off_zero;
-    const int npass = p.split ? 2 : 1;
-    // This lane feeds operand B only for the column (= block within the group) it matches.
+    // 32-bit shared-window addresses: every load below is [register + immediate].
+    const uint32_t ring32 = s_u32(ring);
+    const uint32_t lane_off = static_cast<uint32_t>(g * p.pitch + t * 36);
+    const uint32_t hi_row_off = static_cast<uint32_t>(8 * p.pitch);
+    // This lane feeds operand B only for the column (= block of the group) it matches; all
+    // other lanes read a zeroed 64-byte region.
     const bool feeds_even = (g == 2 * t), feeds_odd = (g == 2 * t + 1);
+    const uint32_t base_e = feeds_even ? s_u32(smem + p.off_xfrag) : s_u32(smem + p.off_zero);
+    const uint32_t base_o = feeds_odd ? s_u32(smem + p.off_xfrag) + 64u : s_u32(smem + p.off_zero);
+    const uint32_t mask_e = feeds_even ? 0xffffffffu : 0u, mask_o = feeds_odd ? 0xffffffffu : 0u;
+    const uint32_t pass_stride = static_cast<uint32_t>(p.nb) * 64u;
+    const bool fast_items = (ips == 8);
 
     for (int panel = 0; panel < panels; ++panel) {
         float acc[MB][2];
@@ -338,69 +358,65 @@ __global__ void __maxnreg__(112) gemv_q4_mma_kernel(const MmaParams p) {
         int id = first + ((warp - first % kConsumerWarps) + kConsumerWarps) % kConsumerWarps;
         for (; id < first + ipp; id += kConsumerWarps) {
             const int rem = id - first;
-            const int chunk = rem / ips, bgl = rem - chunk * ips;
-            const int s = panel * p.chunks + chunk;
-            const int slot = s % p.ns;
+            const int chunk = fast_items ? (rem >> 3) : (rem / ips);
+            const int bgl = fast_items ? (rem & 7) : (rem - chunk * ips);
+            const uint32_t s = static_cast<uint32_t>(panel * p.chunks + chunk);
+            const uint32_t use = __umulhi(s, p.ns_magic);          // s / ns
+            const uint32_t slot = s - use * static_cast<uint32_t>(p.ns);
             if (*abort_flag) continue;
-            if (!bar_wait(&full[slot], static_cast<uint32_t>((s / p.ns) & 1), abort_flag)) {
+            if (!bar_wait(&full[slot], use & 1u, abort_flag)) {
                 if (lane == 0) { *abort_flag = 1; atomicOr(p.err, ERR_WAIT_TIMEOUT); }
                 continue;
             }
-            const uint8_t* st = ring + static_cast<size_t>(slot) * stage_bytes;
-            const uint32_t* wlo = reinterpret_cast<const uint32_t*>(
-                st + static_cast<size_t>(g) * p.pitch + bgl * 144 + t * 36);
-            const uint32_t* whi = reinterpret_cast<const uint32_t*>(
-                st + static_cast<size_t>(g + 8) * p.pitch + bgl * 144 + t * 36);
+            const uint32_t wa_addr = ring32 + slot * static_cast<uint32_t>(stage_bytes) + lane_off +
+                                     static_cast<uint32_t>(bgl) * 144u;
+            const uint32_t wb_addr = wa_addr + hi_row_off;
             uint32_t wa[9], wb[9];
 #pragma unroll
-            for (int i = 0; i < 9; ++i) { wa[i] = wlo[i]; wb[i] = whi[i]; }
+            for (int i = 0; i < 9; ++i) { wa[i] = lds32(wa_addr + 4 * i); wb[i] = lds32(wb_addr + 4 * i); }
             __syncwarp();
             if (lane == 0) bar_arrive(&empty[slot]);  // data is in registers: slot may refill
 
-            // code words: even block of the pair straddles word boundaries by 2 bytes
+            // code words: the even block of the pair straddles word boundaries by 2 bytes
             uint32_t ea[4], eb[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 ea[i] = __funnelshift_r(wa[i], wa[i + 1], 16);
                 eb[i] = __funnelshift_r(wb[i], wb[i + 1], 16);
             }
-            const int blk = (chunk * p.kc) + bgl * 8 + 2 * t;   // even block index in the row
+            const int blk = chunk * p.kc + bgl * 8 + 2 * t;      // even block index in the row
+            const uint32_t xoff = static_cast<uint32_t>(blk) * 64u;
 #pragma unroll
             for (int m = 0; m < MB; ++m) {
-                // four independent accumulation chains (one per nibble variant) hide MMA latency
-                float c[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-                float c2[4] = {0.f, 0.f, 0.f, 0.f}, c3[4] = {0.f, 0.f, 0.f, 0.f};
-                for (int ps = 0; ps < npass; ++ps) {
-                    const uint32_t* xf = xfrag + (static_cast<size_t>(m * npass + ps) * p.nb + blk) * 16;
-                    const uint4* pe = feeds_even ? reinterpret_cast<const uint4*>(xf)
-                                                 : reinterpret_cast<const uint4*>(zero);
-                    const uint4* po = feeds_odd ? reinterpret_cast<const uint4*>(xf + 16)
-                                                : reinterpret_cast<const uint4*>(zero);
+                // two independent accumulation chains hide the MMA latency
+                float c[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int ps = 0; ps < NPASS; ++ps) {
+                    const uint32_t off = xoff + static_cast<uint32_t>(m * NPASS + ps) * pass_stride;
+                    const uint32_t pe = base_e + (off & mask_e), po = base_o + (off & mask_o);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const uint4 be = pe[feeds_even ? i : 0];
-                        const uint4 bo = po[feeds_odd ? i : 0];
+                        const uint4 be = lds128(pe + 16 * i);
+                        const uint4 bo = lds128(po + 16 * i);
                         const uint32_t sa = ea[i] >> 8, sb = eb[i] >> 8;
                         const uint32_t oa = wa[5 + i], ob = wb[5 + i];
                         const uint32_t ta = oa >> 8, tb = ob >> 8;
                         mma16816(c, ea[i] & 0x000f000fu, eb[i] & 0x000f000fu, oa & 0x000f000fu,
                                  ob & 0x000f000fu, be.x, bo.x);
-                        mma16816(c1, ea[i] & 0x00f000f0u, eb[i] & 0x00f000f0u, oa & 0x00f000f0u,
+                        mma16816(d, ea[i] & 0x00f000f0u, eb[i] & 0x00f000f0u, oa & 0x00f000f0u,
                                  ob & 0x00f000f0u, be.y, bo.y);
-                        mma16816(c2, sa & 0x000f000fu, sb & 0x000f000fu, ta & 0x000f000fu,
+                        mma16816(c, sa & 0x000f000fu, sb & 0x000f000fu, ta & 0x000f000fu,
                                  tb & 0x000f000fu, be.z, bo.z);
-                        mma16816(c3, sa & 0x00f000f0u, sb & 0x00f000f0u, ta & 0x00f000f0u,
+                        mma16816(d, sa & 0x00f000f0u, sb & 0x00f000f0u, ta & 0x00f000f0u,
                                  tb & 0x00f000f0u, be.w, bo.w);
                     }
                 }
-#pragma unroll
-                for (int q = 0; q < 4; ++q) c[q] = (c[q] + c1[q]) + (c2[q] + c3[q]);
-                // c[0]: row g x even block, c[1]: row g x odd, c[2]/c[3]: row g+8.
+                // c[0]+d[0]: row g x even block, [1]: row g x odd block, [2]/[3]: row g+8.
                 const float2 zs = *reinterpret_cast<const float2*>(&sxs[m * p.nb + blk]);
                 const float de_a = hbits2f(wa[0] & 0xffffu), do_a = hbits2f(wa[4] >> 16);
                 const float de_b = hbits2f(wb[0] & 0xffffu), do_b = hbits2f(wb[4] >> 16);
-                acc[m][0] = fmaf(de_a, c[0] - zs.x, fmaf(do_a, c[1] - zs.y, acc[m][0]));
-                acc[m][1] = fmaf(de_b, c[2] - zs.x, fmaf(do_b, c[3] - zs.y, acc[m][1]));
+                acc[m][0] = fmaf(de_a, (c[0] - zs.x) + d[0], fmaf(do_a, (c[1] - zs.y) + d[1], acc[m][0]));
+                acc[m][1] = fmaf(de_b, (c[2] - zs.x) + d[2], fmaf(do_b, (c[3] - zs.y) + d[3], acc[m][1]));
             }
         }
         // combine the four block-pair lanes of each row, then the eight warps
@@ -441,11 +457,14 @@ inline int up(int v, int a) { return (v + a - 1) / a * a; }
 }  // namespace
 
 cudaError_t init_mma_kernels(int smem_optin) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_q4_mma_kernel<1>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+    cudaError_t e = cudaSuccess;
+#define TCB_MMA_SET(MB, NP)                                                                  \
+    e = cudaFuncSetAttribute(gemv_q4_mma_kernel<MB, NP>,                                     \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);       \
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(gemv_q4_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                smem_optin);
+    TCB_MMA_SET(1, 1) TCB_MMA_SET(1, 2) TCB_MMA_SET(2, 1) TCB_MMA_SET(2, 2)
+#undef TCB_MMA_SET
+    return e;
 }
 
 // Returns cudaErrorNotSupported when the shape / alignment is outside this kernel's domain
@@ -488,6 +507,7 @@ cudaError_t launch_gemv_q4_mma(const GemvQArgs& a, const LaunchEnv& env, cudaStr
     if (ns < 2) return cudaErrorNotSupported;
     if (ns > kMaxStages) ns = kMaxStages;
     p.ns = ns;
+    p.ns_magic = static_cast<uint32_t>(0xFFFFFFFFu / static_cast<uint32_t>(ns)) + 1u;
     const int smem = off + ns * stage_bytes;
 
     static const int ctas_per_sm = [] {
@@ -513,8 +533,11 @@ cudaError_t launch_gemv_q4_mma(const GemvQArgs& a, const LaunchEnv& env, cudaStr
         cfg.numAttrs = 1;
     }
     if (name) *name = split ? "q4_0_gemv_mma_split_sm100" : "q4_0_gemv_mma_sm100";
-    return a.M == 1 ? cudaLaunchKernelEx(&cfg, gemv_q4_mma_kernel<1>, p)
-                    : cudaLaunchKernelEx(&cfg, gemv_q4_mma_kernel<2>, p);
+    if (a.M == 1)
+        return split ? cudaLaunchKernelEx(&cfg, gemv_q4_mma_kernel<1, 2>, p)
+                     : cudaLaunchKernelEx(&cfg, gemv_q4_mma_kernel<1, 1>, p);
+    return split ? cudaLaunchKernelEx(&cfg, gemv_q4_mma_kernel<2, 2>, p)
+                 : cudaLaunchKernelEx(&cfg, gemv_q4_mma_kernel<2, 1>, p);
 }
 
 }  // namespace tcb

@@ -41,7 +41,7 @@ typedef struct tch_session {
     tch_model_desc d;
     std::vector<tc_buffer*> wq, wk, wv, wo, wgate, wup, wdown, attn_norm, ffn_norm;
     tc_stream* stream;
-    tc_buffer *x[2], *q, *k, *v, *o, *gate, *up, *logits;
+    tc_buffer *x[3], *q, *k, *v, *o, *gate, *up, *logits;   // x[0]: step input, x[1..2]: hidden
     cudaEvent_t ev0, ev1;
 } tch_session;
 
@@ -52,7 +52,7 @@ static void copy_list(std::vector<tc_buffer*>& dst, tc_buffer** src, int n) {
 
 void tch_session_destroy(tch_session* s) {
     if (!s) return;
-    tc_buffer* bufs[] = {s->x[0], s->x[1], s->q, s->k, s->v, s->o, s->gate, s->up, s->logits};
+    tc_buffer* bufs[] = {s->x[0], s->x[1], s->x[2], s->q, s->k, s->v, s->o, s->gate, s->up, s->logits};
     for (tc_buffer* b : bufs)
         if (b) tc_buffer_free(s->ctx, b);
     if (s->stream) tc_stream_destroy(s->ctx, s->stream);
@@ -75,15 +75,16 @@ int tch_session_create(tc_context* ctx, const tch_model_desc* d, tch_session** o
     copy_list(s->ffn_norm, d->ffn_norm, L);
     s->stream = nullptr;
     s->ev0 = s->ev1 = nullptr;
-    tc_buffer** slots[] = {&s->x[0], &s->x[1], &s->q, &s->k, &s->v, &s->o, &s->gate, &s->up,
-                           &s->logits};
+    tc_buffer** slots[] = {&s->x[0], &s->x[1], &s->x[2], &s->q, &s->k, &s->v, &s->o, &s->gate,
+                           &s->up, &s->logits};
     const size_t widths[] = {(size_t)d->d_model, (size_t)d->d_model, (size_t)d->d_model,
+                             (size_t)d->d_model,
                              (size_t)d->d_kv, (size_t)d->d_kv, (size_t)d->d_model,
                              (size_t)d->d_ff, (size_t)d->d_ff,
                              (size_t)(d->vocab > 0 ? d->vocab : 1)};
     for (tc_buffer** p : slots) *p = nullptr;
     int st = TC_OK;
-    for (int i = 0; i < 9 && st == TC_OK; ++i)
+    for (int i = 0; i < 10 && st == TC_OK; ++i)
         st = tc_buffer_alloc(ctx, widths[i] * (size_t)d->M * 2, slots[i]);
     if (st == TC_OK) st = tc_stream_create(ctx, &s->stream);
     if (st == TC_OK && (cudaEventCreate(&s->ev0) != cudaSuccess ||
@@ -96,7 +97,7 @@ int tch_session_create(tc_context* ctx, const tch_model_desc* d, tch_session** o
 
 tc_buffer* tch_session_x(tch_session* s) { return s ? s->x[0] : nullptr; }
 tc_buffer* tch_session_logits(tch_session* s) { return s ? s->logits : nullptr; }
-tc_buffer* tch_session_hidden(tch_session* s, int which) { return s ? s->x[which & 1] : nullptr; }
+tc_buffer* tch_session_hidden(tch_session* s, int which) { return s ? s->x[1 + (which & 1)] : nullptr; }
 
 // One projection.  mode 0: tc_gemv_quantized_async (the reference entry point).
 // mode 1 with gamma: RMSNorm prologue fused into the GEMV (tcx_fused_rmsnorm_gemv_quantized_ex).
@@ -109,15 +110,17 @@ static int proj(tch_session* s, int mode, tc_buffer* x, tc_buffer* gamma, tc_buf
     return tc_gemv_quantized_async(s->ctx, x, w, y, fmt, s->d.M, N, K, s->stream);
 }
 
-// Records one token's projections.  The hidden state ping-pongs between x[0] and x[1]; the
+// Records one token's projections.  The step input x[0] is only read; the hidden state then
+// ping-pongs between x[1] and x[2]; the
 // attention mix and the SwiGLU gate, which lie outside this path, are stood in for by feeding
 // the q projection to o_proj and the gate projection to down_proj, so that every GEMV reads
 // the output of an earlier one (a true dependency chain) with the real shapes.
 static int record_token(tch_session* s, int mode) {
     const tch_model_desc& d = s->d;
     int st = TC_OK;
-    int cur = 0;
+    int cur = 0;   // index into x[]: layer l reads x[cur], writes x[nxt]
     for (int l = 0; l < d.n_layers && st == TC_OK; ++l) {
+        const int nxt = (cur == 1) ? 2 : 1;
         tc_buffer* an = s->attn_norm.empty() ? nullptr : s->attn_norm[l];
         tc_buffer* fn = s->ffn_norm.empty() ? nullptr : s->ffn_norm[l];
         st = proj(s, mode, s->x[cur], an, s->wq[l], s->q, d.d_model, d.d_model);
@@ -126,8 +129,8 @@ static int record_token(tch_session* s, int mode) {
         if (st == TC_OK) st = proj(s, 0, s->q, nullptr, s->wo[l], s->o, d.d_model, d.d_model);
         if (st == TC_OK) st = proj(s, mode, s->o, fn, s->wgate[l], s->gate, d.d_ff, d.d_model);
         if (st == TC_OK) st = proj(s, mode, s->o, fn, s->wup[l], s->up, d.d_ff, d.d_model);
-        if (st == TC_OK) st = proj(s, 0, s->gate, nullptr, s->wdown[l], s->x[cur ^ 1], d.d_model, d.d_ff);
-        cur ^= 1;
+        if (st == TC_OK) st = proj(s, 0, s->gate, nullptr, s->wdown[l], s->x[nxt], d.d_model, d.d_ff);
+        cur = nxt;
     }
     if (st == TC_OK && d.lm_head)
         st = proj(s, mode, s->x[cur], d.out_norm, d.lm_head, s->logits, d.vocab, d.d_model);

@@ -321,6 +321,7 @@ extern "C" tc_status_t tc_init(tc_context** out_ctx) {
     ctx->stream0 = nullptr;
     ctx->err_host = nullptr;
     ctx->err_dev = nullptr;
+    if (const char* v = std::getenv("TC_GEMV_VARIANT")) (void)tcx_set_gemv_variant(v);
     ctx->pdl = env_flag("TC_PDL", true);
     ctx->graphs = env_flag("TC_STREAM_GRAPH", true);
     const tc_status_t st = setup_device(ctx, device);

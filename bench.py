@@ -369,6 +369,8 @@ def main() -> None:
         out = tp.run_bench(args)
         if rank == 0 and out is not None:
             print(json.dumps(out), flush=True)
+        sys.stdout.flush()
+        tp.shutdown()
         return
     print(json.dumps(run_single_gpu(args)), flush=True)
 

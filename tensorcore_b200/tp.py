@@ -342,5 +342,15 @@ def run_bench(args):
             "gpu_launches": per_token_launches * args.steps,
             "clocks": clocks,
         }
-    dist.destroy_process_group()
+    # Tear-down order matters: a CUDA graph that holds captured NCCL kernels must be released
+    # before the communicator is destroyed (destroying first blocks forever).
+    del graph
+    torch.cuda.synchronize()
+    dist.barrier()
     return out
+
+
+def shutdown() -> None:
+    import torch.distributed as dist
+    if dist.is_initialized():
+        dist.destroy_process_group()

@@ -304,9 +304,12 @@ def run_single_gpu(args) -> dict:
     sess.run(3, fused_norms=True, host_x=hx.data_ptr(), host_logits=hl.data_ptr())
     _, e2e_wall_ms = sess.run(args.steps, fused_norms=True, host_x=hx.data_ptr(),
                               host_logits=hl.data_ptr())
-    if not np.array_equal(hl.numpy().view(np.uint16), logits.view(np.uint16)):
-        # same input, same kernels: the e2e path must reproduce the resident path's logits
-        print("warning: e2e logits differ from resident-run logits", file=sys.stderr)
+    # same input, same kernels: the e2e path must reproduce the resident path's logits, up to
+    # the summation order of the shared-memory accumulators (fp16 rounding flips)
+    a, b = hl.numpy().astype(np.float64), logits.astype(np.float64)
+    drift = float(np.sqrt(np.mean((a - b) ** 2)) / max(np.sqrt(np.mean(b ** 2)), 1e-30))
+    if not drift <= 2e-3:
+        raise SystemExit(f"e2e logits differ from resident-run logits (scaled rms {drift})")
 
     total_b, weight_b = algorithmic_bytes_per_token(shape)
     ms_per_step = gpu_ms / args.steps

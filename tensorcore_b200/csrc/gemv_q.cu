@@ -37,8 +37,10 @@ cudaError_t launch_gemv_q4_mma(const GemvQArgs& a, const LaunchEnv& env, cudaStr
                                const char** name);
 namespace {
 
-constexpr int kWarps = 8;
+constexpr int kWarps = 8;               // generic kernel
 constexpr int kThreads = kWarps * 32;
+constexpr int kMaxStreamWarps = 16;     // streaming kernel: 8 or 16 warps, chosen per launch
+constexpr int kMaxStreamThreads = kMaxStreamWarps * 32;
 constexpr int kGroupBlocks = 8;
 constexpr int kMaxMB = 4;
 
@@ -157,15 +159,15 @@ __device__ __forceinline__ int x_chunk_index(int k_chunk, int gpr) {
 }
 
 // Sum over a thread block of one double per thread (result broadcast to all threads).
-__device__ double block_sum_f64(double v, double* scratch /* >= kWarps doubles */) {
+__device__ double block_sum_f64(double v, double* scratch /* one double per warp */) {
+    const int nwarps = blockDim.x >> 5;
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
     __syncthreads();
     if (l == 0) scratch[w] = v;
     __syncthreads();
     double t = 0.0;
-#pragma unroll
-    for (int i = 0; i < kWarps; ++i) t += scratch[i];
+    for (int i = 0; i < nwarps; ++i) t += scratch[i];
     return t;
 }
 
@@ -180,7 +182,7 @@ __device__ void stage_activations(const StreamParams& p, uint8_t* smem, float ze
     const int K = p.K, gpr = p.gpr, nb = p.nb;
     uint8_t* xs = smem + p.off_x;
     float* sx = reinterpret_cast<float*>(smem + p.off_sx);
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, nthreads = blockDim.x;
     const size_t row_bytes = static_cast<size_t>(K) * (XF32 ? 4 : 2);
 
     for (int m = 0; m < MB; ++m) {
@@ -189,7 +191,7 @@ __device__ void stage_activations(const StreamParams& p, uint8_t* smem, float ze
             const int nchunks = K / (XF32 ? 4 : 8);
             const uint4* src = reinterpret_cast<const uint4*>(
                 static_cast<const uint8_t*>(p.X) + m * row_bytes);
-            for (int i = tid; i < nchunks; i += kThreads)
+            for (int i = tid; i < nchunks; i += nthreads)
                 dst[x_chunk_index<XF32>(i, gpr)] = __ldg(src + i);
         } else if (XF32) {
             const int nquads = K / 4;
@@ -197,7 +199,7 @@ __device__ void stage_activations(const StreamParams& p, uint8_t* smem, float ze
             if (p.x_src_f16) {
                 const uint2* xr = reinterpret_cast<const uint2*>(
                     static_cast<const __half*>(p.X) + static_cast<size_t>(m) * K);
-                for (int i = tid; i < nquads; i += kThreads) {
+                for (int i = tid; i < nquads; i += nthreads) {
                     const uint2 v = __ldg(xr + i);
                     const double a = h2f(lo16(v.x)), b = h2f(hi16(v.x));
                     const double c = h2f(lo16(v.y)), d = h2f(hi16(v.y));
@@ -206,7 +208,7 @@ __device__ void stage_activations(const StreamParams& p, uint8_t* smem, float ze
             } else {
                 const float4* xr = reinterpret_cast<const float4*>(
                     static_cast<const float*>(p.X) + static_cast<size_t>(m) * K);
-                for (int i = tid; i < nquads; i += kThreads) {
+                for (int i = tid; i < nquads; i += nthreads) {
                     const float4 v = __ldg(xr + i);
                     const double a = v.x, b = v.y, c = v.z, d = v.w;
                     ss += a * a + b * b + c * c + d * d;
@@ -216,7 +218,7 @@ __device__ void stage_activations(const StreamParams& p, uint8_t* smem, float ze
             const float rstd =
                 1.0f / sqrtf(static_cast<float>(ss / static_cast<double>(K)) + p.eps);
             float4* dstf = reinterpret_cast<float4*>(dst);
-            for (int i = tid; i < nquads; i += kThreads) {
+            for (int i = tid; i < nquads; i += nthreads) {
                 float4 xv, gv;
                 if (p.x_src_f16) {
                     const uint2 xb = __ldg(reinterpret_cast<const uint2*>(
@@ -239,7 +241,7 @@ __device__ void stage_activations(const StreamParams& p, uint8_t* smem, float ze
         }
     }
     __syncthreads();
-    for (int t = tid; t < MB * nb; t += kThreads) {
+    for (int t = tid; t < MB * nb; t += nthreads) {
         const int m = t / nb, b = t % nb;
         const int kg = b >> 3, j = b & 7;
         const uint4* xrow = reinterpret_cast<const uint4*>(xs + m * row_bytes);
@@ -394,15 +396,16 @@ __device__ __forceinline__ void group_dot(const uint32_t (&w)[Fmt<FMT>::kGroupV4
 // The streaming kernel.
 // ---------------------------------------------------------------------------------------
 template <int FMT, bool XF32, int MB>
-__global__ void __launch_bounds__(kThreads, 2) gemv_q_stream_kernel(const StreamParams p) {
+__global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q_stream_kernel(const StreamParams p) {
     using F = Fmt<FMT>;
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                  // [kWarps*ns]
-    double* red_scratch = reinterpret_cast<double*>(smem + 8 * kWarps * 4);  // after <=32 bars
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                  // [nwarps*ns]
+    double* red_scratch = reinterpret_cast<double*>(smem + 8 * kMaxStreamWarps * 4);  // after the barriers
     float* rowacc = reinterpret_cast<float*>(smem + p.off_rowacc);
     uint8_t* ring = smem + p.off_ring;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nwarps = blockDim.x >> 5, nthreads = blockDim.x;
     const int ns = p.ns, gpr = p.gpr;
     constexpr int kChunkBytes = 32 * F::kGroupBytes;
 
@@ -413,19 +416,19 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_q_stream_kernel(const Stream
     const long long g_base = static_cast<long long>(r0) * gpr;
     const int g_count = rows * gpr;
     const int nchunks = (g_count + 31) >> 5;
-    const int my_n = nchunks > warp ? (nchunks - warp + kWarps - 1) / kWarps : 0;
+    const int my_n = nchunks > warp ? (nchunks - warp + nwarps - 1) / nwarps : 0;
 
     pdl_launch_dependents();
 
     if (tid == 0) {
-        for (int i = 0; i < kWarps * ns; ++i) mbar_init(&bars[i], 1);
+        for (int i = 0; i < nwarps * ns; ++i) mbar_init(&bars[i], 1);
         fence_barrier_init();
     }
-    for (int i = tid; i < rows * MB; i += kThreads) rowacc[i] = 0.f;
+    for (int i = tid; i < rows * MB; i += nthreads) rowacc[i] = 0.f;
     __syncthreads();
 
     auto issue = [&](int i) {  // lane 0 only: start the copy of this warp's i-th chunk
-        const int c = warp + kWarps * i;
+        const int c = warp + nwarps * i;
         const int first = c << 5;
         const int ng = min(32, g_count - first);
         const uint32_t bytes = static_cast<uint32_t>(ng) * F::kGroupBytes;
@@ -458,7 +461,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_q_stream_kernel(const Stream
             break;
         }
         waited = i + 1;
-        const int c = warp + kWarps * i;
+        const int c = warp + nwarps * i;
         const int gl = (c << 5) + lane;           // group index local to the CTA
         const bool valid = gl < g_count;
 
@@ -518,7 +521,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_q_stream_kernel(const Stream
     }
     __syncthreads();
 
-    for (int i = tid; i < rows * MB; i += kThreads) {
+    for (int i = tid; i < rows * MB; i += nthreads) {
         const int r = i / MB, m = i - r * MB;
         const size_t o = static_cast<size_t>(m) * p.N + (r0 + r);
         const float v = rowacc[i];
@@ -626,6 +629,7 @@ inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
 struct StreamPlan {
     bool ok = false;
+    int warps = 8;
     int ns = 0;
     int grid = 0;
     int smem = 0;
@@ -652,7 +656,7 @@ StreamPlan plan_stream(const GemvQArgs& a, int mb, bool stage_f32, const LaunchE
     const int grid = a.N < want ? a.N : want;
     const int max_rows = (a.N + grid - 1) / grid + 1;
 
-    int off = 8 * kWarps * 4 + 8 * kWarps;  // barriers (up to 4 stages) + reduction scratch
+    int off = 8 * kMaxStreamWarps * 4 + 8 * kMaxStreamWarps;  // barriers (<= 4 stages) + scratch
     off = align_up(off, 16);
     const int off_rowacc = off;
     off += align_up(max_rows * mb * 4, 16);
@@ -662,23 +666,38 @@ StreamPlan plan_stream(const GemvQArgs& a, int mb, bool stage_f32, const LaunchE
     off += align_up(mb * a.K * (stage_f32 ? 4 : 2), 128);
     const int off_ring = off;
 
-    const int half_budget = (env.smem_optin > 0 ? env.smem_optin : 232448) / 2 - 1024;
-    const int full_budget = (env.smem_optin > 0 ? env.smem_optin : 232448);
+    const int optin = env.smem_optin > 0 ? env.smem_optin : 232448;
+    const int half_budget = optin / 2 - 1024;
+    // Warp count: 16 warps (one CTA fills the SM: no co-resident successor, but twice the
+    // latency hiding) when each SM has enough work to amortise it, else 8 warps with a ring
+    // small enough for two CTAs (this kernel and the next one in the stream) per SM.
+    static const int force_warps = [] {
+        const char* v = std::getenv("TC_GEMV_WARPS");
+        return v ? std::atoi(v) : 0;
+    }();
+    const long long bytes_per_cta = static_cast<long long>(a.N) * nb * (a.fmt == FMT_Q4_0 ? 18 : 34) / grid;
+    int warps = bytes_per_cta >= (256 << 10) ? 16 : 8;
+    if (force_warps == 8 || force_warps == 16) warps = force_warps;
     int ns = 0;
-    for (int cand = 4; cand >= 2; --cand) {
-        if (off_ring + kWarps * cand * chunk_bytes <= half_budget) { ns = cand; break; }
+    if (warps == 16) {
+        for (int cand = 3; cand >= 2; --cand)
+            if (off_ring + 16 * cand * chunk_bytes <= optin - 2048) { ns = cand; break; }
+        if (ns == 0) warps = 8;
     }
-    if (ns == 0) {
-        for (int cand = 3; cand >= 1; --cand) {
-            if (off_ring + kWarps * cand * chunk_bytes <= full_budget) { ns = cand; break; }
-        }
+    if (warps == 8) {
+        for (int cand = 4; cand >= 2; --cand)
+            if (off_ring + 8 * cand * chunk_bytes <= half_budget) { ns = cand; break; }
+        if (ns == 0)
+            for (int cand = 3; cand >= 1; --cand)
+                if (off_ring + 8 * cand * chunk_bytes <= optin) { ns = cand; break; }
     }
     if (ns == 0) return pl;
 
     pl.ok = true;
     pl.ns = ns;
     pl.grid = grid;
-    pl.smem = off_ring + kWarps * ns * chunk_bytes;
+    pl.warps = warps;
+    pl.smem = off_ring + warps * ns * chunk_bytes;
     StreamParams& p = pl.p;
     p.W = a.W; p.X = a.X; p.Y = a.Y; p.gamma = a.gamma; p.err = env.err_word;
     p.M = mb; p.N = a.N; p.K = a.K; p.nb = nb; p.gpr = gpr; p.ns = ns;
@@ -690,7 +709,7 @@ StreamPlan plan_stream(const GemvQArgs& a, int mb, bool stage_f32, const LaunchE
 
 template <int FMT, bool XF32>
 cudaError_t launch_stream_mb(int mb, const StreamPlan& pl, cudaStream_t st, bool pdl) {
-    const dim3 grid(pl.grid), block(kThreads);
+    const dim3 grid(pl.grid), block(pl.warps * 32);
     switch (mb) {
         case 1: return launch_with_attrs(gemv_q_stream_kernel<FMT, XF32, 1>, grid, block, pl.smem, st, pdl, pl.p);
         case 2: return launch_with_attrs(gemv_q_stream_kernel<FMT, XF32, 2>, grid, block, pl.smem, st, pdl, pl.p);

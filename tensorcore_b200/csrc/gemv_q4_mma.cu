@@ -37,7 +37,11 @@
 namespace tcb {
 namespace {
 
-constexpr int kConsumerWarps = 8;
+#ifndef TCB_MMA_WARPS
+#define TCB_MMA_WARPS 16
+#endif
+constexpr int kConsumerWarps = TCB_MMA_WARPS;   // one 8-block group of a stage per warp
+constexpr int kMaxKc = kConsumerWarps * 8;      // blocks per row per stage
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kMmaThreads = kConsumerThreads + 32;  // + producer warp
 constexpr int kPanelRows = 16;
@@ -51,7 +55,7 @@ struct MmaParams {
     uint32_t* err;
     int M, N, K;
     int nb;            // blocks per row
-    int kc;            // blocks per chunk (multiple of 8, <= 64)
+    int kc;            // blocks per chunk (multiple of 8, <= kMaxKc)
     int chunks;        // chunks per panel = ceil(nb / kc)
     int pitch;         // bytes between rows of a stage
     int ns;            // ring stages
@@ -271,12 +275,12 @@ __device__ void stage_x(const MmaParams& p, uint8_t* smem, double* scratch) {
 }
 
 template <int MB, int NPASS>
-__global__ void __maxnreg__(112) gemv_q4_mma_kernel(const MmaParams p) {
+__global__ void __maxnreg__(kConsumerWarps > 8 ? 96 : 112) gemv_q4_mma_kernel(const MmaParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);            // [kMaxStages]
     uint64_t* empty = full + kMaxStages;                           // [kMaxStages]
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 16 * kMaxStages);
-    double* scratch = reinterpret_cast<double*>(smem + 16 * kMaxStages + 16);  // 8 doubles
+    double* scratch = reinterpret_cast<double*>(smem + 16 * kMaxStages + 16);  // kConsumerWarps doubles
     float* red = reinterpret_cast<float*>(smem + p.off_red);       // [2][8 warps][16 rows][MB]
     uint8_t* ring = smem + p.off_ring;
 
@@ -347,7 +351,7 @@ __global__ void __maxnreg__(112) gemv_q4_mma_kernel(const MmaParams p) {
     const uint32_t base_o = feeds_odd ? s_u32(smem + p.off_xfrag) + 64u : s_u32(smem + p.off_zero);
     const uint32_t mask_e = feeds_even ? 0xffffffffu : 0u, mask_o = feeds_odd ? 0xffffffffu : 0u;
     const uint32_t pass_stride = static_cast<uint32_t>(p.nb) * 64u;
-    const bool fast_items = (ips == 8);
+    const bool fast_items = (ips == kConsumerWarps);
 
     for (int panel = 0; panel < panels; ++panel) {
         float acc[MB][2];
@@ -358,8 +362,8 @@ __global__ void __maxnreg__(112) gemv_q4_mma_kernel(const MmaParams p) {
         int id = first + ((warp - first % kConsumerWarps) + kConsumerWarps) % kConsumerWarps;
         for (; id < first + ipp; id += kConsumerWarps) {
             const int rem = id - first;
-            const int chunk = fast_items ? (rem >> 3) : (rem / ips);
-            const int bgl = fast_items ? (rem & 7) : (rem - chunk * ips);
+            const int chunk = fast_items ? (rem / kConsumerWarps) : (rem / ips);
+            const int bgl = fast_items ? (rem % kConsumerWarps) : (rem - chunk * ips);
             const uint32_t s = static_cast<uint32_t>(panel * p.chunks + chunk);
             const uint32_t use = __umulhi(s, p.ns_magic);          // s / ns
             const uint32_t slot = s - use * static_cast<uint32_t>(p.ns);
@@ -480,7 +484,7 @@ cudaError_t launch_gemv_q4_mma(const GemvQArgs& a, const LaunchEnv& env, cudaStr
     MmaParams p;
     p.W = a.W; p.X = a.X; p.Y = a.Y; p.gamma = a.gamma; p.err = env.err_word;
     p.M = a.M; p.N = a.N; p.K = a.K; p.nb = nb;
-    p.kc = nb < 64 ? nb : 64;
+    p.kc = nb < kMaxKc ? nb : kMaxKc;
     p.chunks = (nb + p.kc - 1) / p.kc;
     const int m8 = p.kc / 8;
     p.pitch = p.kc * 18 + ((m8 & 1) ? 32 : 16);   // pitch / 16 odd: conflict-free row stride
@@ -488,7 +492,7 @@ cudaError_t launch_gemv_q4_mma(const GemvQArgs& a, const LaunchEnv& env, cudaStr
     p.y_f32 = a.y_f32 ? 1 : 0;
     p.split = split ? 1 : 0;
     p.eps = a.eps;
-    int off = 16 * kMaxStages + 16 + 64;
+    int off = 16 * kMaxStages + 16 + 8 * kConsumerWarps;
     off = up(off, 16);
     p.off_red = off;
     off += up(2 * kConsumerWarps * kPanelRows * a.M * 4, 16);
@@ -501,7 +505,8 @@ cudaError_t launch_gemv_q4_mma(const GemvQArgs& a, const LaunchEnv& env, cudaStr
     p.off_ring = off;
     const int stage_bytes = kPanelRows * p.pitch;
     const int optin = env.smem_optin > 0 ? env.smem_optin : 232448;
-    const int half_budget = optin / 2 - 1024;
+    // 17 warps at 112 registers fill the register file: no second CTA fits, use all shared memory
+    const int half_budget = kConsumerWarps > 8 ? optin - 2048 : optin / 2 - 1024;
     int ns = (half_budget - off) / stage_bytes;
     if (ns < 2) ns = (optin - off) / stage_bytes;       // one CTA per SM
     if (ns < 2) return cudaErrorNotSupported;

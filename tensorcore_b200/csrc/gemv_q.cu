@@ -74,6 +74,7 @@ struct StreamParams {
     // shared-memory offsets (bytes)
     int off_rowacc, off_sx, off_x, off_ring;
     int max_rows;  // rows per CTA upper bound
+    int dbg_skip;  // measurement aid: stream the weights but skip the arithmetic
 };
 
 // ---------------------------------------------------------------------------------------
@@ -139,6 +140,19 @@ __device__ __forceinline__ uint16_t lo16(uint32_t v) { return static_cast<uint16
 __device__ __forceinline__ uint16_t hi16(uint32_t v) { return static_cast<uint16_t>(v >> 16); }
 __device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
+// fp32 activations in shared memory: low half = fp16 head, high half = fp16 remainder
+// (x = head + remainder to 2^-22 relative); both multiply the code with the mixed-precision FMA.
+__device__ __forceinline__ uint32_t split_f32(float x) {
+    const __half h = __float2half_rn(x);
+    const __half l = __float2half_rn(x - __half2float(h));
+    return static_cast<uint32_t>(__half_as_ushort(h)) |
+           (static_cast<uint32_t>(__half_as_ushort(l)) << 16);
+}
+__device__ __forceinline__ float joined_f32(uint32_t w) { return h2f(lo16(w)) + h2f(hi16(w)); }
+__device__ __forceinline__ float fma_hl(uint16_t code, uint32_t xw, float acc) {
+    return fma_h(code, hi16(xw), fma_h(code, lo16(xw), acc));
+}
+
 __device__ __forceinline__ uint32_t get4(const uint4& v, int i) {
     return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
 }
@@ -176,7 +190,14 @@ __device__ double block_sum_f64(double v, double* scratch /* one double per warp
 // Without gamma the rows are copied as they are (staging type == source type).  With gamma the
 // RMSNorm prologue runs first: sum of squares in double, rstd = 1/sqrtf(float(ss/K)+eps),
 // row = (x*rstd)*gamma, kept in fp32 (XF32 staging) whether the source is fp16 or fp32.
-template <bool XF32, int MB>
+// COHERENT: the activations may have been written by other CTAs of the same (persistent)
+// kernel, so they are read with L2-coherent loads instead of the read-only path.
+template <bool COHERENT, typename T>
+__device__ __forceinline__ T ld_act(const T* ptr) {
+    return COHERENT ? __ldcg(ptr) : __ldg(ptr);
+}
+
+template <bool XF32, int MB, bool COHERENT = false>
 __device__ void stage_activations(const StreamParams& p, uint8_t* smem, float zero_point,
                                   double* red_scratch) {
     const int K = p.K, gpr = p.gpr, nb = p.nb;
@@ -191,8 +212,13 @@ __device__ void stage_activations(const StreamParams& p, uint8_t* smem, float ze
             const int nchunks = K / (XF32 ? 4 : 8);
             const uint4* src = reinterpret_cast<const uint4*>(
                 static_cast<const uint8_t*>(p.X) + m * row_bytes);
-            for (int i = tid; i < nchunks; i += nthreads)
-                dst[x_chunk_index<XF32>(i, gpr)] = __ldg(src + i);
+            for (int i = tid; i < nchunks; i += nthreads) {
+                uint4 v = ld_act<COHERENT>(src + i);
+                if (XF32)   // fp32 activations are staged as fp16 head + fp16 remainder
+                    v = make_uint4(split_f32(__uint_as_float(v.x)), split_f32(__uint_as_float(v.y)),
+                                   split_f32(__uint_as_float(v.z)), split_f32(__uint_as_float(v.w)));
+                dst[x_chunk_index<XF32>(i, gpr)] = v;
+            }
         } else if (XF32) {
             const int nquads = K / 4;
             double ss = 0.0;
@@ -200,7 +226,7 @@ __device__ void stage_activations(const StreamParams& p, uint8_t* smem, float ze
                 const uint2* xr = reinterpret_cast<const uint2*>(
                     static_cast<const __half*>(p.X) + static_cast<size_t>(m) * K);
                 for (int i = tid; i < nquads; i += nthreads) {
-                    const uint2 v = __ldg(xr + i);
+                    const uint2 v = ld_act<COHERENT>(xr + i);
                     const double a = h2f(lo16(v.x)), b = h2f(hi16(v.x));
                     const double c = h2f(lo16(v.y)), d = h2f(hi16(v.y));
                     ss += a * a + b * b + c * c + d * d;
@@ -209,7 +235,7 @@ __device__ void stage_activations(const StreamParams& p, uint8_t* smem, float ze
                 const float4* xr = reinterpret_cast<const float4*>(
                     static_cast<const float*>(p.X) + static_cast<size_t>(m) * K);
                 for (int i = tid; i < nquads; i += nthreads) {
-                    const float4 v = __ldg(xr + i);
+                    const float4 v = ld_act<COHERENT>(xr + i);
                     const double a = v.x, b = v.y, c = v.z, d = v.w;
                     ss += a * a + b * b + c * c + d * d;
                 }
@@ -217,17 +243,16 @@ __device__ void stage_activations(const StreamParams& p, uint8_t* smem, float ze
             ss = block_sum_f64(ss, red_scratch);
             const float rstd =
                 1.0f / sqrtf(static_cast<float>(ss / static_cast<double>(K)) + p.eps);
-            float4* dstf = reinterpret_cast<float4*>(dst);
             for (int i = tid; i < nquads; i += nthreads) {
                 float4 xv, gv;
                 if (p.x_src_f16) {
-                    const uint2 xb = __ldg(reinterpret_cast<const uint2*>(
+                    const uint2 xb = ld_act<COHERENT>(reinterpret_cast<const uint2*>(
                         static_cast<const __half*>(p.X) + static_cast<size_t>(m) * K) + i);
                     const uint2 gb = __ldg(reinterpret_cast<const uint2*>(p.gamma) + i);
                     xv = make_float4(h2f(lo16(xb.x)), h2f(hi16(xb.x)), h2f(lo16(xb.y)), h2f(hi16(xb.y)));
                     gv = make_float4(h2f(lo16(gb.x)), h2f(hi16(gb.x)), h2f(lo16(gb.y)), h2f(hi16(gb.y)));
                 } else {
-                    xv = __ldg(reinterpret_cast<const float4*>(
+                    xv = ld_act<COHERENT>(reinterpret_cast<const float4*>(
                         static_cast<const float*>(p.X) + static_cast<size_t>(m) * K) + i);
                     gv = __ldg(reinterpret_cast<const float4*>(p.gamma) + i);
                 }
@@ -236,7 +261,8 @@ __device__ void stage_activations(const StreamParams& p, uint8_t* smem, float ze
                 o.y = __fmul_rn(__fmul_rn(xv.y, rstd), gv.y);
                 o.z = __fmul_rn(__fmul_rn(xv.z, rstd), gv.z);
                 o.w = __fmul_rn(__fmul_rn(xv.w, rstd), gv.w);
-                dstf[x_chunk_index<true>(i, gpr)] = o;
+                dst[x_chunk_index<true>(i, gpr)] =
+                    make_uint4(split_f32(o.x), split_f32(o.y), split_f32(o.z), split_f32(o.w));
             }
         }
     }
@@ -250,10 +276,10 @@ __device__ void stage_activations(const StreamParams& p, uint8_t* smem, float ze
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 const uint4 v = xrow[(8 * j + q) * gpr + kg];
-                s += __uint_as_float(v.x);
-                s += __uint_as_float(v.y);
-                s += __uint_as_float(v.z);
-                s += __uint_as_float(v.w);
+                s += joined_f32(v.x);
+                s += joined_f32(v.y);
+                s += joined_f32(v.z);
+                s += joined_f32(v.w);
             }
         } else {
 #pragma unroll
@@ -338,14 +364,14 @@ __device__ __forceinline__ void group_dot(const uint32_t (&w)[Fmt<FMT>::kGroupV4
                         const uint32_t s8 = q[t] >> 8;
                         const uint32_t v2 = s8 & 0x000f000fu;
                         const uint32_t v3 = s8 & 0x00f000f0u;
-                        a0 = fmaf(h2f(lo16(v0)), __uint_as_float(xl.x), a0);
-                        a1 = fmaf(h2f(lo16(v2)), __uint_as_float(xl.y), a1);
-                        a0 = fmaf(h2f(hi16(v0)), __uint_as_float(xl.z), a0);
-                        a1 = fmaf(h2f(hi16(v2)), __uint_as_float(xl.w), a1);
-                        a2 = fmaf(h2f(lo16(v1)), __uint_as_float(xh.x), a2);
-                        a3 = fmaf(h2f(lo16(v3)), __uint_as_float(xh.y), a3);
-                        a2 = fmaf(h2f(hi16(v1)), __uint_as_float(xh.z), a2);
-                        a3 = fmaf(h2f(hi16(v3)), __uint_as_float(xh.w), a3);
+                        a0 = fma_hl(lo16(v0), xl.x, a0);
+                        a1 = fma_hl(lo16(v2), xl.y, a1);
+                        a0 = fma_hl(hi16(v0), xl.z, a0);
+                        a1 = fma_hl(hi16(v2), xl.w, a1);
+                        a2 = fma_hl(lo16(v1), xh.x, a2);
+                        a3 = fma_hl(lo16(v3), xh.y, a3);
+                        a2 = fma_hl(hi16(v1), xh.z, a2);
+                        a3 = fma_hl(hi16(v3), xh.w, a3);
                     }
                 }
                 const float s = sx[m * nb + j * gpr + kg];
@@ -378,10 +404,10 @@ __device__ __forceinline__ void group_dot(const uint32_t (&w)[Fmt<FMT>::kGroupV4
                         const uint32_t u = q[t] ^ 0x80808080u;
                         const uint32_t p01 = __byte_perm(u, 0u, 0x4140);
                         const uint32_t p23 = __byte_perm(u, 0u, 0x4342);
-                        a0 = fmaf(h2f(lo16(p01)), __uint_as_float(xq.x), a0);
-                        a1 = fmaf(h2f(hi16(p01)), __uint_as_float(xq.y), a1);
-                        a2 = fmaf(h2f(lo16(p23)), __uint_as_float(xq.z), a2);
-                        a3 = fmaf(h2f(hi16(p23)), __uint_as_float(xq.w), a3);
+                        a0 = fma_hl(lo16(p01), xq.x, a0);
+                        a1 = fma_hl(hi16(p01), xq.y, a1);
+                        a2 = fma_hl(lo16(p23), xq.z, a2);
+                        a3 = fma_hl(hi16(p23), xq.w, a3);
                     }
                 }
                 const float s = sx[m * nb + j * gpr + kg];
@@ -492,6 +518,8 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q_stream_kernel(con
         if (valid) {
             row = gl / gpr;
             const int kg = gl - row * gpr;
+            if (p.dbg_skip) out[0] = __uint_as_float(w[0] ^ w[35]);
+            else
             group_dot<FMT, XF32, MB>(w, xs, sx, kg, gpr, p.K, p.nb, out);
         }
         // Segmented reduction over lanes that hold groups of the same row (contiguous runs).
@@ -527,6 +555,201 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q_stream_kernel(con
         const float v = rowacc[i];
         if (p.y_f32) static_cast<float*>(p.Y)[o] = v;
         else static_cast<__half*>(p.Y)[o] = __float2half_rn(v);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Persistent decode kernel: a whole recorded list of Q4_0, M = 1 GEMVs in ONE launch.
+//
+// One CTA per SM (cooperative launch: all CTAs are co-resident).  Every warp keeps its ring of
+// weight chunks full ACROSS operations: when it has issued the last chunk of operation i it
+// goes on with the first chunks of operation i+1, so HBM keeps streaming while the CTA finishes
+// i, writes its rows and waits for the other CTAs.  Operations that read what an earlier one
+// wrote are separated by a grid-wide barrier (one 64-bit counter in global memory, release /
+// acquire, bounded spin); operations that share their input (q/k/v, gate/up) are not, and reuse
+// the staged activations.  Activations written earlier in the same launch are read with
+// L2-coherent loads.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+struct WarpGeom {            // one operation as seen by one warp of one CTA
+    const uint8_t* wbase;    // first byte of the CTA's row range
+    int r0, rows, gpr, g_count, my_n;
+};
+
+__device__ __forceinline__ WarpGeom make_geom(const MegaOp& op, int warp, int nwarps) {
+    WarpGeom g;
+    g.r0 = static_cast<int>(static_cast<long long>(op.N) * blockIdx.x / gridDim.x);
+    const int r1 = static_cast<int>(static_cast<long long>(op.N) * (blockIdx.x + 1) / gridDim.x);
+    g.rows = r1 - g.r0;
+    g.gpr = op.K >> 8;
+    g.g_count = g.rows * g.gpr;
+    const int nchunks = (g.g_count + 31) >> 5;
+    g.my_n = nchunks > warp ? (nchunks - warp + nwarps - 1) / nwarps : 0;
+    g.wbase = op.W + static_cast<size_t>(g.r0) * g.gpr * 144;
+    return g;
+}
+
+template <bool XF32>
+__device__ __forceinline__ void mega_chunk(const uint32_t (&w)[36], bool valid, int gl, int gpr,
+                                           const uint8_t* xs, const float* sx, int K, float* rowacc,
+                                           int lane) {
+    float out[1] = {0.f};
+    int row = -1 - lane;
+    if (valid) {
+        row = gl / gpr;
+        const int kg = gl - row * gpr;
+        group_dot<FMT_Q4_0, XF32, 1>(w, xs, sx, kg, gpr, K, K >> 5, out);
+    }
+#pragma unroll
+    for (int dlt = 1; dlt < 32; dlt <<= 1) {
+        const int r2 = __shfl_down_sync(0xffffffffu, row, dlt);
+        const float v2 = __shfl_down_sync(0xffffffffu, out[0], dlt);
+        if ((lane + dlt < 32) && (r2 == row)) out[0] += v2;
+    }
+    const int rprev = __shfl_up_sync(0xffffffffu, row, 1);
+    if (valid && (lane == 0 || rprev != row)) atomicAdd(&rowacc[row], out[0]);
+}
+
+__global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(const MegaParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                               // [nwarps*ns]
+    double* red_scratch = reinterpret_cast<double*>(smem + 8 * kMaxStreamWarps * 4);  // after barriers
+    volatile int* abort_s = reinterpret_cast<volatile int*>(smem + 8 * kMaxStreamWarps * 4 +
+                                                            8 * kMaxStreamWarps);
+    float* rowacc = reinterpret_cast<float*>(smem + p.off_rowacc);
+    uint8_t* ring = smem + p.off_ring;
+    const uint8_t* xs = smem + p.off_x;
+    const float* sx = reinterpret_cast<const float*>(smem + p.off_sx);
+    constexpr int kChunkBytes = 32 * 144;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nwarps = blockDim.x >> 5, nthreads = blockDim.x;
+    const int ns = p.ns, n_ops = p.n_ops;
+
+    if (tid == 0) {
+        for (int i = 0; i < nwarps * ns; ++i) mbar_init(&bars[i], 1);
+        *abort_s = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    // ---- per-warp weight stream: issue cursor runs ahead of the consume cursor ----
+    int iop = 0, ii = 0;                 // next chunk to issue: operation, index within it
+    MegaOp op_i = p.ops[0];
+    WarpGeom gi = make_geom(op_i, warp, nwarps);
+    int islot = 0, cslot = 0;            // ring slots of the next issue / next consume
+    uint32_t cphase = 0;                 // parity of the consume slot's current use
+    int inflight = 0;
+    auto try_issue = [&]() {
+        while (iop < n_ops && ii >= gi.my_n) {
+            ++iop;
+            ii = 0;
+            if (iop < n_ops) { op_i = p.ops[iop]; gi = make_geom(op_i, warp, nwarps); }
+        }
+        if (iop >= n_ops || inflight >= ns) return;
+        if (lane == 0) {
+            const int first = (warp + nwarps * ii) << 5;
+            const int ng = min(32, gi.g_count - first);
+            const uint32_t bytes = static_cast<uint32_t>(ng) * 144u;
+            uint64_t* bar = &bars[warp * ns + islot];
+            fence_proxy_async();
+            mbar_expect_tx(bar, bytes);
+            bulk_g2s(ring + static_cast<size_t>(warp * ns + islot) * kChunkBytes,
+                     gi.wbase + static_cast<size_t>(first) * 144, bytes, bar);
+        }
+        ++ii;
+        ++inflight;
+        if (++islot == ns) islot = 0;
+    };
+    for (int i = 0; i < ns; ++i) try_issue();
+
+    unsigned long long target = p.base;
+    bool failed = false;
+    for (int o = 0; o < n_ops && !failed; ++o) {
+        const MegaOp op = p.ops[o];
+        const WarpGeom gc = make_geom(op, warp, nwarps);
+        // Everyone must be done with the previous operation's shared memory; if this operation
+        // reads another CTA's output, everyone in the grid must be done with the previous one.
+        __syncthreads();
+        if (op.flags & MOP_BARRIER) {
+            target += gridDim.x;
+            if (tid == 0) {
+                __threadfence();
+                atomicAdd(p.counter, 1ULL);
+                const long long t0 = clock64();
+                while (ld_acquire_u64(p.counter) < target) {
+                    if (clock64() - t0 > 2000000000LL) {
+                        *abort_s = 1;
+                        atomicOr(p.err, ERR_WAIT_TIMEOUT);
+                        break;
+                    }
+                }
+                __threadfence();
+            }
+            __syncthreads();
+            if (*abort_s) { failed = true; break; }
+        }
+        const bool f32stage = (op.flags & (MOP_X_F32 | MOP_FUSED)) != 0;
+        if (op.flags & MOP_RESTAGE) {
+            StreamParams sp;
+            sp.X = op.X; sp.gamma = (op.flags & MOP_FUSED) ? op.gamma : nullptr;
+            sp.K = op.K; sp.nb = op.K >> 5; sp.gpr = op.K >> 8; sp.eps = op.eps;
+            sp.x_src_f16 = (op.flags & MOP_X_F32) ? 0 : 1;
+            sp.off_x = p.off_x; sp.off_sx = p.off_sx;
+            if (f32stage) stage_activations<true, 1, true>(sp, smem, 8.0f, red_scratch);
+            else stage_activations<false, 1, true>(sp, smem, 8.0f, red_scratch);
+        }
+        for (int i = tid; i < gc.rows; i += nthreads) rowacc[i] = 0.f;
+        __syncthreads();
+
+        for (int i = 0; i < gc.my_n; ++i) {
+            uint64_t* bar = &bars[warp * ns + cslot];
+            if (!mbar_wait_bounded(bar, cphase)) { failed = true; break; }
+            const int gl = ((warp + nwarps * i) << 5) + lane;
+            const bool valid = gl < gc.g_count;
+            uint32_t w[36];
+            if (valid) {
+                const uint4* src = reinterpret_cast<const uint4*>(
+                    ring + static_cast<size_t>(warp * ns + cslot) * kChunkBytes +
+                    static_cast<size_t>(lane) * 144);
+#pragma unroll
+                for (int v = 0; v < 9; ++v) {
+                    const uint4 t = src[v];
+                    w[4 * v + 0] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
+                }
+            } else {
+#pragma unroll
+                for (int v = 0; v < 36; ++v) w[v] = 0u;
+            }
+            __syncwarp();
+            --inflight;
+            if (++cslot == ns) { cslot = 0; cphase ^= 1u; }
+            try_issue();                           // refill: this or a later operation's weights
+            if (p.dbg_skip) { if (valid && lane == 0) atomicAdd(&rowacc[0], __uint_as_float(w[0] ^ w[35])); }
+            else if (f32stage) mega_chunk<true>(w, valid, gl, gc.gpr, xs, sx, op.K, rowacc, lane);
+            else mega_chunk<false>(w, valid, gl, gc.gpr, xs, sx, op.K, rowacc, lane);
+        }
+        if (__any_sync(0xffffffffu, failed)) { failed = true; }
+        if (failed) { if (lane == 0) { *abort_s = 1; atomicOr(p.err, ERR_WAIT_TIMEOUT); } }
+        __syncthreads();
+        if (*abort_s) { failed = true; break; }
+        for (int i = tid; i < gc.rows; i += nthreads) {
+            const float v = rowacc[i];
+            if (op.flags & MOP_Y_F32) static_cast<float*>(op.Y)[gc.r0 + i] = v;
+            else static_cast<__half*>(op.Y)[gc.r0 + i] = __float2half_rn(v);
+        }
+    }
+    if (failed) {
+        // let copies that are still in flight land before the CTA's shared memory is released
+        for (int i = 0; i < inflight; ++i) {
+            (void)mbar_wait_bounded(&bars[warp * ns + cslot], cphase);
+            if (++cslot == ns) { cslot = 0; cphase ^= 1u; }
+        }
     }
 }
 
@@ -704,6 +927,8 @@ StreamPlan plan_stream(const GemvQArgs& a, int mb, bool stage_f32, const LaunchE
     p.y_f32 = a.y_f32 ? 1 : 0; p.eps = a.eps;
     p.off_rowacc = off_rowacc; p.off_sx = off_sx; p.off_x = off_x; p.off_ring = off_ring;
     p.max_rows = max_rows;
+    static const int dbg_skip = [] { const char* v = std::getenv("TC_GEMV_DBG_SKIP"); return v ? std::atoi(v) : 0; }();
+    p.dbg_skip = dbg_skip;
     return pl;
 }
 
@@ -725,8 +950,12 @@ cudaError_t set_smem(K kernel, int bytes) {
 
 }  // namespace
 
+cudaError_t init_decode_kernel(int smem_optin);
+
 cudaError_t init_gemv_kernels(int smem_optin) {
     cudaError_t e = init_mma_kernels(smem_optin);
+    if (e != cudaSuccess) return e;
+    e = init_decode_kernel(smem_optin);
     if (e != cudaSuccess) return e;
 #define TCB_SET(FMT, XF, MB)                                                      \
     e = set_smem(gemv_q_stream_kernel<FMT, XF, MB>, smem_optin);                  \
@@ -802,6 +1031,59 @@ cudaError_t launch_gemv_q(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t
     if (launches) *launches += count;
     if (name) *name = used;
     return err;
+}
+
+
+cudaError_t init_decode_kernel(int smem_optin) {
+    return cudaFuncSetAttribute(gemv_q4_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                smem_optin);
+}
+
+cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops, int n_ops,
+                                  unsigned long long* counter, unsigned long long base,
+                                  const LaunchEnv& env, cudaStream_t stream, int* barriers) {
+    if (n_ops <= 0) return cudaErrorInvalidValue;
+    int k_max = 0, n_max = 0, nbar = 0;
+    bool any_f32 = false;
+    for (int i = 0; i < n_ops; ++i) {
+        k_max = host_ops[i].K > k_max ? host_ops[i].K : k_max;
+        n_max = host_ops[i].N > n_max ? host_ops[i].N : n_max;
+        if (host_ops[i].flags & (MOP_X_F32 | MOP_FUSED)) any_f32 = true;
+        if (host_ops[i].flags & MOP_BARRIER) ++nbar;
+    }
+    static const int want_warps = [] {
+        const char* v = std::getenv("TC_MEGA_WARPS");
+        const int n = v ? std::atoi(v) : 16;
+        return (n == 8 || n == 16) ? n : 16;
+    }();
+    const int grid = env.sm_count;
+    const int max_rows = (n_max + grid - 1) / grid + 1;
+    const int optin = env.smem_optin > 0 ? env.smem_optin : 232448;
+    MegaParams p;
+    p.ops = dev_ops; p.n_ops = n_ops; p.counter = counter; p.base = base; p.err = env.err_word;
+    static const int dbg_skip = [] { const char* v = std::getenv("TC_GEMV_DBG_SKIP"); return v ? std::atoi(v) : 0; }();
+    p.dbg_skip = dbg_skip;
+    int off = 8 * kMaxStreamWarps * 4 + 8 * kMaxStreamWarps + 16;   // barriers, scratch, abort flag
+    off = align_up(off, 16);
+    p.off_rowacc = off;
+    off += align_up(max_rows * 4, 16);
+    p.off_sx = off;
+    off += align_up((k_max / 32) * 4, 16);
+    p.off_x = off;
+    off += align_up(k_max * (any_f32 ? 4 : 2), 128);
+    p.off_ring = off;
+    int warps = want_warps, ns = 0;
+    for (; warps >= 8 && ns == 0; warps -= 8)
+        for (int cand = 4; cand >= 2; --cand)
+            if (off + warps * cand * 4608 <= optin - 1024) { ns = cand; break; }
+    if (ns == 0) return cudaErrorNotSupported;
+    warps += 8;   // undo the loop's last decrement
+    p.ns = ns;
+    const size_t smem = static_cast<size_t>(off) + static_cast<size_t>(warps) * ns * 4608;
+    void* args[] = {&p};
+    if (barriers) *barriers = nbar;
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(gemv_q4_decode_kernel),
+                                       dim3(grid), dim3(warps * 32), args, smem, stream);
 }
 
 }  // namespace tcb

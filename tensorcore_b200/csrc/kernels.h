@@ -46,6 +46,35 @@ struct DenseNormGemvArgs {
     float eps = 0.f;
 };
 
+// One operation of a persistent decode launch (Q4_0, M = 1); 64 bytes, read by the device.
+struct MegaOp {
+    const uint8_t* W;
+    const void* X;
+    void* Y;
+    const void* gamma;
+    int N, K;
+    uint32_t flags;
+    float eps;
+    int pad[4];
+};
+enum : uint32_t {
+    MOP_BARRIER = 1u,   // grid-wide barrier before this operation (it depends on earlier output)
+    MOP_X_F32 = 2u,     // activations (and gamma) are fp32
+    MOP_Y_F32 = 4u,     // result is fp32
+    MOP_FUSED = 8u,     // RMSNorm prologue with gamma
+    MOP_RESTAGE = 16u,  // (re)load the activations into shared memory for this operation
+};
+struct MegaParams {
+    const MegaOp* ops;              // device memory
+    int n_ops;
+    unsigned long long* counter;    // device memory: grid barrier arrivals, never reset
+    unsigned long long base;        // counter value all earlier launches add up to
+    uint32_t* err;
+    int ns;
+    int off_rowacc, off_sx, off_x, off_ring;
+    int dbg_skip;                   // measurement aid: stream and synchronise, skip arithmetic
+};
+
 // Error bits ORed into LaunchEnv::err_word by kernels.
 enum : uint32_t { ERR_WAIT_TIMEOUT = 1u, ERR_BAD_SHAPE = 2u };
 
@@ -58,6 +87,13 @@ cudaError_t launch_gemv_q(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t
                           int* launches, const char** name);
 cudaError_t launch_dense_norm_gemv(const DenseNormGemvArgs& a, const LaunchEnv& env,
                                    cudaStream_t stream, int* launches, const char** name);
+
+// Persistent decode launch of `n_ops` operations described by `host_ops` (already uploaded to
+// `dev_ops`).  Returns cudaErrorNotSupported when the list does not fit the kernel's shared
+// memory.  *barriers receives the number of grid barriers the launch executes.
+cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops, int n_ops,
+                                  unsigned long long* counter, unsigned long long base,
+                                  const LaunchEnv& env, cudaStream_t stream, int* barriers);
 
 // One-time per-device kernel attribute setup (max dynamic shared memory).
 cudaError_t init_kernels_for_device(int smem_optin);

@@ -50,6 +50,14 @@ struct tc_context {
     cudaStream_t stream0;
     uint32_t* err_host;   // pinned, mapped
     uint32_t* err_dev;
+    // scratch of the persistent decode launch: operation table (pinned staging + device copy)
+    // and the grid-barrier arrival counter
+    bool mega_on;
+    tcb::MegaOp* mega_host;
+    tcb::MegaOp* mega_dev;
+    unsigned long long* mega_counter;
+    unsigned long long mega_base;
+    int mega_uploaded;    // number of table entries currently valid on the device
 };
 
 struct tc_buffer {
@@ -237,6 +245,14 @@ tc_status_t setup_device(tc_context* ctx, int device) {
 void teardown_device(tc_context* ctx) {
     if (ctx->stream0) cudaStreamDestroy(ctx->stream0);
     if (ctx->err_host) cudaFreeHost(ctx->err_host);
+    if (ctx->mega_host) cudaFreeHost(ctx->mega_host);
+    if (ctx->mega_dev) cudaFree(ctx->mega_dev);
+    if (ctx->mega_counter) cudaFree(ctx->mega_counter);
+    ctx->mega_host = nullptr;
+    ctx->mega_dev = nullptr;
+    ctx->mega_counter = nullptr;
+    ctx->mega_base = 0;
+    ctx->mega_uploaded = 0;
     ctx->stream0 = nullptr;
     ctx->err_host = nullptr;
     ctx->err_dev = nullptr;
@@ -322,6 +338,12 @@ extern "C" tc_status_t tc_init(tc_context** out_ctx) {
     ctx->err_host = nullptr;
     ctx->err_dev = nullptr;
     if (const char* v = std::getenv("TC_GEMV_VARIANT")) (void)tcx_set_gemv_variant(v);
+    ctx->mega_on = env_flag("TC_MEGA", true);
+    ctx->mega_host = nullptr;
+    ctx->mega_dev = nullptr;
+    ctx->mega_counter = nullptr;
+    ctx->mega_base = 0;
+    ctx->mega_uploaded = 0;
     ctx->pdl = env_flag("TC_PDL", true);
     ctx->graphs = env_flag("TC_STREAM_GRAPH", true);
     const tc_status_t st = setup_device(ctx, device);
@@ -623,6 +645,103 @@ cudaError_t launch_recorded(tc_context* ctx, const RecordedOp& op, cudaStream_t 
     return tcb::launch_gemv_q(op.a, env, st, launches, name);
 }
 
+constexpr int kMegaMaxOps = 1024;
+
+struct Range { uintptr_t lo, hi; };
+bool overlaps(const std::vector<Range>& v, Range r) {
+    for (const Range& q : v)
+        if (r.lo < q.hi && q.lo < r.hi) return true;
+    return false;
+}
+
+// Tries to run the whole recorded list as ONE persistent launch (Q4_0, M = 1 lists: a decode
+// token).  Returns cudaErrorNotSupported when the list does not qualify; nothing has been
+// enqueued in that case.
+cudaError_t submit_as_persistent_launch(tc_stream* s, int* launches, const char** name) {
+    tc_context* ctx = s->owner;
+    const size_t n = s->pending.size();
+    if (!ctx->mega_on || n < 2 || n > static_cast<size_t>(kMegaMaxOps)) return cudaErrorNotSupported;
+    for (const RecordedOp& op : s->pending) {
+        const tcb::GemvQArgs& a = op.a;
+        if (op.kind != OP_GEMV_Q || a.fmt != tcb::FMT_Q4_0 || a.M != 1 || a.K % 256 != 0)
+            return cudaErrorNotSupported;
+        if ((reinterpret_cast<uintptr_t>(a.W) | reinterpret_cast<uintptr_t>(a.X) |
+             reinterpret_cast<uintptr_t>(a.gamma)) & 15u)
+            return cudaErrorNotSupported;
+    }
+    if (!ctx->mega_host) {
+        if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->mega_host), kMegaMaxOps * sizeof(tcb::MegaOp),
+                          cudaHostAllocDefault) != cudaSuccess ||
+            cudaMalloc(reinterpret_cast<void**>(&ctx->mega_dev), kMegaMaxOps * sizeof(tcb::MegaOp)) != cudaSuccess ||
+            cudaMalloc(reinterpret_cast<void**>(&ctx->mega_counter), sizeof(unsigned long long)) != cudaSuccess ||
+            cudaMemset(ctx->mega_counter, 0, sizeof(unsigned long long)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            ctx->mega_on = false;
+            return cudaErrorNotSupported;
+        }
+        ctx->mega_base = 0;
+        ctx->mega_uploaded = 0;
+    }
+    // Build the table.  An operation gets a grid barrier when it reads something an operation
+    // since the last barrier wrote, or writes something one of them read or wrote.
+    std::vector<tcb::MegaOp> table(n);
+    std::vector<Range> reads, writes;
+    for (size_t i = 0; i < n; ++i) {
+        const tcb::GemvQArgs& a = s->pending[i].a;
+        const size_t xs = a.x_f32 ? 4 : 2, ys = a.y_f32 ? 4 : 2;
+        const Range rx{reinterpret_cast<uintptr_t>(a.X), reinterpret_cast<uintptr_t>(a.X) + a.K * xs};
+        const Range rg{reinterpret_cast<uintptr_t>(a.gamma),
+                       reinterpret_cast<uintptr_t>(a.gamma) + (a.gamma ? a.K * xs : 0)};
+        const Range ry{reinterpret_cast<uintptr_t>(a.Y), reinterpret_cast<uintptr_t>(a.Y) + a.N * ys};
+        const Range rw{reinterpret_cast<uintptr_t>(a.W),
+                       reinterpret_cast<uintptr_t>(a.W) + s->pending[i].w_bytes};
+        bool barrier = overlaps(writes, rx) || overlaps(writes, rg) || overlaps(writes, rw) ||
+                       overlaps(writes, ry) || overlaps(reads, ry);
+        if (i == 0) barrier = false;
+        if (barrier) { reads.clear(); writes.clear(); }
+        reads.push_back(rx);
+        if (a.gamma) reads.push_back(rg);
+        reads.push_back(rw);
+        writes.push_back(ry);
+        tcb::MegaOp& m = table[i];
+        std::memset(&m, 0, sizeof(m));
+        m.W = a.W; m.X = a.X; m.Y = a.Y; m.gamma = a.gamma; m.N = a.N; m.K = a.K; m.eps = a.eps;
+        m.flags = (barrier ? tcb::MOP_BARRIER : 0u) | (a.x_f32 ? tcb::MOP_X_F32 : 0u) |
+                  (a.y_f32 ? tcb::MOP_Y_F32 : 0u) | (a.gamma ? tcb::MOP_FUSED : 0u);
+        bool restage = true;
+        if (i > 0 && !barrier) {
+            const tcb::GemvQArgs& b = s->pending[i - 1].a;
+            restage = !(b.X == a.X && b.gamma == a.gamma && b.K == a.K && b.x_f32 == a.x_f32);
+        }
+        if (restage) m.flags |= tcb::MOP_RESTAGE;
+    }
+    const bool same = ctx->mega_uploaded == static_cast<int>(n) &&
+                      std::memcmp(ctx->mega_host, table.data(), n * sizeof(tcb::MegaOp)) == 0;
+    cudaError_t e = cudaSuccess;
+    if (!same) {
+        // the pinned staging copy may still be read by an earlier upload on this stream
+        e = cudaStreamSynchronize(s->s);
+        if (e != cudaSuccess) return e;
+        std::memcpy(ctx->mega_host, table.data(), n * sizeof(tcb::MegaOp));
+        e = cudaMemcpyAsync(ctx->mega_dev, ctx->mega_host, n * sizeof(tcb::MegaOp),
+                            cudaMemcpyHostToDevice, s->s);
+        if (e != cudaSuccess) return e;
+        ctx->mega_uploaded = static_cast<int>(n);
+    }
+    int barriers = 0;
+    e = tcb::launch_gemv_q4_decode(ctx->mega_host, ctx->mega_dev, static_cast<int>(n),
+                                   ctx->mega_counter, ctx->mega_base, make_env(ctx, false), s->s,
+                                   &barriers);
+    if (e == cudaErrorCooperativeLaunchTooLarge) { (void)cudaGetLastError(); return cudaErrorNotSupported; }
+    if (e == cudaErrorNotSupported) return e;
+    if (e == cudaSuccess) {
+        ctx->mega_base += static_cast<unsigned long long>(barriers) * ctx->sm_count;
+        *launches += 1;
+        *name = "q4_0_decode_persistent_sm100";
+    }
+    return e;
+}
+
 // Submits the recorded operations.  Lists without host-staged buffers are replayed as a CUDA
 // graph from the second time the identical list (same kernels, pointers and shapes) is seen;
 // the first submission of a list, and lists that need staging copies, launch directly.
@@ -655,7 +774,13 @@ tc_status_t submit_pending(tc_stream* s) {
     const char* name = t_last_kernel;
     int launches = 0;
     bool done = false;
-    if (ctx->graphs && !any_staged && s->pending.size() > 1) {
+    if (!any_staged) {
+        const cudaError_t me = submit_as_persistent_launch(s, &launches, &name);
+        if (me == cudaSuccess) done = true;
+        else if (me != cudaErrorNotSupported) e = me;
+        else (void)cudaGetLastError();
+    }
+    if (!done && e == cudaSuccess && ctx->graphs && !any_staged && s->pending.size() > 1) {
         CachedGraph& cg = s->cache[sig];
         if (cg.exec) {
             e = cudaGraphLaunch(cg.exec, s->s);
@@ -722,6 +847,11 @@ extern "C" tc_status_t tc_stream_sync(tc_stream* s) {
     const cudaError_t e = cudaStreamSynchronize(s->s);
     if (st == TC_OK) st = from_cuda(e, TC_ERR_DISPATCH);
     if (st == TC_OK) st = check_device_error(s->owner);
+    if (st != TC_OK && s->owner->mega_counter) {
+        // an aborted persistent launch leaves the barrier counter at an arbitrary value
+        cudaMemset(s->owner->mega_counter, 0, sizeof(unsigned long long));
+        s->owner->mega_base = 0;
+    }
     return st;
 }
 

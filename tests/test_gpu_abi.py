@@ -137,7 +137,8 @@ def test_async_stream_records_and_replays(tc, ctx, oracle):
             assert oracle.scaled_rms(o, w) <= 1e-4
         if first is None:
             first = outs
-    assert tc.launch_count() - launches0 == 5 * len(Ns)
+    # one kernel per GEMV, or one persistent launch per synchronisation for a qualifying list
+    assert tc.launch_count() - launches0 in (5 * len(Ns), 5)
     assert tc.take_device_error(ctx) == 0
     # a dependent chain on one stream: y of one GEMV is x of the next
     Wa = oracle.quantize_weights((rng.standard_normal((K, K)) * 0.05).astype(np.float16), 0)

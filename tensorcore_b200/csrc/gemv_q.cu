@@ -570,6 +570,9 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q_stream_kernel(con
 // the staged activations.  Activations written earlier in the same launch are read with
 // L2-coherent loads.
 // ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_release_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
     unsigned long long v;
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -677,6 +680,10 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
         // reads another CTA's output, everyone in the grid must be done with the previous one.
         __syncthreads();
         if (op.flags & MOP_BARRIER) {
+            // One 64-bit arrival counter that is never reset: barrier j of this launch is
+            // complete when it reaches base + (j+1) * gridDim.  One thread per CTA arrives
+            // (release) and polls (acquire); the wait is bounded.  (Measured alternatives - a
+            // separately published generation word, per-CTA flag words, back-off - were slower.)
             target += gridDim.x;
             if (tid == 0) {
                 __threadfence();

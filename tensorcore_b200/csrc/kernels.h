@@ -67,7 +67,7 @@ enum : uint32_t {
 struct MegaParams {
     const MegaOp* ops;              // device memory
     int n_ops;
-    unsigned long long* counter;    // device memory: grid barrier arrivals, never reset
+    unsigned long long* counter;    // device memory: grid-barrier arrival counter, never reset
     unsigned long long base;        // counter value all earlier launches add up to
     uint32_t* err;
     int ns;

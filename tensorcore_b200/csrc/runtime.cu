@@ -646,6 +646,7 @@ cudaError_t launch_recorded(tc_context* ctx, const RecordedOp& op, cudaStream_t 
 }
 
 constexpr int kMegaMaxOps = 1024;
+constexpr size_t kMegaFlagBytes = 256;   // arrival counter and published generation, 128 B apart
 
 struct Range { uintptr_t lo, hi; };
 bool overlaps(const std::vector<Range>& v, Range r) {
@@ -673,8 +674,8 @@ cudaError_t submit_as_persistent_launch(tc_stream* s, int* launches, const char*
         if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->mega_host), kMegaMaxOps * sizeof(tcb::MegaOp),
                           cudaHostAllocDefault) != cudaSuccess ||
             cudaMalloc(reinterpret_cast<void**>(&ctx->mega_dev), kMegaMaxOps * sizeof(tcb::MegaOp)) != cudaSuccess ||
-            cudaMalloc(reinterpret_cast<void**>(&ctx->mega_counter), sizeof(unsigned long long)) != cudaSuccess ||
-            cudaMemset(ctx->mega_counter, 0, sizeof(unsigned long long)) != cudaSuccess) {
+            cudaMalloc(reinterpret_cast<void**>(&ctx->mega_counter), kMegaFlagBytes) != cudaSuccess ||
+            cudaMemset(ctx->mega_counter, 0, kMegaFlagBytes) != cudaSuccess) {
             (void)cudaGetLastError();
             ctx->mega_on = false;
             return cudaErrorNotSupported;
@@ -849,7 +850,7 @@ extern "C" tc_status_t tc_stream_sync(tc_stream* s) {
     if (st == TC_OK) st = check_device_error(s->owner);
     if (st != TC_OK && s->owner->mega_counter) {
         // an aborted persistent launch leaves the barrier counter at an arbitrary value
-        cudaMemset(s->owner->mega_counter, 0, sizeof(unsigned long long));
+        cudaMemset(s->owner->mega_counter, 0, kMegaFlagBytes);
         s->owner->mega_base = 0;
     }
     return st;

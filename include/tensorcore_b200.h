@@ -333,6 +333,40 @@ tc_status_t tcx_raw_fused_norm_gemv_f16(tc_context* ctx, const void* X, const vo
                                         void* Y, int M, int N, int K, float eps,
                                         void* cuda_stream);
 
+/* Decode launch that allocates nothing (no counterpart in the reference).
+ *
+ * Runs a whole list of Q4_0, batch-1 GEMVs - one decode step - as one persistent kernel, like a
+ * qualifying tc_stream list, but for callers that cannot tolerate an allocation on this path:
+ * a server whose HBM is fully handed out to weights and KV cache at start-up, or a decode loop
+ * where cudaMalloc's device-wide synchronisation must never occur.  The kernel's scratch (the
+ * operation table and its grid-barrier counter) lives in a fixed 16.25 KB device array inside the
+ * library image, which every GPU that loads the library holds until the process exits; the call
+ * performs no cudaMalloc / cudaFree and uses no allocating library routine.
+ *
+ *  - `ops`: host array of `n_ops` operations in execution order; all pointers inside are device
+ *    addresses owned by the caller (inputs and outputs as for tcx_raw_gemv_quantized with M = 1;
+ *    gamma != NULL adds the RMSNorm prologue).  K must be a multiple of 256, pointers 16-byte
+ *    aligned.  Dependencies between operations are derived from pointer overlap.
+ *  - Limit: n_ops <= TCX_DECODE_STATIC_MAX_OPS (256); more returns TC_ERR_INVALID_SHAPE, as does
+ *    a list whose activations do not fit the kernel's shared memory.
+ *  - The first call on a device looks up the array's device address; make that first call before
+ *    starting any stream capture.
+ *  - All calls on a device share the one array: the call clears the counter and overwrites the
+ *    table itself, but two calls that overlap in time on the GPU (different streams) race.
+ *  - Asynchronous on `cuda_stream`, like the other tcx_raw_* launches. */
+typedef struct {
+    const void* W;        /* Q4_0 blocks, [N][K/32] x 18 bytes */
+    const void* X;        /* [K] activations */
+    void* Y;              /* [N] results */
+    const void* gamma;    /* [K] RMSNorm weights (activation dtype) or NULL */
+    int N, K;
+    tc_dtype_t x_dtype, y_dtype;   /* TC_DTYPE_F16 or TC_DTYPE_F32 */
+    float eps;
+} tcx_decode_op;
+#define TCX_DECODE_STATIC_MAX_OPS 256
+tc_status_t tcx_raw_decode_q4_static(tc_context* ctx, const tcx_decode_op* ops, int n_ops,
+                                     void* cuda_stream);
+
 /* Kernel-variant override for A/B measurements: "auto" (default), "simt", "mma", "tc",
  * "generic".  Returns TC_ERR_INVALID_ARG for an unknown name.  Process-wide. */
 tc_status_t tcx_set_gemv_variant(const char* name);

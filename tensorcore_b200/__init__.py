@@ -87,6 +87,15 @@ class TCGGufQuantizedMatrixInfo(Structure):
                 ("n_bytes", c_size_t), ("buffer", c_void_p)]
 
 
+class TCXDecodeOp(Structure):
+    _fields_ = [("W", c_void_p), ("X", c_void_p), ("Y", c_void_p), ("gamma", c_void_p),
+                ("N", c_int), ("K", c_int), ("x_dtype", c_int), ("y_dtype", c_int),
+                ("eps", c_float)]
+
+
+DECODE_STATIC_MAX_OPS = 256
+
+
 class TensorcoreError(RuntimeError):
     def __init__(self, status: int):
         self.status = int(status)
@@ -183,6 +192,7 @@ def _declare(L) -> None:
     sig("tcx_raw_gemv_quantized", i, vp, vp, vp, vp, i, i, i, i, i, i, vp)
     sig("tcx_raw_fused_rmsnorm_gemv_quantized", i, vp, vp, vp, vp, vp, i, i, i, i, f, i, i, vp)
     sig("tcx_raw_fused_norm_gemv_f16", i, vp, vp, vp, vp, vp, vp, i, i, i, f, vp)
+    sig("tcx_raw_decode_q4_static", i, vp, POINTER(TCXDecodeOp), i, vp)
     sig("tcx_set_gemv_variant", i, c_char_p)
     sig("tcx_take_device_error", c_uint32, vp)
     sig("tcx_launch_count", c_uint64)
@@ -428,6 +438,20 @@ def raw_fused_norm_gemv_f16(ctx, X_ptr, gamma_ptr, beta_ptr, W_ptr, Y_ptr, M, N,
         _h(ctx), c_void_p(X_ptr), c_void_p(gamma_ptr), c_void_p(beta_ptr) if beta_ptr else None,
         c_void_p(W_ptr), c_void_p(Y_ptr), int(M), int(N), int(K), float(eps),
         c_void_p(cuda_stream)))
+
+
+def raw_decode_q4_static(ctx, ops, cuda_stream=0) -> None:
+    """ops: list of dicts with device addresses W, X, Y, optional gamma, and N, K, x_dtype,
+    y_dtype, eps - one decode step as one persistent launch whose scratch is a static device
+    array (no allocation; at most DECODE_STATIC_MAX_OPS operations)."""
+    arr = (TCXDecodeOp * len(ops))()
+    for i, o in enumerate(ops):
+        arr[i].W, arr[i].X, arr[i].Y = o["W"], o["X"], o["Y"]
+        arr[i].gamma = o.get("gamma") or None
+        arr[i].N, arr[i].K = int(o["N"]), int(o["K"])
+        arr[i].x_dtype, arr[i].y_dtype = _dtype(o.get("x_dtype", "f16")), _dtype(o.get("y_dtype", "f16"))
+        arr[i].eps = float(o.get("eps", 1e-5))
+    _check(lib().tcx_raw_decode_q4_static(_h(ctx), arr, len(ops), c_void_p(cuda_stream)))
 
 
 def set_gemv_variant(name: str) -> None:

@@ -1093,4 +1093,109 @@ cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops,
                                        dim3(grid), dim3(warps * 32), args, smem, stream);
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Decode launch for callers that must not allocate.
+//
+// The persistent decode kernel needs two pieces of scratch in global memory: the operation table
+// the CTAs walk and the arrival counter of its grid barrier.  The library normally keeps them in
+// buffers it allocates on first use.  Some callers cannot have that: an inference server that
+// has handed every byte of HBM to weights and KV cache at start-up, or a decode loop in which a
+// cudaMalloc (which synchronises the whole device) is not acceptable at any point.  For them the
+// same kernel is reachable with its scratch in the fixed array below, which is part of the
+// library image on every GPU that loads it (16.25 KB) and is never freed.
+//
+// Layout: bytes [0,256) arrival counter (first 8 bytes used), bytes [256, 256 + 256*64) the
+// operation table, hence at most kStaticMaxOps operations per call.
+// ---------------------------------------------------------------------------------------
+constexpr int kStaticMaxOps = 256;
+static __device__ __align__(256) unsigned char g_decode_static_scratch[256 + kStaticMaxOps * sizeof(MegaOp)];
+
+namespace {
+constexpr int kMaxDevices = 64;
+unsigned char* g_static_scratch_addr[kMaxDevices] = {nullptr};
+
+// The array's name is only a handle on the host; kernels need its device address, which differs
+// per device and is looked up once per device with that device current.
+cudaError_t static_scratch_for_current_device(unsigned char** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
+        if (e != cudaSuccess) return e;
+        g_static_scratch_addr[dev] = static_cast<unsigned char*>(ptr);
+    }
+    *out = g_static_scratch_addr[dev];
+    return cudaSuccess;
+}
+}  // namespace
+
+// ops: host array of n_ops operations in execution order (GemvQArgs with M == 1, Q4_0).  Builds
+// the table on the stack (dependencies from pointer overlap, as the stream path does), copies it
+// into the static scratch, clears the arrival counter and launches.  No allocation of any kind.
+cudaError_t launch_gemv_q4_decode_static(const GemvQArgs* ops, int n_ops, const LaunchEnv& env,
+                                         cudaStream_t stream) {
+    if (n_ops <= 0 || n_ops > kStaticMaxOps) return cudaErrorInvalidValue;
+    MegaOp table[kStaticMaxOps];
+    struct Span { uintptr_t lo, hi; };
+    Span reads[3 * kStaticMaxOps], writes[kStaticMaxOps];
+    int n_reads = 0, n_writes = 0;
+    auto hit = [](const Span* v, int n, Span r) {
+        for (int i = 0; i < n; ++i)
+            if (r.lo < v[i].hi && v[i].lo < r.hi) return true;
+        return false;
+    };
+    for (int i = 0; i < n_ops; ++i) {
+        const GemvQArgs& a = ops[i];
+        if (a.fmt != FMT_Q4_0 || a.M != 1 || a.N <= 0 || a.K <= 0 || a.K % 256 != 0 || !a.W || !a.X || !a.Y)
+            return cudaErrorInvalidValue;
+        if ((reinterpret_cast<uintptr_t>(a.W) | reinterpret_cast<uintptr_t>(a.X) |
+             reinterpret_cast<uintptr_t>(a.gamma)) & 15u)
+            return cudaErrorInvalidValue;
+        const size_t xs = a.x_f32 ? 4 : 2, ys = a.y_f32 ? 4 : 2;
+        const Span rx{reinterpret_cast<uintptr_t>(a.X), reinterpret_cast<uintptr_t>(a.X) + a.K * xs};
+        const Span rg{reinterpret_cast<uintptr_t>(a.gamma),
+                      reinterpret_cast<uintptr_t>(a.gamma) + (a.gamma ? a.K * xs : 0)};
+        const Span rw{reinterpret_cast<uintptr_t>(a.W),
+                      reinterpret_cast<uintptr_t>(a.W) + static_cast<size_t>(a.N) * (a.K / 32) * 18};
+        const Span ry{reinterpret_cast<uintptr_t>(a.Y), reinterpret_cast<uintptr_t>(a.Y) + a.N * ys};
+        bool barrier = i > 0 && (hit(writes, n_writes, rx) || hit(writes, n_writes, rg) ||
+                                 hit(writes, n_writes, rw) || hit(writes, n_writes, ry) ||
+                                 hit(reads, n_reads, ry));
+        if (barrier) { n_reads = 0; n_writes = 0; }
+        reads[n_reads++] = rx;
+        if (a.gamma) reads[n_reads++] = rg;
+        reads[n_reads++] = rw;
+        writes[n_writes++] = ry;
+        MegaOp& m = table[i];
+        m.W = a.W; m.X = a.X; m.Y = a.Y; m.gamma = a.gamma; m.N = a.N; m.K = a.K; m.eps = a.eps;
+        m.pad[0] = m.pad[1] = m.pad[2] = m.pad[3] = 0;
+        m.flags = (barrier ? MOP_BARRIER : 0u) | (a.x_f32 ? MOP_X_F32 : 0u) |
+                  (a.y_f32 ? MOP_Y_F32 : 0u) | (a.gamma ? MOP_FUSED : 0u);
+        bool restage = true;
+        if (i > 0 && !barrier) {
+            const GemvQArgs& b = ops[i - 1];
+            restage = !(b.X == a.X && b.gamma == a.gamma && b.K == a.K && b.x_f32 == a.x_f32);
+        }
+        if (restage) m.flags |= MOP_RESTAGE;
+    }
+    unsigned char* scratch = nullptr;
+    cudaError_t e = static_scratch_for_current_device(&scratch);
+    if (e != cudaSuccess) return e;
+    // The array keeps whatever the previous call left: the counter must start from zero, the
+    // table is overwritten.  (The host table lives on this stack frame: the copy from pageable
+    // memory has consumed it when cudaMemcpyAsync returns.)
+    e = cudaMemsetAsync(scratch, 0, 256, stream);
+    if (e != cudaSuccess) return e;
+    e = cudaMemcpyAsync(scratch + 256, table, static_cast<size_t>(n_ops) * sizeof(MegaOp),
+                        cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return e;
+    return launch_gemv_q4_decode(table, reinterpret_cast<const MegaOp*>(scratch + 256), n_ops,
+                                 reinterpret_cast<unsigned long long*>(scratch), 0ULL, env, stream,
+                                 nullptr);
+}
+
 }  // namespace tcb

@@ -95,6 +95,12 @@ cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops,
                                   unsigned long long* counter, unsigned long long base,
                                   const LaunchEnv& env, cudaStream_t stream, int* barriers);
 
+// The same launch with its scratch (operation table, barrier counter) in a static device array:
+// no allocation.  At most 256 operations; cudaErrorInvalidValue beyond that or for operations
+// outside the kernel's domain.  First use on a device looks up the array's device address.
+cudaError_t launch_gemv_q4_decode_static(const GemvQArgs* ops, int n_ops, const LaunchEnv& env,
+                                         cudaStream_t stream);
+
 // One-time per-device kernel attribute setup (max dynamic shared memory).
 cudaError_t init_kernels_for_device(int smem_optin);
 

@@ -1176,6 +1176,47 @@ extern "C" tc_status_t tcx_raw_fused_norm_gemv_f16(tc_context* ctx, const void* 
 }
 
 // ---------------------------------------------------------------------------------------
+// Decode launch without allocation (see include/tensorcore_b200.h)
+// ---------------------------------------------------------------------------------------
+extern "C" tc_status_t tcx_raw_decode_q4_static(tc_context* ctx, const tcx_decode_op* ops,
+                                                int n_ops, void* cuda_stream) {
+    if (!ctx) return TC_ERR_NOT_INITIALIZED;
+    if (!ops || n_ops <= 0) return TC_ERR_INVALID_ARG;
+    if (n_ops > TCX_DECODE_STATIC_MAX_OPS) {
+        if (trace_enabled())
+            std::fprintf(stderr, "[tensorcore] tcx_raw_decode_q4_static: %d operations exceed the "
+                         "static scratch capacity of %d\n", n_ops, TCX_DECODE_STATIC_MAX_OPS);
+        return TC_ERR_INVALID_SHAPE;
+    }
+    tcb::GemvQArgs args[TCX_DECODE_STATIC_MAX_OPS];
+    for (int i = 0; i < n_ops; ++i) {
+        const tcx_decode_op& o = ops[i];
+        if (!o.W || !o.X || !o.Y || o.N <= 0 || o.K <= 0 || o.K % 32 != 0) return TC_ERR_INVALID_ARG;
+        if ((o.x_dtype != TC_DTYPE_F16 && o.x_dtype != TC_DTYPE_F32) ||
+            (o.y_dtype != TC_DTYPE_F16 && o.y_dtype != TC_DTYPE_F32))
+            return TC_ERR_UNSUPPORTED_DTYPE;
+        if (o.K % 256 != 0) return TC_ERR_INVALID_SHAPE;   // the persistent kernel's domain
+        tcb::GemvQArgs& a = args[i];
+        a.W = static_cast<const uint8_t*>(o.W);
+        a.X = o.X; a.Y = o.Y; a.gamma = o.gamma;
+        a.fmt = tcb::FMT_Q4_0; a.M = 1; a.N = o.N; a.K = o.K;
+        a.x_f32 = o.x_dtype == TC_DTYPE_F32; a.y_f32 = o.y_dtype == TC_DTYPE_F32; a.eps = o.eps;
+    }
+    bind_device(ctx);
+    const cudaError_t e = tcb::launch_gemv_q4_decode_static(args, n_ops, make_env(ctx, false),
+                                                            static_cast<cudaStream_t>(cuda_stream));
+    if (e == cudaErrorInvalidValue || e == cudaErrorNotSupported) {
+        (void)cudaGetLastError();
+        return TC_ERR_INVALID_SHAPE;
+    }
+    if (e == cudaSuccess) {
+        g_launches.fetch_add(1);
+        t_last_kernel = "q4_0_decode_persistent_static_sm100";
+    }
+    return record("tcx_raw_decode_q4_static", from_cuda(e, TC_ERR_DISPATCH));
+}
+
+// ---------------------------------------------------------------------------------------
 // Diagnostics
 // ---------------------------------------------------------------------------------------
 extern "C" tc_status_t tcx_set_gemv_variant(const char* name) {

@@ -35,6 +35,9 @@ namespace tcb {
 cudaError_t init_mma_kernels(int smem_optin);
 cudaError_t launch_gemv_q4_mma(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t stream,
                                const char** name);
+cudaError_t init_tc_kernels(int smem_optin);
+cudaError_t launch_gemv_q4_tc(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t stream,
+                              const char** name);
 namespace {
 
 constexpr int kWarps = 8;               // generic kernel
@@ -43,6 +46,7 @@ constexpr int kMaxStreamWarps = 16;     // streaming kernel: 8 or 16 warps, chos
 constexpr int kMaxStreamThreads = kMaxStreamWarps * 32;
 constexpr int kGroupBlocks = 8;
 constexpr int kMaxMB = 4;
+constexpr int kTcMinBatch = 1 << 30;     // smallest M the tcgen05 kernel takes by default
 
 template <int FMT> struct Fmt;
 template <> struct Fmt<FMT_Q4_0> {
@@ -962,6 +966,8 @@ cudaError_t init_decode_kernel(int smem_optin);
 cudaError_t init_gemv_kernels(int smem_optin) {
     cudaError_t e = init_mma_kernels(smem_optin);
     if (e != cudaSuccess) return e;
+    e = init_tc_kernels(smem_optin);
+    if (e != cudaSuccess) return e;
     e = init_decode_kernel(smem_optin);
     if (e != cudaSuccess) return e;
 #define TCB_SET(FMT, XF, MB)                                                      \
@@ -984,6 +990,29 @@ cudaError_t launch_gemv_q(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t
     const bool fuse = a.gamma != nullptr;
     // The RMSNorm prologue keeps the normalised row in fp32, whatever the activation type.
     const bool stage_f32 = a.x_f32 || fuse;
+
+    // Batched decode: the tcgen05 kernel reads the weights once for up to 32 activation rows.
+    // It rounds dequantised weights to fp16, which only the fp16-activation bound allows.
+    const bool want_tc = env.variant == VARIANT_TC ||
+                         (env.variant == VARIANT_AUTO && a.M >= kTcMinBatch);
+    if (want_tc && a.fmt == FMT_Q4_0 && !a.x_f32 && !fuse) {
+        bool done = true;
+        for (int m0 = 0; m0 < a.M; m0 += 32) {
+            GemvQArgs s = a;
+            s.M = (a.M - m0) < 32 ? (a.M - m0) : 32;
+            s.X = static_cast<const uint8_t*>(a.X) + static_cast<size_t>(m0) * a.K * xsz;
+            s.Y = static_cast<uint8_t*>(a.Y) + static_cast<size_t>(m0) * a.N * ysz;
+            const cudaError_t te = launch_gemv_q4_tc(s, env, stream, &used);
+            if (te == cudaErrorNotSupported && m0 == 0) { done = false; break; }
+            if (te != cudaSuccess) { err = te; break; }
+            ++count;
+        }
+        if (done) {
+            if (launches) *launches += count;
+            if (name) *name = used;
+            return err;
+        }
+    }
 
     // The tensor-core dot kernel (two activation rows per launch) is selected explicitly.
     const bool try_mma = a.fmt == FMT_Q4_0 && env.variant == VARIANT_MMA;

@@ -9,13 +9,15 @@
 //
 //   * A CTA owns 256 weight rows and a K range (a cluster of `split` CTAs shares one row tile
 //     along K).  Its weight rows arrive in shared memory as raw Q4_0 bytes, one 144-byte group
-//     (8 blocks, 256 weights) per row per stage, by bulk copies.
-//   * 16 dequantising warps: one thread per weight row turns a group into fp16
-//     (q - 8) * d - one rounding, |relative error| <= 2^-11 per weight - and stores it with
-//     tcgen05.st into its own TMEM lane: the MMA's A operand (128 lanes = 128 rows) never
-//     touches shared memory.
-//   * 2 warps stage the activations for the same K range as the B operand in shared memory
-//     (canonical no-swizzle K-major core matrices), batch padded with zeros to 16 or 32 columns.
+//     (8 blocks, 256 weights) per row per stage: a single tiled TMA copy of a 256 x 144-byte box
+//     (per-row bulk copies of 144 bytes cost ~30 ns each in the copy engine and were 10x slower).
+//   * 16 dequantising warps in two sets that alternate stages: one thread per weight row turns a
+//     group into fp16 (q - 8) * d - one rounding, |relative error| <= 2^-11 per weight - and
+//     stores it with tcgen05.st into its own TMEM lane: the MMA's A operand (128 lanes = 128
+//     rows) never touches shared memory.
+//   * The same threads stage the activations of their stage as the B operand in shared memory
+//     (canonical no-swizzle K-major core matrices, batch padded with zeros to 16 or 32 columns);
+//     the global loads for a set's next stage are in flight while it dequantises.
 //   * One thread issues tcgen05.mma (M128 x N16|32 x K16, kind::f16, fp32 accumulate); there are
 //     two accumulators (rows 0-127 and 128-255) of 16|32 TMEM columns each.  No per-block
 //     fix-up is needed because the scale is already folded into A.
@@ -33,6 +35,7 @@
 #include "kernels.h"
 #include "sm100_prims.cuh"
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include <cstdlib>
@@ -44,13 +47,12 @@ using namespace sm100;
 
 constexpr int kTileRows = 256;                 // weight rows per CTA (two 128-lane accumulators)
 constexpr int kSets = 2;                       // dequantiser thread sets; set s takes stages s, s+2..
+constexpr int kSetThreads = 256;
 constexpr int kDqWarps = 8 * kSets;
 constexpr int kProducerWarp = kDqWarps;
 constexpr int kMmaWarp = kDqWarps + 1;
-constexpr int kXWarp0 = kDqWarps + 2;
-constexpr int kXWarps = 2;
-constexpr int kTcThreads = (kDqWarps + 2 + kXWarps) * 32;
-constexpr int kRawStages = 3;
+constexpr int kTcThreads = (kDqWarps + 2) * 32;
+constexpr int kRawStages = 4;
 constexpr int kXStages = 3;
 constexpr int kASlots = 3;                     // per accumulator half; 64 TMEM columns each
 constexpr int kGroupBytes = 144;               // 8 Q4_0 blocks
@@ -58,6 +60,11 @@ constexpr int kRawStageBytes = kTileRows * kGroupBytes;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColA = 64;                 // accumulators live in columns [0, 64)
 constexpr int kMaxBatch = 32;
+constexpr int kXPer = kMaxBatch * 32 / kSetThreads;   // activation chunks per thread per stage
+
+#ifndef TCB_TC_DEBUG
+#define TCB_TC_DEBUG 0
+#endif
 
 struct TcParams {
     const uint8_t* W;
@@ -70,6 +77,8 @@ struct TcParams {
     int groups;      // K / 256
     int split;       // CTAs per row tile = cluster size
     int off_raw, off_x;
+    long long* trace; // debug builds: per-stage clock64 stamps of CTA 0, 16 per stage
+    int dbg;          // debug builds: 1 skip dequantisation, 2 skip MMA issue, 4 skip activation loads
 };
 
 struct Ring {
@@ -108,37 +117,39 @@ __device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cas
 //   out[0] = (k0, k0+2)   out[1] = (k0+16, k0+18)   out[2] = (k0+1, k0+3)   out[3] = (k0+17, k0+19)
 // A nibble ORed into the mantissa of 1024.0 (bits 0-3) or of 64.0 (bits 4-7) is that constant
 // plus the nibble exactly; subtracting 1032 or 72 leaves q - 8.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t bits) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(bits));
+    return r;
+}
 __device__ __forceinline__ void unpack_word(uint32_t w, __half2 d2, uint32_t* out) {
     const uint32_t ws = w >> 8;
     const __half2 c_lo = bits_h2(0x64086408u);   // 1032
     const __half2 c_hi = bits_h2(0x54805480u);   // 72
-    const uint32_t r0 = (w & 0x000F000Fu) | 0x64006400u;
-    const uint32_t r1 = (w & 0x00F000F0u) | 0x54005400u;
-    const uint32_t r2 = (ws & 0x000F000Fu) | 0x64006400u;
-    const uint32_t r3 = (ws & 0x00F000F0u) | 0x54005400u;
+    const uint32_t r0 = and_or(w, 0x000F000Fu, 0x64006400u);
+    const uint32_t r1 = and_or(w, 0x00F000F0u, 0x54005400u);
+    const uint32_t r2 = and_or(ws, 0x000F000Fu, 0x64006400u);
+    const uint32_t r3 = and_or(ws, 0x00F000F0u, 0x54005400u);
     out[0] = h2_bits(__hmul2(__hsub2(bits_h2(r0), c_lo), d2));
     out[1] = h2_bits(__hmul2(__hsub2(bits_h2(r1), c_hi), d2));
     out[2] = h2_bits(__hmul2(__hsub2(bits_h2(r2), c_lo), d2));
     out[3] = h2_bits(__hmul2(__hsub2(bits_h2(r3), c_hi), d2));
 }
 
-// Block B (0..7) of a 144-byte group held as 36 words: 16 packed fp16 pairs.
-template <int B>
-__device__ __forceinline__ void dequant_block(const uint32_t (&g)[36], uint32_t (&out)[16]) {
-    constexpr int byte0 = 18 * B;
-    constexpr int w0 = byte0 / 4;
-    uint32_t dd;
-    if constexpr ((B & 1) == 0) {
-        dd = __byte_perm(g[w0], 0, 0x1010);       // scale in the low half of word w0
-    } else {
-        dd = __byte_perm(g[w0], 0, 0x3232);       // scale in the high half
-    }
+// Block B (0..7) of a 144-byte group, of which the caller holds words W0 .. W0+19: 16 packed
+// fp16 pairs.  Block B starts at byte 18*B: its scale sits in the low or high half of a word and
+// its quants are word-aligned (odd B) or straddle words by two bytes (even B).
+template <int B, int W0>
+__device__ __forceinline__ void dequant_block(const uint32_t (&g)[20], uint32_t (&out)[16]) {
+    constexpr int w0 = (18 * B) / 4 - W0;
+    static_assert(w0 >= 0 && w0 + 5 <= 20, "block outside the held words");
+    const uint32_t dd = __byte_perm(g[w0], 0, (B & 1) == 0 ? 0x1010 : 0x3232);
     const __half2 d2 = bits_h2(dd);
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
         uint32_t w;
         if constexpr ((B & 1) == 0) {
-            w = __byte_perm(g[w0 + t], g[w0 + t + 1], 0x5432);  // quants start 2 bytes into w0
+            w = __byte_perm(g[w0 + t], g[w0 + t + 1], 0x5432);
         } else {
             w = g[w0 + 1 + t];
         }
@@ -146,7 +157,45 @@ __device__ __forceinline__ void dequant_block(const uint32_t (&g)[36], uint32_t 
     }
 }
 
-__global__ void __launch_bounds__(kTcThreads, 1) gemv_q4_tc_kernel(const TcParams p) {
+// Activation chunk loads of one stage for one thread: chunk c = tl + 256 * u covers activation
+// row n = 8 * u + (tl & 7) and the 8 K values {k0..k0+3, k0+16..k0+19}, k0 from kc = tl >> 3.
+struct XRegs {
+    uint2 a[kXPer], b[kXPer];
+};
+__device__ __forceinline__ void x_load(const TcParams& p, int group, int tl, int nb, XRegs& r) {
+    const int n_lo = tl & 7, kc = tl >> 3;
+    const __half* base = p.X + static_cast<size_t>(group) * 256 + (kc >> 2) * 32 + (kc & 3) * 4;
+#pragma unroll
+    for (int u = 0; u < kXPer; ++u) {
+        const int n = u * 8 + n_lo;
+        r.a[u] = make_uint2(0u, 0u);
+        r.b[u] = make_uint2(0u, 0u);
+        if (u * 8 < nb && n < p.M) {
+            const __half* xr = base + static_cast<size_t>(n) * p.K;
+            r.a[u] = *reinterpret_cast<const uint2*>(xr);        // k0 .. k0+3
+            r.b[u] = *reinterpret_cast<const uint2*>(xr + 16);   // k0+16 .. k0+19
+        }
+    }
+}
+// Writes the chunks in the dequantiser's K order as no-swizzle K-major core matrices:
+// chunk (n, kc) at kc * lbo + (n / 8) * 128 + (n % 8) * 16.
+__device__ __forceinline__ void x_store(uint32_t dst0, uint32_t lbo, int tl, int nb, const XRegs& r) {
+    const int n_lo = tl & 7, kc = tl >> 3;
+    const uint32_t dst = dst0 + static_cast<uint32_t>(kc) * lbo + n_lo * 16;
+#pragma unroll
+    for (int u = 0; u < kXPer; ++u) {
+        if (u * 8 >= nb) break;
+        uint4 v;
+        v.x = __byte_perm(r.a[u].x, r.a[u].y, 0x5410);   // (k0,   k0+2)
+        v.y = __byte_perm(r.b[u].x, r.b[u].y, 0x5410);   // (k0+16, k0+18)
+        v.z = __byte_perm(r.a[u].x, r.a[u].y, 0x7632);   // (k0+1, k0+3)
+        v.w = __byte_perm(r.b[u].x, r.b[u].y, 0x7632);   // (k0+17, k0+19)
+        sts128(dst + u * 128, v);
+    }
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
     extern __shared__ __align__(128) uint8_t smem[];
     Barriers* bars = reinterpret_cast<Barriers*>(smem);
     volatile int* abort_flag = &bars->abort_flag;
@@ -160,7 +209,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_q4_tc_kernel(const TcParam
     const int g1 = p.groups * (crank + 1) / split;
     const int ng = g1 - g0;
     const int row0 = tile * kTileRows;
-    const int valid_rows = min(kTileRows, p.N - row0);
     const int nb = p.nbatch;
     const uint32_t lbo = static_cast<uint32_t>(nb) * 16u;        // bytes between K core matrices
     const uint32_t x_stage_bytes = static_cast<uint32_t>(nb) * 512u;
@@ -173,12 +221,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_q4_tc_kernel(const TcParam
             bar_init(&bars->raw_empty[i], 8);       // the 8 warps of the set that read the stage
         }
         for (int i = 0; i < kXStages; ++i) {
-            bar_init(&bars->x_full[i], kXWarps);
+            bar_init(&bars->x_full[i], 8);          // the 8 warps of the set that staged it
             bar_init(&bars->x_empty[i], 1);
         }
         for (int h = 0; h < 2; ++h)
             for (int i = 0; i < kASlots; ++i) {
-                bar_init(&bars->a_full[h][i], 4);   // the 4 warps that own this half's lanes
+                bar_init(&bars->a_full[h][i], 128); // every thread that owns one of this half's lanes
                 bar_init(&bars->a_empty[h][i], 1);
             }
         bar_init(&bars->d_full, 1);
@@ -192,106 +240,175 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_q4_tc_kernel(const TcParam
     const uint32_t tmem_base = bars->tmem_base;
 
     bool failed = false;
+#if TCB_TC_DEBUG
+#define TCB_TR(COL, I) do { if (p.trace && blockIdx.x == 0) p.trace[(I) * 16 + (COL)] = clock64(); } while (0)
+#define TCB_DBG(BIT) (p.dbg & (BIT))
+#else
+#define TCB_TR(COL, I) do { } while (0)
+#define TCB_DBG(BIT) ((BIT) == 64 && (p.dbg & 64))
+#endif
 
     if (warp < kDqWarps) {
-        // ---------------- dequantisers: one thread per weight row --------------------------------
+        // ---------------- dequantisers: one thread per weight row; they also stage activations ----
         const int set = warp >> 3, wl = warp & 7, h = wl >> 2, q = wl & 3;
+        const int tl = tid & (kSetThreads - 1);
         const int row_local = h * 128 + q * 32 + lane;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-        Ring raw, slot;
+        const bool tr = (wl == 0 && lane == 0);
+        Ring raw, slot, xs;
         raw.set(set, kRawStages);
+        xs.set(set, kXStages);
         slot.set(2 * set, kASlots);
+        XRegs xr;
+        if (set < ng && !TCB_DBG(4)) x_load(p, g0 + set, tl, nb, xr);
         for (int i = set; i < ng && !failed; i += kSets) {
-            if (!bar_wait(&bars->raw_full[raw.idx], raw.phase, abort_flag)) { failed = true; break; }
-            const uint32_t src = raw_base + raw.idx * kRawStageBytes + row_local * kGroupBytes;
-            uint32_t g[36];
-#pragma unroll
-            for (int v = 0; v < 9; ++v) {
-                const uint4 t4 = lds128(src + 16 * v);
-                g[4 * v] = t4.x; g[4 * v + 1] = t4.y; g[4 * v + 2] = t4.z; g[4 * v + 3] = t4.w;
-            }
+            // Activations of this stage: loaded a stage ago, now permuted into shared memory.
+            if (!bar_wait_warp(&bars->x_empty[xs.idx], xs.phase ^ 1u, abort_flag)) { failed = true; break; }
+            if (tr) TCB_TR(12, i);
+            x_store(x_base + xs.idx * x_stage_bytes, lbo, tl, nb, xr);
+            fence_proxy_async();
             __syncwarp();
-            if (lane == 0) bar_arrive(&bars->raw_empty[raw.idx]);
+            if (lane == 0) bar_arrive(&bars->x_full[xs.idx]);
+            if (i + kSets < ng && !TCB_DBG(4)) x_load(p, g0 + i + kSets, tl, nb, xr);
+            if (tr) TCB_TR(13, i);
+
+            if (!bar_wait_warp(&bars->raw_full[raw.idx], raw.phase, abort_flag)) { failed = true; break; }
+            if (tr) TCB_TR(1, i);
+            const uint32_t src = raw_base + raw.idx * kRawStageBytes + row_local * kGroupBytes;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 if (failed) break;
-                if (!bar_wait(&bars->a_empty[h][slot.idx], slot.phase ^ 1u, abort_flag)) {
+                // Blocks 0-3 live in bytes [0,72) of the group, blocks 4-7 in [72,144): five
+                // 16-byte loads from byte 0 or byte 64 cover either half.
+                uint32_t g[20];
+#pragma unroll
+                for (int v = 0; v < 5; ++v) {
+                    const uint4 t4 = lds128(src + 64 * half + 16 * v);
+                    g[4 * v] = t4.x; g[4 * v + 1] = t4.y; g[4 * v + 2] = t4.z; g[4 * v + 3] = t4.w;
+                }
+                if (!bar_wait_warp(&bars->a_empty[h][slot.idx], slot.phase ^ 1u, abort_flag)) {
                     failed = true;
                     break;
                 }
+                if (tr) TCB_TR(3 + 2 * half, i);
                 tc_fence_after_sync();
                 const uint32_t col = lane_base + kColA + static_cast<uint32_t>((h * kASlots + slot.idx) * 64);
                 uint32_t out[16];
-                if (half == 0) {
-                    dequant_block<0>(g, out); tmem_st16(col, out);
-                    dequant_block<1>(g, out); tmem_st16(col + 16, out);
-                    dequant_block<2>(g, out); tmem_st16(col + 32, out);
-                    dequant_block<3>(g, out); tmem_st16(col + 48, out);
+                if (TCB_DBG(1)) {
+                } else if (half == 0) {
+                    dequant_block<0, 0>(g, out); tmem_st16(col, out);
+                    dequant_block<1, 0>(g, out); tmem_st16(col + 16, out);
+                    dequant_block<2, 0>(g, out); tmem_st16(col + 32, out);
+                    dequant_block<3, 0>(g, out); tmem_st16(col + 48, out);
                 } else {
-                    dequant_block<4>(g, out); tmem_st16(col, out);
-                    dequant_block<5>(g, out); tmem_st16(col + 16, out);
-                    dequant_block<6>(g, out); tmem_st16(col + 32, out);
-                    dequant_block<7>(g, out); tmem_st16(col + 48, out);
+                    dequant_block<4, 16>(g, out); tmem_st16(col, out);
+                    dequant_block<5, 16>(g, out); tmem_st16(col + 16, out);
+                    dequant_block<6, 16>(g, out); tmem_st16(col + 32, out);
+                    dequant_block<7, 16>(g, out); tmem_st16(col + 48, out);
                 }
                 tmem_wait_st();
                 tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) bar_arrive(&bars->a_full[h][slot.idx]);
+                bar_arrive(&bars->a_full[h][slot.idx]);
+                if (half == 1) {
+                    // The raw stage is released only here, after every value loaded from it has
+                    // been consumed by a tcgen05.st that has completed.  Releasing it right after
+                    // the loads were issued let the next tiled copy overwrite rows whose loads the
+                    // scheduler had deferred (seen as a block holding the data of 4 stages later).
+                    __syncwarp();
+                    if (lane == 0) bar_arrive(&bars->raw_empty[raw.idx]);
+                    if (tr) TCB_TR(2, i);
+                }
+                if (tr) TCB_TR(4 + 2 * half, i);
                 slot.advance(half == 0 ? 1 : 2 * kSets - 1, kASlots);
             }
             raw.advance(kSets, kRawStages);
+            xs.advance(kSets, kXStages);
         }
     } else if (warp == kProducerWarp) {
-        // ---------------- weight producer: 144 bytes per row per stage ---------------------------
-        const size_t row_bytes = static_cast<size_t>(p.groups) * kGroupBytes;
-        const uint8_t* wbase = p.W + static_cast<size_t>(row0) * row_bytes + static_cast<size_t>(g0) * kGroupBytes;
+        // ---------------- weight producer: one 256-row x 144-byte box per stage ------------------
+        // The weights are a 2-D byte tensor [N][K/32*18]; rows past N read as zeros.
         Ring raw;
         raw.set(0, kRawStages);
         int issued = 0;
-        for (int i = 0; i < ng; ++i) {
-            if (!bar_wait(&bars->raw_empty[raw.idx], raw.phase ^ 1u, abort_flag)) { failed = true; break; }
-            if (lane == 0) bar_expect_tx(&bars->raw_full[raw.idx], static_cast<uint32_t>(valid_rows) * kGroupBytes);
-            __syncwarp();
-            uint8_t* dst = smem + p.off_raw + raw.idx * kRawStageBytes;
-            for (int r = lane; r < valid_rows; r += 32)
-                bulk_load(dst + r * kGroupBytes, wbase + r * row_bytes + static_cast<size_t>(i) * kGroupBytes,
-                          kGroupBytes, &bars->raw_full[raw.idx]);
-            ++issued;
-            raw.advance(1, kRawStages);
-        }
-        if (failed || *abort_flag) {
-            // Let copies already in flight land before the CTA's shared memory is released.
-            const int first = issued > kRawStages ? issued - kRawStages : 0;
-            for (int s = first; s < issued; ++s) {
-                Ring r;
-                r.set(s, kRawStages);
-                bar_wait(&bars->raw_full[r.idx], r.phase, nullptr, 100000000LL);
+#if 1
+        if (TCB_DBG(64)) {
+            // Debug comparison path: one 144-byte bulk copy per row instead of the tiled load.
+            const size_t row_bytes = static_cast<size_t>(p.groups) * kGroupBytes;
+            const int valid_rows = min(kTileRows, p.N - row0);
+            const uint8_t* wbase = p.W + static_cast<size_t>(row0) * row_bytes + static_cast<size_t>(g0) * kGroupBytes;
+            for (int i = 0; i < ng; ++i) {
+                if (!bar_wait_warp(&bars->raw_empty[raw.idx], raw.phase ^ 1u, abort_flag)) { failed = true; break; }
+                if (lane == 0) bar_expect_tx(&bars->raw_full[raw.idx], static_cast<uint32_t>(valid_rows) * kGroupBytes);
+                __syncwarp();
+                uint8_t* dst = smem + p.off_raw + raw.idx * kRawStageBytes;
+                for (int r = lane; r < valid_rows; r += 32)
+                    bulk_load(dst + r * kGroupBytes, wbase + r * row_bytes + static_cast<size_t>(i) * kGroupBytes,
+                              kGroupBytes, &bars->raw_full[raw.idx]);
+                raw.advance(1, kRawStages);
+            }
+        } else
+#endif
+        if (lane == 0) {
+            for (int i = 0; i < ng; ++i) {
+                if (!bar_wait(&bars->raw_empty[raw.idx], raw.phase ^ 1u, abort_flag)) { failed = true; break; }
+                TCB_TR(0, i);
+                bar_expect_tx(&bars->raw_full[raw.idx], kRawStageBytes);
+                tensor_load_2d(smem + p.off_raw + raw.idx * kRawStageBytes, &wmap,
+                               (g0 + i) * kGroupBytes, row0, &bars->raw_full[raw.idx]);
+                ++issued;
+                raw.advance(1, kRawStages);
+            }
+            if (failed || *abort_flag) {
+                // Let copies already in flight land before the CTA's shared memory is released.
+                const int first = issued > kRawStages ? issued - kRawStages : 0;
+                for (int s = first; s < issued; ++s) {
+                    Ring r;
+                    r.set(s, kRawStages);
+                    bar_wait(&bars->raw_full[r.idx], r.phase, nullptr, 100000000LL);
+                }
             }
         }
-    } else if (warp == kMmaWarp) {
+    } else {
         // ---------------- MMA issue ----------------------------------------------------------------
         if (lane == 0) {
             const uint32_t idesc = idesc_f16_f32(128, nb);
             Ring xs, slot;
             xs.set(0, kXStages);
             slot.set(0, kASlots);
+            uint32_t accumulate = 0u;   // the first MMA into each accumulator overwrites it
             for (int i = 0; i < ng && !failed; ++i) {
                 if (!bar_wait(&bars->x_full[xs.idx], xs.phase, abort_flag)) { failed = true; break; }
+                TCB_TR(7, i);
                 const uint32_t xs_addr = x_base + xs.idx * x_stage_bytes;
+                // Descriptor of the stage's first K step; each further step starts 2 * lbo bytes on.
+                const uint64_t desc0 = smem_desc_kmajor(xs_addr, lbo, 128u);
+                const uint32_t desc_hi = static_cast<uint32_t>(desc0 >> 32);
+                uint32_t desc_lo = static_cast<uint32_t>(desc0);
+                const uint32_t desc_step = (2u * lbo) >> 4;
                 for (int half = 0; half < 2 && !failed; ++half) {
-                    for (int h = 0; h < 2; ++h) {
-                        if (!bar_wait(&bars->a_full[h][slot.idx], slot.phase, abort_flag)) { failed = true; break; }
-                        tc_fence_after_sync();
-                        const uint32_t a_col = tmem_base + kColA + static_cast<uint32_t>((h * kASlots + slot.idx) * 64);
-                        const uint32_t d_col = tmem_base + static_cast<uint32_t>(h * kMaxBatch);
+                    if (!bar_wait(&bars->a_full[0][slot.idx], slot.phase, abort_flag) ||
+                        !bar_wait(&bars->a_full[1][slot.idx], slot.phase, abort_flag)) {
+                        failed = true;
+                        break;
+                    }
+                    TCB_TR(8 + 2 * half, i);
+                    tc_fence_after_sync();
+                    const uint32_t a0 = tmem_base + kColA + static_cast<uint32_t>(slot.idx * 64);
+                    const uint32_t a1 = a0 + static_cast<uint32_t>(kASlots * 64);
+                    if (!TCB_DBG(2)) {
+                        // The two accumulators alternate so consecutive MMAs are independent.
 #pragma unroll
                         for (int jj = 0; jj < 8; ++jj) {
-                            const int kstep = half * 8 + jj;
-                            const uint64_t bdesc = smem_desc_kmajor(xs_addr + 2u * kstep * lbo, lbo, 128u);
-                            mma_f16_ts(d_col, a_col + 8u * jj, bdesc, idesc, (i | half | jj) != 0 ? 1u : 0u);
+                            const uint64_t bdesc = (static_cast<uint64_t>(desc_hi) << 32) | (desc_lo + jj * desc_step);
+                            mma_f16_ts(tmem_base, a0 + 8u * jj, bdesc, idesc, accumulate);
+                            mma_f16_ts(tmem_base + kMaxBatch, a1 + 8u * jj, bdesc, idesc, accumulate);
+                            accumulate = 1u;
                         }
-                        mma_commit(&bars->a_empty[h][slot.idx]);
                     }
+                    desc_lo += 8u * desc_step;
+                    mma_commit(&bars->a_empty[0][slot.idx]);
+                    mma_commit(&bars->a_empty[1][slot.idx]);
+                    TCB_TR(9 + 2 * half, i);
                     slot.advance(1, kASlots);
                 }
                 if (!failed) mma_commit(&bars->x_empty[xs.idx]);
@@ -300,37 +417,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_q4_tc_kernel(const TcParam
             mma_commit(&bars->d_full);
             if (failed || *abort_flag) bar_wait(&bars->d_full, 0, nullptr, 100000000LL);
         }
-    } else {
-        // ---------------- activation stager ----------------------------------------------------------
-        const int tx = tid - kXWarp0 * 32;
-        const int chunks = 32 * nb;   // 16-byte chunks per stage
-        Ring xs;
-        xs.set(0, kXStages);
-        for (int i = 0; i < ng; ++i) {
-            if (!bar_wait(&bars->x_empty[xs.idx], xs.phase ^ 1u, abort_flag)) { failed = true; break; }
-            const uint32_t dst0 = x_base + xs.idx * x_stage_bytes;
-            const size_t kg = static_cast<size_t>(g0 + i) * 256;
-            for (int c = tx; c < chunks; c += kXWarps * 32) {
-                const int n_lo = c & 7, kc = (c >> 3) & 31, n_hi = c >> 8;
-                const int n = n_hi * 8 + n_lo;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (n < p.M) {
-                    const __half* xr = p.X + static_cast<size_t>(n) * p.K + kg + (kc >> 2) * 32 + (kc & 3) * 4;
-                    const uint2 a = *reinterpret_cast<const uint2*>(xr);        // k0 .. k0+3
-                    const uint2 b = *reinterpret_cast<const uint2*>(xr + 16);   // k0+16 .. k0+19
-                    v.x = __byte_perm(a.x, a.y, 0x5410);   // (k0,   k0+2)
-                    v.y = __byte_perm(b.x, b.y, 0x5410);   // (k0+16, k0+18)
-                    v.z = __byte_perm(a.x, a.y, 0x7632);   // (k0+1, k0+3)
-                    v.w = __byte_perm(b.x, b.y, 0x7632);   // (k0+17, k0+19)
-                }
-                sts128(dst0 + static_cast<uint32_t>(kc) * lbo + n_hi * 128 + n_lo * 16, v);
-            }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) bar_arrive(&bars->x_full[xs.idx]);
-            xs.advance(1, kXStages);
-        }
     }
+#undef TCB_TR
+#undef TCB_DBG
 
     if (failed) {
         *abort_flag = 1;
@@ -343,7 +432,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_q4_tc_kernel(const TcParam
     if (warp < 8) {
         const int h = warp >> 2, q = warp & 3;
         const int row_local = h * 128 + q * 32 + lane;
-        const bool ok = bar_wait(&bars->d_full, 0, abort_flag) && !*abort_flag;
+        const bool ok = bar_wait_warp(&bars->d_full, 0, abort_flag) && __all_sync(0xffffffffu, !*abort_flag);
         if (!ok && !*abort_flag) {
             *abort_flag = 1;
             if (p.err) atomicOr(p.err, ERR_WAIT_TIMEOUT);
@@ -407,6 +496,31 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_q4_tc_kernel(const TcParam
     }
 }
 
+// Tiled tensor map over the quantised weights seen as bytes: dimension 0 = the bytes of a row,
+// dimension 1 = rows; box = one 8-block group (144 bytes) of 256 rows.
+bool encode_weight_map(CUtensorMap* map, const void* W, int N, size_t row_bytes) {
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+    static EncodeFn encode = [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            fn = nullptr;
+        return reinterpret_cast<EncodeFn>(fn);
+    }();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(N)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kGroupBytes), static_cast<cuuint32_t>(kTileRows)};
+    const cuuint32_t estr[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(W), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 cudaError_t init_tc_kernels(int smem_optin) {
@@ -438,10 +552,18 @@ cudaError_t launch_gemv_q4_tc(const GemvQArgs& a, const LaunchEnv& env, cudaStre
     if (split > p.groups) split = p.groups;
     if (split < 1) split = 1;
     p.split = split;
+    if (const char* s = std::getenv("TC_TC_DBG")) p.dbg = std::atoi(s);
+#if TCB_TC_DEBUG
+    if (const char* s = std::getenv("TC_TC_TRACE")) p.trace = reinterpret_cast<long long*>(std::strtoull(s, nullptr, 0));
+#endif
     p.off_raw = kBarrierBytes;
     p.off_x = p.off_raw + kRawStages * kRawStageBytes;
     const int smem = p.off_x + kXStages * p.nbatch * 512;
     if (smem > env.smem_optin) return cudaErrorNotSupported;
+
+    CUtensorMap wmap;
+    if (!encode_weight_map(&wmap, a.W, a.N, static_cast<size_t>(p.groups) * kGroupBytes))
+        return cudaErrorNotSupported;
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles * split);
@@ -456,7 +578,7 @@ cudaError_t launch_gemv_q4_tc(const GemvQArgs& a, const LaunchEnv& env, cudaStre
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (name) *name = "q4_0_gemv_tcgen05_sm100";
-    return cudaLaunchKernelEx(&cfg, gemv_q4_tc_kernel, p);
+    return cudaLaunchKernelEx(&cfg, gemv_q4_tc_kernel, p, wmap);
 }
 
 }  // namespace tcb

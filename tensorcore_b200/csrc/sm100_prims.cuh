@@ -25,13 +25,15 @@ __device__ __forceinline__ void bar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void bar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool bar_try_wait(uint64_t* bar, uint32_t parity) {
+// One try; the hardware may park the warp for up to `hint_ns` before answering, and wakes it as
+// soon as the phase completes.
+__device__ __forceinline__ bool bar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns = 2000u) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(s_u32(bar)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(s_u32(bar)), "r"(parity), "r"(hint_ns) : "memory");
     return ok != 0;
 }
 // False when `*abort_flag` is raised by another thread or `limit` clocks have passed.
@@ -44,6 +46,17 @@ __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatil
         if (clock64() - t0 > limit) return false;
     }
     return true;
+}
+// Whole-warp wait that leaves the warp converged: lane 0 polls, then every lane observes the
+// completed phase itself (one try that succeeds at once).  Needed before .sync.aligned
+// instructions (tcgen05.st/ld/wait), which a polling loop left by lanes at different iterations
+// would otherwise reach diverged.
+__device__ __forceinline__ bool bar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = bar_wait(bar, parity, abort_flag) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok) ok = bar_try_wait(bar, parity, 0u) ? 1 : 0;
+    return __all_sync(0xffffffffu, ok) != 0;
 }
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -60,6 +73,17 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(s_u32(dst)), "l"(src), "r"(bytes), "r"(s_u32(bar)) : "memory");
+}
+
+// Tiled 2-D TMA load: the box at element coordinates (x, y) of the tensor map; x * element size
+// must be a multiple of 16 bytes.  Out-of-range parts of the box are filled with zeros and still
+// count toward the transaction bytes.
+__device__ __forceinline__ void tensor_load_2d(void* dst, const void* tmap, int x, int y,
+                                               uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];"
+        ::"r"(s_u32(dst)), "l"(tmap), "r"(x), "r"(y), "r"(s_u32(bar)) : "memory");
 }
 
 // ---- shared memory loads/stores by 32-bit address -----------------------------------------------

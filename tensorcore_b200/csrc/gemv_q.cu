@@ -46,7 +46,7 @@ constexpr int kMaxStreamWarps = 16;     // streaming kernel: 8 or 16 warps, chos
 constexpr int kMaxStreamThreads = kMaxStreamWarps * 32;
 constexpr int kGroupBlocks = 8;
 constexpr int kMaxMB = 4;
-constexpr int kTcMinBatch = 1 << 30;     // smallest M the tcgen05 kernel takes by default
+constexpr int kTcMinBatch = 8;            // smallest M the tcgen05 kernel takes by default
 
 template <int FMT> struct Fmt;
 template <> struct Fmt<FMT_Q4_0> {

@@ -18,9 +18,9 @@
 //   * The same threads stage the activations of their stage as the B operand in shared memory
 //     (canonical no-swizzle K-major core matrices, batch padded with zeros to 16 or 32 columns);
 //     the global loads for a set's next stage are in flight while it dequantises.
-//   * One thread issues tcgen05.mma (M128 x N16|32 x K16, kind::f16, fp32 accumulate); there are
-//     two accumulators (rows 0-127 and 128-255) of 16|32 TMEM columns each.  No per-block
-//     fix-up is needed because the scale is already folded into A.
+//   * Two threads, one per 128-row half, issue tcgen05.mma (M128 x N16|32 x K16, kind::f16, fp32
+//     accumulate) into that half's accumulator of 16|32 TMEM columns.  No per-block fix-up is
+//     needed because the scale is already folded into A.
 //   * Epilogue: tcgen05.ld, then either a direct store or, when K is split, a deterministic
 //     reduction over the cluster through distributed shared memory.
 //
@@ -51,7 +51,7 @@ constexpr int kSetThreads = 256;
 constexpr int kDqWarps = 8 * kSets;
 constexpr int kProducerWarp = kDqWarps;
 constexpr int kMmaWarp = kDqWarps + 1;
-constexpr int kTcThreads = (kDqWarps + 2) * 32;
+constexpr int kTcThreads = (kDqWarps + 3) * 32;   // + producer + one MMA issuer per half
 constexpr int kRawStages = 4;
 constexpr int kXStages = 3;
 constexpr int kASlots = 3;                     // per accumulator half; 64 TMEM columns each
@@ -215,6 +215,7 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
     const uint32_t raw_base = s_u32(smem + p.off_raw);
     const uint32_t x_base = s_u32(smem + p.off_x);
 
+    if (tid == kProducerWarp * 32) prefetch_tensormap(&wmap);
     if (tid == 0) {
         for (int i = 0; i < kRawStages; ++i) {
             bar_init(&bars->raw_full[i], 1);
@@ -222,14 +223,14 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
         }
         for (int i = 0; i < kXStages; ++i) {
             bar_init(&bars->x_full[i], 8);          // the 8 warps of the set that staged it
-            bar_init(&bars->x_empty[i], 1);
+            bar_init(&bars->x_empty[i], 2);         // one commit per MMA issuer
         }
         for (int h = 0; h < 2; ++h)
             for (int i = 0; i < kASlots; ++i) {
                 bar_init(&bars->a_full[h][i], 128); // every thread that owns one of this half's lanes
                 bar_init(&bars->a_empty[h][i], 1);
             }
-        bar_init(&bars->d_full, 1);
+        bar_init(&bars->d_full, 2);
         bars->abort_flag = 0;
         fence_barrier_init();
     }
@@ -238,6 +239,17 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = bars->tmem_base;
+    if (warp < 8) {
+        // Zero both accumulators: warp w owns lanes 32 * (w % 4) of accumulator w / 4.
+        uint32_t z[16] = {};
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>((warp >> 2) * kMaxBatch);
+        tmem_st16(taddr, z);
+        tmem_st16(taddr + 16, z);
+        tmem_wait_st();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
 
     bool failed = false;
 #if TCB_TC_DEBUG
@@ -369,46 +381,38 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
             }
         }
     } else {
-        // ---------------- MMA issue ----------------------------------------------------------------
+        // ---------------- MMA issue: one thread per accumulator half -------------------------------
+        // The MMAs are tiny (M128 x N<=32 x K16) and the issuing thread is on the critical path, so
+        // each half has its own issuer on its own scheduler, all operands are computed before the
+        // wait, and every MMA accumulates (the accumulators were zeroed at start-up).
         if (lane == 0) {
+            const int h = warp - kMmaWarp;
             const uint32_t idesc = idesc_f16_f32(128, nb);
+            const uint32_t desc_step = (2u * lbo) >> 4;
+            const uint32_t d_col = tmem_base + static_cast<uint32_t>(h * kMaxBatch);
             Ring xs, slot;
             xs.set(0, kXStages);
             slot.set(0, kASlots);
-            uint32_t accumulate = 0u;   // the first MMA into each accumulator overwrites it
             for (int i = 0; i < ng && !failed; ++i) {
-                if (!bar_wait(&bars->x_full[xs.idx], xs.phase, abort_flag)) { failed = true; break; }
-                TCB_TR(7, i);
-                const uint32_t xs_addr = x_base + xs.idx * x_stage_bytes;
                 // Descriptor of the stage's first K step; each further step starts 2 * lbo bytes on.
-                const uint64_t desc0 = smem_desc_kmajor(xs_addr, lbo, 128u);
-                const uint32_t desc_hi = static_cast<uint32_t>(desc0 >> 32);
-                uint32_t desc_lo = static_cast<uint32_t>(desc0);
-                const uint32_t desc_step = (2u * lbo) >> 4;
-                for (int half = 0; half < 2 && !failed; ++half) {
-                    if (!bar_wait(&bars->a_full[0][slot.idx], slot.phase, abort_flag) ||
-                        !bar_wait(&bars->a_full[1][slot.idx], slot.phase, abort_flag)) {
-                        failed = true;
-                        break;
-                    }
-                    TCB_TR(8 + 2 * half, i);
-                    tc_fence_after_sync();
-                    const uint32_t a0 = tmem_base + kColA + static_cast<uint32_t>(slot.idx * 64);
-                    const uint32_t a1 = a0 + static_cast<uint32_t>(kASlots * 64);
-                    if (!TCB_DBG(2)) {
-                        // The two accumulators alternate so consecutive MMAs are independent.
+                const uint64_t desc0 = smem_desc_kmajor(x_base + xs.idx * x_stage_bytes, lbo, 128u);
+                if (!bar_wait(&bars->x_full[xs.idx], xs.phase, abort_flag)) { failed = true; break; }
+                if (h == 0) TCB_TR(7, i);
 #pragma unroll
-                        for (int jj = 0; jj < 8; ++jj) {
-                            const uint64_t bdesc = (static_cast<uint64_t>(desc_hi) << 32) | (desc_lo + jj * desc_step);
-                            mma_f16_ts(tmem_base, a0 + 8u * jj, bdesc, idesc, accumulate);
-                            mma_f16_ts(tmem_base + kMaxBatch, a1 + 8u * jj, bdesc, idesc, accumulate);
-                            accumulate = 1u;
-                        }
+                for (int half = 0; half < 2; ++half) {
+                    const uint32_t a_col = tmem_base + kColA + static_cast<uint32_t>((h * kASlots + slot.idx) * 64);
+                    uint64_t bdesc[8];
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) bdesc[jj] = desc0 + static_cast<uint64_t>((half * 8 + jj) * desc_step);
+                    if (!bar_wait(&bars->a_full[h][slot.idx], slot.phase, abort_flag)) { failed = true; break; }
+                    if (h == 0) TCB_TR(8 + 2 * half, i);
+                    tc_fence_after_sync();
+                    if (!TCB_DBG(2)) {
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj) mma_f16_ts_acc(d_col, a_col + 8u * jj, bdesc[jj], idesc);
                     }
-                    desc_lo += 8u * desc_step;
-                    mma_commit(&bars->a_empty[0][slot.idx]);
-                    mma_commit(&bars->a_empty[1][slot.idx]);
-                    TCB_TR(9 + 2 * half, i);
+                    mma_commit(&bars->a_empty[h][slot.idx]);
+                    if (h == 0) TCB_TR(9 + 2 * half, i);
                     slot.advance(1, kASlots);
                 }
                 if (!failed) mma_commit(&bars->x_empty[xs.idx]);
@@ -521,6 +525,35 @@ bool encode_weight_map(CUtensorMap* map, const void* W, int N, size_t row_bytes)
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// How many clusters of `size` CTAs of this kernel the device can hold at once; cached per size
+// and shared-memory footprint (the two batch widths).  0 when the query fails.
+int max_active_clusters(int size, int smem) {
+    static int cache[2][9] = {};
+    static bool known[2][9] = {};
+    const int w = smem > kBarrierBytes + kRawStages * kRawStageBytes + kXStages * 16 * 512 ? 1 : 0;
+    if (!known[w][size]) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(size * 64);
+        cfg.blockDim = dim3(kTcThreads);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = size;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemv_q4_tc_kernel, &cfg) != cudaSuccess) {
+            n = 0;
+            (void)cudaGetLastError();
+        }
+        cache[w][size] = n;
+        known[w][size] = true;
+    }
+    return cache[w][size];
+}
+
 }  // namespace
 
 cudaError_t init_tc_kernels(int smem_optin) {
@@ -546,7 +579,18 @@ cudaError_t launch_gemv_q4_tc(const GemvQArgs& a, const LaunchEnv& env, cudaStre
     p.nbatch = a.M <= 16 ? 16 : 32;
     p.groups = a.K / 256;
     const int tiles = (a.N + kTileRows - 1) / kTileRows;
-    int split = env.sm_count > 0 ? env.sm_count / tiles : 1;
+    p.off_raw = kBarrierBytes;
+    p.off_x = p.off_raw + kRawStages * kRawStageBytes;
+    const int smem = p.off_x + kXStages * p.nbatch * 512;
+    if (smem > env.smem_optin) return cudaErrorNotSupported;
+    // K is split over a cluster when there are fewer row tiles than SMs: the largest cluster size
+    // whose clusters can all be resident at once (one wave), so that the split shortens the
+    // per-CTA K loop instead of queueing clusters.
+    int split = 1;
+    for (int s = 8; s > 1; --s) {
+        if (s > p.groups || tiles * s > env.sm_count) continue;
+        if (tiles <= max_active_clusters(s, smem)) { split = s; break; }
+    }
     if (const char* s = std::getenv("TC_TC_SPLIT")) split = std::atoi(s);
     if (split > 8) split = 8;
     if (split > p.groups) split = p.groups;
@@ -556,10 +600,6 @@ cudaError_t launch_gemv_q4_tc(const GemvQArgs& a, const LaunchEnv& env, cudaStre
 #if TCB_TC_DEBUG
     if (const char* s = std::getenv("TC_TC_TRACE")) p.trace = reinterpret_cast<long long*>(std::strtoull(s, nullptr, 0));
 #endif
-    p.off_raw = kBarrierBytes;
-    p.off_x = p.off_raw + kRawStages * kRawStageBytes;
-    const int smem = p.off_x + kXStages * p.nbatch * 512;
-    if (smem > env.smem_optin) return cudaErrorNotSupported;
 
     CUtensorMap wmap;
     if (!encode_weight_map(&wmap, a.W, a.N, static_cast<size_t>(p.groups) * kGroupBytes))

@@ -1,0 +1,128 @@
+"""GPU: the tcgen05 batched-decode GEMV (Q4_0, fp16 activations, 8 <= M) against the oracle.
+
+The kernel dequantises weights to fp16 for the tensor cores, so its bar is the 2e-3 scaled-RMS
+bound that applies to fp16 activations (observed 1.8e-4 against an fp64 dequantise-and-dot, 2.8e-4
+with fp16 outputs).  Covered: both batch widths (16 and 32 MMA columns), M above 32 (several
+launches), row counts that are not a multiple of the 256-row tile, every K-split (cluster) size,
+repeated launches on cache-resident weights (the timing that once exposed a stale-stage race),
+and that calls outside the kernel's domain go elsewhere.
+"""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3
+
+
+def case(oracle, N, K, M, seed=0):
+    rng = np.random.default_rng(N * 7 + K * 3 + M + seed)
+    W = (rng.standard_normal((N, K)) * 0.02).astype(np.float32).astype(np.float16)
+    X = rng.standard_normal((M, K)).astype(np.float16)
+    Wq = oracle.quantize_weights(W, 0)
+    return X, Wq, oracle.dequant_dot_f64(X.astype(np.float64), Wq, 0, N)
+
+
+def run(tc, ctx, X, Wq, N, y_f32, reps=1):
+    M, K = X.shape
+    ydt = np.float32 if y_f32 else np.float16
+    outs = []
+    with ctx.buffer_from_array(X) as bx, ctx.buffer_from_array(Wq) as bw, \
+            ctx.buffer(M * N * np.dtype(ydt).itemsize) as by:
+        for _ in range(reps):
+            if y_f32:
+                tc.gemv_quantized_ex(ctx, bx, bw, by, 0, M, N, K, "f16", "f32", None)
+            else:
+                ctx.gemv_quantized(bx, bw, by, 0, M, N, K)
+            outs.append(by.to_numpy((M, N), ydt).astype(np.float64))
+    return outs
+
+
+@pytest.fixture
+def split_env():
+    old = os.environ.pop("TC_TC_SPLIT", None)
+    yield
+    if old is None:
+        os.environ.pop("TC_TC_SPLIT", None)
+    else:
+        os.environ["TC_TC_SPLIT"] = old
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 16), (256, 512, 8), (512, 1024, 32), (300, 768, 9),
+                                   (130, 256, 32), (1000, 2048, 12), (4096, 4096, 16),
+                                   (4096, 4096, 40), (11008, 4096, 24), (2048, 11008, 32)])
+@pytest.mark.parametrize("y_f32", [True, False])
+def test_batched_matches_fp64_dequant_dot(tc, ctx, oracle, split_env, shape, y_f32):
+    N, K, M = shape
+    X, Wq, want = case(oracle, N, K, M)
+    got = run(tc, ctx, X, Wq, N, y_f32)[0]
+    assert "tcgen05" in tc.cuda_last_kernel_name()
+    assert oracle.scaled_rms(got, want) <= TOL
+    assert tc.take_device_error(ctx) == 0
+
+
+@pytest.mark.parametrize("split", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_every_k_split_size(tc, ctx, oracle, split_env, split):
+    N, K, M = 1024, 4096, 32
+    X, Wq, want = case(oracle, N, K, M)
+    os.environ["TC_TC_SPLIT"] = str(split)
+    got = run(tc, ctx, X, Wq, N, True)[0]
+    assert oracle.scaled_rms(got, want) <= TOL
+    # the split-K reduction is a fixed-order sum: results do not depend on timing
+    again = run(tc, ctx, X, Wq, N, True)[0]
+    assert np.array_equal(got, again)
+
+
+@pytest.mark.parametrize("shape", [(2048, 4096, 32, 1), (1024, 8192, 32, 2), (11008, 4096, 24, 1)])
+def test_repeated_launches_on_resident_weights(tc, ctx, oracle, split_env, shape):
+    N, K, M, split = shape
+    X, Wq, want = case(oracle, N, K, M, seed=5)
+    os.environ["TC_TC_SPLIT"] = str(split)
+    outs = run(tc, ctx, X, Wq, N, True, reps=40)
+    errs = [oracle.scaled_rms(o, want) for o in outs]
+    assert max(errs) <= TOL, errs
+    assert all(np.array_equal(outs[0], o) for o in outs[1:])
+    assert tc.take_device_error(ctx) == 0
+
+
+def test_batched_agrees_with_the_streaming_kernel(tc, ctx, oracle, split_env):
+    N, K, M = 4096, 4096, 16
+    X, Wq, want = case(oracle, N, K, M)
+    try:
+        tc.set_gemv_variant("simt")
+        ref = run(tc, ctx, X, Wq, N, True)[0]
+        assert "stream" in tc.cuda_last_kernel_name()
+        tc.set_gemv_variant("tc")
+        got = run(tc, ctx, X, Wq, N, True)[0]
+        assert "tcgen05" in tc.cuda_last_kernel_name()
+    finally:
+        tc.set_gemv_variant("auto")
+    assert oracle.scaled_rms(got, ref) <= TOL
+    assert oracle.scaled_rms(ref, want) <= 1e-4
+
+
+def test_domain(tc, ctx, oracle, split_env):
+    """fp32 activations, the fused RMSNorm form, Q8_0, small M and K % 256 != 0 stay off it."""
+    rng = np.random.default_rng(3)
+    N, K, M = 256, 512, 16
+    W = (rng.standard_normal((N, K)) * 0.02).astype(np.float16)
+    X16 = rng.standard_normal((M, K)).astype(np.float16)
+    names = {}
+    with ctx.buffer_from_array(oracle.quantize_weights(W, 0)) as w4, \
+            ctx.buffer_from_array(oracle.quantize_weights(W, 1)) as w8, \
+            ctx.buffer_from_array(X16) as x16, ctx.buffer_from_array(X16.astype(np.float32)) as x32, \
+            ctx.buffer_from_array(np.ones(K, np.float16)) as g16, ctx.buffer(M * N * 4) as y:
+        tc.gemv_quantized_ex(ctx, x32, w4, y, 0, M, N, K, "f32", "f32", None)
+        names["f32"] = tc.cuda_last_kernel_name()
+        ctx.fused_rmsnorm_gemv_quantized(x16, g16, w4, y, 0, M, N, K, 1e-5)
+        names["fused"] = tc.cuda_last_kernel_name()
+        ctx.gemv_quantized(x16, w8, y, 1, M, N, K)
+        names["q8"] = tc.cuda_last_kernel_name()
+        ctx.gemv_quantized(x16, w4, y, 0, 4, N, K)
+        names["m4"] = tc.cuda_last_kernel_name()
+        ctx.gemv_quantized(x16, w4, y, 0, M, N, K)
+        names["m16"] = tc.cuda_last_kernel_name()
+    assert "tcgen05" in names.pop("m16")
+    assert all("tcgen05" not in n for n in names.values()), names

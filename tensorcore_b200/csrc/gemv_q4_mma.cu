@@ -378,8 +378,6 @@ __global__ void __maxnreg__(kConsumerWarps > 8 ? 96 : 112) gemv_q4_mma_kernel(co
             uint32_t wa[9], wb[9];
 #pragma unroll
             for (int i = 0; i < 9; ++i) { wa[i] = lds32(wa_addr + 4 * i); wb[i] = lds32(wb_addr + 4 * i); }
-            __syncwarp();
-            if (lane == 0) bar_arrive(&empty[slot]);  // data is in registers: slot may refill
 
             // code words: the even block of the pair straddles word boundaries by 2 bytes
             uint32_t ea[4], eb[4];
@@ -422,6 +420,11 @@ __global__ void __maxnreg__(kConsumerWarps > 8 ? 96 : 112) gemv_q4_mma_kernel(co
                 acc[m][0] = fmaf(de_a, (c[0] - zs.x) + d[0], fmaf(do_a, (c[1] - zs.y) + d[1], acc[m][0]));
                 acc[m][1] = fmaf(de_b, (c[2] - zs.x) + d[2], fmaf(do_b, (c[3] - zs.y) + d[3], acc[m][1]));
             }
+            // Released only after every word loaded from the slot has been used: a release placed
+            // right after issuing the loads does not stop them from being scheduled later, after
+            // the producer's next copy has landed.
+            __syncwarp();
+            if (lane == 0) bar_arrive(&empty[slot]);
         }
         // combine the four block-pair lanes of each row, then the eight warps
         float* rbuf = red + static_cast<size_t>(panel & 1) * kConsumerWarps * kPanelRows * MB;

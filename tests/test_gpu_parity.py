@@ -308,3 +308,29 @@ def test_full_size_shapes(tc, ctx, oracle, case):
     yb = gpu_gemv(tc, ctx, Xb, Wq, fmt, N, y_f32=True)
     yab = gpu_gemv(tc, ctx, Xa + 2 * Xb, Wq, fmt, N, y_f32=True)
     assert oracle.scaled_rms(yab, ya + 2 * yb) <= 1e-5
+
+
+@pytest.mark.parametrize("variant", ["simt", "mma"])
+@pytest.mark.parametrize("tag", ["q4_0", "q8_0"])
+def test_repeated_launches_on_cache_resident_weights(tc, ctx, oracle, variant, tag):
+    """Weights that stay in L2 make the copy engine refill ring slots as fast as it ever will:
+    the timing in which a slot released before its loads were consumed would show stale data."""
+    if variant == "mma" and tag == "q8_0":
+        pytest.skip("the mma.sync kernel is Q4_0 only")
+    fmt, N, K, M = Q[tag], 2048, 4096, 1
+    rng = np.random.default_rng(99)
+    Wq = oracle.quantize_weights(make_weights(rng, N, K), fmt)
+    X = rng.standard_normal((M, K)).astype(np.float32)
+    want = oracle.dequant_dot_f64(X.astype(np.float64), Wq, fmt, N)
+    bx, bw, by = dev(ctx, X), dev(ctx, Wq), ctx.buffer(M * N * 4)
+    try:
+        tc.set_gemv_variant(variant)
+        for rep in range(60):
+            tc.gemv_quantized_ex(ctx, bx, bw, by, fmt, M, N, K, "f32", "f32", None)
+            got = by.to_numpy((M, N), np.float32)
+            assert oracle.scaled_rms(got, want) <= TOL_F32, rep
+    finally:
+        tc.set_gemv_variant("auto")
+        for b in (bx, bw, by):
+            b.close()
+    assert tc.take_device_error(ctx) == 0

@@ -26,6 +26,8 @@
 // fill/drain phases.  Every mbarrier wait is bounded; on expiry the kernel records
 // ERR_WAIT_TIMEOUT, drains its outstanding copies (again bounded) and exits.
 #include "kernels.h"
+#include "sm100_prims.cuh"
+#include "tensor_map.h"
 
 #include <cuda_fp16.h>
 
@@ -46,6 +48,13 @@ constexpr int kMaxStreamWarps = 16;     // streaming kernel: 8 or 16 warps, chos
 constexpr int kMaxStreamThreads = kMaxStreamWarps * 32;
 constexpr int kGroupBlocks = 8;
 constexpr int kMaxMB = 4;
+#ifndef TCB_ACT_I16
+#define TCB_ACT_I16 1
+#endif
+#ifndef TCB_MEGA_TRACE
+#define TCB_MEGA_TRACE 0
+#endif
+constexpr bool kActI16 = TCB_ACT_I16 != 0;   // integer activation path (see stage_activations_i16)
 constexpr int kTcMinBatch = 8;            // smallest M the tcgen05 kernel takes by default
 
 template <int FMT> struct Fmt;
@@ -79,6 +88,7 @@ struct StreamParams {
     int off_rowacc, off_sx, off_x, off_ring;
     int max_rows;  // rows per CTA upper bound
     int dbg_skip;  // measurement aid: stream the weights but skip the arithmetic
+    long long* trace = nullptr;  // debug builds: stamps of the staging phases (CTA 0, thread 0)
 };
 
 // ---------------------------------------------------------------------------------------
@@ -185,6 +195,20 @@ __device__ double block_sum_f64(double v, double* scratch /* one double per warp
     if (l == 0) scratch[w] = v;
     __syncthreads();
     double t = 0.0;
+    for (int i = 0; i < nwarps; ++i) t += scratch[i];
+    return t;
+}
+
+// Sum over a thread block of one float per thread (result broadcast to all threads): shuffles,
+// one shared-memory slot per warp, and the per-warp partials added in a fixed order.
+__device__ float block_sum_f32(float v, float* scratch /* one float per warp */) {
+    const int nwarps = blockDim.x >> 5;
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __syncthreads();
+    if (l == 0) scratch[w] = v;
+    __syncthreads();
+    float t = 0.f;
     for (int i = 0; i < nwarps; ++i) t += scratch[i];
     return t;
 }
@@ -423,6 +447,278 @@ __device__ __forceinline__ void group_dot(const uint32_t (&w)[Fmt<FMT>::kGroupV4
 }
 
 // ---------------------------------------------------------------------------------------
+// Integer activation path.
+//
+// Activations are staged once per CTA as int16 with one fp32 scale per 32-element block
+// (scale = max|x| / 32767 over the block, so every element is within 2^-16 of its block's
+// maximum, insensitive to outliers elsewhere in the row; fp16 inputs use a power-of-two scale
+// and are exact down to 1/16 of the block maximum).  Measured against an fp64 dequantise-and-dot
+// on Gaussian rows: 2.2e-5 scaled RMS for fp32 rows (5e-5 for heavy-tailed ones), 7e-6 for fp16.  The dot product of a block is then exact integer arithmetic
+// on the dp2a unit (two 16-bit x two 8-bit products per lane per instruction):
+//     y += d_w * s_x * (sum_k q_k * xq_k  -  zp * sum_k xq_k)
+// which needs about one issued instruction per weight where the fp16-FMA formulation needs
+// three.  Layout of the staged row: the fp16 chunk layout above (16-byte chunks of 8 values,
+// chunk c of group kg at (c*gpr + kg)*16).  sx2[m*nb + j*gpr + kg] = {scale, zp * sum(xq)}.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ int dp2a_lo_su(uint32_t x_s16x2, uint32_t q_u8x4, int c) {
+    int d;
+    asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(x_s16x2), "r"(q_u8x4), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp2a_hi_su(uint32_t x_s16x2, uint32_t q_u8x4, int c) {
+    int d;
+    asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(x_s16x2), "r"(q_u8x4), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp2a_lo_ss(uint32_t x_s16x2, uint32_t q_s8x4, int c) {
+    int d;
+    asm("dp2a.lo.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x_s16x2), "r"(q_s8x4), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp2a_hi_ss(uint32_t x_s16x2, uint32_t q_s8x4, int c) {
+    int d;
+    asm("dp2a.hi.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x_s16x2), "r"(q_s8x4), "r"(c));
+    return d;
+}
+
+// Eight consecutive activations (and, fused, their gammas) of row m starting at k = 8*i.
+template <bool COHERENT>
+__device__ __forceinline__ void load8(const void* base, bool f16, size_t elem0, float (&v)[8]) {
+    if (f16) {
+        const uint4 t = ld_act<COHERENT>(reinterpret_cast<const uint4*>(static_cast<const __half*>(base) + elem0));
+        v[0] = h2f(lo16(t.x)); v[1] = h2f(hi16(t.x)); v[2] = h2f(lo16(t.y)); v[3] = h2f(hi16(t.y));
+        v[4] = h2f(lo16(t.z)); v[5] = h2f(hi16(t.z)); v[6] = h2f(lo16(t.w)); v[7] = h2f(hi16(t.w));
+    } else {
+        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem0);
+        const float4 a = ld_act<COHERENT>(src), b = ld_act<COHERENT>(src + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+}
+
+// Stages MB rows as int16 + per-block scales.  With gamma the RMSNorm prologue runs first: sum of
+// squares in double, rstd = 1/sqrtf(float(ss/K)+eps), row = (x*rstd)*gamma in fp32 - the
+// reference's order - and that row is what gets quantised.  `zp` is the weight zero point (8 for
+// Q4_0 codes taken as unsigned nibbles, 0 for Q8_0's signed bytes).
+// Quantises one 8-value chunk (index i of row m) held in v[] and stores it; the four lanes of a
+// quad hold the four chunks of a 32-element block and share its scale.  Every lane of the warp
+// calls this (dead lanes with live = false and zeros) so the quad shuffles are among live lanes.
+template <bool NATURAL>
+__device__ __forceinline__ void quantise_chunk(const float (&v)[8], bool live, int i, int m, int zp,
+                                               bool pow2, int gpr, int nb, uint4* dst, float2* sx2) {
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    // fp16 sources get a power-of-two scale (block maximum mapped into [16384, 32768)): every
+    // element within a factor 16 of the maximum is then represented exactly.
+    float scale = amax * (1.0f / 32767.0f), inv = amax > 0.f ? 32767.0f / amax : 0.f;
+    if (pow2 && amax > 0.f) {
+        const uint32_t e = __float_as_uint(amax) & 0x7f800000u;
+        scale = __uint_as_float(e - (14u << 23));
+        inv = __uint_as_float((254u << 23) - (e - (14u << 23)));
+    }
+    int q[8], isum = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        // round to nearest even without the conversion unit: adding 1.5 * 2^23 leaves the
+        // integer in the low mantissa bits (|v * inv| <= 32767.5 by construction)
+        q[e] = __float_as_int(__fadd_rn(v[e] * inv, 12582912.0f)) - 0x4B400000;
+        q[e] = max(-32767, min(32767, q[e]));
+        isum += q[e];
+    }
+    isum += __shfl_xor_sync(0xffffffffu, isum, 1);
+    isum += __shfl_xor_sync(0xffffffffu, isum, 2);
+    if (live) {
+        uint4 o;
+        o.x = (static_cast<uint32_t>(q[0]) & 0xffffu) | (static_cast<uint32_t>(q[1]) << 16);
+        o.y = (static_cast<uint32_t>(q[2]) & 0xffffu) | (static_cast<uint32_t>(q[3]) << 16);
+        o.z = (static_cast<uint32_t>(q[4]) & 0xffffu) | (static_cast<uint32_t>(q[5]) << 16);
+        o.w = (static_cast<uint32_t>(q[6]) & 0xffffu) | (static_cast<uint32_t>(q[7]) << 16);
+        dst[NATURAL ? i : x_chunk_index<false>(i, gpr)] = o;
+        if ((i & 3) == 0) {
+            const int b = i >> 2, kg = b >> 3, j = b & 7;
+            sx2[m * nb + (NATURAL ? b : j * gpr + kg)] = make_float2(scale, __int_as_float(zp * isum));
+        }
+    }
+}
+
+// Stages MB rows as int16 + per-block scales.  With gamma the RMSNorm prologue runs first: sum of
+// squares in double, rstd = 1/sqrtf(float(ss/K)+eps), row = (x*rstd)*gamma in fp32 - the
+// reference's order - and that row is what gets quantised.  `zp` is the weight zero point (8 for
+// Q4_0 codes taken as unsigned nibbles, 0 for Q8_0's signed bytes).
+// NATURAL: the staged row and the scales keep the order of k (every lane of a warp then reads the
+// same activations: one broadcast per load); otherwise the chunk-transposed layout above.
+// Rows of up to 4 chunks per thread (K <= 32 * blockDim) are loaded once, activations and gamma
+// in the same round trip, and held in registers across the reduction; longer rows are read twice.
+template <int MB, bool COHERENT = false, bool NATURAL = false>
+__device__ void stage_activations_i16(const StreamParams& p, uint8_t* smem, int zp, double* red_scratch) {
+    const int K = p.K, gpr = p.gpr, nb = p.nb;
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    const int nchunks = K >> 3;
+    const bool f16 = p.x_src_f16 != 0;
+    const bool fused = p.gamma != nullptr;
+    const bool pow2 = f16 && !fused;
+    float2* sx2 = reinterpret_cast<float2*>(smem + p.off_sx);
+    constexpr int kHold = 4;
+    for (int m = 0; m < MB; ++m) {
+        uint4* dst = reinterpret_cast<uint4*>(smem + p.off_x + static_cast<size_t>(m) * K * 2);
+        const size_t row0 = static_cast<size_t>(m) * K;
+        if (nchunks <= kHold * nthreads) {
+            float v[kHold][8], g[kHold][8];
+#pragma unroll
+            for (int r = 0; r < kHold; ++r) {
+                const int i = tid + r * nthreads;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { v[r][e] = 0.f; g[r][e] = 1.f; }
+                if (i < nchunks) {
+                    load8<COHERENT>(p.X, f16, row0 + 8 * static_cast<size_t>(i), v[r]);
+                    if (fused) load8<false>(p.gamma, f16, 8 * static_cast<size_t>(i), g[r]);
+                }
+            }
+#if TCB_MEGA_TRACE
+#define STR(C) do { if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[C] = clock64(); } while (0)
+#else
+#define STR(C) do { } while (0)
+#endif
+            STR(0);
+            {
+                float dep = 0.f;
+#pragma unroll
+                for (int r = 0; r < kHold; ++r) dep += v[r][0] + g[r][7];
+                if (dep == 1.2345e-30f) sx2[0].x = dep;   // forces the loads to have landed
+            }
+            STR(1);
+            float rstd = 1.0f;
+            if (fused) {
+                // Sum of squares in fp32, pairwise within the thread and across the block: the
+                // relative error (about 1e-7) is far below what the int16 staging resolves, and
+                // fp64 arithmetic is slow on this part (the fp64 version of this reduction took
+                // 2200 cycles per call).
+                float part[kHold];
+#pragma unroll
+                for (int r = 0; r < kHold; ++r) {
+                    const float s01 = fmaf(v[r][0], v[r][0], v[r][1] * v[r][1]);
+                    const float s23 = fmaf(v[r][2], v[r][2], v[r][3] * v[r][3]);
+                    const float s45 = fmaf(v[r][4], v[r][4], v[r][5] * v[r][5]);
+                    const float s67 = fmaf(v[r][6], v[r][6], v[r][7] * v[r][7]);
+                    part[r] = (s01 + s23) + (s45 + s67);
+                }
+                float ss = 0.f;
+#pragma unroll
+                for (int r = 0; r < kHold; r += 2) ss += part[r] + (r + 1 < kHold ? part[r + 1] : 0.f);
+                ss = block_sum_f32(ss, reinterpret_cast<float*>(red_scratch));
+                rstd = 1.0f / sqrtf(ss / static_cast<float>(K) + p.eps);
+            }
+            STR(2);
+#pragma unroll
+            for (int r = 0; r < kHold; ++r) {
+                const int i = tid + r * nthreads;
+                if (r * nthreads >= nchunks) break;   // uniform: no lane has a chunk in this round
+                if (fused) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[r][e] = __fmul_rn(__fmul_rn(v[r][e], rstd), g[r][e]);
+                }
+                quantise_chunk<NATURAL>(v[r], i < nchunks, i, m, zp, pow2, gpr, nb, dst, sx2);
+            }
+            STR(3);
+        } else {
+            float rstd = 1.0f;
+            if (fused) {
+                double ss = 0.0;
+                for (int i = tid; i < nchunks; i += nthreads) {
+                    float v[8];
+                    load8<COHERENT>(p.X, f16, row0 + 8 * static_cast<size_t>(i), v);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ss += static_cast<double>(v[e]) * static_cast<double>(v[e]);
+                }
+                ss = block_sum_f64(ss, red_scratch);
+                rstd = 1.0f / sqrtf(static_cast<float>(ss / static_cast<double>(K)) + p.eps);
+            }
+            for (int base = 0; base < nchunks; base += nthreads) {
+                const int i = base + tid;
+                const bool live = i < nchunks;
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = 0.f;
+                if (live) {
+                    load8<COHERENT>(p.X, f16, row0 + 8 * static_cast<size_t>(i), v);
+                    if (fused) {
+                        float g[8];
+                        load8<false>(p.gamma, f16, 8 * static_cast<size_t>(i), g);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(__fmul_rn(v[e], rstd), g[e]);
+                    }
+                }
+                quantise_chunk<NATURAL>(v, live, i, m, zp, pow2, gpr, nb, dst, sx2);
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// One group (8 blocks, 256 weights) against MB staged rows, integer dot products.
+template <int FMT, int MB, bool NATURAL = false>
+__device__ __forceinline__ void group_dot_i16(const uint32_t (&w)[Fmt<FMT>::kGroupV4 * 4],
+                                              const uint8_t* xs, const float2* sx2, int kg, int gpr,
+                                              int K, int nb, float (&out)[MB]) {
+#pragma unroll
+    for (int j = 0; j < kGroupBlocks; ++j) {
+        constexpr int kHwPerBlock = Fmt<FMT>::kBlockBytes / 2;  // 9 or 17 halfwords
+        const int hw = kHwPerBlock * j;                          // halfword index of the scale
+        const uint32_t sw = w[hw >> 1];
+        const float d = h2f((hw & 1) ? hi16(sw) : lo16(sw));
+        const int qhw = hw + 1;                                  // first halfword of the codes
+        constexpr int kQWords = (Fmt<FMT>::kBlockBytes - 2) / 4; // 4 or 8 code words
+        uint32_t q[kQWords];
+#pragma unroll
+        for (int t = 0; t < kQWords; ++t) {
+            if (qhw & 1) q[t] = __funnelshift_r(w[(qhw >> 1) + t], w[(qhw >> 1) + t + 1], 16);
+            else q[t] = w[(qhw >> 1) + t];
+        }
+        uint32_t lo4[4], hi4[4];
+        if (FMT == FMT_Q4_0) {
+            // byte i of the block: low nibble <-> x[i], high nibble <-> x[i+16]
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                lo4[t] = q[t] & 0x0f0f0f0fu;
+                hi4[t] = (q[t] >> 4) & 0x0f0f0f0fu;
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < MB; ++m) {
+            const uint4* xrow = reinterpret_cast<const uint4*>(xs + static_cast<size_t>(m) * K * 2);
+            uint4 xv[4];   // x[8c .. 8c+7] of this block as int16 pairs
+#pragma unroll
+            for (int c = 0; c < 4; ++c) xv[c] = NATURAL ? xrow[(kg * 8 + j) * 4 + c] : xrow[(4 * j + c) * gpr + kg];
+            int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+            if (FMT == FMT_Q4_0) {
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const uint32_t l01 = get4(xv[t >> 1], (t & 1) * 2), l23 = get4(xv[t >> 1], (t & 1) * 2 + 1);
+                    const uint32_t h01 = get4(xv[2 + (t >> 1)], (t & 1) * 2), h23 = get4(xv[2 + (t >> 1)], (t & 1) * 2 + 1);
+                    a0 = dp2a_lo_su(l01, lo4[t], a0);
+                    a1 = dp2a_lo_su(h01, hi4[t], a1);
+                    a2 = dp2a_hi_su(l23, lo4[t], a2);
+                    a3 = dp2a_hi_su(h23, hi4[t], a3);
+                }
+            } else {
+                // Q8_0: byte i <-> x[i], signed
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    const uint32_t x01 = get4(xv[t >> 1], (t & 1) * 2), x23 = get4(xv[t >> 1], (t & 1) * 2 + 1);
+                    if (t & 1) { a2 = dp2a_lo_ss(x01, q[t], a2); a3 = dp2a_hi_ss(x23, q[t], a3); }
+                    else { a0 = dp2a_lo_ss(x01, q[t], a0); a1 = dp2a_hi_ss(x23, q[t], a1); }
+                }
+            }
+            const float2 sc = sx2[m * nb + (NATURAL ? kg * 8 + j : j * gpr + kg)];
+            const int dot = (a0 + a1) + (a2 + a3) - __float_as_int(sc.y);
+            out[m] = fmaf(d * sc.x, static_cast<float>(dot), out[m]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // The streaming kernel.
 // ---------------------------------------------------------------------------------------
 template <int FMT, bool XF32, int MB>
@@ -476,7 +772,8 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q_stream_kernel(con
 
     // Activations may be the previous kernel's output: wait for it, then stage them.
     pdl_wait();
-    stage_activations<XF32, MB>(p, smem, F::kZeroPoint, red_scratch);
+    if (kActI16) stage_activations_i16<MB>(p, smem, FMT == FMT_Q4_0 ? 8 : 0, red_scratch);
+    else stage_activations<XF32, MB>(p, smem, F::kZeroPoint, red_scratch);
 
     const uint8_t* xs = smem + p.off_x;
     const float* sx = reinterpret_cast<const float*>(smem + p.off_sx);
@@ -524,7 +821,8 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q_stream_kernel(con
             const int kg = gl - row * gpr;
             if (p.dbg_skip) out[0] = __uint_as_float(w[0] ^ w[35]);
             else
-            group_dot<FMT, XF32, MB>(w, xs, sx, kg, gpr, p.K, p.nb, out);
+            if (kActI16) group_dot_i16<FMT, MB>(w, xs, reinterpret_cast<const float2*>(sx), kg, gpr, p.K, p.nb, out);
+            else group_dot<FMT, XF32, MB>(w, xs, sx, kg, gpr, p.K, p.nb, out);
         }
         // Segmented reduction over lanes that hold groups of the same row (contiguous runs).
 #pragma unroll
@@ -565,8 +863,13 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q_stream_kernel(con
 // ---------------------------------------------------------------------------------------
 // Persistent decode kernel: a whole recorded list of Q4_0, M = 1 GEMVs in ONE launch.
 //
-// One CTA per SM (cooperative launch: all CTAs are co-resident).  Every warp keeps its ring of
-// weight chunks full ACROSS operations: when it has issued the last chunk of operation i it
+// One CTA per SM (cooperative launch: all CTAs are co-resident).  The unit of work is a box of 32
+// weight rows x one 8-block group (144 bytes per row), fetched by one tiled TMA copy through a
+// per-operation tensor map.  A lane owns a ROW of the box, so all lanes of a warp read the same
+// activations from shared memory (one broadcast per load instead of 32 different 16-byte chunks:
+// the activation reads were what saturated shared-memory bandwidth with a lane per K group), and
+// a lane adds its partial dot product to its row's accumulator.  Every warp keeps its ring of
+// boxes full ACROSS operations: when it has issued the last chunk of operation i it
 // goes on with the first chunks of operation i+1, so HBM keeps streaming while the CTA finishes
 // i, writes its rows and waits for the other CTAs.  Operations that read what an earlier one
 // wrote are separated by a grid-wide barrier (one 64-bit counter in global memory, release /
@@ -584,8 +887,9 @@ __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long
 }
 
 struct WarpGeom {            // one operation as seen by one warp of one CTA
-    const uint8_t* wbase;    // first byte of the CTA's row range
-    int r0, rows, gpr, g_count, my_n;
+    int r0, rows, gpr;       // the CTA's row range, groups per row
+    int n_units;             // (32-row block, group) pairs of the CTA
+    int my_n;                // how many of them this warp takes: units warp, warp + nwarps, ...
 };
 
 __device__ __forceinline__ WarpGeom make_geom(const MegaOp& op, int warp, int nwarps) {
@@ -594,32 +898,9 @@ __device__ __forceinline__ WarpGeom make_geom(const MegaOp& op, int warp, int nw
     const int r1 = static_cast<int>(static_cast<long long>(op.N) * (blockIdx.x + 1) / gridDim.x);
     g.rows = r1 - g.r0;
     g.gpr = op.K >> 8;
-    g.g_count = g.rows * g.gpr;
-    const int nchunks = (g.g_count + 31) >> 5;
-    g.my_n = nchunks > warp ? (nchunks - warp + nwarps - 1) / nwarps : 0;
-    g.wbase = op.W + static_cast<size_t>(g.r0) * g.gpr * 144;
+    g.n_units = ((g.rows + 31) >> 5) * g.gpr;
+    g.my_n = g.n_units > warp ? (g.n_units - warp + nwarps - 1) / nwarps : 0;
     return g;
-}
-
-template <bool XF32>
-__device__ __forceinline__ void mega_chunk(const uint32_t (&w)[36], bool valid, int gl, int gpr,
-                                           const uint8_t* xs, const float* sx, int K, float* rowacc,
-                                           int lane) {
-    float out[1] = {0.f};
-    int row = -1 - lane;
-    if (valid) {
-        row = gl / gpr;
-        const int kg = gl - row * gpr;
-        group_dot<FMT_Q4_0, XF32, 1>(w, xs, sx, kg, gpr, K, K >> 5, out);
-    }
-#pragma unroll
-    for (int dlt = 1; dlt < 32; dlt <<= 1) {
-        const int r2 = __shfl_down_sync(0xffffffffu, row, dlt);
-        const float v2 = __shfl_down_sync(0xffffffffu, out[0], dlt);
-        if ((lane + dlt < 32) && (r2 == row)) out[0] += v2;
-    }
-    const int rprev = __shfl_up_sync(0xffffffffu, row, 1);
-    if (valid && (lane == 0 || rprev != row)) atomicAdd(&rowacc[row], out[0]);
 }
 
 __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(const MegaParams p) {
@@ -646,7 +927,8 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
     __syncthreads();
 
     // ---- per-warp weight stream: issue cursor runs ahead of the consume cursor ----
-    int iop = 0, ii = 0;                 // next chunk to issue: operation, index within it
+    const uint8_t* maps = static_cast<const uint8_t*>(p.maps);   // one 128-byte tensor map per operation
+    int iop = 0, ii = 0;                 // next box to issue: operation, index within it
     MegaOp op_i = p.ops[0];
     WarpGeom gi = make_geom(op_i, warp, nwarps);
     int islot = 0, cslot = 0;            // ring slots of the next issue / next consume
@@ -660,14 +942,13 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
         }
         if (iop >= n_ops || inflight >= ns) return;
         if (lane == 0) {
-            const int first = (warp + nwarps * ii) << 5;
-            const int ng = min(32, gi.g_count - first);
-            const uint32_t bytes = static_cast<uint32_t>(ng) * 144u;
+            const int u = warp + nwarps * ii;
+            const int rb = u / gi.gpr, kg = u - rb * gi.gpr;
             uint64_t* bar = &bars[warp * ns + islot];
             fence_proxy_async();
-            mbar_expect_tx(bar, bytes);
-            bulk_g2s(ring + static_cast<size_t>(warp * ns + islot) * kChunkBytes,
-                     gi.wbase + static_cast<size_t>(first) * 144, bytes, bar);
+            mbar_expect_tx(bar, kChunkBytes);
+            sm100::tensor_load_2d(ring + static_cast<size_t>(warp * ns + islot) * kChunkBytes,
+                                  maps + static_cast<size_t>(iop) * 128, kg * 144, gi.r0 + rb * 32, bar);
         }
         ++ii;
         ++inflight;
@@ -675,6 +956,11 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
     };
     for (int i = 0; i < ns; ++i) try_issue();
 
+#if TCB_MEGA_TRACE
+#define MTR(COL) do { if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[o * 8 + (COL)] = clock64(); } while (0)
+#else
+#define MTR(COL) do { } while (0)
+#endif
     unsigned long long target = p.base;
     bool failed = false;
     for (int o = 0; o < n_ops && !failed; ++o) {
@@ -683,6 +969,7 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
         // Everyone must be done with the previous operation's shared memory; if this operation
         // reads another CTA's output, everyone in the grid must be done with the previous one.
         __syncthreads();
+        MTR(0);
         if (op.flags & MOP_BARRIER) {
             // One 64-bit arrival counter that is never reset: barrier j of this launch is
             // complete when it reaches base + (j+1) * gridDim.  One thread per CTA arrives
@@ -705,26 +992,32 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
             __syncthreads();
             if (*abort_s) { failed = true; break; }
         }
-        const bool f32stage = (op.flags & (MOP_X_F32 | MOP_FUSED)) != 0;
+        MTR(1);
         if (op.flags & MOP_RESTAGE) {
             StreamParams sp;
             sp.X = op.X; sp.gamma = (op.flags & MOP_FUSED) ? op.gamma : nullptr;
             sp.K = op.K; sp.nb = op.K >> 5; sp.gpr = op.K >> 8; sp.eps = op.eps;
             sp.x_src_f16 = (op.flags & MOP_X_F32) ? 0 : 1;
             sp.off_x = p.off_x; sp.off_sx = p.off_sx;
-            if (f32stage) stage_activations<true, 1, true>(sp, smem, 8.0f, red_scratch);
-            else stage_activations<false, 1, true>(sp, smem, 8.0f, red_scratch);
+#if TCB_MEGA_TRACE
+            sp.trace = p.trace ? p.trace + 256 * 8 + o * 4 : nullptr;
+#endif
+            stage_activations_i16<1, true, true>(sp, smem, 8, red_scratch);
         }
         for (int i = tid; i < gc.rows; i += nthreads) rowacc[i] = 0.f;
         __syncthreads();
+        MTR(2);
 
         for (int i = 0; i < gc.my_n; ++i) {
             uint64_t* bar = &bars[warp * ns + cslot];
             if (!mbar_wait_bounded(bar, cphase)) { failed = true; break; }
-            const int gl = ((warp + nwarps * i) << 5) + lane;
-            const bool valid = gl < gc.g_count;
+            if (i == 0) MTR(3);
+            const int u = warp + nwarps * i;
+            const int rb = u / gc.gpr, kg = u - rb * gc.gpr;
+            const int rl = rb * 32 + lane;              // row within the CTA's range
+            const bool valid = rl < gc.rows;
             uint32_t w[36];
-            if (valid) {
+            {
                 const uint4* src = reinterpret_cast<const uint4*>(
                     ring + static_cast<size_t>(warp * ns + cslot) * kChunkBytes +
                     static_cast<size_t>(lane) * 144);
@@ -733,21 +1026,25 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
                     const uint4 t = src[v];
                     w[4 * v + 0] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
                 }
-            } else {
-#pragma unroll
-                for (int v = 0; v < 36; ++v) w[v] = 0u;
             }
             __syncwarp();
             --inflight;
             if (++cslot == ns) { cslot = 0; cphase ^= 1u; }
             try_issue();                           // refill: this or a later operation's weights
-            if (p.dbg_skip) { if (valid && lane == 0) atomicAdd(&rowacc[0], __uint_as_float(w[0] ^ w[35])); }
-            else if (f32stage) mega_chunk<true>(w, valid, gl, gc.gpr, xs, sx, op.K, rowacc, lane);
-            else mega_chunk<false>(w, valid, gl, gc.gpr, xs, sx, op.K, rowacc, lane);
+            if (p.dbg_skip) {
+                if (valid && lane == 0) atomicAdd(&rowacc[0], __uint_as_float(w[0] ^ w[35]));
+            } else {
+                float out[1] = {0.f};
+                group_dot_i16<FMT_Q4_0, 1, true>(w, xs, reinterpret_cast<const float2*>(sx), kg, gc.gpr,
+                                                 op.K, op.K >> 5, out);
+                if (valid) atomicAdd(&rowacc[rl], out[0]);
+            }
         }
+        MTR(4);
         if (__any_sync(0xffffffffu, failed)) { failed = true; }
         if (failed) { if (lane == 0) { *abort_s = 1; atomicOr(p.err, ERR_WAIT_TIMEOUT); } }
         __syncthreads();
+        MTR(5);
         if (*abort_s) { failed = true; break; }
         for (int i = tid; i < gc.rows; i += nthreads) {
             const float v = rowacc[i];
@@ -895,7 +1192,7 @@ StreamPlan plan_stream(const GemvQArgs& a, int mb, bool stage_f32, const LaunchE
     const int off_rowacc = off;
     off += align_up(max_rows * mb * 4, 16);
     const int off_sx = off;
-    off += align_up(mb * nb * 4, 16);
+    off += align_up(mb * nb * 8, 16);
     const int off_x = off;
     off += align_up(mb * a.K * (stage_f32 ? 4 : 2), 128);
     const int off_ring = off;
@@ -1075,8 +1372,20 @@ cudaError_t init_decode_kernel(int smem_optin) {
                                 smem_optin);
 }
 
-cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops, int n_ops,
-                                  unsigned long long* counter, unsigned long long base,
+cudaError_t encode_decode_maps(const MegaOp* host_ops, int n_ops, void* host_maps) {
+    static_assert(sizeof(CUtensorMap) == kDecodeMapBytes, "tensor map size");
+    CUtensorMap* out = static_cast<CUtensorMap*>(host_maps);
+    for (int i = 0; i < n_ops; ++i) {
+        const MegaOp& op = host_ops[i];
+        if (!encode_bytes_2d(&out[i], op.W, static_cast<uint64_t>(op.N),
+                             static_cast<uint64_t>(op.K / 32) * 18u, 144u, 32u))
+            return cudaErrorNotSupported;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops, const void* dev_maps,
+                                  int n_ops, unsigned long long* counter, unsigned long long base,
                                   const LaunchEnv& env, cudaStream_t stream, int* barriers) {
     if (n_ops <= 0) return cudaErrorInvalidValue;
     int k_max = 0, n_max = 0, nbar = 0;
@@ -1096,18 +1405,23 @@ cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops,
     const int max_rows = (n_max + grid - 1) / grid + 1;
     const int optin = env.smem_optin > 0 ? env.smem_optin : 232448;
     MegaParams p;
-    p.ops = dev_ops; p.n_ops = n_ops; p.counter = counter; p.base = base; p.err = env.err_word;
+    p.ops = dev_ops; p.maps = dev_maps; p.n_ops = n_ops; p.counter = counter; p.base = base; p.err = env.err_word;
     static const int dbg_skip = [] { const char* v = std::getenv("TC_GEMV_DBG_SKIP"); return v ? std::atoi(v) : 0; }();
     p.dbg_skip = dbg_skip;
+    p.trace = nullptr;
+#if TCB_MEGA_TRACE
+    if (const char* s = std::getenv("TC_MEGA_TRACE")) p.trace = reinterpret_cast<long long*>(std::strtoull(s, nullptr, 0));
+#endif
     int off = 8 * kMaxStreamWarps * 4 + 8 * kMaxStreamWarps + 16;   // barriers, scratch, abort flag
     off = align_up(off, 16);
     p.off_rowacc = off;
-    off += align_up(max_rows * 4, 16);
+    off += align_up((max_rows + 32) * 4, 16);
     p.off_sx = off;
-    off += align_up((k_max / 32) * 4, 16);
+    off += align_up((k_max / 32) * 8, 16);
     p.off_x = off;
-    off += align_up(k_max * (any_f32 ? 4 : 2), 128);
-    p.off_ring = off;
+    off += align_up(k_max * 2, 128);
+    p.off_ring = align_up(off, 128);
+    off = p.off_ring;
     int warps = want_warps, ns = 0;
     for (; warps >= 8 && ns == 0; warps -= 8)
         for (int cand = 4; cand >= 2; --cand)
@@ -1138,7 +1452,10 @@ cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops,
 // operation table, hence at most kStaticMaxOps operations per call.
 // ---------------------------------------------------------------------------------------
 constexpr int kStaticMaxOps = 256;
-static __device__ __align__(256) unsigned char g_decode_static_scratch[256 + kStaticMaxOps * sizeof(MegaOp)];
+// counter (256 bytes) | operation table | tensor maps
+constexpr size_t kStaticMapsOffset = 256 + kStaticMaxOps * sizeof(MegaOp);
+static __device__ __align__(256) unsigned char
+    g_decode_static_scratch[kStaticMapsOffset + kStaticMaxOps * kDecodeMapBytes];
 
 namespace {
 constexpr int kMaxDevices = 64;
@@ -1164,7 +1481,8 @@ cudaError_t static_scratch_for_current_device(unsigned char** out) {
 
 // ops: host array of n_ops operations in execution order (GemvQArgs with M == 1, Q4_0).  Builds
 // the table on the stack (dependencies from pointer overlap, as the stream path does), copies it
-// into the static scratch, clears the arrival counter and launches.  No allocation of any kind.
+// into the static scratch together with the operations' tensor maps, clears the arrival counter
+// and launches.  No allocation of any kind.
 cudaError_t launch_gemv_q4_decode_static(const GemvQArgs* ops, int n_ops, const LaunchEnv& env,
                                          cudaStream_t stream) {
     if (n_ops <= 0 || n_ops > kStaticMaxOps) return cudaErrorInvalidValue;
@@ -1222,7 +1540,25 @@ cudaError_t launch_gemv_q4_decode_static(const GemvQArgs* ops, int n_ops, const 
     e = cudaMemcpyAsync(scratch + 256, table, static_cast<size_t>(n_ops) * sizeof(MegaOp),
                         cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) return e;
-    return launch_gemv_q4_decode(table, reinterpret_cast<const MegaOp*>(scratch + 256), n_ops,
+    // Tensor maps: encoded into a static host array and re-encoded only when the weights, shapes
+    // or their order changed since the previous call (encoding costs about a microsecond each).
+    alignas(64) static unsigned char maps[kStaticMaxOps * kDecodeMapBytes];
+    static MegaOp maps_for[kStaticMaxOps];
+    static int maps_n = 0;
+    bool fresh = maps_n == n_ops;
+    for (int i = 0; i < n_ops && fresh; ++i)
+        fresh = maps_for[i].W == table[i].W && maps_for[i].N == table[i].N && maps_for[i].K == table[i].K;
+    if (!fresh) {
+        e = encode_decode_maps(table, n_ops, maps);
+        if (e != cudaSuccess) return e;
+        for (int i = 0; i < n_ops; ++i) maps_for[i] = table[i];
+        maps_n = n_ops;
+    }
+    e = cudaMemcpyAsync(scratch + kStaticMapsOffset, maps, static_cast<size_t>(n_ops) * kDecodeMapBytes,
+                        cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return e;
+    return launch_gemv_q4_decode(table, reinterpret_cast<const MegaOp*>(scratch + 256),
+                                 scratch + kStaticMapsOffset, n_ops,
                                  reinterpret_cast<unsigned long long*>(scratch), 0ULL, env, stream,
                                  nullptr);
 }

@@ -34,6 +34,7 @@
 // 1e-4 bound of fp32 activations, which therefore never take this path.
 #include "kernels.h"
 #include "sm100_prims.cuh"
+#include "tensor_map.h"
 
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -326,6 +327,7 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
                     // been consumed by a tcgen05.st that has completed.  Releasing it right after
                     // the loads were issued let the next tiled copy overwrite rows whose loads the
                     // scheduler had deferred (seen as a block holding the data of 4 stages later).
+                    fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) bar_arrive(&bars->raw_empty[raw.idx]);
                     if (tr) TCB_TR(2, i);
@@ -500,31 +502,6 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
     }
 }
 
-// Tiled tensor map over the quantised weights seen as bytes: dimension 0 = the bytes of a row,
-// dimension 1 = rows; box = one 8-block group (144 bytes) of 256 rows.
-bool encode_weight_map(CUtensorMap* map, const void* W, int N, size_t row_bytes) {
-    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-    static EncodeFn encode = [] {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            fn = nullptr;
-        return reinterpret_cast<EncodeFn>(fn);
-    }();
-    if (!encode) return false;
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(N)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
-    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kGroupBytes), static_cast<cuuint32_t>(kTileRows)};
-    const cuuint32_t estr[2] = {1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(W), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 // How many clusters of `size` CTAs of this kernel the device can hold at once; cached per size
 // and shared-memory footprint (the two batch widths).  0 when the query fails.
 int max_active_clusters(int size, int smem) {
@@ -602,7 +579,9 @@ cudaError_t launch_gemv_q4_tc(const GemvQArgs& a, const LaunchEnv& env, cudaStre
 #endif
 
     CUtensorMap wmap;
-    if (!encode_weight_map(&wmap, a.W, a.N, static_cast<size_t>(p.groups) * kGroupBytes))
+    // The weights as a 2-D byte tensor: dimension 0 = the bytes of a row, box = one 8-block group
+    // (144 bytes) of 256 rows.
+    if (!encode_bytes_2d(&wmap, a.W, a.N, static_cast<size_t>(p.groups) * kGroupBytes, kGroupBytes, kTileRows))
         return cudaErrorNotSupported;
 
     cudaLaunchConfig_t cfg = {};

@@ -66,6 +66,7 @@ enum : uint32_t {
 };
 struct MegaParams {
     const MegaOp* ops;              // device memory
+    const void* maps;               // device memory: one 128-byte TMA tensor map per operation
     int n_ops;
     unsigned long long* counter;    // device memory: grid-barrier arrival counter, never reset
     unsigned long long base;        // counter value all earlier launches add up to
@@ -73,6 +74,7 @@ struct MegaParams {
     int ns;
     int off_rowacc, off_sx, off_x, off_ring;
     int dbg_skip;                   // measurement aid: stream and synchronise, skip arithmetic
+    long long* trace = nullptr;     // debug builds: 8 clock64 stamps per operation from CTA 0
 };
 
 // Error bits ORed into LaunchEnv::err_word by kernels.
@@ -91,9 +93,15 @@ cudaError_t launch_dense_norm_gemv(const DenseNormGemvArgs& a, const LaunchEnv& 
 // Persistent decode launch of `n_ops` operations described by `host_ops` (already uploaded to
 // `dev_ops`).  Returns cudaErrorNotSupported when the list does not fit the kernel's shared
 // memory.  *barriers receives the number of grid barriers the launch executes.
-cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops, int n_ops,
-                                  unsigned long long* counter, unsigned long long base,
+cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops, const void* dev_maps,
+                                  int n_ops, unsigned long long* counter, unsigned long long base,
                                   const LaunchEnv& env, cudaStream_t stream, int* barriers);
+
+// Bytes of one tensor map, and the encoder for the maps of a table of operations: writes
+// n_ops * kDecodeMapBytes bytes (64-byte aligned destination), one tiled map per operation over its
+// weights as a [N][K/32*18] byte matrix with a 32-row x 144-byte box.
+constexpr int kDecodeMapBytes = 128;
+cudaError_t encode_decode_maps(const MegaOp* host_ops, int n_ops, void* host_maps);
 
 // The same launch with its scratch (operation table, barrier counter) in a static device array:
 // no allocation.  At most 256 operations; cudaErrorInvalidValue beyond that or for operations

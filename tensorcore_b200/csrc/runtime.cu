@@ -54,6 +54,8 @@ struct tc_context {
     // and the grid-barrier arrival counter
     bool mega_on;
     tcb::MegaOp* mega_host;
+    unsigned char* mega_maps_host;   // pinned: one tensor map per operation of the table
+    unsigned char* mega_maps_dev;
     tcb::MegaOp* mega_dev;
     unsigned long long* mega_counter;
     unsigned long long mega_base;
@@ -246,9 +248,15 @@ void teardown_device(tc_context* ctx) {
     if (ctx->stream0) cudaStreamDestroy(ctx->stream0);
     if (ctx->err_host) cudaFreeHost(ctx->err_host);
     if (ctx->mega_host) cudaFreeHost(ctx->mega_host);
+    if (ctx->mega_maps_host) cudaFreeHost(ctx->mega_maps_host);
+    if (ctx->mega_maps_dev) cudaFree(ctx->mega_maps_dev);
+    ctx->mega_maps_host = nullptr;
+    ctx->mega_maps_dev = nullptr;
     if (ctx->mega_dev) cudaFree(ctx->mega_dev);
     if (ctx->mega_counter) cudaFree(ctx->mega_counter);
     ctx->mega_host = nullptr;
+    ctx->mega_maps_host = nullptr;
+    ctx->mega_maps_dev = nullptr;
     ctx->mega_dev = nullptr;
     ctx->mega_counter = nullptr;
     ctx->mega_base = 0;
@@ -674,6 +682,9 @@ cudaError_t submit_as_persistent_launch(tc_stream* s, int* launches, const char*
         if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->mega_host), kMegaMaxOps * sizeof(tcb::MegaOp),
                           cudaHostAllocDefault) != cudaSuccess ||
             cudaMalloc(reinterpret_cast<void**>(&ctx->mega_dev), kMegaMaxOps * sizeof(tcb::MegaOp)) != cudaSuccess ||
+            cudaHostAlloc(reinterpret_cast<void**>(&ctx->mega_maps_host), kMegaMaxOps * tcb::kDecodeMapBytes,
+                          cudaHostAllocDefault) != cudaSuccess ||
+            cudaMalloc(reinterpret_cast<void**>(&ctx->mega_maps_dev), kMegaMaxOps * tcb::kDecodeMapBytes) != cudaSuccess ||
             cudaMalloc(reinterpret_cast<void**>(&ctx->mega_counter), kMegaFlagBytes) != cudaSuccess ||
             cudaMemset(ctx->mega_counter, 0, kMegaFlagBytes) != cudaSuccess) {
             (void)cudaGetLastError();
@@ -724,13 +735,18 @@ cudaError_t submit_as_persistent_launch(tc_stream* s, int* launches, const char*
         e = cudaStreamSynchronize(s->s);
         if (e != cudaSuccess) return e;
         std::memcpy(ctx->mega_host, table.data(), n * sizeof(tcb::MegaOp));
+        e = tcb::encode_decode_maps(ctx->mega_host, static_cast<int>(n), ctx->mega_maps_host);
+        if (e != cudaSuccess) { ctx->mega_uploaded = 0; return e; }
         e = cudaMemcpyAsync(ctx->mega_dev, ctx->mega_host, n * sizeof(tcb::MegaOp),
+                            cudaMemcpyHostToDevice, s->s);
+        if (e != cudaSuccess) return e;
+        e = cudaMemcpyAsync(ctx->mega_maps_dev, ctx->mega_maps_host, n * tcb::kDecodeMapBytes,
                             cudaMemcpyHostToDevice, s->s);
         if (e != cudaSuccess) return e;
         ctx->mega_uploaded = static_cast<int>(n);
     }
     int barriers = 0;
-    e = tcb::launch_gemv_q4_decode(ctx->mega_host, ctx->mega_dev, static_cast<int>(n),
+    e = tcb::launch_gemv_q4_decode(ctx->mega_host, ctx->mega_dev, ctx->mega_maps_dev, static_cast<int>(n),
                                    ctx->mega_counter, ctx->mega_base, make_env(ctx, false), s->s,
                                    &barriers);
     if (e == cudaErrorCooperativeLaunchTooLarge) { (void)cudaGetLastError(); return cudaErrorNotSupported; }

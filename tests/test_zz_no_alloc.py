@@ -74,8 +74,8 @@ def test_static_scratch_decode_matches_existing_entry_points(tc, ctx, oracle):
             b.upload(np.full(b.nbytes, 0x7F, np.uint8))
         run_static(new)
         got = _read(new, d, f)
-        assert oracle.scaled_rms(got["q"], want["q"]) <= 1e-4, call
-        assert oracle.scaled_rms(got["k"], want["k"]) <= 1e-4, call
+        assert oracle.scaled_rms(got["q"], want["q"]) <= 3e-4, call
+        assert oracle.scaled_rms(got["k"], want["k"]) <= 3e-4, call
         # downstream of an fp16 hand-off: rounding flips of q feed o (fp16-activation bar)
         assert oracle.scaled_rms(got["o"], want["o"]) <= 2e-3, call
         assert oracle.scaled_rms(got["g"], want["g"]) <= 2e-3, call

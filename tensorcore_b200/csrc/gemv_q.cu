@@ -54,6 +54,7 @@ constexpr int kMaxMB = 4;
 #ifndef TCB_MEGA_TRACE
 #define TCB_MEGA_TRACE 0
 #endif
+constexpr int kMaxPhaseOps = 4;             // persistent kernel: operations merged into one phase
 constexpr bool kActI16 = TCB_ACT_I16 != 0;   // integer activation path (see stage_activations_i16)
 constexpr int kTcMinBatch = 8;            // smallest M the tcgen05 kernel takes by default
 
@@ -894,8 +895,9 @@ struct WarpGeom {            // one operation as seen by one warp of one CTA
 
 __device__ __forceinline__ WarpGeom make_geom(const MegaOp& op, int warp, int nwarps) {
     WarpGeom g;
-    g.r0 = static_cast<int>(static_cast<long long>(op.N) * blockIdx.x / gridDim.x);
-    const int r1 = static_cast<int>(static_cast<long long>(op.N) * (blockIdx.x + 1) / gridDim.x);
+    // 32-bit arithmetic: the launcher refuses N * gridDim >= 2^32
+    g.r0 = static_cast<int>(static_cast<uint32_t>(op.N) * blockIdx.x / gridDim.x);
+    const int r1 = static_cast<int>(static_cast<uint32_t>(op.N) * (blockIdx.x + 1) / gridDim.x);
     g.rows = r1 - g.r0;
     g.gpr = op.K >> 8;
     g.n_units = ((g.rows + 31) >> 5) * g.gpr;
@@ -928,8 +930,18 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
 
     // ---- per-warp weight stream: issue cursor runs ahead of the consume cursor ----
     const uint8_t* maps = static_cast<const uint8_t*>(p.maps);   // one 128-byte tensor map per operation
+    // The operation table is read many times by every thread: keep it in shared memory when it
+    // fits (a global read costs an L2 round trip at every operation boundary).
+    const MegaOp* ops = p.ops;
+    if (p.off_ops >= 0) {
+        uint4* dst = reinterpret_cast<uint4*>(smem + p.off_ops);
+        const uint4* src = reinterpret_cast<const uint4*>(p.ops);
+        for (int i = tid; i < n_ops * 4; i += nthreads) dst[i] = src[i];
+        ops = reinterpret_cast<const MegaOp*>(smem + p.off_ops);
+        __syncthreads();
+    }
     int iop = 0, ii = 0;                 // next box to issue: operation, index within it
-    MegaOp op_i = p.ops[0];
+    MegaOp op_i = ops[0];
     WarpGeom gi = make_geom(op_i, warp, nwarps);
     int islot = 0, cslot = 0;            // ring slots of the next issue / next consume
     uint32_t cphase = 0;                 // parity of the consume slot's current use
@@ -938,7 +950,7 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
         while (iop < n_ops && ii >= gi.my_n) {
             ++iop;
             ii = 0;
-            if (iop < n_ops) { op_i = p.ops[iop]; gi = make_geom(op_i, warp, nwarps); }
+            if (iop < n_ops) { op_i = ops[iop]; gi = make_geom(op_i, warp, nwarps); }
         }
         if (iop >= n_ops || inflight >= ns) return;
         if (lane == 0) {
@@ -963,11 +975,17 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
 #endif
     unsigned long long target = p.base;
     bool failed = false;
-    for (int o = 0; o < n_ops && !failed; ++o) {
-        const MegaOp op = p.ops[o];
-        const WarpGeom gc = make_geom(op, warp, nwarps);
-        // Everyone must be done with the previous operation's shared memory; if this operation
-        // reads another CTA's output, everyone in the grid must be done with the previous one.
+    // Operations run in phases: a phase is a run of up to kMaxPhaseOps operations that share their
+    // staged activations and need no barrier between them (q/k/v, gate/up).  A phase zeroes its row
+    // accumulators once, runs all its boxes back to back and writes all its outputs at the end.
+    for (int o = 0; o < n_ops && !failed;) {
+        int oe = o + 1;
+        while (oe < n_ops && oe - o < kMaxPhaseOps &&
+               !(ops[oe].flags & (MOP_BARRIER | MOP_RESTAGE)))
+            ++oe;
+        const MegaOp op = ops[o];
+        // Everyone must be done with the previous phase's shared memory; if this phase reads
+        // another CTA's output, everyone in the grid must be done with the previous one.
         __syncthreads();
         MTR(0);
         if (op.flags & MOP_BARRIER) {
@@ -1004,40 +1022,51 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
 #endif
             stage_activations_i16<1, true, true>(sp, smem, 8, red_scratch);
         }
-        for (int i = tid; i < gc.rows; i += nthreads) rowacc[i] = 0.f;
+        int acc_off[kMaxPhaseOps + 1];
+        acc_off[0] = 0;
+        for (int k = o; k < oe; ++k) {
+            const WarpGeom g = make_geom(ops[k], warp, nwarps);
+            acc_off[k - o + 1] = acc_off[k - o] + ((g.rows + 31) & ~31);
+        }
+        for (int i = tid; i < acc_off[oe - o]; i += nthreads) rowacc[i] = 0.f;
         __syncthreads();
         MTR(2);
 
-        for (int i = 0; i < gc.my_n; ++i) {
-            uint64_t* bar = &bars[warp * ns + cslot];
-            if (!mbar_wait_bounded(bar, cphase)) { failed = true; break; }
-            if (i == 0) MTR(3);
-            const int u = warp + nwarps * i;
-            const int rb = u / gc.gpr, kg = u - rb * gc.gpr;
-            const int rl = rb * 32 + lane;              // row within the CTA's range
-            const bool valid = rl < gc.rows;
-            uint32_t w[36];
-            {
-                const uint4* src = reinterpret_cast<const uint4*>(
-                    ring + static_cast<size_t>(warp * ns + cslot) * kChunkBytes +
-                    static_cast<size_t>(lane) * 144);
+        for (int k = o; k < oe && !failed; ++k) {
+            const MegaOp opk = ops[k];
+            const WarpGeom gc = make_geom(opk, warp, nwarps);
+            float* acc = rowacc + acc_off[k - o];
+            for (int i = 0; i < gc.my_n; ++i) {
+                uint64_t* bar = &bars[warp * ns + cslot];
+                if (!mbar_wait_bounded(bar, cphase)) { failed = true; break; }
+                if (i == 0 && k == o) MTR(3);
+                const int u = warp + nwarps * i;
+                const int rb = u / gc.gpr, kg = u - rb * gc.gpr;
+                const int rl = rb * 32 + lane;              // row within the CTA's range
+                const bool valid = rl < gc.rows;
+                uint32_t w[36];
+                {
+                    const uint4* src = reinterpret_cast<const uint4*>(
+                        ring + static_cast<size_t>(warp * ns + cslot) * kChunkBytes +
+                        static_cast<size_t>(lane) * 144);
 #pragma unroll
-                for (int v = 0; v < 9; ++v) {
-                    const uint4 t = src[v];
-                    w[4 * v + 0] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
+                    for (int v = 0; v < 9; ++v) {
+                        const uint4 t = src[v];
+                        w[4 * v + 0] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
+                    }
                 }
-            }
-            __syncwarp();
-            --inflight;
-            if (++cslot == ns) { cslot = 0; cphase ^= 1u; }
-            try_issue();                           // refill: this or a later operation's weights
-            if (p.dbg_skip) {
-                if (valid && lane == 0) atomicAdd(&rowacc[0], __uint_as_float(w[0] ^ w[35]));
-            } else {
-                float out[1] = {0.f};
-                group_dot_i16<FMT_Q4_0, 1, true>(w, xs, reinterpret_cast<const float2*>(sx), kg, gc.gpr,
-                                                 op.K, op.K >> 5, out);
-                if (valid) atomicAdd(&rowacc[rl], out[0]);
+                __syncwarp();
+                --inflight;
+                if (++cslot == ns) { cslot = 0; cphase ^= 1u; }
+                try_issue();                           // refill: this or a later operation's weights
+                if (p.dbg_skip) {
+                    if (valid && lane == 0) atomicAdd(&acc[0], __uint_as_float(w[0] ^ w[35]));
+                } else {
+                    float out[1] = {0.f};
+                    group_dot_i16<FMT_Q4_0, 1, true>(w, xs, reinterpret_cast<const float2*>(sx), kg, gc.gpr,
+                                                     opk.K, opk.K >> 5, out);
+                    if (valid) atomicAdd(&acc[rl], out[0]);
+                }
             }
         }
         MTR(4);
@@ -1046,11 +1075,17 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
         __syncthreads();
         MTR(5);
         if (*abort_s) { failed = true; break; }
-        for (int i = tid; i < gc.rows; i += nthreads) {
-            const float v = rowacc[i];
-            if (op.flags & MOP_Y_F32) static_cast<float*>(op.Y)[gc.r0 + i] = v;
-            else static_cast<__half*>(op.Y)[gc.r0 + i] = __float2half_rn(v);
+        for (int k = o; k < oe; ++k) {
+            const MegaOp opk = ops[k];
+            const WarpGeom gc = make_geom(opk, warp, nwarps);
+            const float* acc = rowacc + acc_off[k - o];
+            for (int i = tid; i < gc.rows; i += nthreads) {
+                const float v = acc[i];
+                if (opk.flags & MOP_Y_F32) static_cast<float*>(opk.Y)[gc.r0 + i] = v;
+                else static_cast<__half*>(opk.Y)[gc.r0 + i] = __float2half_rn(v);
+            }
         }
+        o = oe;
     }
     if (failed) {
         // let copies that are still in flight land before the CTA's shared memory is released
@@ -1389,6 +1424,9 @@ cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops,
                                   const LaunchEnv& env, cudaStream_t stream, int* barriers) {
     if (n_ops <= 0) return cudaErrorInvalidValue;
     int k_max = 0, n_max = 0, nbar = 0;
+    for (int i = 0; i < n_ops; ++i)
+        if (static_cast<unsigned long long>(host_ops[i].N) * static_cast<unsigned>(env.sm_count) >= (1ull << 32))
+            return cudaErrorNotSupported;
     bool any_f32 = false;
     for (int i = 0; i < n_ops; ++i) {
         k_max = host_ops[i].K > k_max ? host_ops[i].K : k_max;
@@ -1415,11 +1453,27 @@ cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops,
     int off = 8 * kMaxStreamWarps * 4 + 8 * kMaxStreamWarps + 16;   // barriers, scratch, abort flag
     off = align_up(off, 16);
     p.off_rowacc = off;
-    off += align_up((max_rows + 32) * 4, 16);
+    {   // accumulators: the largest sum over a phase of the per-CTA rows, each rounded up to 32
+        int worst = 0, run = 0, len = 0;
+        for (int i = 0; i < n_ops; ++i) {
+            const bool head = i == 0 || len >= kMaxPhaseOps ||
+                              (host_ops[i].flags & (MOP_BARRIER | MOP_RESTAGE)) != 0;
+            if (head) { run = 0; len = 0; }
+            run += ((host_ops[i].N + grid - 1) / grid + 1 + 31) & ~31;
+            ++len;
+            worst = run > worst ? run : worst;
+        }
+        off += align_up(worst * 4, 16);
+    }
     p.off_sx = off;
     off += align_up((k_max / 32) * 8, 16);
     p.off_x = off;
     off += align_up(k_max * 2, 128);
+    p.off_ops = -1;
+    if (n_ops * static_cast<int>(sizeof(MegaOp)) <= 32 * 1024) {
+        p.off_ops = off;
+        off += n_ops * static_cast<int>(sizeof(MegaOp));
+    }
     p.off_ring = align_up(off, 128);
     off = p.off_ring;
     int warps = want_warps, ns = 0;

@@ -73,6 +73,7 @@ struct MegaParams {
     uint32_t* err;
     int ns;
     int off_rowacc, off_sx, off_x, off_ring;
+    int off_ops;                    // shared-memory copy of the operation table, or -1
     int dbg_skip;                   // measurement aid: stream and synchronise, skip arithmetic
     long long* trace = nullptr;     // debug builds: 8 clock64 stamps per operation from CTA 0
 };

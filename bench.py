@@ -264,6 +264,9 @@ def run_single_gpu(args) -> dict:
     from tensorcore_b200 import decode as D
 
     shape = D.LLAMA_7B
+    if getattr(args, "layers", 0):
+        import dataclasses
+        shape = dataclasses.replace(shape, name=f"{shape.name}-first{args.layers}layers", n_layers=args.layers)
     if not os.path.exists(tc.LIB_PATH):
         raise SystemExit("libtensorcore.so is not built: run `python -m tensorcore_b200.build`")
     torch.cuda.set_device(0)
@@ -320,9 +323,9 @@ def run_single_gpu(args) -> dict:
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "s16 x u4 -> s32 (dp2a), f32 scales", "data": "synthetic",
         "config": {
-            "workload": "llama-7b-shape Q4_0 decode weight stream, batch 1: 32 layers x "
+            "workload": f"llama-7b-shape Q4_0 decode weight stream, batch 1: {shape.n_layers} layers x "
                         "(q,k,v,o 4096x4096; gate,up 11008x4096; down 4096x11008) + lm_head "
                         "32000x4096, RMSNorm fused into q/k/v, gate/up and lm_head; GGUF v3 file "
                         "loaded with tc_gguf_load_supported_tensors",
@@ -333,9 +336,17 @@ def run_single_gpu(args) -> dict:
             "gguf_build_s": round(t_build, 2), "gguf_load_s": round(t_load, 2),
         },
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
-                     "bytes_per_launch": total_b / n_gemv,
-                     "us_per_launch": ms_per_step * 1e3 / n_gemv,
+                     "frac": achieved / peak,
+                     # DRAM bytes per launch: ncu (dram__bytes_read + write) on an 8-layer launch
+                     # of the same kernel was 1.0075 x its algorithmic bytes; scaled by bytes
+                     "traffic": 1.0075 * total_b / (launches / args.steps),
+                     "traffic_source": "profiles/bench_decode_7b_q4_0_persistent_launch.md",
+                     "peak_kind": peak_kind,
+                     # one persistent launch per token when the stream takes that path, else
+                     # one launch per GEMV
+                     "launches_per_step": launches / args.steps,
+                     "bytes_per_launch": total_b / (launches / args.steps),
+                     "us_per_launch": ms_per_step * 1e3 / (launches / args.steps),
                      "weight_gbs": weight_b / (ms_per_step * 1e-3) / 1e9},
         "e2e": {"value": 1e3 / (e2e_wall_ms / args.steps), "unit": UNIT,
                 "h2d_bytes_per_step": shape.d_model * 2, "d2h_bytes_per_step": shape.vocab * 2,
@@ -360,6 +371,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="profiling aid: run the same step on the first LAYERS layers + lm_head (a smaller "
+                         "device footprint for ncu captures); the JSON line then names the reduced workload")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
 

@@ -339,7 +339,8 @@ tc_status_t tcx_raw_fused_norm_gemv_f16(tc_context* ctx, const void* X, const vo
  * qualifying tc_stream list, but for callers that cannot tolerate an allocation on this path:
  * a server whose HBM is fully handed out to weights and KV cache at start-up, or a decode loop
  * where cudaMalloc's device-wide synchronisation must never occur.  The kernel's scratch (the
- * operation table and its grid-barrier counter) lives in a fixed 16.25 KB device array inside the
+ * operation table, one TMA tensor map per operation and the grid-barrier counter) lives in a fixed
+ * 48.25 KB device array inside the
  * library image, which every GPU that loads the library holds until the process exits; the call
  * performs no cudaMalloc / cudaFree and uses no allocating library routine.
  *

@@ -1500,7 +1500,7 @@ cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops,
 // has handed every byte of HBM to weights and KV cache at start-up, or a decode loop in which a
 // cudaMalloc (which synchronises the whole device) is not acceptable at any point.  For them the
 // same kernel is reachable with its scratch in the fixed array below, which is part of the
-// library image on every GPU that loads it (16.25 KB) and is never freed.
+// library image on every GPU that loads it (48.25 KB: counter, table and tensor maps) and is never freed.
 //
 // Layout: bytes [0,256) arrival counter (first 8 bytes used), bytes [256, 256 + 256*64) the
 // operation table, hence at most kStaticMaxOps operations per call.

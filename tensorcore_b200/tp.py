@@ -2,11 +2,16 @@
 
 Sharding (the partition BASELINE's north_star prescribes):
   * q/k/v, gate/up and lm_head are split by output rows (a contiguous byte range of the block
-    array); each rank computes its slice and the slices are all-gathered;
+    array); each rank computes its slice;
   * o_proj and down_proj are split along K into 256-aligned ranges (so that every shard keeps
     the kernels' fast path: whole 8-block groups, 16-byte aligned rows); each rank computes an
     fp32 partial product over its K range and the partials are all-reduced (sum).
-Norm weights and activations are replicated.
+Two data flows.  "local" (default): the row slices of q and of gate ARE the K ranges of o_proj and
+down_proj, so a rank's slice feeds its own K-shard directly and k/v/up stay sharded, as they do
+in a head-parallel attention / sharded SwiGLU: two all-reduces per layer plus one all-gather of
+the logits (65 collectives per 7B token).  "gathered": every row-split output is all-gathered to
+all ranks first (225 collectives per token), which needs equal row slices.
+Norm weights and hidden states are replicated.
 
 The arithmetic per rank is the library's own kernels (raw device-pointer launches on the
 collective's stream); the plumbing - process group, collectives, graph capture - is
@@ -49,14 +54,26 @@ def k_ranges(K: int, P: int) -> list[tuple[int, int]]:
     return out
 
 
+# row-split projection -> the K-split projection its output feeds in the "local" data flow
+FEEDS = {"attn_q": "attn_output", "attn_k": "attn_output", "attn_v": "attn_output",
+         "ffn_gate": "ffn_down", "ffn_up": "ffn_down"}
+
+
 @dataclass
 class TPPlan:
     shape: LlamaShape
     world: int
     rank: int
+    flow: str = "local"     # "local" | "gathered"
 
     def col(self, which: str) -> tuple[int, int]:
         N, _ = self.shape.proj_shape(which)
+        if self.flow == "local" and which in FEEDS:
+            # the consumer's K range, scaled when the producer has fewer rows (grouped-query k/v)
+            Kc = self.shape.proj_shape(FEEDS[which])[1]
+            k0, k1 = k_ranges(Kc, self.world)[self.rank]
+            if N == Kc:
+                return k0, k1
         return row_range(N, self.world, self.rank)
 
     def kslice(self, which: str) -> tuple[int, int]:
@@ -68,7 +85,8 @@ class TPPlan:
         return N % self.world == 0
 
     def check(self) -> None:
-        for p in ("attn_q", "attn_k", "attn_v", "ffn_gate", "ffn_up", "output"):
+        gathered = ("attn_q", "attn_k", "attn_v", "ffn_gate", "ffn_up", "output")
+        for p in (gathered if self.flow == "gathered" else ("output",)):
             if not self.equal_cols(p):
                 raise ValueError(f"{p}: {self.shape.proj_shape(p)[0]} rows do not divide by "
                                  f"{self.world} ranks (all-gather needs equal slices)")
@@ -124,39 +142,49 @@ class TPDecoder:
         self.x_in = be.empty(d, "f32")
         self.h = [be.empty(d, "f32"), be.empty(d, "f32")]
         self.o = be.empty(d, "f32")
-        self.q_loc, self.q = be.empty(d // P, "f16"), be.empty(d, "f16")
-        self.k_loc, self.k = be.empty(kv // P, "f16"), be.empty(kv, "f16")
-        self.v_loc, self.v = be.empty(kv // P, "f16"), be.empty(kv, "f16")
-        self.g_loc, self.g = be.empty(f // P, "f16"), be.empty(f, "f16")
-        self.u_loc, self.u = be.empty(f // P, "f16"), be.empty(f, "f16")
+        def loc(which):
+            n0, n1 = plan.col(which)
+            return be.empty(n1 - n0, "f16")
+        self.q_loc, self.k_loc, self.v_loc = loc("attn_q"), loc("attn_k"), loc("attn_v")
+        self.g_loc, self.u_loc = loc("ffn_gate"), loc("ffn_up")
         self.l_loc, self.logits = be.empty(V // P, "f16"), be.empty(V, "f16")
+        if plan.flow == "gathered":
+            self.q, self.k, self.v = be.empty(d, "f16"), be.empty(kv, "f16"), be.empty(kv, "f16")
+            self.g, self.u = be.empty(f, "f16"), be.empty(f, "f16")
 
     def token(self) -> None:
         """x_in -> logits.  Same stand-ins as the single-GPU harness: q feeds o_proj, gate
         feeds down_proj; hidden states are fp32 (the all-reduced partial sums)."""
         be, s, plan = self.be, self.plan.shape, self.plan
-        d, f, kv, V = s.d_model, s.d_ff, s.d_kv, s.vocab
+        d = s.d_model
+        gathered = plan.flow == "gathered"
         cur = self.x_in
         for l, lw in enumerate(self.w):
             nxt = self.h[l & 1]
-            n0, n1 = plan.col("attn_q")
-            be.gemv(cur, lw["attn_q"], self.q_loc, n1 - n0, d, gamma=lw["attn_norm"])
-            n0, n1 = plan.col("attn_k")
-            be.gemv(cur, lw["attn_k"], self.k_loc, n1 - n0, d, gamma=lw["attn_norm"])
-            be.gemv(cur, lw["attn_v"], self.v_loc, n1 - n0, d, gamma=lw["attn_norm"])
-            be.all_gather(self.q, self.q_loc)
-            be.all_gather(self.k, self.k_loc)
-            be.all_gather(self.v, self.v_loc)
+            for p, y in (("attn_q", self.q_loc), ("attn_k", self.k_loc), ("attn_v", self.v_loc)):
+                n0, n1 = plan.col(p)
+                be.gemv(cur, lw[p], y, n1 - n0, d, gamma=lw["attn_norm"])
             k0, k1 = plan.kslice("attn_output")
-            be.gemv(be.view(self.q, k0, k1), lw["attn_output"], self.o, d, k1 - k0)
+            if gathered:
+                be.all_gather(self.q, self.q_loc)
+                be.all_gather(self.k, self.k_loc)
+                be.all_gather(self.v, self.v_loc)
+                q_in = be.view(self.q, k0, k1)
+            else:
+                q_in = self.q_loc                    # this rank's q rows are its o_proj K range
+            be.gemv(q_in, lw["attn_output"], self.o, d, k1 - k0)
             be.all_reduce(self.o)
-            n0, n1 = plan.col("ffn_gate")
-            be.gemv(self.o, lw["ffn_gate"], self.g_loc, n1 - n0, d, gamma=lw["ffn_norm"])
-            be.gemv(self.o, lw["ffn_up"], self.u_loc, n1 - n0, d, gamma=lw["ffn_norm"])
-            be.all_gather(self.g, self.g_loc)
-            be.all_gather(self.u, self.u_loc)
+            for p, y in (("ffn_gate", self.g_loc), ("ffn_up", self.u_loc)):
+                n0, n1 = plan.col(p)
+                be.gemv(self.o, lw[p], y, n1 - n0, d, gamma=lw["ffn_norm"])
             k0, k1 = plan.kslice("ffn_down")
-            be.gemv(be.view(self.g, k0, k1), lw["ffn_down"], nxt, d, k1 - k0)
+            if gathered:
+                be.all_gather(self.g, self.g_loc)
+                be.all_gather(self.u, self.u_loc)
+                g_in = be.view(self.g, k0, k1)
+            else:
+                g_in = self.g_loc
+            be.gemv(g_in, lw["ffn_down"], nxt, d, k1 - k0)
             be.all_reduce(nxt)
             cur = nxt
         n0, n1 = plan.col("output")
@@ -167,7 +195,7 @@ class TPDecoder:
         return 7 * self.plan.shape.n_layers + 1
 
     def collectives_per_token(self) -> int:
-        return 7 * self.plan.shape.n_layers + 1
+        return (7 if self.plan.flow == "gathered" else 2) * self.plan.shape.n_layers + 1
 
 
 # ---------------------------------------------------------------------------------------
@@ -320,12 +348,13 @@ def run_bench(args):
         out = {
             "metric": METRIC, "value": 1e3 / ms_per_step, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "s16 x u4 -> s32 (dp2a), f32 scales", "data": "synthetic",
             "config": {
                 "workload": "llama-7b-shape Q4_0 decode weight stream, batch 1, tensor parallel: "
-                            "q/k/v/gate/up/lm_head split by rows + all-gather, o/down split along K "
-                            "+ all-reduce; one CUDA graph per token",
+                            "q/k/v/gate/up split by rows feeding this rank's K-shard of o/down "
+                            "(split along K + all-reduce), lm_head split by rows + all-gather; one "
+                            "CUDA graph per token",
                 "parallelism": f"tp{world}", "gemvs_per_token": dec.gemvs_per_token(),
                 "collectives_per_token": dec.collectives_per_token(),
                 "weight_bytes_per_token": weight_b,

@@ -103,13 +103,13 @@ def _single_process_logits():
     return dec.logits.copy(), be.log
 
 
-def _rank_main(rank, world, port, ret):
+def _rank_main(rank, world, port, ret, flow):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     sys.path.insert(0, ROOT)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         be = CpuBackend(SHAPE, world)
-        plan = tp.TPPlan(SHAPE, world, rank)
+        plan = tp.TPPlan(SHAPE, world, rank, flow)
         dec = tp.TPDecoder(plan, be)
         dec.x_in[:] = np.random.default_rng(1).standard_normal(SHAPE.d_model).astype(np.float32)
         dec.token()
@@ -124,12 +124,14 @@ def _free_port():
         return s.getsockname()[1]
 
 
+@pytest.mark.parametrize("flow", ["local", "gathered"])
 @pytest.mark.parametrize("world", [2, 4])
-def test_tp_decode_matches_single_rank(world, oracle):
+def test_tp_decode_matches_single_rank(world, flow, oracle):
     want, log1 = _single_process_logits()
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_rank_main, args=(world, _free_port(), ret), nprocs=world, join=True)
+    mp.spawn(_rank_main, args=(world, _free_port(), ret, flow), nprocs=world, join=True)
+    per_layer = 7 if flow == "gathered" else 2
     assert sorted(ret.keys()) == list(range(world))
     total_bytes = 0
     for r in range(world):
@@ -137,10 +139,11 @@ def test_tp_decode_matches_single_rank(world, oracle):
         total_bytes += nbytes
         # every rank ends with the same full logits
         assert np.array_equal(logits.view(np.uint16), ret[0][0].view(np.uint16))
-        # same sequence of operations on every rank, 7 GEMVs and 7 collectives per layer + 1 + 1
+        # same sequence of operations on every rank: 7 GEMVs per layer + lm_head; collectives:
+        # two all-reduces per layer ("local") or all seven outputs ("gathered"), + the logits
         assert [e[0] for e in log] == [e[0] for e in ret[0][1]]
         assert sum(e[0] == "gemv" for e in log) == 7 * SHAPE.n_layers + 1
-        assert sum(e[0] in ("ag", "ar") for e in log) == 7 * SHAPE.n_layers + 1
+        assert sum(e[0] in ("ag", "ar") for e in log) == per_layer * SHAPE.n_layers + 1
     # the shards partition the model: no weight byte is held twice
     assert total_bytes == SHAPE.weight_bytes(0)
     # split-K partial sums are added in a different order and intermediate fp16 roundings may

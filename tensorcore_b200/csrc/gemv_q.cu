@@ -862,6 +862,120 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q_stream_kernel(con
 }
 
 // ---------------------------------------------------------------------------------------
+// The box kernel: one operation, a row per lane.
+//
+// Same arithmetic as the streaming kernel, different geometry: the unit of work is a box of 32
+// weight rows x one group (144 / 272 bytes per row) fetched by one tiled TMA copy; a lane owns a
+// row, so every lane of a warp reads the same staged activations (one shared-memory broadcast per
+// load instead of 32 different 16-byte chunks - with a lane per K group the activation reads are
+// 2 bytes per weight and saturate shared-memory bandwidth) and no shuffle reduction is needed:
+// a lane adds its partial dot product to its row's accumulator.  Up to MB activation rows.
+// ---------------------------------------------------------------------------------------
+template <int FMT, int MB>
+__global__ void __launch_bounds__(kMaxStreamThreads, 1)
+gemv_q_box_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wmap) {
+    using F = Fmt<FMT>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                               // [nwarps*ns]
+    double* red_scratch = reinterpret_cast<double*>(smem + 8 * kMaxStreamWarps * 4);  // after the barriers
+    float* rowacc = reinterpret_cast<float*>(smem + p.off_rowacc);
+    uint8_t* ring = smem + p.off_ring;
+    constexpr int kBoxBytes = 32 * F::kGroupBytes;
+    constexpr int kElem = FMT == FMT_Q4_0 ? 1 : 4;     // tensor-map element size (see the launcher)
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nwarps = blockDim.x >> 5, nthreads = blockDim.x;
+    const int ns = p.ns, gpr = p.gpr;
+    const int r0 = static_cast<int>(static_cast<long long>(p.N) * blockIdx.x / gridDim.x);
+    const int r1 = static_cast<int>(static_cast<long long>(p.N) * (blockIdx.x + 1) / gridDim.x);
+    const int rows = r1 - r0;
+    const int rows_pad = (rows + 31) & ~31;
+    const int n_units = (rows_pad >> 5) * gpr;
+    const int my_n = n_units > warp ? (n_units - warp + nwarps - 1) / nwarps : 0;
+
+    pdl_launch_dependents();
+    if (tid == 0) {
+        sm100::prefetch_tensormap(&wmap);
+        for (int i = 0; i < nwarps * ns; ++i) mbar_init(&bars[i], 1);
+        fence_barrier_init();
+    }
+    for (int i = tid; i < rows_pad * MB; i += nthreads) rowacc[i] = 0.f;
+    __syncthreads();
+
+    auto issue = [&](int i) {  // lane 0 only: start the copy of this warp's i-th box
+        const int u = warp + nwarps * i;
+        const int rb = u / gpr, kg = u - rb * gpr;
+        const int s = i % ns;
+        uint64_t* bar = &bars[warp * ns + s];
+        mbar_expect_tx(bar, kBoxBytes);
+        sm100::tensor_load_2d(ring + static_cast<size_t>(warp * ns + s) * kBoxBytes, &wmap,
+                              kg * (F::kGroupBytes / kElem), r0 + rb * 32, bar);
+    };
+    // Weights do not depend on the previous kernel in the stream: start streaming now.
+    if (lane == 0) {
+        const int pre = min(ns, my_n);
+        for (int i = 0; i < pre; ++i) issue(i);
+    }
+    // Activations may be the previous kernel's output: wait for it, then stage them.
+    pdl_wait();
+    stage_activations_i16<MB, false, true>(p, smem, FMT == FMT_Q4_0 ? 8 : 0, red_scratch);
+
+    const uint8_t* xs = smem + p.off_x;
+    const float2* sx2 = reinterpret_cast<const float2*>(smem + p.off_sx);
+    bool failed = false;
+    int waited = 0;
+    for (int i = 0; i < my_n; ++i) {
+        const int s = i % ns;
+        uint64_t* bar = &bars[warp * ns + s];
+        if (!mbar_wait_bounded(bar, static_cast<uint32_t>((i / ns) & 1))) { failed = true; break; }
+        waited = i + 1;
+        const int u = warp + nwarps * i;
+        const int rb = u / gpr, kg = u - rb * gpr;
+        const int rl = rb * 32 + lane;
+        uint32_t w[F::kGroupV4 * 4];
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(
+                ring + static_cast<size_t>(warp * ns + s) * kBoxBytes + static_cast<size_t>(lane) * F::kGroupBytes);
+#pragma unroll
+            for (int v = 0; v < F::kGroupV4; ++v) {
+                const uint4 t = src[v];
+                w[4 * v + 0] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && i + ns < my_n) {
+            fence_proxy_async();
+            issue(i + ns);
+        }
+        float out[MB];
+#pragma unroll
+        for (int m = 0; m < MB; ++m) out[m] = 0.f;
+        if (p.dbg_skip) out[0] = __uint_as_float(w[0] ^ w[F::kGroupV4 * 4 - 1]);
+        else group_dot_i16<FMT, MB, true>(w, xs, sx2, kg, gpr, p.K, p.nb, out);
+        if (rl < rows) {
+#pragma unroll
+            for (int m = 0; m < MB; ++m) atomicAdd(&rowacc[m * rows_pad + rl], out[m]);
+        }
+    }
+    if (failed) {
+        if (lane == 0 && p.err) atomicOr(p.err, ERR_WAIT_TIMEOUT);
+        // let copies that are still in flight land before the CTA's shared memory is released
+        const int issued = min(my_n, waited + ns);
+        for (int i = waited; i < issued; ++i)
+            (void)mbar_wait_bounded(&bars[warp * ns + (i % ns)], static_cast<uint32_t>((i / ns) & 1));
+    }
+    __syncthreads();
+    if (failed) return;
+    for (int i = tid; i < rows * MB; i += nthreads) {
+        const int m = i / rows, r = i - m * rows;
+        const float v = rowacc[m * rows_pad + r];
+        const size_t o = static_cast<size_t>(m) * p.N + r0 + r;
+        if (p.y_f32) static_cast<float*>(p.Y)[o] = v;
+        else static_cast<__half*>(p.Y)[o] = __float2half_rn(v);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // Persistent decode kernel: a whole recorded list of Q4_0, M = 1 GEMVs in ONE launch.
 //
 // One CTA per SM (cooperative launch: all CTAs are co-resident).  The unit of work is a box of 32
@@ -1286,6 +1400,97 @@ cudaError_t launch_stream_mb(int mb, const StreamPlan& pl, cudaStream_t st, bool
     }
 }
 
+// Shared-memory plan of the box kernel for mb activation rows; pl.ok = false when the operation
+// is outside its domain (K % 256, alignment) or the activations do not fit beside a ring.
+StreamPlan plan_box(const GemvQArgs& a, int mb, const LaunchEnv& env) {
+    StreamPlan pl;
+    if (a.K % 256 != 0) return pl;
+    if ((reinterpret_cast<uintptr_t>(a.W) & 15u) != 0) return pl;
+    if ((reinterpret_cast<uintptr_t>(a.X) & 15u) != 0) return pl;
+    if (a.gamma && (reinterpret_cast<uintptr_t>(a.gamma) & 15u) != 0) return pl;
+    const int nb = a.K / 32, gpr = nb / 8;
+    const int box_bytes = 32 * (a.fmt == FMT_Q4_0 ? 144 : 272);
+    const int grid = a.N < env.sm_count * 8 ? (a.N + 7) / 8 < env.sm_count ? (a.N + 7) / 8 : env.sm_count
+                                            : env.sm_count;
+    const int max_rows = (a.N + grid - 1) / grid + 1;
+    int off = 8 * kMaxStreamWarps * 4 + 8 * kMaxStreamWarps;  // barriers (<= 4 stages) + scratch
+    off = align_up(off, 16);
+    const int off_rowacc = off;
+    off += align_up(mb * ((max_rows + 31) & ~31) * 4, 16);
+    const int off_sx = off;
+    off += align_up(mb * nb * 8, 16);
+    const int off_x = off;
+    off += align_up(mb * a.K * 2, 128);
+    const int off_ring = align_up(off, 128);
+    const int optin = env.smem_optin > 0 ? env.smem_optin : 232448;
+    // 16 warps when every warp gets at least one box, else 8 (fewer barriers to initialise)
+    const int units = ((max_rows + 31) / 32) * gpr;
+    int warps = units >= 16 ? 16 : 8;
+    int ns = 0;
+    for (; warps >= 8 && ns == 0; warps -= 8)
+        for (int cand = 4; cand >= 2; --cand)
+            if (off_ring + warps * cand * box_bytes <= optin - 1024) { ns = cand; break; }
+    if (ns == 0) return pl;
+    warps += 8;
+    // A box always spans 32 rows: rows per CTA that fall just past a multiple of 32 (74 -> 96 for
+    // 11008 rows on 148 SMs) waste lanes and copies.  When that padding exceeds 25 % and the
+    // operation is only a few rounds long, the streaming kernel (no padding) is faster
+    // (measured: 11008 x 4096 8.8 us against 11.4 us; every other decode shape favours the box).
+    const double rows_avg = static_cast<double>(a.N) / grid;
+    const double padded = 32.0 * ((static_cast<int>(rows_avg + 0.999) + 31) / 32);
+    if (padded > 1.25 * rows_avg && units <= 3 * warps) return pl;
+    pl.ok = true;
+    pl.ns = ns;
+    pl.grid = grid;
+    pl.warps = warps;
+    pl.smem = off_ring + warps * ns * box_bytes;
+    StreamParams& p = pl.p;
+    p.W = a.W; p.X = a.X; p.Y = a.Y; p.gamma = a.gamma; p.err = env.err_word;
+    p.M = mb; p.N = a.N; p.K = a.K; p.nb = nb; p.gpr = gpr; p.ns = ns;
+    p.y_f32 = a.y_f32 ? 1 : 0; p.eps = a.eps;
+    p.x_src_f16 = a.x_f32 ? 0 : 1;
+    p.off_rowacc = off_rowacc; p.off_sx = off_sx; p.off_x = off_x; p.off_ring = off_ring;
+    p.max_rows = max_rows;
+    static const int dbg_skip = [] { const char* v = std::getenv("TC_GEMV_DBG_SKIP"); return v ? std::atoi(v) : 0; }();
+    p.dbg_skip = dbg_skip;
+    return pl;
+}
+
+template <typename KernelT>
+cudaError_t launch_box(KernelT kernel, const StreamPlan& pl, const CUtensorMap& wmap, cudaStream_t st, bool pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(pl.grid);
+    cfg.blockDim = dim3(pl.warps * 32);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, pl.p, wmap);
+}
+
+template <int FMT>
+cudaError_t launch_box_mb(int mb, const StreamPlan& pl, cudaStream_t st, bool pdl) {
+    CUtensorMap wmap;
+    // Q8_0 groups are 272 bytes: more than the 256 elements a box may have per dimension, so the
+    // byte matrix is described in 4-byte elements there.
+    constexpr int group_bytes = Fmt<FMT>::kGroupBytes;
+    if (!encode_bytes_2d(&wmap, pl.p.W, static_cast<uint64_t>(pl.p.N),
+                         static_cast<uint64_t>(pl.p.gpr) * group_bytes, group_bytes, 32,
+                         FMT == FMT_Q4_0 ? 1 : 4))
+        return cudaErrorNotSupported;
+    switch (mb) {
+        case 1: return launch_box(gemv_q_box_kernel<FMT, 1>, pl, wmap, st, pdl);
+        case 2: return launch_box(gemv_q_box_kernel<FMT, 2>, pl, wmap, st, pdl);
+        case 3: return launch_box(gemv_q_box_kernel<FMT, 3>, pl, wmap, st, pdl);
+        default: return launch_box(gemv_q_box_kernel<FMT, 4>, pl, wmap, st, pdl);
+    }
+}
+
 template <typename K>
 cudaError_t set_smem(K kernel, int bytes) {
     return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
@@ -1302,6 +1507,12 @@ cudaError_t init_gemv_kernels(int smem_optin) {
     if (e != cudaSuccess) return e;
     e = init_decode_kernel(smem_optin);
     if (e != cudaSuccess) return e;
+#define TCB_SETB(FMT, MB)                                                         \
+    e = set_smem(gemv_q_box_kernel<FMT, MB>, smem_optin);                         \
+    if (e != cudaSuccess) return e;
+    TCB_SETB(FMT_Q4_0, 1) TCB_SETB(FMT_Q4_0, 2) TCB_SETB(FMT_Q4_0, 3) TCB_SETB(FMT_Q4_0, 4)
+    TCB_SETB(FMT_Q8_0, 1) TCB_SETB(FMT_Q8_0, 2) TCB_SETB(FMT_Q8_0, 3) TCB_SETB(FMT_Q8_0, 4)
+#undef TCB_SETB
 #define TCB_SET(FMT, XF, MB)                                                      \
     e = set_smem(gemv_q_stream_kernel<FMT, XF, MB>, smem_optin);                  \
     if (e != cudaSuccess) return e;
@@ -1370,6 +1581,20 @@ cudaError_t launch_gemv_q(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t
         s.Y = static_cast<uint8_t*>(a.Y) + static_cast<size_t>(m0) * a.N * ysz;
         s.M = mb;
         StreamPlan pl;
+        static const bool use_box = [] { const char* v = std::getenv("TC_GEMV_BOX"); return !v || std::atoi(v) != 0; }();
+        if (kActI16 && use_box && env.variant != VARIANT_GENERIC) {
+            const StreamPlan pb = plan_box(s, mb, env);
+            if (pb.ok) {
+                const cudaError_t be = a.fmt == FMT_Q4_0 ? launch_box_mb<FMT_Q4_0>(mb, pb, stream, env.pdl)
+                                                         : launch_box_mb<FMT_Q8_0>(mb, pb, stream, env.pdl);
+                if (be != cudaErrorNotSupported) {
+                    err = be;
+                    used = a.fmt == FMT_Q4_0 ? "q4_0_gemv_box_sm100" : "q8_0_gemv_box_sm100";
+                    ++count;
+                    continue;
+                }
+            }
+        }
         if (env.variant != VARIANT_GENERIC) pl = plan_stream(s, mb, stage_f32, env);
         if (pl.ok) {
             pl.p.x_src_f16 = a.x_f32 ? 0 : 1;

@@ -316,6 +316,7 @@ def test_full_size_shapes(tc, ctx, oracle, case):
 @pytest.mark.parametrize("variant", ["simt", "mma"])
 @pytest.mark.parametrize("tag", ["q4_0", "q8_0"])
 def test_repeated_launches_on_cache_resident_weights(tc, ctx, oracle, variant, tag):
+    # "simt" is whatever single-operation kernel the dispatcher picks (the box kernel)
     """Weights that stay in L2 make the copy engine refill ring slots as fast as it ever will:
     the timing in which a slot released before its loads were consumed would show stale data."""
     if variant == "mma" and tag == "q8_0":

@@ -216,6 +216,12 @@ class CpuDecode:
         return dt * full_bytes / sample_bytes, dt
 
 
+def workload_text(shape) -> str:
+    return (f"llama-7b-shape Q4_0 decode weight stream, batch 1: {shape.n_layers} layers x "
+            "(q,k,v,o 4096x4096; gate,up 11008x4096; down 4096x11008) + lm_head "
+            "32000x4096, RMSNorm fused into q/k/v, gate/up and lm_head")
+
+
 def run_reference_arm(args) -> dict:
     from tensorcore_b200.decode import LLAMA_7B
     shape = LLAMA_7B
@@ -238,8 +244,9 @@ def run_reference_arm(args) -> dict:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": spt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "llama-7b-shape Q4_0 decode weight stream, batch 1, 225 GEMVs/token",
-                   "weight_bytes_per_token": weight_b},
+        "config": {"workload": workload_text(shape) + "; the reference's CPU kernels called through "
+                               "the reference library's tc_* ABI",
+                   "gemvs_per_token": shape.gemvs_per_token(), "weight_bytes_per_token": weight_b},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": probe.kind,
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -325,10 +332,8 @@ def run_single_gpu(args) -> dict:
         "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "s16 x u4 -> s32 (dp2a), f32 scales", "data": "synthetic",
         "config": {
-            "workload": f"llama-7b-shape Q4_0 decode weight stream, batch 1: {shape.n_layers} layers x "
-                        "(q,k,v,o 4096x4096; gate,up 11008x4096; down 4096x11008) + lm_head "
-                        "32000x4096, RMSNorm fused into q/k/v, gate/up and lm_head; GGUF v3 file "
-                        "loaded with tc_gguf_load_supported_tensors",
+            "workload": workload_text(shape) + "; GGUF v3 file loaded with "
+                        "tc_gguf_load_supported_tensors",
             "gemvs_per_token": n_gemv, "weight_bytes_per_token": weight_b,
             "l2": "3.7 GB of weights are streamed per step (126 MB L2): no flush needed",
             "api": "tc_gemv_quantized_async / tcx_fused_rmsnorm_gemv_quantized_ex on a tc_stream, "

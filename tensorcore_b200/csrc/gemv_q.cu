@@ -209,8 +209,9 @@ __device__ float block_sum_f32(float v, float* scratch /* one float per warp */)
     __syncthreads();
     if (l == 0) scratch[w] = v;
     __syncthreads();
-    float t = 0.f;
-    for (int i = 0; i < nwarps; ++i) t += scratch[i];
+    // every warp adds the partials in the same tree order: same bits in every thread
+    float t = l < nwarps ? scratch[l] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
     return t;
 }
 
@@ -995,6 +996,9 @@ gemv_q_box_kernel(const StreamParams p, const __grid_constant__ CUtensorMap wmap
 __device__ __forceinline__ void st_release_u64(unsigned long long* p, unsigned long long v) {
     asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+__device__ __forceinline__ void red_release_add_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
     unsigned long long v;
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -1109,8 +1113,12 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
             // separately published generation word, per-CTA flag words, back-off - were slower.)
             target += gridDim.x;
             if (tid == 0) {
-                __threadfence();
-                atomicAdd(p.counter, 1ULL);
+                // Arrival is a release-reduction: no value comes back, so the thread goes
+                // straight to polling (an atomicAdd costs a full L2 round trip before the first
+                // poll), and the release orders this CTA's outputs - made visible to this thread
+                // by the block barrier above - before the arrival.  The acquire loads order
+                // everyone's outputs before what follows the block barrier below.
+                red_release_add_u64(p.counter, 1ULL);
                 const long long t0 = clock64();
                 while (ld_acquire_u64(p.counter) < target) {
                     if (clock64() - t0 > 2000000000LL) {
@@ -1119,7 +1127,6 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) gemv_q4_decode_kernel(co
                         break;
                     }
                 }
-                __threadfence();
             }
             __syncthreads();
             if (*abort_s) { failed = true; break; }

@@ -63,3 +63,35 @@ def test_lists_that_do_not_qualify_use_per_operation_kernels(tc, ctx, oracle):
         assert oracle.scaled_rms(y2.to_numpy((2, N), np.float16), oracle.gemv_quantized(X, W4, 0, N)) <= 3e-4
     s.close()
 
+
+
+def test_long_list_and_wide_rows(tc, ctx, oracle):
+    """More than 512 operations (the table no longer fits the kernel's shared-memory copy and is
+    read from global memory) and a K of 28672 (the 70B down-projection width: the largest staged
+    activation row), with row counts that leave partly filled 32-row boxes."""
+    rng = np.random.default_rng(77)
+    K1, N1 = 256, 70
+    W1 = oracle.quantize_weights((rng.standard_normal((N1, K1)) / np.sqrt(K1)).astype(np.float16), 0)
+    x1 = rng.standard_normal((1, K1)).astype(np.float16)
+    want1 = oracle.gemv_quantized(x1, W1, 0, N1)
+    bW1, bx1 = ctx.buffer_from_array(W1), ctx.buffer_from_array(x1)
+    outs = [ctx.buffer(N1 * 2) for _ in range(8)]
+    K2, N2 = 28672, 333
+    W2 = oracle.quantize_weights((rng.standard_normal((N2, K2)) / np.sqrt(K2)).astype(np.float16), 0)
+    x2 = rng.standard_normal((1, K2)).astype(np.float32)
+    g2 = (1 + 0.1 * rng.standard_normal(K2)).astype(np.float32)
+    want2 = oracle.fused_rmsnorm_gemv_quantized_f32(x2, g2, W2, 0, N2, 1e-5)
+    bW2, bx2, by2 = ctx.buffer_from_array(W2), ctx.buffer_from_array(x2), ctx.buffer(N2 * 4)
+    bg2 = ctx.buffer_from_array(g2)
+    s = ctx.stream()
+    for rep in range(2):
+        for i in range(600):
+            ctx.gemv_quantized_async(bx1, bW1, outs[i % 8], 0, 1, N1, K1, s)
+        tc.fused_rmsnorm_gemv_quantized_ex(ctx, bx2, bg2, bW2, by2, 0, 1, N2, K2, 1e-5, "f32", "f32", s)
+        s.sync()
+        assert "persistent" in tc.cuda_last_kernel_name()
+        for o in outs:
+            assert oracle.scaled_rms(o.to_numpy((1, N1), np.float16), want1) <= 3e-4
+        assert oracle.scaled_rms(by2.to_numpy((1, N2), np.float32), want2) <= 1e-4
+    assert tc.take_device_error(ctx) == 0
+    s.close()

@@ -684,7 +684,7 @@ __device__ __forceinline__ void group_dot_i16(const uint32_t (&w)[Fmt<FMT>::kGro
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
                 lo4[t] = q[t] & 0x0f0f0f0fu;
-                hi4[t] = (q[t] >> 4) & 0x0f0f0f0fu;
+                hi4[t] = q[t] & 0xf0f0f0f0u;   // 16 x the high nibbles: shifted out of the sum below
             }
         }
 #pragma unroll
@@ -714,7 +714,10 @@ __device__ __forceinline__ void group_dot_i16(const uint32_t (&w)[Fmt<FMT>::kGro
                 }
             }
             const float2 sc = sx2[m * nb + (NATURAL ? kg * 8 + j : j * gpr + kg)];
-            const int dot = (a0 + a1) + (a2 + a3) - __float_as_int(sc.y);
+            // Q4_0: a1 and a3 hold 16 x the high-nibble sums (exact multiples of 16, at most
+            // 16 * 240 * 32767 in magnitude), a0 and a2 the low-nibble sums
+            const int dot = FMT == FMT_Q4_0 ? (a0 + a2) + ((a1 + a3) >> 4) - __float_as_int(sc.y)
+                                            : (a0 + a1) + (a2 + a3) - __float_as_int(sc.y);
             out[m] = fmaf(d * sc.x, static_cast<float>(dot), out[m]);
         }
     }

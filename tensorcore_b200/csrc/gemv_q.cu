@@ -56,7 +56,7 @@ constexpr int kMaxMB = 4;
 #endif
 constexpr int kMaxPhaseOps = 4;             // persistent kernel: operations merged into one phase
 constexpr bool kActI16 = TCB_ACT_I16 != 0;   // integer activation path (see stage_activations_i16)
-constexpr int kTcMinBatch = 8;            // smallest M the tcgen05 kernel takes by default
+constexpr int kTcMinBatch = 5;            // smallest M the tcgen05 kernel takes by default (measured: faster from M = 5 on every decode shape)
 
 template <int FMT> struct Fmt;
 template <> struct Fmt<FMT_Q4_0> {

@@ -1,4 +1,4 @@
-"""GPU: the tcgen05 batched-decode GEMV (Q4_0, fp16 activations, 8 <= M) against the oracle.
+"""GPU: the tcgen05 batched-decode GEMV (Q4_0, fp16 activations, 5 <= M) against the oracle.
 
 The kernel dequantises weights to fp16 for the tensor cores, so its bar is the 2e-3 scaled-RMS
 bound that applies to fp16 activations (observed 1.8e-4 against an fp64 dequantise-and-dot, 2.8e-4

@@ -7,7 +7,7 @@ take exact integer dot products, so the error is the 2^-16-of-block-maximum quan
 fp16-ABI GEMV / fused outputs within 3e-4 of the oracle's fp16 outputs (both sides rounded to
 fp16, so the difference is fp16 rounding flips: observed 1.0-1.9e-4; the bound stated for fp16
 activations is 2e-3) and within 2.5e-4 of fp64 (the fp16 output rounding floor is 2.1e-4).  Batched
-calls (M >= 8, Q4_0, fp16 activations) run on the tcgen05 kernel, which rounds dequantised weights
+calls (M >= 5, Q4_0, fp16 activations) run on the tcgen05 kernel, which rounds dequantised weights
 to fp16 (observed 1.8e-4): for those the bar is the 2e-3 that applies to fp16 activations.
 """
 import os
@@ -144,7 +144,7 @@ def test_gemv_fp16_abi(tc, ctx, oracle, tag, shape):
     want16 = oracle.gemv_quantized(X, Wq, fmt, N)
     want64 = oracle.dequant_dot_f64(X.astype(np.float64), Wq, fmt, N)
     batched = "tcgen05" in tc.cuda_last_kernel_name()
-    assert batched == (tag == "q4_0" and M >= 8 and K % 256 == 0)
+    assert batched == (tag == "q4_0" and M >= 5 and K % 256 == 0)
     assert oracle.scaled_rms(got, want16) <= tol_f16(tc)
     if M * N >= 64:   # an RMS over a handful of fp16 roundings is not a statistic
         assert oracle.scaled_rms(got, want64) <= (TOL_F16_ACT if batched else TOL_VS_F64_F16OUT)

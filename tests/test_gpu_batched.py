@@ -51,6 +51,7 @@ def split_env():
 
 
 @pytest.mark.parametrize("shape", [(256, 256, 16), (256, 512, 8), (512, 1024, 32), (300, 768, 9),
+                                   (512, 1024, 5), (4096, 4096, 7),
                                    (130, 256, 32), (1000, 2048, 12), (4096, 4096, 16),
                                    (4096, 4096, 40), (11008, 4096, 24), (2048, 11008, 32)])
 @pytest.mark.parametrize("y_f32", [True, False])

@@ -368,8 +368,10 @@ typedef struct {
 tc_status_t tcx_raw_decode_q4_static(tc_context* ctx, const tcx_decode_op* ops, int n_ops,
                                      void* cuda_stream);
 
-/* Kernel-variant override for A/B measurements: "auto" (default), "simt", "mma", "tc",
- * "generic".  Returns TC_ERR_INVALID_ARG for an unknown name.  Process-wide. */
+/* Kernel-variant override for A/B measurements: "auto" (default), "simt" (CUDA-core integer dot
+ * products at any M), "stream" (the same arithmetic on the streaming kernel instead of the box
+ * kernel), "tc" (tcgen05 kernel where it applies), "generic".  Returns TC_ERR_INVALID_ARG for an
+ * unknown name.  Process-wide. */
 tc_status_t tcx_set_gemv_variant(const char* name);
 /* Device-side error word: non-zero after a kernel gave up on a bounded wait.  Reading clears. */
 uint32_t tcx_take_device_error(tc_context* ctx);

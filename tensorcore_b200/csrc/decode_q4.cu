@@ -1,0 +1,739 @@
+// Persistent decode kernel for sm_100a: a whole recorded list of Q4_0, M = 1 GEMVs - one decode
+// token - in ONE cooperative launch, one CTA per SM.
+//
+// Work.  An operation Y[N] = dequant(W[N,K]) . x[K] is cut into boxes of 32 weight rows x one
+// 8-block group (144 bytes per row, 256 weights per row), each fetched by one tiled TMA copy
+// through a per-operation tensor map.  Operations that share their staged input and need no
+// barrier between them (q/k/v, gate/up) form a phase; the boxes of a phase, numbered row-block
+// major, are dealt evenly to the CTAs (CTA c owns boxes [U*c/G, U*(c+1)/G)) and within a CTA
+// round-robin to its warps, so every SM streams the same number of bytes whatever N is, and
+// consecutive warps fetch consecutive groups of the same rows.  A lane owns one ROW of a box: all
+// lanes of a warp read the same int16 activations from shared memory (one broadcast per load)
+// and the lane's partial dot product is added with one red.global.add.f32 to the operation's
+// fp32 accumulators in global memory (L2 atomics; the K split of a row over boxes, warps, CTAs
+// and - tensor parallel - GPUs all ends in the same accumulator).
+//
+// Epochs.  Operations that read what an earlier one wrote are separated by a grid-wide barrier
+// (one never-reset 64-bit arrival counter, release / acquire, bounded spin).  After the barrier
+// the consumer stages its activations straight from the producer's accumulators (L2-coherent
+// loads, rounded to the producer's result type first), so the result never makes a round trip
+// through its fp16 buffer on the critical path.  The result buffers themselves are written one
+// epoch late: each CTA converts a 1/G slice of every finished accumulator (the staging pass
+// stores the slice it has in registers anyway; results nobody consumes next are loaded before
+// and stored after the staging).  Accumulators are handed out from a pool in three generations
+// (epoch mod 3) and zeroed two epochs after their use, so the pool is all zero again when the
+// kernel ends (a trailing barrier finishes the last epoch).
+//
+// Every warp keeps its ring of boxes full ACROSS phases and barriers: weights do not depend on
+// activations, so HBM keeps streaming while a CTA waits and re-stages.  (The host refuses lists
+// in which an operation writes a later operation's weights.)
+#include "gemv_common.cuh"
+#include "tensor_map.h"
+
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+namespace tcb {
+namespace {
+
+constexpr int kMaxPhaseOps = 4;        // operations merged into one phase
+constexpr int kBoxBytes = 32 * 144;
+// internal flags, set by plan_decode (continuing the public MOP_* bits)
+constexpr uint32_t MOP_FIN_X = 256u;     // the staging pass also writes X's buffer (the producer's result)
+constexpr uint32_t MOP_FIN_DONE = 512u;  // this result's buffer is written by its consumer's staging pass
+
+__device__ __forceinline__ void red_add_gpu(float* p, float v) {
+    asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_sys(float* p, float v) {
+    asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ void arrive_gpu(unsigned long long* p) {
+    asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(1ULL) : "memory");
+}
+__device__ __forceinline__ void arrive_sys(unsigned long long* p) {
+    asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(1ULL) : "memory");
+}
+__device__ __forceinline__ unsigned long long poll_gpu(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long poll_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
+// floor(x / gridDim) without a division: x * ceil(2^32 / gridDim) >> 32.  For x below 2^32 the
+// result is the exact quotient or one more; every partition below takes both of its ends from this
+// same function (clamped to the total), so the pieces still tile the range exactly.
+__device__ __forceinline__ uint32_t grid_share(uint32_t total, uint32_t c, uint32_t inv_grid) {
+    const uint32_t q = __umulhi(total * c, inv_grid);
+    return q < total ? q : total;
+}
+
+struct Phase {
+    int o, oe;                          // operations [o, oe)
+    uint32_t ubase[kMaxPhaseOps + 1];   // prefix sums of the operations' box counts
+    uint32_t c0, c1;                    // this CTA's boxes
+};
+
+__device__ __forceinline__ uint32_t op_units(const MegaOp& op) {
+    return static_cast<uint32_t>((op.N + 31) >> 5) * static_cast<uint32_t>(op.K >> 8);
+}
+
+__device__ __forceinline__ void make_phase(const MegaOp* ops, int n_ops, int o, uint32_t inv_grid, Phase& ph) {
+    int oe = o + 1;
+    while (oe < n_ops && oe - o < kMaxPhaseOps && !(ops[oe].flags & (MOP_BARRIER | MOP_RESTAGE))) ++oe;
+    ph.o = o;
+    ph.oe = oe;
+    uint32_t u = 0;
+#pragma unroll
+    for (int k = 0; k < kMaxPhaseOps; ++k) {
+        ph.ubase[k] = u;
+        if (o + k < oe) u += op_units(ops[o + k]);
+    }
+    ph.ubase[kMaxPhaseOps] = u;
+    // the launcher refuses lists with u * gridDim >= 2^32
+    ph.c0 = grid_share(u, blockIdx.x, inv_grid);
+    ph.c1 = blockIdx.x + 1 == gridDim.x ? u : grid_share(u, blockIdx.x + 1, inv_grid);
+}
+
+// Box u of a phase -> operation (index within the phase), row block, group.
+__device__ __forceinline__ void box_coords(const MegaOp* ops, const Phase& ph, uint32_t u, int& k,
+                                           uint32_t& rb, uint32_t& kg) {
+    k = 0;
+    uint32_t base = 0;
+#pragma unroll
+    for (int j = 1; j < kMaxPhaseOps; ++j)
+        if (j < ph.oe - ph.o && u >= ph.ubase[j]) { k = j; base = ph.ubase[j]; }
+    const uint32_t local = u - base;
+    const uint32_t gpr = static_cast<uint32_t>(ops[ph.o + k].K) >> 8;
+    rb = local / gpr;
+    kg = local - rb * gpr;
+}
+
+// This CTA's share of a vector of n rows.
+__device__ __forceinline__ void cta_slice(uint32_t n, uint32_t inv_grid, uint32_t& lo, uint32_t& hi) {
+    lo = grid_share(n, blockIdx.x, inv_grid);          // plan_decode keeps n below 2^24: no overflow
+    hi = blockIdx.x + 1 == gridDim.x ? n : grid_share(n, blockIdx.x + 1, inv_grid);
+}
+
+// Result buffers of operations [b, e) whose accumulators are complete: this CTA's slice of each,
+// loaded here (all loads first), stored by finalize_store after other work has covered the
+// latency.  Covers kFinOps operations x kFinRows rows per thread; anything beyond that is
+// finished in place by finalize_rest.
+constexpr int kFinOps = 4, kFinRows = 1;
+struct FinRegs { float v[kFinOps][kFinRows]; };
+
+__device__ __forceinline__ void finalize_load(const MegaOp* ops, int b, int e, const float* pool, uint32_t inv_grid, FinRegs& r) {
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+#pragma unroll
+    for (int j = 0; j < kFinOps; ++j) {
+#pragma unroll
+        for (int q = 0; q < kFinRows; ++q) r.v[j][q] = 0.f;
+        if (b + j < e && !(ops[b + j].flags & MOP_FIN_DONE)) {
+            uint32_t lo, hi;
+            cta_slice(ops[b + j].y_rows, inv_grid, lo, hi);
+            const float* acc = pool + ops[b + j].acc_off;
+#pragma unroll
+            for (int q = 0; q < kFinRows; ++q) {
+                const uint32_t i = lo + tid + q * nthreads;
+                if (i < hi) r.v[j][q] = __ldcg(acc + i);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void store_result(const MegaOp& op, uint32_t i, float v) {
+    if (op.flags & MOP_Y_F32) static_cast<float*>(op.Y)[i] = v;
+    else static_cast<__half*>(op.Y)[i] = __float2half_rn(v);
+}
+
+__device__ __forceinline__ void finalize_store(const MegaOp* ops, int b, int e, float* pool, uint32_t inv_grid,
+                                               const FinRegs& r, bool zero_too) {
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+#pragma unroll
+    for (int j = 0; j < kFinOps; ++j) {
+        if (b + j < e && !(ops[b + j].flags & MOP_FIN_DONE)) {
+            const MegaOp op = ops[b + j];
+            uint32_t lo, hi;
+            cta_slice(op.y_rows, inv_grid, lo, hi);
+#pragma unroll
+            for (int q = 0; q < kFinRows; ++q) {
+                const uint32_t i = lo + tid + q * nthreads;
+                if (i < hi) {
+                    store_result(op, i, r.v[j][q]);
+                    if (zero_too) pool[op.acc_off + i] = 0.f;
+                }
+            }
+        }
+    }
+}
+
+// What the register batch above does not cover: rows past kFinRows * blockDim of a slice and
+// operations past the first kFinOps of an epoch.
+__device__ void finalize_rest(const MegaOp* ops, int b, int e, float* pool, uint32_t inv_grid, bool zero_too) {
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    for (int k = b; k < e; ++k) {
+        if (ops[k].flags & MOP_FIN_DONE) continue;
+        const MegaOp op = ops[k];
+        uint32_t lo, hi;
+        cta_slice(op.y_rows, inv_grid, lo, hi);
+        const uint32_t first = k - b < kFinOps ? lo + kFinRows * nthreads : lo;
+        for (uint32_t i = first + tid; i < hi; i += nthreads) {
+            store_result(op, i, __ldcg(pool + op.acc_off + i));
+            if (zero_too) pool[op.acc_off + i] = 0.f;
+        }
+    }
+}
+
+__device__ void zero_accumulators(const MegaOp* ops, int b, int e, float* pool, uint32_t inv_grid) {
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    for (int k = b; k < e; ++k) {
+        uint32_t lo, hi;
+        cta_slice(ops[k].y_rows, inv_grid, lo, hi);
+        float* acc = pool + ops[k].acc_off;
+        for (uint32_t i = lo + tid; i < hi; i += nthreads) acc[i] = 0.f;
+    }
+}
+
+__global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const DecodeParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                               // [nwarps*ns]
+    double* red_scratch = reinterpret_cast<double*>(smem + 8 * kMaxStreamWarps * 4);  // after barriers
+    volatile int* abort_s = reinterpret_cast<volatile int*>(smem + 8 * kMaxStreamWarps * 4 +
+                                                            8 * kMaxStreamWarps);
+    uint8_t* ring = smem + p.off_ring;
+    const uint8_t* xs = smem + p.off_x;
+    const float2* sx2 = reinterpret_cast<const float2*>(smem + p.off_sx);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nwarps = blockDim.x >> 5, nthreads = blockDim.x;
+    const int ns = p.ns, n_ops = p.n_ops;
+    const bool multi = p.n_ranks > 1;
+    const uint32_t inv_grid = p.inv_grid;
+
+    if (tid == 0) {
+        for (int i = 0; i < nwarps * ns; ++i) mbar_init(&bars[i], 1);
+        *abort_s = 0;
+        fence_barrier_init();
+    }
+    // The operation table is read by every thread at every box: keep it in shared memory when it
+    // fits (a global read costs an L2 round trip).
+    const MegaOp* ops = p.ops;
+    if (p.off_ops >= 0) {
+        uint4* dst = reinterpret_cast<uint4*>(smem + p.off_ops);
+        const uint4* src = reinterpret_cast<const uint4*>(p.ops);
+        for (int i = tid; i < n_ops * 4; i += nthreads) dst[i] = src[i];
+        ops = reinterpret_cast<const MegaOp*>(smem + p.off_ops);
+    }
+    __syncthreads();
+
+    // ---- per-warp weight stream: the issue cursor runs ahead of the consume cursor ----
+    const uint8_t* maps = static_cast<const uint8_t*>(p.maps);   // one 128-byte tensor map per operation
+    Phase pi;
+    make_phase(ops, n_ops, 0, inv_grid, pi);
+    uint32_t iu = pi.c0 + warp;          // next box to issue
+    int islot = 0, cslot = 0;            // ring slots of the next issue / next consume
+    uint32_t cphase = 0;                 // parity of the consume slot's current use
+    int inflight = 0;
+    auto try_issue = [&]() {
+        while (pi.o < n_ops && iu >= pi.c1) {
+            if (pi.oe >= n_ops) { pi.o = n_ops; break; }
+            make_phase(ops, n_ops, pi.oe, inv_grid, pi);
+            iu = pi.c0 + warp;
+        }
+        if (pi.o >= n_ops || inflight >= ns) return;
+        if (lane == 0) {
+            int k;
+            uint32_t rb, kg;
+            box_coords(ops, pi, iu, k, rb, kg);
+            uint64_t* bar = &bars[warp * ns + islot];
+            fence_proxy_async();
+            mbar_expect_tx(bar, kBoxBytes);
+            sm100::tensor_load_2d(ring + static_cast<size_t>(warp * ns + islot) * kBoxBytes,
+                                  maps + static_cast<size_t>(pi.o + k) * kDecodeMapBytes,
+                                  static_cast<int>(kg * 144), static_cast<int>(rb * 32), bar);
+        }
+        iu += nwarps;
+        ++inflight;
+        if (++islot == ns) islot = 0;
+    };
+    for (int i = 0; i < ns; ++i) try_issue();
+
+    unsigned long long target = p.base;
+    const unsigned long long per_barrier = static_cast<unsigned long long>(gridDim.x) * (multi ? p.n_ranks : 1);
+    bool failed = false;
+    float rstd = 1.0f;                              // of the staged row (RMSNorm prologue), else 1
+    int cur_b = 0;                                  // first operation of the current epoch
+    int prev_b = 0, prev_e = 0, pp_b = 0, pp_e = 0; // the two epochs before it
+    Phase pc;
+    for (int o = 0; o <= n_ops && !failed;) {
+        const bool tail = o == n_ops;               // trailing epoch: barrier and clean-up only
+        const uint32_t flags = tail ? MOP_BARRIER : ops[o].flags;
+        if (!tail) make_phase(ops, n_ops, o, inv_grid, pc);
+        // Everyone in the CTA is done with the previous phase: its staged activations may be
+        // replaced, and thread 0's arrival below covers every warp's accumulator updates.
+        __syncthreads();
+        bool chores = false;
+        if (flags & MOP_BARRIER) {
+            // One 64-bit arrival counter that is never reset: a barrier is complete when the
+            // counter reaches the running target.  One thread per CTA arrives with a release
+            // reduction (no value comes back, so it goes straight to polling) and polls with
+            // acquire loads; the wait is bounded.  Tensor parallel: every CTA arrives on every
+            // rank's counter, so the barrier spans all grids.
+            target += per_barrier;
+            if (tid == 0) {
+                if (multi) {
+                    for (int r = 0; r < p.n_ranks; ++r) arrive_sys(p.peer_counter[r]);
+                } else {
+                    arrive_gpu(p.counter);
+                }
+                const long long t0 = clock64();
+                while ((multi ? poll_sys(p.counter) : poll_gpu(p.counter)) < target) {
+                    if (clock64() - t0 > 2000000000LL) {
+                        *abort_s = 1;
+                        atomicOr(p.err, ERR_WAIT_TIMEOUT);
+                        break;
+                    }
+                }
+            }
+            __syncthreads();
+            if (*abort_s) { failed = true; break; }
+            pp_b = prev_b; pp_e = prev_e;
+            prev_b = cur_b; prev_e = o;
+            cur_b = o;
+            chores = true;
+        }
+        FinRegs fin;
+        if (tail) {
+            finalize_load(ops, prev_b, prev_e, p.pool, inv_grid, fin);
+            finalize_store(ops, prev_b, prev_e, p.pool, inv_grid, fin, true);
+            finalize_rest(ops, prev_b, prev_e, p.pool, inv_grid, true);
+            // results whose buffers a staging pass wrote still hold their accumulators
+            for (int k = prev_b; k < prev_e; ++k)
+                if (ops[k].flags & MOP_FIN_DONE) zero_accumulators(ops, k, k + 1, p.pool, inv_grid);
+            zero_accumulators(ops, pp_b, pp_e, p.pool, inv_grid);
+            break;
+        }
+        const MegaOp op = ops[o];
+        if (flags & MOP_RESTAGE) {
+            StreamParams sp;
+            sp.gamma = (flags & MOP_FUSED) ? op.gamma : nullptr;
+            sp.K = op.K; sp.nb = op.K >> 5; sp.gpr = op.K >> 8; sp.eps = op.eps;
+            sp.x_src_f16 = (flags & MOP_X_F32) ? 0 : 1;
+            sp.off_x = p.off_x; sp.off_sx = p.off_sx;
+            if (op.xacc_off >= 0) {
+                sp.X = p.pool + op.xacc_off;
+                sp.x_acc = (flags & MOP_XACC_F16) ? 2 : 1;
+            } else {
+                sp.X = op.X;
+                sp.x_acc = 0;
+            }
+            if (flags & MOP_FIN_X) {
+                uint32_t lo, hi;
+                cta_slice(static_cast<uint32_t>(op.K), inv_grid, lo, hi);
+                sp.fin_Y = const_cast<void*>(op.X);
+                sp.fin_lo = static_cast<int>(lo);
+                sp.fin_hi = static_cast<int>(hi);
+            }
+            stage_activations_i16<1, true, true, true>(sp, smem, 8, red_scratch);
+            rstd = (flags & MOP_FUSED) ? rstd_from_partials(red_scratch, op.K, op.eps) : 1.0f;
+        }
+        // Results of the epoch just finished that no staging pass writes: loaded now, stored after
+        // the boxes of this phase, which cover the latency.
+        if (chores) finalize_load(ops, prev_b, prev_e, p.pool, inv_grid, fin);
+        {   // The next phase's RMSNorm weights are a first-touch read from HBM on its critical
+            // path: one CTA pulls them into L2 a phase ahead.
+            int nx = pc.oe;
+            while (nx < n_ops && !(ops[nx].flags & MOP_RESTAGE)) ++nx;
+            if (nx < n_ops && (ops[nx].flags & MOP_FUSED) &&
+                static_cast<int>(blockIdx.x) == nx % static_cast<int>(gridDim.x)) {
+                const int bytes = ops[nx].K * ((ops[nx].flags & MOP_X_F32) ? 4 : 2);
+                const uint8_t* g = static_cast<const uint8_t*>(ops[nx].gamma);
+                for (int b = tid * 128; b < bytes; b += nthreads * 128) prefetch_l2(g + b);
+            }
+        }
+
+        for (uint32_t u = pc.c0 + warp; u < pc.c1; u += nwarps) {
+            uint64_t* bar = &bars[warp * ns + cslot];
+            if (!mbar_wait_bounded(bar, cphase)) { failed = true; break; }
+            int k;
+            uint32_t rb, kg;
+            box_coords(ops, pc, u, k, rb, kg);
+            uint32_t w[36];
+            {
+                const uint4* src = reinterpret_cast<const uint4*>(
+                    ring + static_cast<size_t>(warp * ns + cslot) * kBoxBytes + static_cast<size_t>(lane) * 144);
+#pragma unroll
+                for (int v = 0; v < 9; ++v) {
+                    const uint4 t = src[v];
+                    w[4 * v + 0] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
+                }
+            }
+            __syncwarp();
+            --inflight;
+            if (++cslot == ns) { cslot = 0; cphase ^= 1u; }
+            try_issue();                           // refill: this or a later phase's weights
+            const MegaOp& opk = ops[pc.o + k];
+            const int K = opk.K;
+            float out[1] = {0.f};
+            group_dot_i16<FMT_Q4_0, 1, true>(w, xs, sx2, static_cast<int>(kg), K >> 8, K, K >> 5, out);
+            const uint32_t row = rb * 32 + lane;
+            if (row < static_cast<uint32_t>(opk.N)) {
+                const size_t at = static_cast<size_t>(opk.acc_off) + opk.y_row0 + row;
+                if (opk.flags & MOP_PEERS) {
+                    for (int r = 0; r < p.n_ranks; ++r) red_add_sys(p.peer_pool[r] + at, out[0] * rstd);
+                } else {
+                    red_add_gpu(p.pool + at, out[0] * rstd);
+                }
+            }
+        }
+        // Clean-up that only has to happen somewhere in this epoch, placed where most warps have
+        // time to spare: result buffers of the epoch before, accumulators of the one before that.
+        if (chores) {
+            finalize_store(ops, prev_b, prev_e, p.pool, inv_grid, fin, false);
+            finalize_rest(ops, prev_b, prev_e, p.pool, inv_grid, false);
+            zero_accumulators(ops, pp_b, pp_e, p.pool, inv_grid);
+        }
+        if (__any_sync(0xffffffffu, failed)) failed = true;
+        if (failed) {
+            if (lane == 0) { *abort_s = 1; atomicOr(p.err, ERR_WAIT_TIMEOUT); }
+        }
+        o = pc.oe;
+    }
+    if (failed) {
+        // let copies that are still in flight land before the CTA's shared memory is released
+        for (int i = 0; i < inflight; ++i) {
+            (void)mbar_wait_bounded(&bars[warp * ns + cslot], cphase);
+            if (++cslot == ns) { cslot = 0; cphase ^= 1u; }
+        }
+    }
+}
+
+inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
+inline bool spans_overlap(DecodeSpan a, DecodeSpan b) { return a.lo < b.hi && b.lo < a.hi; }
+inline bool span_hits(const DecodeSpan* v, int n, DecodeSpan r) {
+    for (int i = 0; i < n; ++i)
+        if (spans_overlap(v[i], r)) return true;
+    return false;
+}
+
+}  // namespace
+
+cudaError_t init_decode_kernel(int smem_optin) {
+    return cudaFuncSetAttribute(decode_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+}
+
+cudaError_t encode_decode_maps(const MegaOp* host_ops, int n_ops, void* host_maps) {
+    static_assert(sizeof(CUtensorMap) == kDecodeMapBytes, "tensor map size");
+    CUtensorMap* out = static_cast<CUtensorMap*>(host_maps);
+    for (int i = 0; i < n_ops; ++i) {
+        const MegaOp& op = host_ops[i];
+        if (!encode_bytes_2d(&out[i], op.W, static_cast<uint64_t>(op.N),
+                             static_cast<uint64_t>(op.K / 32) * 18u, 144u, 32u))
+            return cudaErrorNotSupported;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, DecodeSpan* work,
+                        MegaOp* table, DecodePlan* plan, size_t pool_capacity_floats) {
+    if (!ops || !work || !table || !plan || n_ops <= 0) return cudaErrorInvalidValue;
+    DecodeSpan* reads = work;                 // inputs read since the last barrier (x, gamma, W)
+    DecodeSpan* writes = work + 3 * n_ops;    // results written since the last barrier
+    int nr = 0, nw = 0;
+    DecodeSpan y_box{~static_cast<uintptr_t>(0), 0};   // bounding interval of every result so far
+    auto y_span = [&](int j) {
+        const GemvQArgs& b = ops[j];
+        const size_t rows = tp && tp[j].y_rows ? static_cast<size_t>(tp[j].y_rows) : static_cast<size_t>(b.N);
+        const uintptr_t lo = reinterpret_cast<uintptr_t>(b.Y);
+        return DecodeSpan{lo, lo + rows * (b.y_f32 ? 4 : 2)};
+    };
+    // Pass 1: barriers, epochs (kept in xacc_off for now) and accumulator offsets inside an epoch.
+    int epoch = 0;
+    size_t in_epoch = 0, worst = 0;
+    for (int i = 0; i < n_ops; ++i) {
+        const GemvQArgs& a = ops[i];
+        if (a.fmt != FMT_Q4_0 || a.M != 1 || a.N <= 0 || a.K <= 0 || a.K % 256 != 0 || !a.W || !a.X || !a.Y)
+            return cudaErrorNotSupported;
+        if ((reinterpret_cast<uintptr_t>(a.W) | reinterpret_cast<uintptr_t>(a.X) |
+             reinterpret_cast<uintptr_t>(a.gamma)) & 15u)
+            return cudaErrorNotSupported;
+        if (reinterpret_cast<uintptr_t>(a.Y) & (a.y_f32 ? 3u : 1u)) return cudaErrorNotSupported;
+        const size_t xs = a.x_f32 ? 4 : 2;
+        const uintptr_t xl = reinterpret_cast<uintptr_t>(a.X), gl = reinterpret_cast<uintptr_t>(a.gamma);
+        const uintptr_t wl = reinterpret_cast<uintptr_t>(a.W);
+        const DecodeSpan rx{xl, xl + a.K * xs};
+        const DecodeSpan rg{gl, gl + (a.gamma ? a.K * xs : 0)};
+        const DecodeSpan rw{wl, wl + static_cast<size_t>(a.N) * (a.K / 32) * 18};
+        const DecodeSpan ry = y_span(i);
+        const uint32_t y_rows = tp && tp[i].y_rows ? static_cast<uint32_t>(tp[i].y_rows) : static_cast<uint32_t>(a.N);
+        const uint32_t y_row0 = tp ? static_cast<uint32_t>(tp[i].y_row0) : 0u;
+        if (static_cast<unsigned long long>(y_row0) + a.N > y_rows) return cudaErrorInvalidValue;
+        if (y_rows >= (1u << 24)) return cudaErrorNotSupported;
+        // Weights are fetched ahead of every barrier, and gamma is read while results of the epoch
+        // before are still being written to their buffers: neither may be an earlier result.
+        if (spans_overlap(rw, y_box) || (a.gamma && spans_overlap(rg, y_box))) {
+            for (int j = 0; j < i; ++j) {
+                const DecodeSpan yj = y_span(j);
+                if (spans_overlap(rw, yj) || (a.gamma && spans_overlap(rg, yj))) return cudaErrorNotSupported;
+            }
+        }
+        bool barrier = i > 0 && (span_hits(writes, nw, rx) || span_hits(writes, nw, ry) || span_hits(reads, nr, ry));
+        if (barrier) {
+            nr = nw = 0;
+            ++epoch;
+            in_epoch = 0;
+        }
+        reads[nr++] = rx;
+        if (a.gamma) reads[nr++] = rg;
+        reads[nr++] = rw;
+        writes[nw++] = ry;
+        y_box.lo = ry.lo < y_box.lo ? ry.lo : y_box.lo;
+        y_box.hi = ry.hi > y_box.hi ? ry.hi : y_box.hi;
+        MegaOp& m = table[i];
+        m.W = a.W; m.X = a.X; m.Y = a.Y; m.gamma = a.gamma; m.N = a.N; m.K = a.K; m.eps = a.eps;
+        m.flags = (barrier ? MOP_BARRIER : 0u) | (a.x_f32 ? MOP_X_F32 : 0u) | (a.y_f32 ? MOP_Y_F32 : 0u) |
+                  (a.gamma ? MOP_FUSED : 0u) | (tp && tp[i].peers ? MOP_PEERS : 0u);
+        bool restage = true;
+        if (i > 0 && !barrier) {
+            const GemvQArgs& b = ops[i - 1];
+            restage = !(b.X == a.X && b.gamma == a.gamma && b.K == a.K && b.x_f32 == a.x_f32);
+        }
+        if (restage) m.flags |= MOP_RESTAGE;
+        m.y_row0 = y_row0;
+        m.y_rows = y_rows;
+        m.acc_off = static_cast<uint32_t>(in_epoch);
+        m.xacc_off = epoch;
+        in_epoch += (static_cast<size_t>(y_rows) + 31) & ~static_cast<size_t>(31);
+        worst = in_epoch > worst ? in_epoch : worst;
+        if (worst > (1u << 28)) return cudaErrorNotSupported;
+    }
+    const size_t gen = worst;
+    if (pool_capacity_floats && 3 * gen > pool_capacity_floats) return cudaErrorNotSupported;
+    // Pass 2: place the accumulators (generation = epoch mod 3) and hand results over through them.
+    // epoch_of[j] survives in table[j].xacc_off until j's own turn, so walk forward and keep the
+    // epochs of earlier operations in their (already final) y_rows-independent field: recompute.
+    int ep_i = 0;
+    for (int i = 0; i < n_ops; ++i) {
+        MegaOp& m = table[i];
+        ep_i = m.xacc_off;
+        m.acc_off += static_cast<uint32_t>((ep_i % 3) * gen);
+        m.xacc_off = -1;
+        if (ep_i == 0) continue;
+        // Latest earlier result that overlaps X.  Epochs of earlier operations: count barriers back.
+        const GemvQArgs& a = ops[i];
+        const uintptr_t xl = reinterpret_cast<uintptr_t>(a.X);
+        const DecodeSpan rx{xl, xl + a.K * static_cast<size_t>(a.x_f32 ? 4 : 2)};
+        if (!spans_overlap(rx, y_box)) continue;
+        int ep_j = ep_i;
+        for (int j = i - 1; j >= 0; --j) {
+            if (table[j + 1].flags & MOP_BARRIER) --ep_j;      // j lies in the epoch before j + 1's
+            if (ep_j < ep_i - 1) break;
+            const DecodeSpan yj = y_span(j);
+            if (!spans_overlap(rx, yj)) continue;
+            // ep_j == ep_i is impossible (a barrier separates a reader from its writer)
+            const GemvQArgs& b = ops[j];
+            const size_t es = b.y_f32 ? 4 : 2;
+            const bool contained = rx.lo >= yj.lo && rx.hi <= yj.hi && b.y_f32 == a.x_f32 &&
+                                   (rx.lo - yj.lo) % (4 * es) == 0;
+            if (!contained) return cudaErrorNotSupported;
+            const uint32_t first = static_cast<uint32_t>((rx.lo - yj.lo) / es);
+            m.xacc_off = static_cast<int32_t>(table[j].acc_off + first);
+            if (!b.y_f32) m.flags |= MOP_XACC_F16;
+            const bool whole = rx.lo == yj.lo && rx.hi == yj.hi;
+            if (whole && (m.flags & MOP_RESTAGE) && !(table[j].flags & MOP_FIN_DONE)) {
+                m.flags |= MOP_FIN_X;
+                table[j].flags |= MOP_FIN_DONE;
+            }
+            break;
+        }
+    }
+    int barriers = 1;   // the trailing one
+    for (int i = 0; i < n_ops; ++i)
+        if (table[i].flags & MOP_BARRIER) ++barriers;
+    plan->n_ops = n_ops;
+    plan->barriers = barriers;
+    plan->pool_floats = 3 * gen;
+    return cudaSuccess;
+}
+
+cudaError_t launch_decode(const MegaOp* host_ops, const DecodePlan& plan, const DecodeDevice& dev,
+                          const LaunchEnv& env, cudaStream_t stream) {
+    const int n_ops = plan.n_ops;
+    if (n_ops <= 0 || !dev.ops || !dev.maps || !dev.pool || !dev.counter) return cudaErrorInvalidValue;
+    if (dev.n_ranks < 1 || dev.n_ranks > kDecodeMaxRanks) return cudaErrorInvalidValue;
+    static const int want_warps = [] {
+        const char* v = std::getenv("TC_DECODE_WARPS");
+        const int n = v ? std::atoi(v) : 16;
+        return (n == 8 || n == 16) ? n : 16;
+    }();
+    const int grid = env.sm_count;
+    int k_max = 0;
+    {   // box numbering is 32-bit: the boxes of a phase times the grid must stay below 2^32
+        unsigned long long run = 0;
+        int len = 0;
+        for (int i = 0; i < n_ops; ++i) {
+            const bool head = i == 0 || len >= kMaxPhaseOps || (host_ops[i].flags & (MOP_BARRIER | MOP_RESTAGE)) != 0;
+            if (head) { run = 0; len = 0; }
+            run += static_cast<unsigned long long>((host_ops[i].N + 31) / 32) * (host_ops[i].K / 256);
+            ++len;
+            if (run * static_cast<unsigned>(grid) >= (1ull << 32)) return cudaErrorNotSupported;
+            k_max = host_ops[i].K > k_max ? host_ops[i].K : k_max;
+        }
+    }
+    const int optin = env.smem_optin > 0 ? env.smem_optin : 232448;
+    DecodeParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.ops = dev.ops; p.maps = dev.maps; p.n_ops = n_ops; p.pool = dev.pool;
+    p.counter = dev.counter; p.base = dev.base; p.err = env.err_word;
+    p.n_ranks = dev.n_ranks; p.rank = dev.rank;
+    p.inv_grid = static_cast<uint32_t>(((1ull << 32) + grid - 1) / grid);
+    for (int r = 0; r < dev.n_ranks; ++r) { p.peer_pool[r] = dev.peer_pool[r]; p.peer_counter[r] = dev.peer_counter[r]; }
+    int off = 8 * kMaxStreamWarps * 4 + 8 * kMaxStreamWarps + 16;   // barriers, scratch, abort flag
+    off = align_up(off, 16);
+    p.off_sx = off;
+    off += align_up((k_max / 32) * 8, 16);
+    off = align_up(off, 128);
+    p.off_x = off;
+    off += align_up(k_max * 2, 128);
+    p.off_ops = -1;
+    if (n_ops * static_cast<int>(sizeof(MegaOp)) <= 32 * 1024) {
+        p.off_ops = off;
+        off += n_ops * static_cast<int>(sizeof(MegaOp));
+    }
+    p.off_ring = align_up(off, 128);
+    off = p.off_ring;
+    int warps = want_warps, ns = 0;
+    for (; warps >= 8 && ns == 0; warps -= 8)
+        for (int cand = 4; cand >= 2; --cand)
+            if (off + warps * cand * kBoxBytes <= optin - 1024) { ns = cand; break; }
+    if (ns == 0) return cudaErrorNotSupported;
+    warps += 8;   // undo the loop's last decrement
+    p.ns = ns;
+    const size_t smem = static_cast<size_t>(off) + static_cast<size_t>(warps) * ns * kBoxBytes;
+    void* args[] = {&p};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(decode_q4_kernel), dim3(grid),
+                                       dim3(warps * 32), args, smem, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Decode launch for callers that must not allocate.
+//
+// The persistent decode kernel needs scratch in global memory: the operation table the CTAs walk,
+// one tensor map per operation, the arrival counter of its grid barrier and the fp32 accumulators
+// its results are summed in.  The library normally keeps them in buffers it allocates on first
+// use.  Some callers cannot have that: an inference server that has handed every byte of HBM to
+// weights and KV cache at start-up, or a decode loop in which a cudaMalloc (which synchronises the
+// whole device) is not acceptable at any point.  For them the same kernel is reachable with its
+// scratch in the fixed array below, which is part of the library image on every GPU that loads it
+// and is never freed.
+//
+// Layout: [0,256) arrival counter (first 8 bytes used) | operation table | tensor maps |
+// accumulators.  Hence at most kDecodeStaticMaxOps operations per call and
+// kDecodeStaticPoolFloats accumulators.
+// ---------------------------------------------------------------------------------------
+constexpr size_t kStaticTableOffset = 256;
+constexpr size_t kStaticMapsOffset = kStaticTableOffset + kDecodeStaticMaxOps * sizeof(MegaOp);
+constexpr size_t kStaticPoolOffset = kStaticMapsOffset + kDecodeStaticMaxOps * kDecodeMapBytes;
+constexpr size_t kStaticBytes = kStaticPoolOffset + kDecodeStaticPoolFloats * sizeof(float);
+static_assert(kStaticPoolOffset % 256 == 0, "accumulators start on a 256-byte boundary");
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+// Host-side state of the static launch site, one per device: the array's device address and the
+// tensor maps encoded for the previous call (re-encoded only when weights, shapes or their order
+// change; encoding costs about a microsecond each).  Guarded by one mutex: calls from several
+// host threads are serialised here, whatever device they target.
+struct StaticSite {
+    unsigned char* addr = nullptr;
+    int maps_n = 0;
+    MegaOp maps_for[kDecodeStaticMaxOps];
+    alignas(64) unsigned char maps[kDecodeStaticMaxOps * kDecodeMapBytes];
+};
+std::mutex g_static_mutex;
+StaticSite* g_static_site[kMaxDevices] = {nullptr};
+StaticSite g_static_first;     // device 0 (or whichever comes first) needs no host allocation
+
+// The array's name is only a handle on the host; kernels need its device address, which differs
+// per device and is looked up once per device with that device current.
+cudaError_t static_site_for_current_device(StaticSite** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (g_static_site[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
+        if (e != cudaSuccess) return e;
+        // host bookkeeping (plain new, no device allocation) for the second and later devices
+        StaticSite* s = g_static_first.addr == nullptr ? &g_static_first : new (std::nothrow) StaticSite();
+        if (!s) return cudaErrorMemoryAllocation;
+        s->addr = static_cast<unsigned char*>(ptr);
+        g_static_site[dev] = s;
+    }
+    *out = g_static_site[dev];
+    return cudaSuccess;
+}
+}  // namespace
+
+// ops: host array of n_ops operations in execution order (GemvQArgs with M == 1, Q4_0).  Plans the
+// table on the stack, copies it into the static scratch together with the operations' tensor
+// maps, clears the arrival counter and the accumulators the table uses, and launches.  No device
+// allocation of any kind.
+cudaError_t launch_gemv_q4_decode_static(const GemvQArgs* ops, int n_ops, const LaunchEnv& env,
+                                         cudaStream_t stream) {
+    if (n_ops <= 0 || n_ops > kDecodeStaticMaxOps) return cudaErrorNotSupported;
+    MegaOp table[kDecodeStaticMaxOps];
+    DecodeSpan work[4 * kDecodeStaticMaxOps];
+    DecodePlan plan;
+    cudaError_t e = plan_decode(ops, nullptr, n_ops, work, table, &plan, kDecodeStaticPoolFloats);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticSite* site = nullptr;
+    e = static_site_for_current_device(&site);
+    if (e != cudaSuccess) return e;
+    unsigned char* scratch = site->addr;
+    // The array keeps whatever the previous call left.  The counter must start from zero; the
+    // accumulators are all zero after a call that ran to its end, but not after one that gave up
+    // on a bounded wait, so the part this table uses is cleared as well; the table and the maps
+    // are overwritten.  (The host table lives on this stack frame: the copy from pageable memory
+    // has consumed it when cudaMemcpyAsync returns.)
+    e = cudaMemsetAsync(scratch, 0, 256, stream);
+    if (e != cudaSuccess) return e;
+    e = cudaMemsetAsync(scratch + kStaticPoolOffset, 0, plan.pool_floats * sizeof(float), stream);
+    if (e != cudaSuccess) return e;
+    e = cudaMemcpyAsync(scratch + kStaticTableOffset, table, static_cast<size_t>(n_ops) * sizeof(MegaOp),
+                        cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return e;
+    bool fresh = site->maps_n == n_ops;
+    for (int i = 0; i < n_ops && fresh; ++i)
+        fresh = site->maps_for[i].W == table[i].W && site->maps_for[i].N == table[i].N &&
+                site->maps_for[i].K == table[i].K;
+    if (!fresh) {
+        e = encode_decode_maps(table, n_ops, site->maps);
+        if (e != cudaSuccess) { site->maps_n = 0; return e; }
+        for (int i = 0; i < n_ops; ++i) site->maps_for[i] = table[i];
+        site->maps_n = n_ops;
+    }
+    e = cudaMemcpyAsync(scratch + kStaticMapsOffset, site->maps, static_cast<size_t>(n_ops) * kDecodeMapBytes,
+                        cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return e;
+    DecodeDevice dev;
+    dev.ops = reinterpret_cast<const MegaOp*>(scratch + kStaticTableOffset);
+    dev.maps = scratch + kStaticMapsOffset;
+    dev.pool = reinterpret_cast<float*>(scratch + kStaticPoolOffset);
+    dev.counter = reinterpret_cast<unsigned long long*>(scratch);
+    dev.base = 0;
+    return launch_decode(table, plan, dev, env, stream);
+}
+
+}  // namespace tcb

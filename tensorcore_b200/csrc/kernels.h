@@ -12,8 +12,8 @@ enum QuantFmt : int { FMT_Q4_0 = 0, FMT_Q8_0 = 1 };
 // Kernel families for the quantized GEMV (see gemv_q.cu).
 enum GemvVariant : int {
     VARIANT_AUTO = 0,
-    VARIANT_SIMT = 1,     // CUDA-core dequant-dot, streamed through shared memory
-    VARIANT_MMA = 2,      // warp-level tensor-core dot for 1 <= M <= 8
+    VARIANT_SIMT = 1,     // integer dot products on the CUDA cores (never the tcgen05 kernel)
+    VARIANT_STREAM = 2,   // as SIMT, but the streaming kernel (a lane per K group) instead of the box kernel
     VARIANT_TC = 3,       // tcgen05 path for batched decode
     VARIANT_GENERIC = 4,  // any K % 32 == 0, any alignment; correctness path for odd shapes
 };
@@ -46,7 +46,10 @@ struct DenseNormGemvArgs {
     float eps = 0.f;
 };
 
-// One operation of a persistent decode launch (Q4_0, M = 1); 64 bytes, read by the device.
+// ---------------------------------------------------------------------------------------
+// Persistent decode launch (decode_q4.cu): a list of Q4_0, M = 1 GEMVs as one cooperative kernel.
+// ---------------------------------------------------------------------------------------
+// One operation of the list; 64 bytes, read by the device.
 struct MegaOp {
     const uint8_t* W;
     const void* X;
@@ -55,7 +58,12 @@ struct MegaOp {
     int N, K;
     uint32_t flags;
     float eps;
-    int pad[4];
+    uint32_t acc_off;   // accumulator pool: float index of Y's row 0
+    int32_t xacc_off;   // >= 0: the activations are the accumulators at this float index (results of
+                        // the epoch before); < 0: read X
+    uint32_t y_row0;    // this operation's row 0 is row y_row0 of Y (row-sharded results that are
+                        // gathered into one vector); 0 otherwise
+    uint32_t y_rows;    // rows of Y (>= y_row0 + N)
 };
 enum : uint32_t {
     MOP_BARRIER = 1u,   // grid-wide barrier before this operation (it depends on earlier output)
@@ -63,19 +71,27 @@ enum : uint32_t {
     MOP_Y_F32 = 4u,     // result is fp32
     MOP_FUSED = 8u,     // RMSNorm prologue with gamma
     MOP_RESTAGE = 16u,  // (re)load the activations into shared memory for this operation
+    MOP_XACC_F16 = 32u, // activations taken from accumulators are rounded to fp16 first
+    MOP_PEERS = 64u,    // partial sums are added into every rank's accumulators (tensor parallel)
 };
-struct MegaParams {
+constexpr int kDecodeMaxRanks = 8;
+struct DecodeParams {
     const MegaOp* ops;              // device memory
     const void* maps;               // device memory: one 128-byte TMA tensor map per operation
     int n_ops;
+    float* pool;                    // device memory: fp32 accumulators, all zero between launches
     unsigned long long* counter;    // device memory: grid-barrier arrival counter, never reset
     unsigned long long base;        // counter value all earlier launches add up to
     uint32_t* err;
     int ns;
-    int off_rowacc, off_sx, off_x, off_ring;
+    int off_sx, off_x, off_ring;
     int off_ops;                    // shared-memory copy of the operation table, or -1
-    int dbg_skip;                   // measurement aid: stream and synchronise, skip arithmetic
-    long long* trace = nullptr;     // debug builds: 8 clock64 stamps per operation from CTA 0
+    uint32_t inv_grid;              // ceil(2^32 / gridDim.x): divisions by the grid size as multiplies
+    // tensor parallel: every barrier spans all ranks' grids; peer pointers are device addresses
+    // of the other ranks' pools and counters, valid on this device
+    int n_ranks, rank;
+    float* peer_pool[kDecodeMaxRanks];
+    unsigned long long* peer_counter[kDecodeMaxRanks];
 };
 
 // Error bits ORed into LaunchEnv::err_word by kernels.
@@ -91,12 +107,41 @@ cudaError_t launch_gemv_q(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t
 cudaError_t launch_dense_norm_gemv(const DenseNormGemvArgs& a, const LaunchEnv& env,
                                    cudaStream_t stream, int* launches, const char** name);
 
-// Persistent decode launch of `n_ops` operations described by `host_ops` (already uploaded to
-// `dev_ops`).  Returns cudaErrorNotSupported when the list does not fit the kernel's shared
-// memory.  *barriers receives the number of grid barriers the launch executes.
-cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops, const void* dev_maps,
-                                  int n_ops, unsigned long long* counter, unsigned long long base,
-                                  const LaunchEnv& env, cudaStream_t stream, int* barriers);
+// --- persistent decode launch: planning on the host, then the launch -----------------------
+struct DecodeSpan { uintptr_t lo, hi; };
+struct DecodePlan {
+    int n_ops = 0;
+    int barriers = 0;          // grid barriers the launch executes (the trailing one included)
+    size_t pool_floats = 0;    // accumulator pool the table addresses
+};
+// Tensor-parallel extras of one operation (all zero on one GPU).
+struct DecodeTpOp {
+    int peers = 0;             // add the partial sums into every rank's accumulators
+    int y_row0 = 0, y_rows = 0;   // placement of the N rows inside a longer gathered vector
+};
+// Builds the device table for `ops` (GemvQArgs with M == 1, Q4_0): barriers from pointer overlap,
+// accumulator placement, hand-over of results through the accumulators.  `work` is caller scratch
+// of 4 * n_ops spans, `table` receives n_ops entries; nothing is allocated.  `tp` may be null.
+// cudaErrorNotSupported: the list is outside the kernel's domain (shapes, alignment, an
+// operation that writes a later operation's weights, a partial overlap between a result and the
+// next epoch's input, more accumulators than pool_capacity_floats when that is non-zero).
+cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, DecodeSpan* work,
+                        MegaOp* table, DecodePlan* plan, size_t pool_capacity_floats);
+// Device-side state of one launch site (a tc_stream, or the static scratch).
+struct DecodeDevice {
+    const MegaOp* ops = nullptr;
+    const void* maps = nullptr;
+    float* pool = nullptr;
+    unsigned long long* counter = nullptr;
+    unsigned long long base = 0;
+    int n_ranks = 1, rank = 0;
+    float* peer_pool[kDecodeMaxRanks] = {};
+    unsigned long long* peer_counter[kDecodeMaxRanks] = {};
+};
+// Launches the table (already uploaded to dev.ops with its tensor maps in dev.maps).
+// cudaErrorNotSupported when the list does not fit the kernel's shared memory.
+cudaError_t launch_decode(const MegaOp* host_ops, const DecodePlan& plan, const DecodeDevice& dev,
+                          const LaunchEnv& env, cudaStream_t stream);
 
 // Bytes of one tensor map, and the encoder for the maps of a table of operations: writes
 // n_ops * kDecodeMapBytes bytes (64-byte aligned destination), one tiled map per operation over its
@@ -104,9 +149,12 @@ cudaError_t launch_gemv_q4_decode(const MegaOp* host_ops, const MegaOp* dev_ops,
 constexpr int kDecodeMapBytes = 128;
 cudaError_t encode_decode_maps(const MegaOp* host_ops, int n_ops, void* host_maps);
 
-// The same launch with its scratch (operation table, barrier counter) in a static device array:
-// no allocation.  At most 256 operations; cudaErrorInvalidValue beyond that or for operations
-// outside the kernel's domain.  First use on a device looks up the array's device address.
+// The same launch with all of its scratch (operation table, tensor maps, barrier counter,
+// accumulators) in a static device array: no allocation.  At most kDecodeStaticMaxOps operations
+// and kDecodeStaticPoolFloats accumulators; cudaErrorNotSupported beyond that or for operations
+// outside the kernel's domain (any other error comes from the CUDA runtime).  First use on a device looks up the array's device address.
+constexpr int kDecodeStaticMaxOps = 256;
+constexpr size_t kDecodeStaticPoolFloats = 3 * 160 * 1024;
 cudaError_t launch_gemv_q4_decode_static(const GemvQArgs* ops, int n_ops, const LaunchEnv& env,
                                          cudaStream_t stream);
 

@@ -50,16 +50,7 @@ struct tc_context {
     cudaStream_t stream0;
     uint32_t* err_host;   // pinned, mapped
     uint32_t* err_dev;
-    // scratch of the persistent decode launch: operation table (pinned staging + device copy)
-    // and the grid-barrier arrival counter
-    bool mega_on;
-    tcb::MegaOp* mega_host;
-    unsigned char* mega_maps_host;   // pinned: one tensor map per operation of the table
-    unsigned char* mega_maps_dev;
-    tcb::MegaOp* mega_dev;
-    unsigned long long* mega_counter;
-    unsigned long long mega_base;
-    int mega_uploaded;    // number of table entries currently valid on the device
+    bool mega_on;         // route qualifying recorded lists to the persistent decode kernel
 };
 
 struct tc_buffer {
@@ -93,11 +84,35 @@ struct CachedGraph {
 
 }  // namespace
 
+// Scratch of the persistent decode launch.  One per tc_stream: two streams may submit different
+// lists without waiting for each other, and the kernel reads its table, tensor maps, counter and
+// accumulators for as long as it runs.
+struct DecodeSite {
+    tcb::MegaOp* host = nullptr;          // pinned copy of the table that is on the device
+    tcb::MegaOp* dev = nullptr;
+    unsigned char* maps_host = nullptr;   // pinned: one tensor map per operation
+    unsigned char* maps_dev = nullptr;
+    float* pool = nullptr;                // fp32 accumulators, all zero between launches
+    size_t pool_floats = 0;
+    unsigned long long* counter = nullptr;   // grid-barrier arrival counter
+    unsigned long long base = 0;             // what all earlier launches add up to
+    int uploaded = 0;                        // table entries currently valid on the device
+    tcb::DecodePlan plan;
+    // tensor parallel (tcx_stream_set_decode_peers): the other ranks' pools and counters
+    int n_ranks = 1, rank = 0;
+    float* peer_pool[tcb::kDecodeMaxRanks] = {};
+    unsigned long long* peer_counter[tcb::kDecodeMaxRanks] = {};
+};
+
 struct tc_stream {
     tc_context* owner;
     cudaStream_t s;
     std::vector<RecordedOp> pending;
     std::unordered_map<uint64_t, CachedGraph> cache;
+    DecodeSite site;
+    std::vector<tcb::MegaOp> table;       // planning scratch, kept to avoid reallocation
+    std::vector<tcb::DecodeSpan> spans;
+    std::vector<tcb::GemvQArgs> args;
 };
 
 namespace {
@@ -247,20 +262,6 @@ tc_status_t setup_device(tc_context* ctx, int device) {
 void teardown_device(tc_context* ctx) {
     if (ctx->stream0) cudaStreamDestroy(ctx->stream0);
     if (ctx->err_host) cudaFreeHost(ctx->err_host);
-    if (ctx->mega_host) cudaFreeHost(ctx->mega_host);
-    if (ctx->mega_maps_host) cudaFreeHost(ctx->mega_maps_host);
-    if (ctx->mega_maps_dev) cudaFree(ctx->mega_maps_dev);
-    ctx->mega_maps_host = nullptr;
-    ctx->mega_maps_dev = nullptr;
-    if (ctx->mega_dev) cudaFree(ctx->mega_dev);
-    if (ctx->mega_counter) cudaFree(ctx->mega_counter);
-    ctx->mega_host = nullptr;
-    ctx->mega_maps_host = nullptr;
-    ctx->mega_maps_dev = nullptr;
-    ctx->mega_dev = nullptr;
-    ctx->mega_counter = nullptr;
-    ctx->mega_base = 0;
-    ctx->mega_uploaded = 0;
     ctx->stream0 = nullptr;
     ctx->err_host = nullptr;
     ctx->err_dev = nullptr;
@@ -347,11 +348,6 @@ extern "C" tc_status_t tc_init(tc_context** out_ctx) {
     ctx->err_dev = nullptr;
     if (const char* v = std::getenv("TC_GEMV_VARIANT")) (void)tcx_set_gemv_variant(v);
     ctx->mega_on = env_flag("TC_MEGA", true);
-    ctx->mega_host = nullptr;
-    ctx->mega_dev = nullptr;
-    ctx->mega_counter = nullptr;
-    ctx->mega_base = 0;
-    ctx->mega_uploaded = 0;
     ctx->pdl = env_flag("TC_PDL", true);
     ctx->graphs = env_flag("TC_STREAM_GRAPH", true);
     const tc_status_t st = setup_device(ctx, device);
@@ -629,6 +625,8 @@ extern "C" tc_status_t tc_stream_create(tc_context* ctx, tc_stream** out) {
     return TC_OK;
 }
 
+namespace { void free_decode_site(DecodeSite& d); }
+
 static void drop_graphs(tc_stream* s) {
     for (auto& kv : s->cache)
         if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
@@ -640,6 +638,7 @@ extern "C" tc_status_t tc_stream_destroy(tc_context* ctx, tc_stream* s) {
     bind_device(ctx);
     cudaStreamSynchronize(s->s);
     drop_graphs(s);
+    free_decode_site(s->site);
     cudaStreamDestroy(s->s);
     delete s;
     return TC_OK;
@@ -654,13 +653,24 @@ cudaError_t launch_recorded(tc_context* ctx, const RecordedOp& op, cudaStream_t 
 }
 
 constexpr int kMegaMaxOps = 1024;
-constexpr size_t kMegaFlagBytes = 256;   // arrival counter and published generation, 128 B apart
+constexpr size_t kMegaFlagBytes = 256;
 
-struct Range { uintptr_t lo, hi; };
-bool overlaps(const std::vector<Range>& v, Range r) {
-    for (const Range& q : v)
-        if (r.lo < q.hi && q.lo < r.hi) return true;
-    return false;
+void free_decode_site(DecodeSite& d) {
+    if (d.host) cudaFreeHost(d.host);
+    if (d.maps_host) cudaFreeHost(d.maps_host);
+    if (d.dev) cudaFree(d.dev);
+    if (d.maps_dev) cudaFree(d.maps_dev);
+    if (d.pool) cudaFree(d.pool);
+    if (d.counter) cudaFree(d.counter);
+    d = DecodeSite();
+}
+
+// After a launch that gave up on a bounded wait the counter and the accumulators hold arbitrary
+// values: start over from zero.
+void reset_decode_site(DecodeSite& d) {
+    if (d.counter) cudaMemset(d.counter, 0, kMegaFlagBytes);
+    if (d.pool) cudaMemset(d.pool, 0, d.pool_floats * sizeof(float));
+    d.base = 0;
 }
 
 // Tries to run the whole recorded list as ONE persistent launch (Q4_0, M = 1 lists: a decode
@@ -670,89 +680,73 @@ cudaError_t submit_as_persistent_launch(tc_stream* s, int* launches, const char*
     tc_context* ctx = s->owner;
     const size_t n = s->pending.size();
     if (!ctx->mega_on || n < 2 || n > static_cast<size_t>(kMegaMaxOps)) return cudaErrorNotSupported;
-    for (const RecordedOp& op : s->pending) {
-        const tcb::GemvQArgs& a = op.a;
-        if (op.kind != OP_GEMV_Q || a.fmt != tcb::FMT_Q4_0 || a.M != 1 || a.K % 256 != 0)
-            return cudaErrorNotSupported;
-        if ((reinterpret_cast<uintptr_t>(a.W) | reinterpret_cast<uintptr_t>(a.X) |
-             reinterpret_cast<uintptr_t>(a.gamma)) & 15u)
-            return cudaErrorNotSupported;
-    }
-    if (!ctx->mega_host) {
-        if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->mega_host), kMegaMaxOps * sizeof(tcb::MegaOp),
+    for (const RecordedOp& op : s->pending)
+        if (op.kind != OP_GEMV_Q || op.a.fmt != tcb::FMT_Q4_0 || op.a.M != 1) return cudaErrorNotSupported;
+    DecodeSite& d = s->site;
+    if (d.n_ranks > 1) return cudaErrorNotSupported;   // tensor-parallel lists go through tcx_stream_decode_tp
+    s->args.resize(n);
+    for (size_t i = 0; i < n; ++i) s->args[i] = s->pending[i].a;
+    s->table.resize(n);
+    s->spans.resize(4 * n);
+    tcb::DecodePlan plan;
+    cudaError_t e = tcb::plan_decode(s->args.data(), nullptr, static_cast<int>(n), s->spans.data(),
+                                     s->table.data(), &plan, 0);
+    if (e != cudaSuccess) return cudaErrorNotSupported;
+    if (!d.host) {
+        if (cudaHostAlloc(reinterpret_cast<void**>(&d.host), kMegaMaxOps * sizeof(tcb::MegaOp),
                           cudaHostAllocDefault) != cudaSuccess ||
-            cudaMalloc(reinterpret_cast<void**>(&ctx->mega_dev), kMegaMaxOps * sizeof(tcb::MegaOp)) != cudaSuccess ||
-            cudaHostAlloc(reinterpret_cast<void**>(&ctx->mega_maps_host), kMegaMaxOps * tcb::kDecodeMapBytes,
+            cudaMalloc(reinterpret_cast<void**>(&d.dev), kMegaMaxOps * sizeof(tcb::MegaOp)) != cudaSuccess ||
+            cudaHostAlloc(reinterpret_cast<void**>(&d.maps_host), kMegaMaxOps * tcb::kDecodeMapBytes,
                           cudaHostAllocDefault) != cudaSuccess ||
-            cudaMalloc(reinterpret_cast<void**>(&ctx->mega_maps_dev), kMegaMaxOps * tcb::kDecodeMapBytes) != cudaSuccess ||
-            cudaMalloc(reinterpret_cast<void**>(&ctx->mega_counter), kMegaFlagBytes) != cudaSuccess ||
-            cudaMemset(ctx->mega_counter, 0, kMegaFlagBytes) != cudaSuccess) {
+            cudaMalloc(reinterpret_cast<void**>(&d.maps_dev), kMegaMaxOps * tcb::kDecodeMapBytes) != cudaSuccess ||
+            cudaMalloc(reinterpret_cast<void**>(&d.counter), kMegaFlagBytes) != cudaSuccess ||
+            cudaMemset(d.counter, 0, kMegaFlagBytes) != cudaSuccess) {
             (void)cudaGetLastError();
-            ctx->mega_on = false;
+            free_decode_site(d);
             return cudaErrorNotSupported;
         }
-        ctx->mega_base = 0;
-        ctx->mega_uploaded = 0;
     }
-    // Build the table.  An operation gets a grid barrier when it reads something an operation
-    // since the last barrier wrote, or writes something one of them read or wrote.
-    std::vector<tcb::MegaOp> table(n);
-    std::vector<Range> reads, writes;
-    for (size_t i = 0; i < n; ++i) {
-        const tcb::GemvQArgs& a = s->pending[i].a;
-        const size_t xs = a.x_f32 ? 4 : 2, ys = a.y_f32 ? 4 : 2;
-        const Range rx{reinterpret_cast<uintptr_t>(a.X), reinterpret_cast<uintptr_t>(a.X) + a.K * xs};
-        const Range rg{reinterpret_cast<uintptr_t>(a.gamma),
-                       reinterpret_cast<uintptr_t>(a.gamma) + (a.gamma ? a.K * xs : 0)};
-        const Range ry{reinterpret_cast<uintptr_t>(a.Y), reinterpret_cast<uintptr_t>(a.Y) + a.N * ys};
-        const Range rw{reinterpret_cast<uintptr_t>(a.W),
-                       reinterpret_cast<uintptr_t>(a.W) + s->pending[i].w_bytes};
-        bool barrier = overlaps(writes, rx) || overlaps(writes, rg) || overlaps(writes, rw) ||
-                       overlaps(writes, ry) || overlaps(reads, ry);
-        if (i == 0) barrier = false;
-        if (barrier) { reads.clear(); writes.clear(); }
-        reads.push_back(rx);
-        if (a.gamma) reads.push_back(rg);
-        reads.push_back(rw);
-        writes.push_back(ry);
-        tcb::MegaOp& m = table[i];
-        std::memset(&m, 0, sizeof(m));
-        m.W = a.W; m.X = a.X; m.Y = a.Y; m.gamma = a.gamma; m.N = a.N; m.K = a.K; m.eps = a.eps;
-        m.flags = (barrier ? tcb::MOP_BARRIER : 0u) | (a.x_f32 ? tcb::MOP_X_F32 : 0u) |
-                  (a.y_f32 ? tcb::MOP_Y_F32 : 0u) | (a.gamma ? tcb::MOP_FUSED : 0u);
-        bool restage = true;
-        if (i > 0 && !barrier) {
-            const tcb::GemvQArgs& b = s->pending[i - 1].a;
-            restage = !(b.X == a.X && b.gamma == a.gamma && b.K == a.K && b.x_f32 == a.x_f32);
-        }
-        if (restage) m.flags |= tcb::MOP_RESTAGE;
-    }
-    const bool same = ctx->mega_uploaded == static_cast<int>(n) &&
-                      std::memcmp(ctx->mega_host, table.data(), n * sizeof(tcb::MegaOp)) == 0;
-    cudaError_t e = cudaSuccess;
-    if (!same) {
-        // the pinned staging copy may still be read by an earlier upload on this stream
+    if (plan.pool_floats > d.pool_floats) {
+        // a larger accumulator pool: the stream's earlier launches must be done with the old one
         e = cudaStreamSynchronize(s->s);
         if (e != cudaSuccess) return e;
-        std::memcpy(ctx->mega_host, table.data(), n * sizeof(tcb::MegaOp));
-        e = tcb::encode_decode_maps(ctx->mega_host, static_cast<int>(n), ctx->mega_maps_host);
-        if (e != cudaSuccess) { ctx->mega_uploaded = 0; return e; }
-        e = cudaMemcpyAsync(ctx->mega_dev, ctx->mega_host, n * sizeof(tcb::MegaOp),
-                            cudaMemcpyHostToDevice, s->s);
-        if (e != cudaSuccess) return e;
-        e = cudaMemcpyAsync(ctx->mega_maps_dev, ctx->mega_maps_host, n * tcb::kDecodeMapBytes,
-                            cudaMemcpyHostToDevice, s->s);
-        if (e != cudaSuccess) return e;
-        ctx->mega_uploaded = static_cast<int>(n);
+        if (d.pool) cudaFree(d.pool);
+        d.pool = nullptr;
+        d.pool_floats = 0;
+        const size_t want = plan.pool_floats + plan.pool_floats / 2;
+        if (cudaMalloc(reinterpret_cast<void**>(&d.pool), want * sizeof(float)) != cudaSuccess ||
+            cudaMemset(d.pool, 0, want * sizeof(float)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            if (d.pool) cudaFree(d.pool);
+            d.pool = nullptr;
+            return cudaErrorNotSupported;
+        }
+        d.pool_floats = want;
     }
-    int barriers = 0;
-    e = tcb::launch_gemv_q4_decode(ctx->mega_host, ctx->mega_dev, ctx->mega_maps_dev, static_cast<int>(n),
-                                   ctx->mega_counter, ctx->mega_base, make_env(ctx, false), s->s,
-                                   &barriers);
+    const bool same = d.uploaded == static_cast<int>(n) &&
+                      std::memcmp(d.host, s->table.data(), n * sizeof(tcb::MegaOp)) == 0;
+    if (!same) {
+        // the pinned staging copy may still be read by an earlier upload on this stream, and the
+        // device copies by an earlier launch
+        e = cudaStreamSynchronize(s->s);
+        if (e != cudaSuccess) return e;
+        std::memcpy(d.host, s->table.data(), n * sizeof(tcb::MegaOp));
+        e = tcb::encode_decode_maps(d.host, static_cast<int>(n), d.maps_host);
+        if (e != cudaSuccess) { d.uploaded = 0; return cudaErrorNotSupported; }
+        e = cudaMemcpyAsync(d.dev, d.host, n * sizeof(tcb::MegaOp), cudaMemcpyHostToDevice, s->s);
+        if (e != cudaSuccess) return e;
+        e = cudaMemcpyAsync(d.maps_dev, d.maps_host, n * tcb::kDecodeMapBytes, cudaMemcpyHostToDevice, s->s);
+        if (e != cudaSuccess) return e;
+        d.uploaded = static_cast<int>(n);
+    }
+    d.plan = plan;
+    tcb::DecodeDevice dev;
+    dev.ops = d.dev; dev.maps = d.maps_dev; dev.pool = d.pool; dev.counter = d.counter; dev.base = d.base;
+    e = tcb::launch_decode(d.host, plan, dev, make_env(ctx, false), s->s);
     if (e == cudaErrorCooperativeLaunchTooLarge) { (void)cudaGetLastError(); return cudaErrorNotSupported; }
     if (e == cudaErrorNotSupported) return e;
     if (e == cudaSuccess) {
-        ctx->mega_base += static_cast<unsigned long long>(barriers) * ctx->sm_count;
+        d.base += static_cast<unsigned long long>(plan.barriers) * ctx->sm_count;
         *launches += 1;
         *name = "q4_0_decode_persistent_sm100";
     }
@@ -769,6 +763,12 @@ tc_status_t submit_pending(tc_stream* s) {
     bool any_staged = false;
     uint64_t sig = 1469598103934665603ull;
     for (RecordedOp& op : s->pending) {
+        // Device addresses are resolved now, not when the operation was recorded: a first
+        // tc_buffer_map between the two moves a buffer to managed storage.
+        op.a.X = op.X->dptr;
+        op.a.W = static_cast<const uint8_t*>(op.W->dptr);
+        op.a.Y = op.Y->dptr;
+        op.a.gamma = op.gamma ? op.gamma->dptr : nullptr;
         tc_buffer* bufs[4] = {op.X, op.W, op.Y, op.gamma};
         for (tc_buffer* b : bufs)
             if (b && staged(b)) any_staged = true;
@@ -864,11 +864,7 @@ extern "C" tc_status_t tc_stream_sync(tc_stream* s) {
     const cudaError_t e = cudaStreamSynchronize(s->s);
     if (st == TC_OK) st = from_cuda(e, TC_ERR_DISPATCH);
     if (st == TC_OK) st = check_device_error(s->owner);
-    if (st != TC_OK && s->owner->mega_counter) {
-        // an aborted persistent launch leaves the barrier counter at an arbitrary value
-        cudaMemset(s->owner->mega_counter, 0, kMegaFlagBytes);
-        s->owner->mega_base = 0;
-    }
+    if (st != TC_OK) reset_decode_site(s->site);
     return st;
 }
 
@@ -1221,7 +1217,7 @@ extern "C" tc_status_t tcx_raw_decode_q4_static(tc_context* ctx, const tcx_decod
     bind_device(ctx);
     const cudaError_t e = tcb::launch_gemv_q4_decode_static(args, n_ops, make_env(ctx, false),
                                                             static_cast<cudaStream_t>(cuda_stream));
-    if (e == cudaErrorInvalidValue || e == cudaErrorNotSupported) {
+    if (e == cudaErrorNotSupported) {   // the launcher's own domain checks; CUDA errors map below
         (void)cudaGetLastError();
         return TC_ERR_INVALID_SHAPE;
     }
@@ -1240,7 +1236,7 @@ extern "C" tc_status_t tcx_set_gemv_variant(const char* name) {
     int v = -1;
     if (!std::strcmp(name, "auto")) v = tcb::VARIANT_AUTO;
     else if (!std::strcmp(name, "simt")) v = tcb::VARIANT_SIMT;
-    else if (!std::strcmp(name, "mma")) v = tcb::VARIANT_MMA;
+    else if (!std::strcmp(name, "stream")) v = tcb::VARIANT_STREAM;
     else if (!std::strcmp(name, "tc")) v = tcb::VARIANT_TC;
     else if (!std::strcmp(name, "generic")) v = tcb::VARIANT_GENERIC;
     if (v < 0) return TC_ERR_INVALID_ARG;

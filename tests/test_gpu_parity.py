@@ -313,14 +313,12 @@ def test_full_size_shapes(tc, ctx, oracle, case):
     assert oracle.scaled_rms(yab, ya + 2 * yb) <= TOL_F32
 
 
-@pytest.mark.parametrize("variant", ["simt", "mma"])
+@pytest.mark.parametrize("variant", ["simt", "stream"])
 @pytest.mark.parametrize("tag", ["q4_0", "q8_0"])
 def test_repeated_launches_on_cache_resident_weights(tc, ctx, oracle, variant, tag):
-    # "simt" is whatever single-operation kernel the dispatcher picks (the box kernel)
+    # "simt" is the box kernel (what the dispatcher picks), "stream" the streaming kernel
     """Weights that stay in L2 make the copy engine refill ring slots as fast as it ever will:
     the timing in which a slot released before its loads were consumed would show stale data."""
-    if variant == "mma" and tag == "q8_0":
-        pytest.skip("the mma.sync kernel is Q4_0 only")
     fmt, N, K, M = Q[tag], 2048, 4096, 1
     rng = np.random.default_rng(99)
     Wq = oracle.quantize_weights(make_weights(rng, N, K), fmt)

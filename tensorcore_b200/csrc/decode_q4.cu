@@ -3,26 +3,31 @@
 //
 // Work.  An operation Y[N] = dequant(W[N,K]) . x[K] is cut into boxes of 32 weight rows x one
 // 8-block group (144 bytes per row, 256 weights per row), each fetched by one tiled TMA copy
-// through a per-operation tensor map.  Operations that share their staged input and need no
-// barrier between them (q/k/v, gate/up) form a phase; the boxes of a phase, numbered row-block
-// major, are dealt evenly to the CTAs (CTA c owns boxes [U*c/G, U*(c+1)/G)) and within a CTA
-// round-robin to its warps, so every SM streams the same number of bytes whatever N is, and
-// consecutive warps fetch consecutive groups of the same rows.  A lane owns one ROW of a box: all
-// lanes of a warp read the same int16 activations from shared memory (one broadcast per load)
-// and the lane's partial dot product is added with one red.global.add.f32 to the operation's
-// fp32 accumulators in global memory (L2 atomics; the K split of a row over boxes, warps, CTAs
-// and - tensor parallel - GPUs all ends in the same accumulator).
+// through a per-operation tensor map.  Operations that share their input and need no barrier
+// between them (q/k/v, gate/up) form a phase.  The boxes of a phase are numbered band-major - a
+// band is four consecutive groups, i.e. 1024 input elements and 576 contiguous bytes of every
+// row - then by row block, then by group inside the band, and dealt evenly to the CTAs (CTA c
+// owns boxes [U*c/G, U*(c+1)/G)) and within a CTA round-robin to its warps.  So every SM streams
+// the same number of bytes whatever N is, four consecutive warps fetch one contiguous piece of
+// 32 rows, and a CTA needs only the one or two bands of the input that its boxes touch.
+// A lane owns one ROW of a box: all lanes of a warp read the same int16 activations from shared
+// memory (one broadcast per load) and the lane's partial dot product is added with one
+// red.global.add.f32 to the operation's fp32 accumulators in global memory (L2 atomics; the K
+// split of a row over boxes, warps, CTAs and - tensor parallel - GPUs all ends in the same
+// accumulator).
 //
 // Epochs.  Operations that read what an earlier one wrote are separated by a grid-wide barrier
 // (one never-reset 64-bit arrival counter, release / acquire, bounded spin).  After the barrier
-// the consumer stages its activations straight from the producer's accumulators (L2-coherent
-// loads, rounded to the producer's result type first), so the result never makes a round trip
-// through its fp16 buffer on the critical path.  The result buffers themselves are written one
-// epoch late: each CTA converts a 1/G slice of every finished accumulator (the staging pass
-// stores the slice it has in registers anyway; results nobody consumes next are loaded before
-// and stored after the staging).  Accumulators are handed out from a pool in three generations
-// (epoch mod 3) and zeroed two epochs after their use, so the pool is all zero again when the
-// kernel ends (a trailing barrier finishes the last epoch).
+// a CTA stages ITS bands of the input straight from the producer's accumulators (L2-coherent
+// loads, scaled and rounded to the producer's result type), quantised to int16 with one scale per
+// 32 elements.  RMSNorm prologue: the row x*gamma is quantised without the 1/rms factor, which
+// needs the whole row; instead the CTAs that stage a band leave the band's sum of squares in a
+// slot beside the accumulators, and whoever reads the accumulators one epoch later (the next
+// staging pass, or the pass that writes the result buffer) multiplies by 1/sqrt(mean square +
+// eps) computed from the slots.  Result buffers are written while a CTA waits at the NEXT barrier
+// (each CTA converts a 1/G slice), accumulators are zeroed one epoch after that; they come from a
+// pool in three generations (epoch mod 3), and a trailing barrier finishes the last epoch, so the
+// pool is all zero again when the kernel ends.
 //
 // Every warp keeps its ring of boxes full ACROSS phases and barriers: weights do not depend on
 // activations, so HBM keeps streaming while a CTA waits and re-stages.  (The host refuses lists
@@ -33,15 +38,15 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <new>
 
 namespace tcb {
 namespace {
 
 constexpr int kMaxPhaseOps = 4;        // operations merged into one phase
 constexpr int kBoxBytes = 32 * 144;
-// internal flags, set by plan_decode (continuing the public MOP_* bits)
-constexpr uint32_t MOP_FIN_X = 256u;     // the staging pass also writes X's buffer (the producer's result)
-constexpr uint32_t MOP_FIN_DONE = 512u;  // this result's buffer is written by its consumer's staging pass
+constexpr int kBandGroups = 4;         // groups per band
+constexpr int kMaxBands = 32;          // slots per staged row: K <= 32 * 1024
 
 __device__ __forceinline__ void red_add_gpu(float* p, float v) {
     asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
@@ -78,44 +83,68 @@ __device__ __forceinline__ uint32_t grid_share(uint32_t total, uint32_t c, uint3
 }
 
 struct Phase {
-    int o, oe;                          // operations [o, oe)
-    uint32_t ubase[kMaxPhaseOps + 1];   // prefix sums of the operations' box counts
+    int o, oe;                          // operations [o, oe): they share their input, hence K
+    uint32_t rbase[kMaxPhaseOps + 1];   // prefix sums of the operations' row-block counts
+    uint32_t gpr;                       // groups per row
     uint32_t c0, c1;                    // this CTA's boxes
 };
-
-__device__ __forceinline__ uint32_t op_units(const MegaOp& op) {
-    return static_cast<uint32_t>((op.N + 31) >> 5) * static_cast<uint32_t>(op.K >> 8);
-}
 
 __device__ __forceinline__ void make_phase(const MegaOp* ops, int n_ops, int o, uint32_t inv_grid, Phase& ph) {
     int oe = o + 1;
     while (oe < n_ops && oe - o < kMaxPhaseOps && !(ops[oe].flags & (MOP_BARRIER | MOP_RESTAGE))) ++oe;
     ph.o = o;
     ph.oe = oe;
-    uint32_t u = 0;
+    uint32_t r = 0;
 #pragma unroll
     for (int k = 0; k < kMaxPhaseOps; ++k) {
-        ph.ubase[k] = u;
-        if (o + k < oe) u += op_units(ops[o + k]);
+        ph.rbase[k] = r;
+        if (o + k < oe) r += static_cast<uint32_t>((ops[o + k].N + 31) >> 5);
     }
-    ph.ubase[kMaxPhaseOps] = u;
-    // the launcher refuses lists with u * gridDim >= 2^32
+    ph.rbase[kMaxPhaseOps] = r;
+    ph.gpr = static_cast<uint32_t>(ops[o].K) >> 8;
+    const uint32_t u = r * ph.gpr;   // the launcher refuses lists with u * gridDim >= 2^32
     ph.c0 = grid_share(u, blockIdx.x, inv_grid);
     ph.c1 = blockIdx.x + 1 == gridDim.x ? u : grid_share(u, blockIdx.x + 1, inv_grid);
 }
 
-// Box u of a phase -> operation (index within the phase), row block, group.
-__device__ __forceinline__ void box_coords(const MegaOp* ops, const Phase& ph, uint32_t u, int& k,
-                                           uint32_t& rb, uint32_t& kg) {
+// Position of a box in its phase: band, row block of the phase's concatenated operations, group
+// inside the band.  Full bands hold 4R boxes (R row blocks), a last narrower band R * (gpr % 4).
+struct Cursor { uint32_t u, band, r, kgi; };
+
+__device__ __forceinline__ void cursor_set(const Phase& ph, uint32_t u, Cursor& c) {
+    const uint32_t R = ph.rbase[kMaxPhaseOps], full = ph.gpr / kBandGroups, per = R * kBandGroups;
+    c.u = u;
+    uint32_t band = u / per;
+    if (band >= full) {
+        band = full;
+        const uint32_t w = ph.gpr % kBandGroups, off = u - full * per;   // callers keep u below R * gpr, so w > 0 here
+        c.r = off / w;
+        c.kgi = off - c.r * w;
+    } else {
+        const uint32_t off = u - band * per;
+        c.r = off / kBandGroups;
+        c.kgi = off % kBandGroups;
+    }
+    c.band = band;
+}
+// Next box of the same warp: `step` (the warp count, a multiple of 4) boxes further, u < limit.
+__device__ __forceinline__ void cursor_advance(const Phase& ph, uint32_t step, uint32_t limit, Cursor& c) {
+    c.u += step;
+    if (c.u >= limit) return;
+    if (c.band < ph.gpr / kBandGroups) {
+        c.r += step / kBandGroups;
+        if (c.r < ph.rbase[kMaxPhaseOps]) return;
+    }
+    cursor_set(ph, c.u, c);
+}
+// Row block r of the phase -> operation (index within the phase) and its row block.
+__device__ __forceinline__ void row_block(const Phase& ph, uint32_t r, int& k, uint32_t& rb) {
     k = 0;
     uint32_t base = 0;
 #pragma unroll
     for (int j = 1; j < kMaxPhaseOps; ++j)
-        if (j < ph.oe - ph.o && u >= ph.ubase[j]) { k = j; base = ph.ubase[j]; }
-    const uint32_t local = u - base;
-    const uint32_t gpr = static_cast<uint32_t>(ops[ph.o + k].K) >> 8;
-    rb = local / gpr;
-    kg = local - rb * gpr;
+        if (j < ph.oe - ph.o && r >= ph.rbase[j]) { k = j; base = ph.rbase[j]; }
+    rb = r - base;
 }
 
 // This CTA's share of a vector of n rows.
@@ -124,71 +153,32 @@ __device__ __forceinline__ void cta_slice(uint32_t n, uint32_t inv_grid, uint32_
     hi = blockIdx.x + 1 == gridDim.x ? n : grid_share(n, blockIdx.x + 1, inv_grid);
 }
 
-// Result buffers of operations [b, e) whose accumulators are complete: this CTA's slice of each,
-// loaded here (all loads first), stored by finalize_store after other work has covered the
-// latency.  Covers kFinOps operations x kFinRows rows per thread; anything beyond that is
-// finished in place by finalize_rest.
-constexpr int kFinOps = 4, kFinRows = 1;
-struct FinRegs { float v[kFinOps][kFinRows]; };
-
-__device__ __forceinline__ void finalize_load(const MegaOp* ops, int b, int e, const float* pool, uint32_t inv_grid, FinRegs& r) {
-    const int tid = threadIdx.x, nthreads = blockDim.x;
-#pragma unroll
-    for (int j = 0; j < kFinOps; ++j) {
-#pragma unroll
-        for (int q = 0; q < kFinRows; ++q) r.v[j][q] = 0.f;
-        if (b + j < e && !(ops[b + j].flags & MOP_FIN_DONE)) {
-            uint32_t lo, hi;
-            cta_slice(ops[b + j].y_rows, inv_grid, lo, hi);
-            const float* acc = pool + ops[b + j].acc_off;
-#pragma unroll
-            for (int q = 0; q < kFinRows; ++q) {
-                const uint32_t i = lo + tid + q * nthreads;
-                if (i < hi) r.v[j][q] = __ldcg(acc + i);
-            }
-        }
-    }
+// 1 / sqrt(mean square + eps) of a row of K elements from its per-band sums of squares.  Called
+// by whole warps; the same bits in every thread (one tree order).
+__device__ __forceinline__ float rstd_from_slots(const float* slots, int K, float eps) {
+    const int nbands = ((K >> 8) + kBandGroups - 1) / kBandGroups, l = threadIdx.x & 31;
+    float t = l < nbands ? __ldcg(slots + l) : 0.f;
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    return 1.0f / sqrtf(t / static_cast<float>(K) + eps);
 }
 
-__device__ __forceinline__ void store_result(const MegaOp& op, uint32_t i, float v) {
-    if (op.flags & MOP_Y_F32) static_cast<float*>(op.Y)[i] = v;
-    else static_cast<__half*>(op.Y)[i] = __float2half_rn(v);
-}
-
-__device__ __forceinline__ void finalize_store(const MegaOp* ops, int b, int e, float* pool, uint32_t inv_grid,
-                                               const FinRegs& r, bool zero_too) {
-    const int tid = threadIdx.x, nthreads = blockDim.x;
-#pragma unroll
-    for (int j = 0; j < kFinOps; ++j) {
-        if (b + j < e && !(ops[b + j].flags & MOP_FIN_DONE)) {
-            const MegaOp op = ops[b + j];
-            uint32_t lo, hi;
-            cta_slice(op.y_rows, inv_grid, lo, hi);
-#pragma unroll
-            for (int q = 0; q < kFinRows; ++q) {
-                const uint32_t i = lo + tid + q * nthreads;
-                if (i < hi) {
-                    store_result(op, i, r.v[j][q]);
-                    if (zero_too) pool[op.acc_off + i] = 0.f;
-                }
-            }
-        }
-    }
-}
-
-// What the register batch above does not cover: rows past kFinRows * blockDim of a slice and
-// operations past the first kFinOps of an epoch.
-__device__ void finalize_rest(const MegaOp* ops, int b, int e, float* pool, uint32_t inv_grid, bool zero_too) {
+// Writes this CTA's slice of the result buffers of operations [b, e), whose accumulators are
+// complete, applying the 1/rms factor their staging pass left out; optionally zeroes the slice.
+__device__ void finalize_results(const MegaOp* ops, int b, int e, float* pool, uint32_t inv_grid, bool zero_too) {
     const int tid = threadIdx.x, nthreads = blockDim.x;
     for (int k = b; k < e; ++k) {
-        if (ops[k].flags & MOP_FIN_DONE) continue;
-        const MegaOp op = ops[k];
+        const MegaOp& op = ops[k];
+        const uint32_t flags = op.flags;
+        const float scale = (flags & MOP_FUSED) ? rstd_from_slots(pool + op.ss_off, op.K, op.eps) : 1.0f;
         uint32_t lo, hi;
         cta_slice(op.y_rows, inv_grid, lo, hi);
-        const uint32_t first = k - b < kFinOps ? lo + kFinRows * nthreads : lo;
-        for (uint32_t i = first + tid; i < hi; i += nthreads) {
-            store_result(op, i, __ldcg(pool + op.acc_off + i));
-            if (zero_too) pool[op.acc_off + i] = 0.f;
+        float* acc = pool + op.acc_off;
+        void* Y = op.Y;
+        for (uint32_t i = lo + tid; i < hi; i += nthreads) {
+            const float v = __ldcg(acc + i) * scale;
+            if (flags & MOP_Y_F32) static_cast<float*>(Y)[i] = v;
+            else static_cast<__half*>(Y)[i] = __float2half_rn(v);
+            if (zero_too) acc[i] = 0.f;
         }
     }
 }
@@ -203,10 +193,74 @@ __device__ void zero_accumulators(const MegaOp* ops, int b, int e, float* pool, 
     }
 }
 
+// Stages bands [band_lo, band_hi] of the input of `op` (the head of a phase) as int16 with one
+// scale per 32 elements, at their natural positions in the shared-memory row.  Four warps take
+// one band (32 chunks of 8 elements each per group), so up to four bands are staged at a time.
+// Fused RMSNorm: quantises x * gamma and stores each band's sum of squares to its slot.
+__device__ void stage_bands(const MegaOp& op, const DecodeParams& p, uint8_t* smem, float* scratch,
+                            uint32_t band_lo, uint32_t band_hi) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nwarps = blockDim.x >> 5;
+    const uint32_t flags = op.flags;
+    const bool fused = (flags & MOP_FUSED) != 0, f16 = !(flags & MOP_X_F32);
+    const bool from_acc = op.xacc_off >= 0, round16 = (flags & MOP_XACC_F16) != 0;
+    const int K = op.K, nb = K >> 5, gpr = K >> 8;
+    const bool pow2 = (from_acc ? round16 : f16) && !fused;
+    const void* X = from_acc ? static_cast<const void*>(p.pool + op.xacc_off) : op.X;
+    const int xkind = from_acc ? 1 : (f16 ? 0 : 1), gkind = f16 ? 0 : 1;
+    uint4* dst = reinterpret_cast<uint4*>(smem + p.off_x);
+    float2* sx2 = reinterpret_cast<float2*>(smem + p.off_sx);
+    // what the producer's result buffer will hold: the accumulator scaled by the producer's own
+    // 1/rms (when its prologue was fused) and rounded to its type
+    const float xs = (from_acc && op.xss_off >= 0) ? rstd_from_slots(p.pool + op.xss_off, op.xss_k, op.xss_eps) : 1.0f;
+    const uint32_t per_pass = static_cast<uint32_t>(nwarps) / 4;
+    for (uint32_t b0 = band_lo; b0 <= band_hi; b0 += per_pass) {
+        const uint32_t band = b0 + static_cast<uint32_t>(warp >> 2);
+        const bool mine = band <= band_hi;
+        const int g0 = static_cast<int>(band) * kBandGroups;
+        const int width = mine ? min(kBandGroups, gpr - g0) : 0;          // groups in this band
+        float ssq = 0.f;
+        for (int c = (warp & 3) * 32 + lane; c - lane < width * 32; c += 128) {   // warp-uniform trip count
+            const bool live = c < width * 32;
+            const int i = g0 * 32 + c;                                    // chunk index in the row
+            float v[8], g[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { v[e] = 0.f; g[e] = 1.f; }
+            if (live) {
+                load8<true>(X, xkind, 8 * static_cast<size_t>(i), v);
+                if (fused) load8<false>(op.gamma, gkind, 8 * static_cast<size_t>(i), g);
+            }
+            if (from_acc) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    v[e] *= xs;
+                    if (round16) v[e] = __half2float(__float2half_rn(v[e]));
+                }
+            }
+            if (fused) {
+                ssq += sumsq8(v);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], g[e]);
+            }
+            quantise_chunk<true>(v, live, i, 0, 8, pow2, gpr, nb, dst, sx2);
+        }
+        if (fused) {
+            for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+            if (lane == 0) scratch[warp] = ssq;
+        }
+        __syncthreads();
+        if (fused && tid < static_cast<int>(per_pass) && b0 + tid <= band_hi) {
+            const float* s4 = scratch + 4 * tid;
+            p.pool[op.ss_off + b0 + tid] = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+        }
+        if (b0 + per_pass <= band_hi) __syncthreads();    // the partial sums are reused by the next pass
+    }
+}
+
 __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                               // [nwarps*ns]
-    double* red_scratch = reinterpret_cast<double*>(smem + 8 * kMaxStreamWarps * 4);  // after barriers
+    float* scratch = reinterpret_cast<float*>(smem + 8 * kMaxStreamWarps * 4);        // after barriers
     volatile int* abort_s = reinterpret_cast<volatile int*>(smem + 8 * kMaxStreamWarps * 4 +
                                                             8 * kMaxStreamWarps);
     uint8_t* ring = smem + p.off_ring;
@@ -230,7 +284,7 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
     if (p.off_ops >= 0) {
         uint4* dst = reinterpret_cast<uint4*>(smem + p.off_ops);
         const uint4* src = reinterpret_cast<const uint4*>(p.ops);
-        for (int i = tid; i < n_ops * 4; i += nthreads) dst[i] = src[i];
+        for (int i = tid; i < n_ops * static_cast<int>(sizeof(MegaOp) / 16); i += nthreads) dst[i] = src[i];
         ops = reinterpret_cast<const MegaOp*>(smem + p.off_ops);
     }
     __syncthreads();
@@ -238,30 +292,34 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
     // ---- per-warp weight stream: the issue cursor runs ahead of the consume cursor ----
     const uint8_t* maps = static_cast<const uint8_t*>(p.maps);   // one 128-byte tensor map per operation
     Phase pi;
+    Cursor ci;
     make_phase(ops, n_ops, 0, inv_grid, pi);
-    uint32_t iu = pi.c0 + warp;          // next box to issue
+    ci.u = pi.c0 + warp;
+    if (ci.u < pi.c1) cursor_set(pi, ci.u, ci);
     int islot = 0, cslot = 0;            // ring slots of the next issue / next consume
     uint32_t cphase = 0;                 // parity of the consume slot's current use
     int inflight = 0;
     auto try_issue = [&]() {
-        while (pi.o < n_ops && iu >= pi.c1) {
+        while (pi.o < n_ops && ci.u >= pi.c1) {
             if (pi.oe >= n_ops) { pi.o = n_ops; break; }
             make_phase(ops, n_ops, pi.oe, inv_grid, pi);
-            iu = pi.c0 + warp;
+            ci.u = pi.c0 + warp;
+            if (ci.u < pi.c1) cursor_set(pi, ci.u, ci);
         }
         if (pi.o >= n_ops || inflight >= ns) return;
         if (lane == 0) {
             int k;
-            uint32_t rb, kg;
-            box_coords(ops, pi, iu, k, rb, kg);
+            uint32_t rb;
+            row_block(pi, ci.r, k, rb);
             uint64_t* bar = &bars[warp * ns + islot];
             fence_proxy_async();
             mbar_expect_tx(bar, kBoxBytes);
             sm100::tensor_load_2d(ring + static_cast<size_t>(warp * ns + islot) * kBoxBytes,
                                   maps + static_cast<size_t>(pi.o + k) * kDecodeMapBytes,
-                                  static_cast<int>(kg * 144), static_cast<int>(rb * 32), bar);
+                                  static_cast<int>((ci.band * kBandGroups + ci.kgi) * 144),
+                                  static_cast<int>(rb * 32), bar);
         }
-        iu += nwarps;
+        cursor_advance(pi, nwarps, pi.c1, ci);
         ++inflight;
         if (++islot == ns) islot = 0;
     };
@@ -270,24 +328,28 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
     unsigned long long target = p.base;
     const unsigned long long per_barrier = static_cast<unsigned long long>(gridDim.x) * (multi ? p.n_ranks : 1);
     bool failed = false;
-    float rstd = 1.0f;                              // of the staged row (RMSNorm prologue), else 1
     int cur_b = 0;                                  // first operation of the current epoch
     int prev_b = 0, prev_e = 0, pp_b = 0, pp_e = 0; // the two epochs before it
     Phase pc;
+    Cursor cc;
     for (int o = 0; o <= n_ops && !failed;) {
         const bool tail = o == n_ops;               // trailing epoch: barrier and clean-up only
         const uint32_t flags = tail ? MOP_BARRIER : ops[o].flags;
         if (!tail) make_phase(ops, n_ops, o, inv_grid, pc);
+        const int rounds = (flags & MOP_BARRIER) ? ((flags & MOP_BARRIER2) ? 2 : 1) : 0;
         // Everyone in the CTA is done with the previous phase: its staged activations may be
         // replaced, and thread 0's arrival below covers every warp's accumulator updates.
-        __syncthreads();
-        bool chores = false;
-        if (flags & MOP_BARRIER) {
+        if (rounds == 0) __syncthreads();
+        for (int round = 0; round < rounds; ++round) {
+            // Accumulators last read two epochs ago (staging) and one epoch ago (result buffers):
+            // zero this CTA's slices before arriving, so that the barrier publishes the zeros.
+            zero_accumulators(ops, pp_b, pp_e, p.pool, inv_grid);
+            __syncthreads();
             // One 64-bit arrival counter that is never reset: a barrier is complete when the
             // counter reaches the running target.  One thread per CTA arrives with a release
-            // reduction (no value comes back, so it goes straight to polling) and polls with
-            // acquire loads; the wait is bounded.  Tensor parallel: every CTA arrives on every
-            // rank's counter, so the barrier spans all grids.
+            // reduction (no value comes back) and polls with acquire loads; the wait is bounded.
+            // Tensor parallel: every CTA arrives on every rank's counter, so the barrier spans all
+            // grids.
             target += per_barrier;
             if (tid == 0) {
                 if (multi) {
@@ -295,6 +357,14 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
                 } else {
                     arrive_gpu(p.counter);
                 }
+            }
+            // While the others arrive: result buffers of the epoch before the one that just ended
+            // (its accumulators were completed by the previous barrier).  These stores are
+            // published by the NEXT barrier, so a buffer can be read three epochs after it was
+            // produced; readers one epoch after take the accumulators, and the host puts an empty
+            // epoch (a second barrier) in front of a reader two epochs after.
+            finalize_results(ops, prev_b, prev_e, p.pool, inv_grid, false);
+            if (tid == 0) {
                 const long long t0 = clock64();
                 while ((multi ? poll_sys(p.counter) : poll_gpu(p.counter)) < target) {
                     if (clock64() - t0 > 2000000000LL) {
@@ -309,50 +379,26 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
             pp_b = prev_b; pp_e = prev_e;
             prev_b = cur_b; prev_e = o;
             cur_b = o;
-            chores = true;
         }
-        FinRegs fin;
+        if (failed) break;
         if (tail) {
-            finalize_load(ops, prev_b, prev_e, p.pool, inv_grid, fin);
-            finalize_store(ops, prev_b, prev_e, p.pool, inv_grid, fin, true);
-            finalize_rest(ops, prev_b, prev_e, p.pool, inv_grid, true);
-            // results whose buffers a staging pass wrote still hold their accumulators
-            for (int k = prev_b; k < prev_e; ++k)
-                if (ops[k].flags & MOP_FIN_DONE) zero_accumulators(ops, k, k + 1, p.pool, inv_grid);
+            // the last epoch's results, and what the regular schedule would zero later
+            finalize_results(ops, prev_b, prev_e, p.pool, inv_grid, true);
             zero_accumulators(ops, pp_b, pp_e, p.pool, inv_grid);
             break;
         }
-        const MegaOp op = ops[o];
-        if (flags & MOP_RESTAGE) {
-            StreamParams sp;
-            sp.gamma = (flags & MOP_FUSED) ? op.gamma : nullptr;
-            sp.K = op.K; sp.nb = op.K >> 5; sp.gpr = op.K >> 8; sp.eps = op.eps;
-            sp.x_src_f16 = (flags & MOP_X_F32) ? 0 : 1;
-            sp.off_x = p.off_x; sp.off_sx = p.off_sx;
-            if (op.xacc_off >= 0) {
-                sp.X = p.pool + op.xacc_off;
-                sp.x_acc = (flags & MOP_XACC_F16) ? 2 : 1;
-            } else {
-                sp.X = op.X;
-                sp.x_acc = 0;
-            }
-            if (flags & MOP_FIN_X) {
-                uint32_t lo, hi;
-                cta_slice(static_cast<uint32_t>(op.K), inv_grid, lo, hi);
-                sp.fin_Y = const_cast<void*>(op.X);
-                sp.fin_lo = static_cast<int>(lo);
-                sp.fin_hi = static_cast<int>(hi);
-            }
-            stage_activations_i16<1, true, true, true>(sp, smem, 8, red_scratch);
-            rstd = (flags & MOP_FUSED) ? rstd_from_partials(red_scratch, op.K, op.eps) : 1.0f;
+        const MegaOp& op = ops[o];
+        if (pc.c0 < pc.c1) {
+            Cursor first, last;
+            cursor_set(pc, pc.c0, first);
+            cursor_set(pc, pc.c1 - 1, last);
+            stage_bands(op, p, smem, scratch, first.band, last.band);
+        } else {
+            __syncthreads();   // keeps the barrier count of stage_bands (one per phase at least)
         }
-        // Results of the epoch just finished that no staging pass writes: loaded now, stored after
-        // the boxes of this phase, which cover the latency.
-        if (chores) finalize_load(ops, prev_b, prev_e, p.pool, inv_grid, fin);
         {   // The next phase's RMSNorm weights are a first-touch read from HBM on its critical
             // path: one CTA pulls them into L2 a phase ahead.
-            int nx = pc.oe;
-            while (nx < n_ops && !(ops[nx].flags & MOP_RESTAGE)) ++nx;
+            const int nx = pc.oe;
             if (nx < n_ops && (ops[nx].flags & MOP_FUSED) &&
                 static_cast<int>(blockIdx.x) == nx % static_cast<int>(gridDim.x)) {
                 const int bytes = ops[nx].K * ((ops[nx].flags & MOP_X_F32) ? 4 : 2);
@@ -361,12 +407,15 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
             }
         }
 
-        for (uint32_t u = pc.c0 + warp; u < pc.c1; u += nwarps) {
+        cc.u = pc.c0 + warp;
+        if (cc.u < pc.c1) cursor_set(pc, cc.u, cc);
+        while (cc.u < pc.c1) {
             uint64_t* bar = &bars[warp * ns + cslot];
             if (!mbar_wait_bounded(bar, cphase)) { failed = true; break; }
             int k;
-            uint32_t rb, kg;
-            box_coords(ops, pc, u, k, rb, kg);
+            uint32_t rb;
+            row_block(pc, cc.r, k, rb);
+            const int kg = static_cast<int>(cc.band * kBandGroups + cc.kgi);
             uint32_t w[36];
             {
                 const uint4* src = reinterpret_cast<const uint4*>(
@@ -384,23 +433,17 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
             const MegaOp& opk = ops[pc.o + k];
             const int K = opk.K;
             float out[1] = {0.f};
-            group_dot_i16<FMT_Q4_0, 1, true>(w, xs, sx2, static_cast<int>(kg), K >> 8, K, K >> 5, out);
+            group_dot_i16<FMT_Q4_0, 1, true>(w, xs, sx2, kg, K >> 8, K, K >> 5, out);
             const uint32_t row = rb * 32 + lane;
             if (row < static_cast<uint32_t>(opk.N)) {
                 const size_t at = static_cast<size_t>(opk.acc_off) + opk.y_row0 + row;
                 if (opk.flags & MOP_PEERS) {
-                    for (int r = 0; r < p.n_ranks; ++r) red_add_sys(p.peer_pool[r] + at, out[0] * rstd);
+                    for (int r = 0; r < p.n_ranks; ++r) red_add_sys(p.peer_pool[r] + at, out[0]);
                 } else {
-                    red_add_gpu(p.pool + at, out[0] * rstd);
+                    red_add_gpu(p.pool + at, out[0]);
                 }
             }
-        }
-        // Clean-up that only has to happen somewhere in this epoch, placed where most warps have
-        // time to spare: result buffers of the epoch before, accumulators of the one before that.
-        if (chores) {
-            finalize_store(ops, prev_b, prev_e, p.pool, inv_grid, fin, false);
-            finalize_rest(ops, prev_b, prev_e, p.pool, inv_grid, false);
-            zero_accumulators(ops, pp_b, pp_e, p.pool, inv_grid);
+            cursor_advance(pc, nwarps, pc.c1, cc);
         }
         if (__any_sync(0xffffffffu, failed)) failed = true;
         if (failed) {
@@ -448,6 +491,7 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
     if (!ops || !work || !table || !plan || n_ops <= 0) return cudaErrorInvalidValue;
     DecodeSpan* reads = work;                 // inputs read since the last barrier (x, gamma, W)
     DecodeSpan* writes = work + 3 * n_ops;    // results written since the last barrier
+    DecodeSpan* epoch_of = work + 4 * n_ops;  // .lo = epoch of an operation
     int nr = 0, nw = 0;
     DecodeSpan y_box{~static_cast<uintptr_t>(0), 0};   // bounding interval of every result so far
     auto y_span = [&](int j) {
@@ -456,13 +500,21 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
         const uintptr_t lo = reinterpret_cast<uintptr_t>(b.Y);
         return DecodeSpan{lo, lo + rows * (b.y_f32 ? 4 : 2)};
     };
-    // Pass 1: barriers, epochs (kept in xacc_off for now) and accumulator offsets inside an epoch.
+    // Pass 1: barriers and epochs, accumulator offsets inside an epoch, hand-over of results.
+    // Timing of a result of epoch p: accumulators complete after the barrier that ends p; read
+    // from there by operations of epoch p + 1; result buffer written during the wait at the
+    // barrier that ends p + 1, hence visible from epoch p + 3; accumulators zeroed at the end of
+    // p + 2.  So a reader of the buffer in epoch p + 2, or another writer in epoch p + 1, gets
+    // one more (empty) epoch in front of it.
     int epoch = 0;
-    size_t in_epoch = 0, worst = 0;
+    size_t in_epoch = 0, worst = 0;         // accumulators of the current epoch, and the largest epoch
+    size_t ss_epoch = 0, ss_worst = 0;      // the same for the sums of squares, which get a region of their own
+    uint32_t ss_cur = 0;
     for (int i = 0; i < n_ops; ++i) {
         const GemvQArgs& a = ops[i];
         if (a.fmt != FMT_Q4_0 || a.M != 1 || a.N <= 0 || a.K <= 0 || a.K % 256 != 0 || !a.W || !a.X || !a.Y)
             return cudaErrorNotSupported;
+        if (a.K / 256 > kBandGroups * kMaxBands) return cudaErrorNotSupported;
         if ((reinterpret_cast<uintptr_t>(a.W) | reinterpret_cast<uintptr_t>(a.X) |
              reinterpret_cast<uintptr_t>(a.gamma)) & 15u)
             return cudaErrorNotSupported;
@@ -478,19 +530,45 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
         const uint32_t y_row0 = tp ? static_cast<uint32_t>(tp[i].y_row0) : 0u;
         if (static_cast<unsigned long long>(y_row0) + a.N > y_rows) return cudaErrorInvalidValue;
         if (y_rows >= (1u << 24)) return cudaErrorNotSupported;
-        // Weights are fetched ahead of every barrier, and gamma is read while results of the epoch
-        // before are still being written to their buffers: neither may be an earlier result.
+        // Weights are fetched ahead of every barrier, and gamma is read while earlier results may
+        // still be on their way to their buffers: neither may be an earlier result.
         if (spans_overlap(rw, y_box) || (a.gamma && spans_overlap(rg, y_box))) {
             for (int j = 0; j < i; ++j) {
                 const DecodeSpan yj = y_span(j);
                 if (spans_overlap(rw, yj) || (a.gamma && spans_overlap(rg, yj))) return cudaErrorNotSupported;
             }
         }
-        bool barrier = i > 0 && (span_hits(writes, nw, rx) || span_hits(writes, nw, ry) || span_hits(reads, nr, ry));
-        if (barrier) {
+        int nbar = (i > 0 && (span_hits(writes, nw, rx) || span_hits(writes, nw, ry) || span_hits(reads, nr, ry))) ? 1 : 0;
+        int producer = -1;
+        if (i > 0 && (spans_overlap(rx, y_box) || spans_overlap(ry, y_box))) {
+            for (int round = 0; round < 3; ++round) {
+                const int e_i = epoch + nbar;
+                bool bump = false, seen_x = false, seen_y = false;
+                producer = -1;
+                for (int j = i - 1; j >= 0 && !(seen_x && seen_y); --j) {
+                    const int d = e_i - static_cast<int>(epoch_of[j].lo);
+                    if (d > 2) break;
+                    const DecodeSpan yj = y_span(j);
+                    if (!seen_x && spans_overlap(rx, yj)) {        // latest writer of what this one reads
+                        seen_x = true;
+                        if (d == 2) bump = true;
+                        else if (d == 1) producer = j;
+                    }
+                    if (!seen_y && spans_overlap(ry, yj)) {        // latest writer of what this one writes
+                        seen_y = true;
+                        if (d == 1) bump = true;
+                    }
+                }
+                if (!bump) break;
+                ++nbar;
+            }
+        }
+        if (nbar > 2) return cudaErrorNotSupported;
+        if (nbar > 0) {
             nr = nw = 0;
-            ++epoch;
+            epoch += nbar;
             in_epoch = 0;
+            ss_epoch = 0;
         }
         reads[nr++] = rx;
         if (a.gamma) reads[nr++] = rg;
@@ -498,12 +576,13 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
         writes[nw++] = ry;
         y_box.lo = ry.lo < y_box.lo ? ry.lo : y_box.lo;
         y_box.hi = ry.hi > y_box.hi ? ry.hi : y_box.hi;
+        epoch_of[i].lo = static_cast<uintptr_t>(epoch);
         MegaOp& m = table[i];
         m.W = a.W; m.X = a.X; m.Y = a.Y; m.gamma = a.gamma; m.N = a.N; m.K = a.K; m.eps = a.eps;
-        m.flags = (barrier ? MOP_BARRIER : 0u) | (a.x_f32 ? MOP_X_F32 : 0u) | (a.y_f32 ? MOP_Y_F32 : 0u) |
-                  (a.gamma ? MOP_FUSED : 0u) | (tp && tp[i].peers ? MOP_PEERS : 0u);
+        m.flags = (nbar > 0 ? MOP_BARRIER : 0u) | (nbar > 1 ? MOP_BARRIER2 : 0u) | (a.x_f32 ? MOP_X_F32 : 0u) |
+                  (a.y_f32 ? MOP_Y_F32 : 0u) | (a.gamma ? MOP_FUSED : 0u) | (tp && tp[i].peers ? MOP_PEERS : 0u);
         bool restage = true;
-        if (i > 0 && !barrier) {
+        if (i > 0 && nbar == 0) {
             const GemvQArgs& b = ops[i - 1];
             restage = !(b.X == a.X && b.gamma == a.gamma && b.K == a.K && b.x_f32 == a.x_f32);
         }
@@ -511,54 +590,58 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
         m.y_row0 = y_row0;
         m.y_rows = y_rows;
         m.acc_off = static_cast<uint32_t>(in_epoch);
-        m.xacc_off = epoch;
         in_epoch += (static_cast<size_t>(y_rows) + 31) & ~static_cast<size_t>(31);
-        worst = in_epoch > worst ? in_epoch : worst;
-        if (worst > (1u << 28)) return cudaErrorNotSupported;
-    }
-    const size_t gen = worst;
-    if (pool_capacity_floats && 3 * gen > pool_capacity_floats) return cudaErrorNotSupported;
-    // Pass 2: place the accumulators (generation = epoch mod 3) and hand results over through them.
-    // epoch_of[j] survives in table[j].xacc_off until j's own turn, so walk forward and keep the
-    // epochs of earlier operations in their (already final) y_rows-independent field: recompute.
-    int ep_i = 0;
-    for (int i = 0; i < n_ops; ++i) {
-        MegaOp& m = table[i];
-        ep_i = m.xacc_off;
-        m.acc_off += static_cast<uint32_t>((ep_i % 3) * gen);
+        m.ss_off = 0;
+        if (a.gamma) {
+            if (restage) {      // operations that share a staged row share its sums of squares
+                ss_cur = static_cast<uint32_t>(ss_epoch);
+                ss_epoch += kMaxBands;
+            }
+            m.ss_off = ss_cur;
+        }
         m.xacc_off = -1;
-        if (ep_i == 0) continue;
-        // Latest earlier result that overlaps X.  Epochs of earlier operations: count barriers back.
-        const GemvQArgs& a = ops[i];
-        const uintptr_t xl = reinterpret_cast<uintptr_t>(a.X);
-        const DecodeSpan rx{xl, xl + a.K * static_cast<size_t>(a.x_f32 ? 4 : 2)};
-        if (!spans_overlap(rx, y_box)) continue;
-        int ep_j = ep_i;
-        for (int j = i - 1; j >= 0; --j) {
-            if (table[j + 1].flags & MOP_BARRIER) --ep_j;      // j lies in the epoch before j + 1's
-            if (ep_j < ep_i - 1) break;
-            const DecodeSpan yj = y_span(j);
-            if (!spans_overlap(rx, yj)) continue;
-            // ep_j == ep_i is impossible (a barrier separates a reader from its writer)
-            const GemvQArgs& b = ops[j];
+        m.xss_off = -1;
+        m.xss_k = 0;
+        m.xss_eps = 0.f;
+        if (producer >= 0) {
+            // the result of the epoch before: taken from its accumulators, if it lies cleanly inside
+            const GemvQArgs& b = ops[producer];
+            const DecodeSpan yj = y_span(producer);
             const size_t es = b.y_f32 ? 4 : 2;
             const bool contained = rx.lo >= yj.lo && rx.hi <= yj.hi && b.y_f32 == a.x_f32 &&
                                    (rx.lo - yj.lo) % (4 * es) == 0;
             if (!contained) return cudaErrorNotSupported;
-            const uint32_t first = static_cast<uint32_t>((rx.lo - yj.lo) / es);
-            m.xacc_off = static_cast<int32_t>(table[j].acc_off + first);
+            m.xacc_off = producer;                                         // resolved in pass 2
+            m.xss_k = static_cast<int32_t>((rx.lo - yj.lo) / es);         // first element, for now
             if (!b.y_f32) m.flags |= MOP_XACC_F16;
-            const bool whole = rx.lo == yj.lo && rx.hi == yj.hi;
-            if (whole && (m.flags & MOP_RESTAGE) && !(table[j].flags & MOP_FIN_DONE)) {
-                m.flags |= MOP_FIN_X;
-                table[j].flags |= MOP_FIN_DONE;
-            }
-            break;
         }
+        worst = in_epoch > worst ? in_epoch : worst;
+        ss_worst = ss_epoch > ss_worst ? ss_epoch : ss_worst;
+        if (worst + ss_worst > (1u << 28)) return cudaErrorNotSupported;
     }
+    // A generation: accumulators first, then the sums of squares.  The two never share an
+    // address: accumulators are zeroed before reuse, the sums are simply overwritten.
+    const size_t gen = worst + ss_worst;
+    if (pool_capacity_floats && 3 * gen > pool_capacity_floats) return cudaErrorNotSupported;
+    // Pass 2: place the accumulators and the sums of squares (generation = epoch mod 3).
     int barriers = 1;   // the trailing one
-    for (int i = 0; i < n_ops; ++i)
-        if (table[i].flags & MOP_BARRIER) ++barriers;
+    for (int i = 0; i < n_ops; ++i) {
+        MegaOp& m = table[i];
+        const uint32_t base = static_cast<uint32_t>((epoch_of[i].lo % 3) * gen);
+        m.acc_off += base;
+        if (m.flags & MOP_FUSED) m.ss_off += base + static_cast<uint32_t>(worst);
+        if (m.xacc_off >= 0) {
+            const MegaOp& pr = table[m.xacc_off];      // earlier in the list: already placed
+            m.xacc_off = static_cast<int32_t>(pr.acc_off + static_cast<uint32_t>(m.xss_k));
+            m.xss_k = 0;
+            if (pr.flags & MOP_FUSED) {
+                m.xss_off = static_cast<int32_t>(pr.ss_off);
+                m.xss_k = pr.K;
+                m.xss_eps = pr.eps;
+            }
+        }
+        if (m.flags & MOP_BARRIER) barriers += (m.flags & MOP_BARRIER2) ? 2 : 1;
+    }
     plan->n_ops = n_ops;
     plan->barriers = barriers;
     plan->pool_floats = 3 * gen;
@@ -693,7 +776,7 @@ cudaError_t launch_gemv_q4_decode_static(const GemvQArgs* ops, int n_ops, const 
                                          cudaStream_t stream) {
     if (n_ops <= 0 || n_ops > kDecodeStaticMaxOps) return cudaErrorNotSupported;
     MegaOp table[kDecodeStaticMaxOps];
-    DecodeSpan work[4 * kDecodeStaticMaxOps];
+    DecodeSpan work[5 * kDecodeStaticMaxOps];
     DecodePlan plan;
     cudaError_t e = plan_decode(ops, nullptr, n_ops, work, table, &plan, kDecodeStaticPoolFloats);
     if (e != cudaSuccess) return e;

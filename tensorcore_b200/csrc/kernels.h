@@ -49,7 +49,7 @@ struct DenseNormGemvArgs {
 // ---------------------------------------------------------------------------------------
 // Persistent decode launch (decode_q4.cu): a list of Q4_0, M = 1 GEMVs as one cooperative kernel.
 // ---------------------------------------------------------------------------------------
-// One operation of the list; 64 bytes, read by the device.
+// One operation of the list; 80 bytes, read by the device.
 struct MegaOp {
     const uint8_t* W;
     const void* X;
@@ -64,7 +64,15 @@ struct MegaOp {
     uint32_t y_row0;    // this operation's row 0 is row y_row0 of Y (row-sharded results that are
                         // gathered into one vector); 0 otherwise
     uint32_t y_rows;    // rows of Y (>= y_row0 + N)
+    uint32_t ss_off;    // MOP_FUSED: pool index of the per-band sums of squares of this operation's
+                        // input (written while it is staged; 1/rms is applied by whoever reads the
+                        // accumulators afterwards)
+    int32_t xss_off;    // >= 0: the accumulators at xacc_off still lack their producer's 1/rms
+                        // factor, whose sums of squares are at this pool index ...
+    int32_t xss_k;      // ... for a row of this many elements ...
+    float xss_eps;      // ... and this epsilon
 };
+static_assert(sizeof(MegaOp) == 80, "the device copies the table in 16-byte pieces");
 enum : uint32_t {
     MOP_BARRIER = 1u,   // grid-wide barrier before this operation (it depends on earlier output)
     MOP_X_F32 = 2u,     // activations (and gamma) are fp32
@@ -73,6 +81,7 @@ enum : uint32_t {
     MOP_RESTAGE = 16u,  // (re)load the activations into shared memory for this operation
     MOP_XACC_F16 = 32u, // activations taken from accumulators are rounded to fp16 first
     MOP_PEERS = 64u,    // partial sums are added into every rank's accumulators (tensor parallel)
+    MOP_BARRIER2 = 128u, // with MOP_BARRIER: two barriers, i.e. one empty epoch, before this operation
 };
 constexpr int kDecodeMaxRanks = 8;
 struct DecodeParams {
@@ -121,7 +130,7 @@ struct DecodeTpOp {
 };
 // Builds the device table for `ops` (GemvQArgs with M == 1, Q4_0): barriers from pointer overlap,
 // accumulator placement, hand-over of results through the accumulators.  `work` is caller scratch
-// of 4 * n_ops spans, `table` receives n_ops entries; nothing is allocated.  `tp` may be null.
+// of 5 * n_ops spans, `table` receives n_ops entries; nothing is allocated.  `tp` may be null.
 // cudaErrorNotSupported: the list is outside the kernel's domain (shapes, alignment, an
 // operation that writes a later operation's weights, a partial overlap between a result and the
 // next epoch's input, more accumulators than pool_capacity_floats when that is non-zero).

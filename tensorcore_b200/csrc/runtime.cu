@@ -687,7 +687,7 @@ cudaError_t submit_as_persistent_launch(tc_stream* s, int* launches, const char*
     s->args.resize(n);
     for (size_t i = 0; i < n; ++i) s->args[i] = s->pending[i].a;
     s->table.resize(n);
-    s->spans.resize(4 * n);
+    s->spans.resize(5 * n);
     tcb::DecodePlan plan;
     cudaError_t e = tcb::plan_decode(s->args.data(), nullptr, static_cast<int>(n), s->spans.data(),
                                      s->table.data(), &plan, 0);

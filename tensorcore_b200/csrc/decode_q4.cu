@@ -82,6 +82,16 @@ __device__ __forceinline__ uint32_t grid_share(uint32_t total, uint32_t c, uint3
     return q < total ? q : total;
 }
 
+// a / b for b > 0 and a < 2^31 without the integer division sequence: a float quotient (which can be
+// off by one either way) corrected with one multiply.
+__device__ __forceinline__ uint32_t div_u32(uint32_t a, uint32_t b) {
+    uint32_t q = __float2uint_rz(__fdividef(__uint2float_rz(a), __uint2float_ru(b)));
+    if (q * b > a) --q;
+    uint32_t r = a - q * b;
+    while (r >= b) { r -= b; ++q; }
+    return q;
+}
+
 struct Phase {
     int o, oe;                          // operations [o, oe): they share their input, hence K
     uint32_t rbase[kMaxPhaseOps + 1];   // prefix sums of the operations' row-block counts
@@ -114,11 +124,11 @@ struct Cursor { uint32_t u, band, r, kgi; };
 __device__ __forceinline__ void cursor_set(const Phase& ph, uint32_t u, Cursor& c) {
     const uint32_t R = ph.rbase[kMaxPhaseOps], full = ph.gpr / kBandGroups, per = R * kBandGroups;
     c.u = u;
-    uint32_t band = u / per;
+    uint32_t band = div_u32(u, per);
     if (band >= full) {
         band = full;
         const uint32_t w = ph.gpr % kBandGroups, off = u - full * per;   // callers keep u below R * gpr, so w > 0 here
-        c.r = off / w;
+        c.r = w == 3 ? div_u32(off, 3) : (w == 2 ? off >> 1 : off);
         c.kgi = off - c.r * w;
     } else {
         const uint32_t off = u - band * per;
@@ -137,6 +147,11 @@ __device__ __forceinline__ void cursor_advance(const Phase& ph, uint32_t step, u
     }
     cursor_set(ph, c.u, c);
 }
+// Band of box u.
+__device__ __forceinline__ uint32_t band_of(const Phase& ph, uint32_t u) {
+    const uint32_t band = div_u32(u, ph.rbase[kMaxPhaseOps] * kBandGroups), full = ph.gpr / kBandGroups;
+    return band < full ? band : full;
+}
 // Row block r of the phase -> operation (index within the phase) and its row block.
 __device__ __forceinline__ void row_block(const Phase& ph, uint32_t r, int& k, uint32_t& rb) {
     k = 0;
@@ -153,29 +168,36 @@ __device__ __forceinline__ void cta_slice(uint32_t n, uint32_t inv_grid, uint32_
     hi = blockIdx.x + 1 == gridDim.x ? n : grid_share(n, blockIdx.x + 1, inv_grid);
 }
 
-// 1 / sqrt(mean square + eps) of a row of K elements from its per-band sums of squares.  Called
-// by whole warps; the same bits in every thread (one tree order).
+// 1 / sqrt(mean square + eps) from a warp's per-lane share of the sums of squares.  One routine
+// for every reader, so that they all get the same bits.
+__device__ __forceinline__ float rstd_from_lane_part(float t, int K, float eps) {
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    return rsqrtf(t / static_cast<float>(K) + eps);
+}
+// The same from the per-band sums of a row of K elements in the pool.  Called by whole warps.
 __device__ __forceinline__ float rstd_from_slots(const float* slots, int K, float eps) {
     const int nbands = ((K >> 8) + kBandGroups - 1) / kBandGroups, l = threadIdx.x & 31;
-    float t = l < nbands ? __ldcg(slots + l) : 0.f;
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    return 1.0f / sqrtf(t / static_cast<float>(K) + eps);
+    return rstd_from_lane_part(l < nbands ? __ldcg(slots + l) : 0.f, K, eps);
 }
 
 // Writes this CTA's slice of the result buffers of operations [b, e), whose accumulators are
 // complete, applying the 1/rms factor their staging pass left out; optionally zeroes the slice.
+// A group of four warps takes one operation (a CTA's slice is a few dozen rows), so the
+// operations of an epoch are finished side by side, each with one round trip to L2.
 __device__ void finalize_results(const MegaOp* ops, int b, int e, float* pool, uint32_t inv_grid, bool zero_too) {
-    const int tid = threadIdx.x, nthreads = blockDim.x;
-    for (int k = b; k < e; ++k) {
+    const int tid = threadIdx.x, grp = tid >> 7, tg = tid & 127, ngrp = blockDim.x >> 7;
+    for (int k = b + grp; k < e; k += ngrp) {
         const MegaOp& op = ops[k];
         const uint32_t flags = op.flags;
-        const float scale = (flags & MOP_FUSED) ? rstd_from_slots(pool + op.ss_off, op.K, op.eps) : 1.0f;
         uint32_t lo, hi;
         cta_slice(op.y_rows, inv_grid, lo, hi);
         float* acc = pool + op.acc_off;
+        const uint32_t first = lo + tg;
+        const float v0 = first < hi ? __ldcg(acc + first) : 0.f;     // in flight together with the sums
+        const float scale = (flags & MOP_FUSED) ? rstd_from_slots(pool + op.ss_off, op.K, op.eps) : 1.0f;
         void* Y = op.Y;
-        for (uint32_t i = lo + tid; i < hi; i += nthreads) {
-            const float v = __ldcg(acc + i) * scale;
+        for (uint32_t i = first; i < hi; i += 128) {
+            const float v = (i == first ? v0 : __ldcg(acc + i)) * scale;
             if (flags & MOP_Y_F32) static_cast<float*>(Y)[i] = v;
             else static_cast<__half*>(Y)[i] = __float2half_rn(v);
             if (zero_too) acc[i] = 0.f;
@@ -184,12 +206,12 @@ __device__ void finalize_results(const MegaOp* ops, int b, int e, float* pool, u
 }
 
 __device__ void zero_accumulators(const MegaOp* ops, int b, int e, float* pool, uint32_t inv_grid) {
-    const int tid = threadIdx.x, nthreads = blockDim.x;
-    for (int k = b; k < e; ++k) {
+    const int tid = threadIdx.x, grp = tid >> 7, tg = tid & 127, ngrp = blockDim.x >> 7;
+    for (int k = b + grp; k < e; k += ngrp) {
         uint32_t lo, hi;
         cta_slice(ops[k].y_rows, inv_grid, lo, hi);
         float* acc = pool + ops[k].acc_off;
-        for (uint32_t i = lo + tid; i < hi; i += nthreads) acc[i] = 0.f;
+        for (uint32_t i = lo + tg; i < hi; i += 128) acc[i] = 0.f;
     }
 }
 
@@ -210,9 +232,6 @@ __device__ void stage_bands(const MegaOp& op, const DecodeParams& p, uint8_t* sm
     const int xkind = from_acc ? 1 : (f16 ? 0 : 1), gkind = f16 ? 0 : 1;
     uint4* dst = reinterpret_cast<uint4*>(smem + p.off_x);
     float2* sx2 = reinterpret_cast<float2*>(smem + p.off_sx);
-    // what the producer's result buffer will hold: the accumulator scaled by the producer's own
-    // 1/rms (when its prologue was fused) and rounded to its type
-    const float xs = (from_acc && op.xss_off >= 0) ? rstd_from_slots(p.pool + op.xss_off, op.xss_k, op.xss_eps) : 1.0f;
     const uint32_t per_pass = static_cast<uint32_t>(nwarps) / 4;
     for (uint32_t b0 = band_lo; b0 <= band_hi; b0 += per_pass) {
         const uint32_t band = b0 + static_cast<uint32_t>(warp >> 2);
@@ -231,6 +250,10 @@ __device__ void stage_bands(const MegaOp& op, const DecodeParams& p, uint8_t* sm
                 if (fused) load8<false>(op.gamma, gkind, 8 * static_cast<size_t>(i), g);
             }
             if (from_acc) {
+                // what the producer's result buffer will hold: the accumulator scaled by the
+                // producer's own 1/rms (when its prologue was fused) and rounded to its type;
+                // the sums of squares are fetched while the loads above are in flight
+                const float xs = op.xss_off >= 0 ? rstd_from_slots(p.pool + op.xss_off, op.xss_k, op.xss_eps) : 1.0f;
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     v[e] *= xs;
@@ -389,10 +412,7 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
         }
         const MegaOp& op = ops[o];
         if (pc.c0 < pc.c1) {
-            Cursor first, last;
-            cursor_set(pc, pc.c0, first);
-            cursor_set(pc, pc.c1 - 1, last);
-            stage_bands(op, p, smem, scratch, first.band, last.band);
+            stage_bands(op, p, smem, scratch, band_of(pc, pc.c0), band_of(pc, pc.c1 - 1));
         } else {
             __syncthreads();   // keeps the barrier count of stage_bands (one per phase at least)
         }

@@ -47,6 +47,7 @@ constexpr int kMaxPhaseOps = 4;        // operations merged into one phase
 constexpr int kBoxBytes = 32 * 144;
 constexpr int kBandGroups = 4;         // groups per band
 constexpr int kMaxBands = 32;          // slots per staged row: K <= 32 * 1024
+constexpr int kPhaseLenShift = 16;     // MegaOp::flags bits 16..18: operations in the phase that starts here
 
 __device__ __forceinline__ void red_add_gpu(float* p, float v) {
     asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
@@ -100,8 +101,8 @@ struct Phase {
 };
 
 __device__ __forceinline__ void make_phase(const MegaOp* ops, int n_ops, int o, uint32_t inv_grid, Phase& ph) {
-    int oe = o + 1;
-    while (oe < n_ops && oe - o < kMaxPhaseOps && !(ops[oe].flags & (MOP_BARRIER | MOP_RESTAGE))) ++oe;
+    // plan_decode leaves the number of operations of the phase that starts at o in the flags
+    const int oe = o + static_cast<int>((ops[o].flags >> kPhaseLenShift) & 7u);
     ph.o = o;
     ph.oe = oe;
     uint32_t r = 0;
@@ -411,6 +412,8 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
             break;
         }
         const MegaOp& op = ops[o];
+        cc.u = pc.c0 + warp;
+        if (cc.u < pc.c1) cursor_set(pc, cc.u, cc);      // ahead of the staging pass, whose loads hide it
         if (pc.c0 < pc.c1) {
             stage_bands(op, p, smem, scratch, band_of(pc, pc.c0), band_of(pc, pc.c1 - 1));
         } else {
@@ -427,8 +430,6 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
             }
         }
 
-        cc.u = pc.c0 + warp;
-        if (cc.u < pc.c1) cursor_set(pc, cc.u, cc);
         while (cc.u < pc.c1) {
             uint64_t* bar = &bars[warp * ns + cslot];
             if (!mbar_wait_bounded(bar, cphase)) { failed = true; break; }
@@ -662,6 +663,12 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
         }
         if (m.flags & MOP_BARRIER) barriers += (m.flags & MOP_BARRIER2) ? 2 : 1;
     }
+    for (int i = 0; i < n_ops;) {          // phases: runs that share their staged input, at most kMaxPhaseOps long
+        int e = i + 1;
+        while (e < n_ops && e - i < kMaxPhaseOps && !(table[e].flags & (MOP_BARRIER | MOP_RESTAGE))) ++e;
+        table[i].flags |= static_cast<uint32_t>(e - i) << kPhaseLenShift;
+        i = e;
+    }
     plan->n_ops = n_ops;
     plan->barriers = barriers;
     plan->pool_floats = 3 * gen;
@@ -684,7 +691,7 @@ cudaError_t launch_decode(const MegaOp* host_ops, const DecodePlan& plan, const 
         unsigned long long run = 0;
         int len = 0;
         for (int i = 0; i < n_ops; ++i) {
-            const bool head = i == 0 || len >= kMaxPhaseOps || (host_ops[i].flags & (MOP_BARRIER | MOP_RESTAGE)) != 0;
+            const bool head = ((host_ops[i].flags >> kPhaseLenShift) & 7u) != 0;
             if (head) { run = 0; len = 0; }
             run += static_cast<unsigned long long>((host_ops[i].N + 31) / 32) * (host_ops[i].K / 256);
             ++len;

@@ -282,6 +282,33 @@ tc_status_t tc_gguf_loaded_tensor_at(const tc_gguf_loaded_model* model, uint64_t
 tc_status_t tc_gguf_loaded_get_tensor(const tc_gguf_loaded_model* model, const char* name,
                                       tc_gguf_loaded_tensor_info* out);
 
+/* --- the operations between the GEMVs of a decode step (include/tensorcore/training.h:19-24,
+ * 38-45, 60-64, 81-85; arithmetic of lib/ops/training_cpu.cpp:126-186, 287-350, 427-482, 541-573):
+ * fp16 data, fp32 arithmetic, statistics accumulated in double.  Synchronous. */
+tc_status_t tc_rmsnorm_forward(tc_context* ctx, const tc_buffer* X, const tc_buffer* gamma, tc_buffer* Y,
+                               tc_buffer* rstd_out, int N, int D, float eps);
+tc_status_t tc_layernorm_forward(tc_context* ctx, const tc_buffer* X, const tc_buffer* gamma,
+                                 const tc_buffer* beta, tc_buffer* Y, tc_buffer* mean_out,
+                                 tc_buffer* rstd_out, int N, int D, float eps);
+tc_status_t tc_rope_forward(tc_context* ctx, tc_buffer* X, const tc_buffer* cos_t, const tc_buffer* sin_t,
+                            int batch, int heads, int seq, int head_dim);
+tc_status_t tc_swiglu_forward(tc_context* ctx, const tc_buffer* gate, const tc_buffer* up, tc_buffer* out,
+                              int n);
+
+/* include/tensorcore/gemm.h:16-58.  Here: the fp16 x fp16 -> fp16 (fp32 accumulate), row-major,
+ * untransposed case for the few rows of a decode step (what tests/test_fused_norm_gemv.c compares
+ * the fused operations against); every other descriptor answers TC_ERR_UNSUPPORTED_DTYPE /
+ * TC_ERR_UNSUPPORTED_FAMILY. */
+typedef struct {
+    int32_t M, N, K;
+    tc_dtype_t a_dtype, b_dtype, c_dtype, accum_dtype;
+    bool transpose_a, transpose_b;
+    float alpha, beta;
+    int32_t lda, ldb, ldc;
+} tc_gemm_desc;
+tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* desc, const tc_buffer* A, const tc_buffer* B,
+                    tc_buffer* C);
+
 extern const int tensorcore_abi_version;            /* lib/c_api/c_api_cpu.c:15-16 */
 
 /* ===================================================================================== *

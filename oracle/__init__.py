@@ -167,6 +167,46 @@ def fused_layernorm_gemv(X_f16, gamma_f16, beta_f16, W_f16, eps=1e-5) -> np.ndar
     return Y.view(np.float16)
 
 
+def rmsnorm_forward(X_f16, gamma_f16, eps=1e-5):
+    """Returns (Y fp16 [N,D], rstd fp32 [N])."""
+    X = np.ascontiguousarray(X_f16).view(np.uint16)
+    g = np.ascontiguousarray(gamma_f16).view(np.uint16)
+    N, D = X.shape
+    Y, r = np.empty((N, D), np.uint16), np.empty(N, np.float32)
+    _call(lib().orc_rmsnorm_forward, _p(X), _p(g), _p(Y), _p(r), c_int(N), c_int(D), c_float(eps))
+    return Y.view(np.float16), r
+
+
+def layernorm_forward(X_f16, gamma_f16, beta_f16, eps=1e-5):
+    """Returns (Y fp16 [N,D], mean fp32 [N], rstd fp32 [N])."""
+    X = np.ascontiguousarray(X_f16).view(np.uint16)
+    g = np.ascontiguousarray(gamma_f16).view(np.uint16)
+    b = np.ascontiguousarray(beta_f16).view(np.uint16)
+    N, D = X.shape
+    Y, m, r = np.empty((N, D), np.uint16), np.empty(N, np.float32), np.empty(N, np.float32)
+    _call(lib().orc_layernorm_forward, _p(X), _p(g), _p(b), _p(Y), _p(m), _p(r), c_int(N), c_int(D),
+          c_float(eps))
+    return Y.view(np.float16), m, r
+
+
+def swiglu_forward(gate_f16, up_f16):
+    g = np.ascontiguousarray(gate_f16).view(np.uint16).ravel()
+    u = np.ascontiguousarray(up_f16).view(np.uint16).ravel()
+    out = np.empty(g.size, np.uint16)
+    _call(lib().orc_swiglu_forward, _p(g), _p(u), _p(out), c_int(g.size))
+    return out.view(np.float16)
+
+
+def rope_forward(X_f16, cos_t, sin_t):
+    """X [B,H,S,D] fp16 (a rotated copy is returned), tables [S, D/2] fp32."""
+    X = np.ascontiguousarray(X_f16).view(np.uint16).copy()
+    B, H, S, D = X.shape
+    c = np.ascontiguousarray(cos_t, dtype=np.float32)
+    s = np.ascontiguousarray(sin_t, dtype=np.float32)
+    _call(lib().orc_rope_forward, _p(X), _p(c), _p(s), c_int(B), c_int(H), c_int(S), c_int(D))
+    return X.view(np.float16)
+
+
 def dequant_dot_f64(X: np.ndarray, Wq: np.ndarray, fmt: int, N: int) -> np.ndarray:
     X = np.ascontiguousarray(X, dtype=np.float64)
     M, K = X.shape
@@ -310,6 +350,64 @@ class RefLib:
         assert st == 0, st
         out = self._read(py, ny, np.uint16).reshape(M, N).view(np.float16)
         self._free(hx, hg, hb, hw, hy)
+        return out
+
+
+    # --- the operations between the GEMVs of a decode step ---
+    def rmsnorm_forward(self, X_f16, gamma_f16, eps=1e-5):
+        X = np.ascontiguousarray(X_f16).view(np.uint16)
+        N, D = X.shape
+        self.L.tc_rmsnorm_forward.argtypes = [c_void_p] * 5 + [c_int, c_int, c_float]
+        hx, _, _ = self._buf(X)
+        hg, _, _ = self._buf(np.ascontiguousarray(gamma_f16).view(np.uint16))
+        hy, py, ny = self._buf(N * D * 2)
+        hr, pr, nr = self._buf(N * 4)
+        st = self.L.tc_rmsnorm_forward(self.ctx, hx, hg, hy, hr, N, D, c_float(eps))
+        assert st == 0, st
+        out = self._read(py, ny, np.uint16).reshape(N, D).view(np.float16), self._read(pr, nr, np.float32)
+        self._free(hx, hg, hy, hr)
+        return out
+
+    def layernorm_forward(self, X_f16, gamma_f16, beta_f16, eps=1e-5):
+        X = np.ascontiguousarray(X_f16).view(np.uint16)
+        N, D = X.shape
+        self.L.tc_layernorm_forward.argtypes = [c_void_p] * 7 + [c_int, c_int, c_float]
+        hx, _, _ = self._buf(X)
+        hg, _, _ = self._buf(np.ascontiguousarray(gamma_f16).view(np.uint16))
+        hb, _, _ = self._buf(np.ascontiguousarray(beta_f16).view(np.uint16))
+        hy, py, ny = self._buf(N * D * 2)
+        hm, pm, nm = self._buf(N * 4)
+        hr, pr, nr = self._buf(N * 4)
+        st = self.L.tc_layernorm_forward(self.ctx, hx, hg, hb, hy, hm, hr, N, D, c_float(eps))
+        assert st == 0, st
+        out = (self._read(py, ny, np.uint16).reshape(N, D).view(np.float16), self._read(pm, nm, np.float32),
+               self._read(pr, nr, np.float32))
+        self._free(hx, hg, hb, hy, hm, hr)
+        return out
+
+    def swiglu_forward(self, gate_f16, up_f16):
+        g = np.ascontiguousarray(gate_f16).view(np.uint16).ravel()
+        self.L.tc_swiglu_forward.argtypes = [c_void_p] * 4 + [c_int]
+        hg, _, _ = self._buf(g)
+        hu, _, _ = self._buf(np.ascontiguousarray(up_f16).view(np.uint16).ravel())
+        ho, po, no = self._buf(g.size * 2)
+        st = self.L.tc_swiglu_forward(self.ctx, hg, hu, ho, g.size)
+        assert st == 0, st
+        out = self._read(po, no, np.uint16).view(np.float16)
+        self._free(hg, hu, ho)
+        return out
+
+    def rope_forward(self, X_f16, cos_t, sin_t):
+        X = np.ascontiguousarray(X_f16).view(np.uint16)
+        B, H, S, D = X.shape
+        self.L.tc_rope_forward.argtypes = [c_void_p] * 4 + [c_int] * 4
+        hx, px, nx = self._buf(X)
+        hc, _, _ = self._buf(np.ascontiguousarray(cos_t, dtype=np.float32))
+        hs, _, _ = self._buf(np.ascontiguousarray(sin_t, dtype=np.float32))
+        st = self.L.tc_rope_forward(self.ctx, hx, hc, hs, B, H, S, D)
+        assert st == 0, st
+        out = self._read(px, nx, np.uint16).reshape(B, H, S, D).view(np.float16)
+        self._free(hx, hc, hs)
         return out
 
 

@@ -312,6 +312,89 @@ int orc_fused_layernorm_gemv(const uint16_t* X, const uint16_t* gamma, const uin
     return 0;
 }
 
+/* lib/ops/training_cpu.cpp:126-186: sum of squares in double, rstd = 1/sqrtf(float(ss/D)+eps),
+ * y = fp16((x*rstd)*gamma); rstd saved per row. */
+int orc_rmsnorm_forward(const uint16_t* X, const uint16_t* gamma, uint16_t* Y, float* rstd_out,
+                        int N, int D, float eps) {
+    if (!X || !gamma || !Y || !rstd_out || N <= 0 || D <= 0) return -1;
+    for (int n = 0; n < N; ++n) {
+        const uint16_t* xr = X + (size_t)n * D;
+        uint16_t* yr = Y + (size_t)n * D;
+        double ss = 0.0;
+        for (int d = 0; d < D; ++d) {
+            const float xv = orc_f16_to_f32(xr[d]);
+            ss += (double)xv * xv;
+        }
+        const float rstd = 1.0f / sqrtf((float)(ss / D) + eps);
+        rstd_out[n] = rstd;
+        for (int d = 0; d < D; ++d)
+            yr[d] = orc_f32_to_f16(orc_f16_to_f32(xr[d]) * rstd * orc_f16_to_f32(gamma[d]));
+    }
+    return 0;
+}
+
+/* lib/ops/training_cpu.cpp:287-350: mean in double narrowed to fp32, centred second moment in
+ * double, y = fp16(((x-mean)*rstd)*gamma + beta); mean and rstd saved per row. */
+int orc_layernorm_forward(const uint16_t* X, const uint16_t* gamma, const uint16_t* beta,
+                          uint16_t* Y, float* mean_out, float* rstd_out, int N, int D, float eps) {
+    if (!X || !gamma || !beta || !Y || !mean_out || !rstd_out || N <= 0 || D <= 0) return -1;
+    for (int n = 0; n < N; ++n) {
+        const uint16_t* xr = X + (size_t)n * D;
+        uint16_t* yr = Y + (size_t)n * D;
+        double s = 0.0;
+        for (int d = 0; d < D; ++d) s += orc_f16_to_f32(xr[d]);
+        const float mean = (float)(s / D);
+        double sq = 0.0;
+        for (int d = 0; d < D; ++d) {
+            const float c = orc_f16_to_f32(xr[d]) - mean;
+            sq += (double)c * c;
+        }
+        const float rstd = 1.0f / sqrtf((float)(sq / D) + eps);
+        mean_out[n] = mean;
+        rstd_out[n] = rstd;
+        for (int d = 0; d < D; ++d)
+            yr[d] = orc_f32_to_f16((orc_f16_to_f32(xr[d]) - mean) * rstd * orc_f16_to_f32(gamma[d]) +
+                                   orc_f16_to_f32(beta[d]));
+    }
+    return 0;
+}
+
+/* lib/ops/training_cpu.cpp:94-101,541-573: out = fp16(silu(gate) * up), silu(x) = x/(1+expf(-x)),
+ * 0 below -50, x above 50. */
+int orc_swiglu_forward(const uint16_t* gate, const uint16_t* up, uint16_t* out, int n) {
+    if (!gate || !up || !out || n <= 0) return -1;
+    for (int i = 0; i < n; ++i) {
+        const float g = orc_f16_to_f32(gate[i]), u = orc_f16_to_f32(up[i]);
+        float s;
+        if (g < -50.0f) s = 0.0f;
+        else if (g > 50.0f) s = g;
+        else s = g / (1.0f + expf(-g));
+        out[i] = orc_f32_to_f16(s * u);
+    }
+    return 0;
+}
+
+/* lib/ops/training_cpu.cpp:427-482: in place on X[B,H,S,D]; pairs (k, k + D/2) rotated by the
+ * angle whose cosine and sine are cos_t / sin_t[s][k] (fp32 tables [S, D/2]). */
+int orc_rope_forward(uint16_t* X, const float* cos_t, const float* sin_t, int batch, int heads,
+                     int seq, int head_dim) {
+    if (!X || !cos_t || !sin_t || batch <= 0 || heads <= 0 || seq <= 0 || head_dim <= 0 || head_dim % 2)
+        return -1;
+    const int half = head_dim / 2;
+    const long total = (long)batch * heads * seq;
+    for (long bhs = 0; bhs < total; ++bhs) {
+        const int s_idx = (int)(bhs % seq);
+        uint16_t* xr = X + (size_t)bhs * head_dim;
+        for (int k = 0; k < half; ++k) {
+            const float x0 = orc_f16_to_f32(xr[k]), x1 = orc_f16_to_f32(xr[k + half]);
+            const float c = cos_t[(size_t)s_idx * half + k], si = sin_t[(size_t)s_idx * half + k];
+            xr[k] = orc_f32_to_f16(x0 * c - x1 * si);
+            xr[k + half] = orc_f32_to_f16(x0 * si + x1 * c);
+        }
+    }
+    return 0;
+}
+
 int orc_dequantize(const uint8_t* Wq, float* out, int fmt, int N, int K) {
     const unsigned bb = block_bytes(fmt);
     if (!Wq || !out || N <= 0 || K <= 0 || (K % 32) != 0 || bb == 0) return -1;

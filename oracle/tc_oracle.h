@@ -62,6 +62,16 @@ int orc_fused_rmsnorm_gemv(const uint16_t* X, const uint16_t* gamma, const uint1
 int orc_fused_layernorm_gemv(const uint16_t* X, const uint16_t* gamma, const uint16_t* beta,
                              const uint16_t* W, uint16_t* Y, int M, int N, int K, float eps);
 
+/* The operations between the GEMVs of a decode step.
+ * lib/ops/training_cpu.cpp:126-186 / 287-350 / 541-573 / 427-482. */
+int orc_rmsnorm_forward(const uint16_t* X, const uint16_t* gamma, uint16_t* Y, float* rstd_out,
+                        int N, int D, float eps);
+int orc_layernorm_forward(const uint16_t* X, const uint16_t* gamma, const uint16_t* beta,
+                          uint16_t* Y, float* mean_out, float* rstd_out, int N, int D, float eps);
+int orc_swiglu_forward(const uint16_t* gate, const uint16_t* up, uint16_t* out, int n);
+int orc_rope_forward(uint16_t* X, const float* cos_t, const float* sin_t, int batch, int heads,
+                     int seq, int head_dim);
+
 /* Double-precision dequantise-and-dot of the stored blocks against X given as double,
  * the yardstick of tests/test_quantized.c:48-94.  Y is [M,N] double. */
 int orc_dequant_dot_f64(const double* X, const uint8_t* W_quant, double* Y,

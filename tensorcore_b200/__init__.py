@@ -154,6 +154,10 @@ def _declare(L) -> None:
     sig("tc_fused_rmsnorm_gemv_quantized", i, vp, vp, vp, vp, vp, i, i, i, i, f)
     sig("tc_fused_rmsnorm_gemv", i, vp, vp, vp, vp, vp, i, i, i, f)
     sig("tc_fused_layernorm_gemv", i, vp, vp, vp, vp, vp, vp, i, i, i, f)
+    sig("tc_rmsnorm_forward", i, vp, vp, vp, vp, vp, i, i, f)
+    sig("tc_layernorm_forward", i, vp, vp, vp, vp, vp, vp, vp, i, i, f)
+    sig("tc_swiglu_forward", i, vp, vp, vp, vp, i)
+    sig("tc_rope_forward", i, vp, vp, vp, vp, i, i, i, i)
     # GGUF
     sig("tc_gguf_open", i, c_char_p, POINTER(vp))
     sig("tc_gguf_close", None, vp)
@@ -396,6 +400,24 @@ def fused_rmsnorm_gemv(ctx, X, gamma, W, Y, M, N, K, eps=1e-5) -> None:
 def fused_layernorm_gemv(ctx, X, gamma, beta, W, Y, M, N, K, eps=1e-5) -> None:
     _check(lib().tc_fused_layernorm_gemv(_h(ctx), _h(X), _h(gamma), _h(beta), _h(W), _h(Y), int(M),
                                          int(N), int(K), float(eps)))
+
+
+def rmsnorm_forward(ctx, X, gamma, Y, rstd_out, N, D, eps=1e-5) -> None:
+    _check(lib().tc_rmsnorm_forward(_h(ctx), _h(X), _h(gamma), _h(Y), _h(rstd_out), int(N), int(D), float(eps)))
+
+
+def layernorm_forward(ctx, X, gamma, beta, Y, mean_out, rstd_out, N, D, eps=1e-5) -> None:
+    _check(lib().tc_layernorm_forward(_h(ctx), _h(X), _h(gamma), _h(beta), _h(Y), _h(mean_out), _h(rstd_out),
+                                      int(N), int(D), float(eps)))
+
+
+def swiglu_forward(ctx, gate, up, out, n) -> None:
+    _check(lib().tc_swiglu_forward(_h(ctx), _h(gate), _h(up), _h(out), int(n)))
+
+
+def rope_forward(ctx, X, cos_t, sin_t, batch, heads, seq, head_dim) -> None:
+    _check(lib().tc_rope_forward(_h(ctx), _h(X), _h(cos_t), _h(sin_t), int(batch), int(heads), int(seq),
+                                 int(head_dim)))
 
 
 def gemv_quantized_ex(ctx, X, W_quant, Y, fmt, M, N, K, x_dtype="f16", y_dtype="f16",
@@ -703,9 +725,9 @@ class Buffer:
     def device_ptr(self) -> int:
         return buffer_device_ptr(self.handle)
 
-    def to_numpy(self, shape, dtype) -> np.ndarray:
+    def to_numpy(self, shape, dtype, offset: int = 0) -> np.ndarray:
         out = np.empty(shape, dtype=dtype)
-        return self.download(out)
+        return self.download(out, offset)
 
 
 class Stream:

@@ -47,6 +47,7 @@ constexpr int kMaxPhaseOps = 4;        // operations merged into one phase
 constexpr int kBoxBytes = 32 * 144;
 constexpr int kBandGroups = 4;         // groups per band
 constexpr int kMaxBands = 32;          // slots per staged row: K <= 32 * 1024
+constexpr uint32_t MOP_NO_STORE = 256u;  // internal: a later operation overwrites this result before anyone reads it
 constexpr int kPhaseLenShift = 16;     // MegaOp::flags bits 16..18: operations in the phase that starts here
 
 __device__ __forceinline__ void red_add_gpu(float* p, float v) {
@@ -194,13 +195,16 @@ __device__ void finalize_results(const MegaOp* ops, int b, int e, float* pool, u
         cta_slice(op.y_rows, inv_grid, lo, hi);
         float* acc = pool + op.acc_off;
         const uint32_t first = lo + tg;
+        if ((flags & MOP_NO_STORE) && !zero_too) continue;
         const float v0 = first < hi ? __ldcg(acc + first) : 0.f;     // in flight together with the sums
         const float scale = (flags & MOP_FUSED) ? rstd_from_slots(pool + op.ss_off, op.K, op.eps) : 1.0f;
         void* Y = op.Y;
         for (uint32_t i = first; i < hi; i += 128) {
             const float v = (i == first ? v0 : __ldcg(acc + i)) * scale;
-            if (flags & MOP_Y_F32) static_cast<float*>(Y)[i] = v;
-            else static_cast<__half*>(Y)[i] = __float2half_rn(v);
+            if (!(flags & MOP_NO_STORE)) {
+                if (flags & MOP_Y_F32) static_cast<float*>(Y)[i] = v;
+                else static_cast<__half*>(Y)[i] = __float2half_rn(v);
+            }
             if (zero_too) acc[i] = 0.f;
         }
     }
@@ -559,7 +563,31 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
                 if (spans_overlap(rw, yj) || (a.gamma && spans_overlap(rg, yj))) return cudaErrorNotSupported;
             }
         }
-        int nbar = (i > 0 && (span_hits(writes, nw, rx) || span_hits(writes, nw, ry) || span_hits(reads, nr, ry))) ? 1 : 0;
+        // A result that is overwritten - same buffer, same extent - before anything reads it never
+        // needs to reach its buffer: the earlier operation is computed but not stored, and the two
+        // need no barrier between them (a benchmark loop that sends every projection of every
+        // layer to one scratch vector is the common case).
+        auto same_span = [](DecodeSpan a, DecodeSpan b) { return a.lo == b.lo && a.hi == b.hi; };
+        auto dead_until = [&](int j) {      // nothing in (j, i) reads operation j's result
+            const DecodeSpan yj = y_span(j);
+            for (int t = j + 1; t < i; ++t) {
+                const uintptr_t tl = reinterpret_cast<uintptr_t>(ops[t].X);
+                if (spans_overlap(DecodeSpan{tl, tl + ops[t].K * static_cast<size_t>(ops[t].x_f32 ? 4 : 2)}, yj)) return false;
+            }
+            return !spans_overlap(rx, yj);
+        };
+        bool waw_only = i > 0 && !span_hits(writes, nw, rx) && !span_hits(reads, nr, ry);
+        if (waw_only) {
+            for (int w = 0; w < nw && waw_only; ++w)
+                if (spans_overlap(writes[w], ry) &&
+                    !(same_span(writes[w], ry) && ops[i - nw + w].y_f32 == a.y_f32 && dead_until(i - nw + w)))
+                    waw_only = false;
+        }
+        int nbar = (i > 0 && !waw_only &&
+                    (span_hits(writes, nw, rx) || span_hits(writes, nw, ry) || span_hits(reads, nr, ry))) ? 1 : 0;
+        if (waw_only)
+            for (int w = 0; w < nw; ++w)
+                if (spans_overlap(writes[w], ry)) table[i - nw + w].flags |= MOP_NO_STORE;
         int producer = -1;
         if (i > 0 && (spans_overlap(rx, y_box) || spans_overlap(ry, y_box))) {
             for (int round = 0; round < 3; ++round) {
@@ -577,7 +605,10 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
                     }
                     if (!seen_y && spans_overlap(ry, yj)) {        // latest writer of what this one writes
                         seen_y = true;
-                        if (d == 1) bump = true;
+                        if (d == 1) {
+                            if (same_span(ry, yj) && ops[j].y_f32 == a.y_f32 && dead_until(j)) table[j].flags |= MOP_NO_STORE;
+                            else bump = true;
+                        }
                     }
                 }
                 if (!bump) break;

@@ -3,9 +3,9 @@
 //
 //   Y[m][n] = sum_k X[m][k] * dequant(W)[n][k],   fp16 X, 5 <= M <= 32 activation rows.
 //
-// The reference computes this case as M independent dequant-dots per output row
-// (lib/ops/quantized/gemv_dispatch.cpp:52-90 with the kernels of metal_quant_kernels.h); a GPU
-// pays the weight stream M times that way.  Here the weight stream is read once:
+// The reference computes this case as M independent dequant-dots per output row, re-reading the
+// weights for every activation row (lib/ops/quantized_cpu.cpp:193-228); a GPU pays the weight
+// stream M times that way.  Here the weight stream is read once:
 //
 //   * A CTA owns 256 weight rows and a K range (a cluster of `split` CTAs shares one row tile
 //     along K).  Its weight rows arrive in shared memory as raw Q4_0 bytes, one 144-byte group
@@ -63,10 +63,6 @@ constexpr uint32_t kColA = 64;                 // accumulators live in columns [
 constexpr int kMaxBatch = 32;
 constexpr int kXPer = kMaxBatch * 32 / kSetThreads;   // activation chunks per thread per stage
 
-#ifndef TCB_TC_DEBUG
-#define TCB_TC_DEBUG 0
-#endif
-
 struct TcParams {
     const uint8_t* W;
     const __half* X;
@@ -78,8 +74,6 @@ struct TcParams {
     int groups;      // K / 256
     int split;       // CTAs per row tile = cluster size
     int off_raw, off_x;
-    long long* trace; // debug builds: per-stage clock64 stamps of CTA 0, 16 per stage
-    int dbg;          // debug builds: 1 skip dequantisation, 2 skip MMA issue, 4 skip activation loads
 };
 
 struct Ring {
@@ -253,13 +247,6 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
     tc_fence_after_sync();
 
     bool failed = false;
-#if TCB_TC_DEBUG
-#define TCB_TR(COL, I) do { if (p.trace && blockIdx.x == 0) p.trace[(I) * 16 + (COL)] = clock64(); } while (0)
-#define TCB_DBG(BIT) (p.dbg & (BIT))
-#else
-#define TCB_TR(COL, I) do { } while (0)
-#define TCB_DBG(BIT) ((BIT) == 64 && (p.dbg & 64))
-#endif
 
     if (warp < kDqWarps) {
         // ---------------- dequantisers: one thread per weight row; they also stage activations ----
@@ -267,26 +254,22 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
         const int tl = tid & (kSetThreads - 1);
         const int row_local = h * 128 + q * 32 + lane;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-        const bool tr = (wl == 0 && lane == 0);
         Ring raw, slot, xs;
         raw.set(set, kRawStages);
         xs.set(set, kXStages);
         slot.set(2 * set, kASlots);
         XRegs xr;
-        if (set < ng && !TCB_DBG(4)) x_load(p, g0 + set, tl, nb, xr);
+        if (set < ng) x_load(p, g0 + set, tl, nb, xr);
         for (int i = set; i < ng && !failed; i += kSets) {
             // Activations of this stage: loaded a stage ago, now permuted into shared memory.
             if (!bar_wait_warp(&bars->x_empty[xs.idx], xs.phase ^ 1u, abort_flag)) { failed = true; break; }
-            if (tr) TCB_TR(12, i);
             x_store(x_base + xs.idx * x_stage_bytes, lbo, tl, nb, xr);
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) bar_arrive(&bars->x_full[xs.idx]);
-            if (i + kSets < ng && !TCB_DBG(4)) x_load(p, g0 + i + kSets, tl, nb, xr);
-            if (tr) TCB_TR(13, i);
+            if (i + kSets < ng) x_load(p, g0 + i + kSets, tl, nb, xr);
 
             if (!bar_wait_warp(&bars->raw_full[raw.idx], raw.phase, abort_flag)) { failed = true; break; }
-            if (tr) TCB_TR(1, i);
             const uint32_t src = raw_base + raw.idx * kRawStageBytes + row_local * kGroupBytes;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
@@ -303,12 +286,10 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
                     failed = true;
                     break;
                 }
-                if (tr) TCB_TR(3 + 2 * half, i);
                 tc_fence_after_sync();
                 const uint32_t col = lane_base + kColA + static_cast<uint32_t>((h * kASlots + slot.idx) * 64);
                 uint32_t out[16];
-                if (TCB_DBG(1)) {
-                } else if (half == 0) {
+                if (half == 0) {
                     dequant_block<0, 0>(g, out); tmem_st16(col, out);
                     dequant_block<1, 0>(g, out); tmem_st16(col + 16, out);
                     dequant_block<2, 0>(g, out); tmem_st16(col + 32, out);
@@ -330,9 +311,7 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) bar_arrive(&bars->raw_empty[raw.idx]);
-                    if (tr) TCB_TR(2, i);
                 }
-                if (tr) TCB_TR(4 + 2 * half, i);
                 slot.advance(half == 0 ? 1 : 2 * kSets - 1, kASlots);
             }
             raw.advance(kSets, kRawStages);
@@ -344,28 +323,9 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
         Ring raw;
         raw.set(0, kRawStages);
         int issued = 0;
-#if 1
-        if (TCB_DBG(64)) {
-            // Debug comparison path: one 144-byte bulk copy per row instead of the tiled load.
-            const size_t row_bytes = static_cast<size_t>(p.groups) * kGroupBytes;
-            const int valid_rows = min(kTileRows, p.N - row0);
-            const uint8_t* wbase = p.W + static_cast<size_t>(row0) * row_bytes + static_cast<size_t>(g0) * kGroupBytes;
-            for (int i = 0; i < ng; ++i) {
-                if (!bar_wait_warp(&bars->raw_empty[raw.idx], raw.phase ^ 1u, abort_flag)) { failed = true; break; }
-                if (lane == 0) bar_expect_tx(&bars->raw_full[raw.idx], static_cast<uint32_t>(valid_rows) * kGroupBytes);
-                __syncwarp();
-                uint8_t* dst = smem + p.off_raw + raw.idx * kRawStageBytes;
-                for (int r = lane; r < valid_rows; r += 32)
-                    bulk_load(dst + r * kGroupBytes, wbase + r * row_bytes + static_cast<size_t>(i) * kGroupBytes,
-                              kGroupBytes, &bars->raw_full[raw.idx]);
-                raw.advance(1, kRawStages);
-            }
-        } else
-#endif
         if (lane == 0) {
             for (int i = 0; i < ng; ++i) {
                 if (!bar_wait(&bars->raw_empty[raw.idx], raw.phase ^ 1u, abort_flag)) { failed = true; break; }
-                TCB_TR(0, i);
                 bar_expect_tx(&bars->raw_full[raw.idx], kRawStageBytes);
                 tensor_load_2d(smem + p.off_raw + raw.idx * kRawStageBytes, &wmap,
                                (g0 + i) * kGroupBytes, row0, &bars->raw_full[raw.idx]);
@@ -399,7 +359,6 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
                 // Descriptor of the stage's first K step; each further step starts 2 * lbo bytes on.
                 const uint64_t desc0 = smem_desc_kmajor(x_base + xs.idx * x_stage_bytes, lbo, 128u);
                 if (!bar_wait(&bars->x_full[xs.idx], xs.phase, abort_flag)) { failed = true; break; }
-                if (h == 0) TCB_TR(7, i);
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     const uint32_t a_col = tmem_base + kColA + static_cast<uint32_t>((h * kASlots + slot.idx) * 64);
@@ -407,14 +366,10 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
 #pragma unroll
                     for (int jj = 0; jj < 8; ++jj) bdesc[jj] = desc0 + static_cast<uint64_t>((half * 8 + jj) * desc_step);
                     if (!bar_wait(&bars->a_full[h][slot.idx], slot.phase, abort_flag)) { failed = true; break; }
-                    if (h == 0) TCB_TR(8 + 2 * half, i);
                     tc_fence_after_sync();
-                    if (!TCB_DBG(2)) {
 #pragma unroll
-                        for (int jj = 0; jj < 8; ++jj) mma_f16_ts_acc(d_col, a_col + 8u * jj, bdesc[jj], idesc);
-                    }
+                    for (int jj = 0; jj < 8; ++jj) mma_f16_ts_acc(d_col, a_col + 8u * jj, bdesc[jj], idesc);
                     mma_commit(&bars->a_empty[h][slot.idx]);
-                    if (h == 0) TCB_TR(9 + 2 * half, i);
                     slot.advance(1, kASlots);
                 }
                 if (!failed) mma_commit(&bars->x_empty[xs.idx]);
@@ -424,8 +379,6 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
             if (failed || *abort_flag) bar_wait(&bars->d_full, 0, nullptr, 100000000LL);
         }
     }
-#undef TCB_TR
-#undef TCB_DBG
 
     if (failed) {
         *abort_flag = 1;
@@ -573,10 +526,6 @@ cudaError_t launch_gemv_q4_tc(const GemvQArgs& a, const LaunchEnv& env, cudaStre
     if (split > p.groups) split = p.groups;
     if (split < 1) split = 1;
     p.split = split;
-    if (const char* s = std::getenv("TC_TC_DBG")) p.dbg = std::atoi(s);
-#if TCB_TC_DEBUG
-    if (const char* s = std::getenv("TC_TC_TRACE")) p.trace = reinterpret_cast<long long*>(std::strtoull(s, nullptr, 0));
-#endif
 
     CUtensorMap wmap;
     // The weights as a 2-D byte tensor: dimension 0 = the bytes of a row, box = one 8-block group

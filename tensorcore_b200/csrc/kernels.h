@@ -167,6 +167,17 @@ constexpr size_t kDecodeStaticPoolFloats = 3 * 160 * 1024;
 cudaError_t launch_gemv_q4_decode_static(const GemvQArgs* ops, int n_ops, const LaunchEnv& env,
                                          cudaStream_t stream);
 
+// --- the small operations between the GEMVs of a decode step (step_ops.cu); fp16 data --------
+cudaError_t launch_norm_forward(const void* X, const void* gamma, const void* beta /* null = RMSNorm */,
+                                void* Y, float* mean_out /* may be null */, float* rstd_out, int N, int D,
+                                float eps, cudaStream_t stream);
+cudaError_t launch_swiglu(const void* gate, const void* up, void* out, int n, cudaStream_t stream);
+cudaError_t launch_rope(void* X, const float* cos_t, const float* sin_t, int batch, int heads, int seq,
+                        int head_dim, cudaStream_t stream);
+// cudaErrorNotSupported when K floats do not fit a CTA's static shared-memory budget.
+cudaError_t launch_gemm_f16_rows(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                                 int ldc, float alpha, float beta, cudaStream_t stream);
+
 // One-time per-device kernel attribute setup (max dynamic shared memory).
 cudaError_t init_kernels_for_device(int smem_optin);
 

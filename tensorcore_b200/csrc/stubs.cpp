@@ -37,7 +37,6 @@ TCB_EXPORT int tc_diloco_apply_outer(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_diloco_finalize(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_diloco_init(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_diloco_step(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_gemm(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_gemm_async(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_gemm_batched(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_hip_device_at(void) { return TCB_UNSUPPORTED; }
@@ -45,16 +44,12 @@ TCB_EXPORT int tc_hip_device_info_get(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_hip_init(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_hip_select_device(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_layernorm_backward(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_layernorm_forward(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_memory_tier_usage(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_rmsnorm_backward(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_rmsnorm_forward(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_rope_backward(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_rope_forward(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_softmax_backward(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_softmax_forward(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_swiglu_backward(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_swiglu_forward(void) { return TCB_UNSUPPORTED; }
 
 TCB_EXPORT int32_t tc_eshkol_attention_forward(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int32_t tc_eshkol_buffer_free(void) { return TCB_UNSUPPORTED; }

@@ -63,6 +63,27 @@ def main() -> None:
         dense[key + "_Yrms"] = R.fused_rmsnorm_gemv(X, g, W, 1e-5).view(np.uint16)
         dense[key + "_Yln"] = R.fused_layernorm_gemv(X, g, b, W, 1e-5).view(np.uint16)
     np.savez_compressed(os.path.join(OUT, "dense_fused.npz"), **dense)
+    step = {}
+    for (N, D) in ((1, 64), (3, 256), (2, 4096)):
+        X = (rng.standard_normal((N, D)) * 1.5).astype(np.float32).astype(np.float16)
+        g = (1.0 + 0.1 * rng.standard_normal(D)).astype(np.float32).astype(np.float16)
+        b = (0.1 * rng.standard_normal(D)).astype(np.float32).astype(np.float16)
+        key = f"norm_N{N}_D{D}"
+        step[key + "_X"], step[key + "_gamma"], step[key + "_beta"] = X.view(np.uint16), g.view(np.uint16), b.view(np.uint16)
+        y, r = R.rmsnorm_forward(X, g, 1e-5)
+        step[key + "_Yrms"], step[key + "_rstd_rms"] = y.view(np.uint16), r
+        y, m, r = R.layernorm_forward(X, g, b, 1e-5)
+        step[key + "_Yln"], step[key + "_mean_ln"], step[key + "_rstd_ln"] = y.view(np.uint16), m, r
+    gate = np.concatenate([rng.standard_normal(2000) * 4, [-60.0, 60.0, 0.0, -0.0, 49.9, -49.9]]).astype(np.float16)
+    up = rng.standard_normal(gate.size).astype(np.float16)
+    step["swiglu_gate"], step["swiglu_up"] = gate.view(np.uint16), up.view(np.uint16)
+    step["swiglu_out"] = R.swiglu_forward(gate, up).view(np.uint16)
+    B, H, S, D = 2, 3, 5, 64
+    X = rng.standard_normal((B, H, S, D)).astype(np.float16)
+    ang = np.outer(np.arange(S), 10000.0 ** (-np.arange(D // 2) / (D // 2))).astype(np.float32)
+    step["rope_X"], step["rope_cos"], step["rope_sin"] = X.view(np.uint16), np.cos(ang), np.sin(ang)
+    step["rope_out"] = R.rope_forward(X, np.cos(ang), np.sin(ang)).view(np.uint16)
+    np.savez_compressed(os.path.join(OUT, "step_ops.npz"), **step)
     print("wrote", sorted(os.listdir(OUT)))
 
 

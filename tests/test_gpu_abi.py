@@ -201,3 +201,32 @@ def test_gguf_load_to_device_and_known_answer(tc, ctx, tmp_path, oracle):
             g.tensor_to_buffer(ctx, "odd")
         for b in (x1, y1, bx, single):
             b.close()
+
+
+def test_first_map_between_record_and_sync(tc, ctx, oracle):
+    """Legal under the reference contract (include/tensorcore/device.h:59-62: the mapped pointer is
+    stable and coherent at sync points): record an operation, map its never-mapped result and
+    input buffers for the first time - which moves them to host-visible storage - then sync and
+    read the result through the mapped pointer."""
+    import ctypes
+    rng = np.random.default_rng(31)
+    N, K = 96, 512
+    for fmt in (0, 1):
+        Wq = oracle.quantize_weights((rng.standard_normal((N, K)) * 0.02).astype(np.float16), fmt)
+        X = rng.standard_normal((1, K)).astype(np.float16)
+        want = oracle.gemv_quantized(X, Wq, fmt, N)
+        bw, bx, by = ctx.buffer_from_array(Wq), ctx.buffer(K * 2), ctx.buffer(N * 2)
+        bx.upload(X)
+        s = ctx.stream()
+        ctx.gemv_quantized_async(bx, bw, by, fmt, 1, N, K, s)
+        ctx.gemv_quantized_async(bx, bw, by, fmt, 1, N, K, s)
+        py = by.map()                    # first map of Y: after recording, before the sync
+        px = bx.map()                    # and of X
+        s.sync()
+        got = np.ctypeslib.as_array(ctypes.cast(py, ctypes.POINTER(ctypes.c_uint16)), (1, N)).view(np.float16)
+        assert oracle.scaled_rms(got.copy(), want) <= 3e-4, fmt
+        assert by.map() == py and bx.map() == px          # stable pointers
+        s.close()
+        for b in (bw, bx, by):
+            b.close()
+    assert tc.take_device_error(ctx) == 0

@@ -281,7 +281,9 @@ def test_dense_fused_matches_reference_golden(tc, ctx, oracle):
 # ---------------------------------------------------------------------------------------
 @pytest.mark.parametrize("case", [("q4_0", 4096, 4096, 1), ("q8_0", 11008, 4096, 1),
                                   ("q4_0", 32000, 4096, 1), ("q4_0", 4096, 11008, 1),
-                                  ("q4_0", 14336, 4096, 4), ("q4_0", 14336, 4096, 8),
+                                  ("q4_0", 14336, 4096, 1), ("q4_0", 14336, 4096, 4),
+                                  ("q4_0", 14336, 4096, 8), ("q4_0", 14336, 4096, 16),
+                                  ("q4_0", 14336, 4096, 32),
                                   ("q4_0", 1024, 8192, 1), ("q4_0", 8192, 28672, 1)])
 def test_full_size_shapes(tc, ctx, oracle, case):
     tag, N, K, M = case
@@ -336,3 +338,239 @@ def test_repeated_launches_on_cache_resident_weights(tc, ctx, oracle, variant, t
         for b in (bx, bw, by):
             b.close()
     assert tc.take_device_error(ctx) == 0
+
+
+@pytest.mark.parametrize("x_f32", [False, True])
+def test_config2_fused_rmsnorm_q8_0_full_size(tc, ctx, oracle, x_f32):
+    """Q8_0 11008 x 4096 with the RMSNorm prologue fused, fp16 and fp32 activations."""
+    fmt, N, K = 1, 11008, 4096
+    rng = np.random.default_rng(20404 + x_f32)
+    Wq = gpu_quantize(tc, ctx, make_weights(rng, N, K), fmt)
+    xdt = np.float32 if x_f32 else np.float16
+    X = rng.standard_normal((1, K)).astype(np.float32).astype(xdt)
+    gam = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32).astype(xdt)
+    if x_f32:
+        got = gpu_gemv(tc, ctx, X, Wq, fmt, N, y_f32=True, gamma=gam)
+        assert oracle.scaled_rms(got, oracle.fused_rmsnorm_gemv_quantized_f32(X, gam, Wq, fmt, N, 1e-5)) <= TOL_F32
+    else:
+        got = gpu_gemv(tc, ctx, X, Wq, fmt, N, gamma=gam)
+        assert oracle.scaled_rms(got, oracle.fused_rmsnorm_gemv_quantized(X, gam, Wq, fmt, N, 1e-5)) <= TOL_VS_ORACLE_F16
+    plain = gpu_gemv(tc, ctx, X, Wq, fmt, N, y_f32=x_f32)
+    want = oracle.gemv_quantized_f32(X, Wq, fmt, N) if x_f32 else oracle.gemv_quantized(X, Wq, fmt, N)
+    assert oracle.scaled_rms(plain, want) <= (TOL_F32 if x_f32 else TOL_VS_ORACLE_F16)
+
+
+@pytest.mark.parametrize("shape", [(28672, 8192), (128256, 8192)])
+def test_llama70b_shapes_sampled_rows(tc, ctx, oracle, shape):
+    """The 70B gate/up and lm_head matrices (up to 590 MB of Q4_0): weights are drawn and
+    quantised on the device; quantiser bytes and GEMV results are checked on sampled rows."""
+    from tensorcore_b200 import decode as D
+    N, K = shape
+    fmt, bb = 0, 18
+    rng = np.random.default_rng(N + K)
+    w16 = D.device_weights_fp16(N, K, 0x70B + N)
+    bq = D.quantize_into(ctx, w16, fmt)
+    rows = np.unique(np.concatenate([[0, 1, N - 1], rng.integers(0, N, 200)]))
+    W_rows = w16[rows.tolist()].cpu().numpy()
+    del w16
+    row_bytes = K // 32 * bb
+    Wq_rows = np.concatenate([bq.to_numpy((row_bytes,), np.uint8, offset=int(r) * row_bytes) for r in rows])
+    assert np.array_equal(Wq_rows, oracle.quantize_weights(W_rows, fmt))
+    X = rng.standard_normal((1, K)).astype(np.float16)
+    with dev(ctx, X) as bx, ctx.buffer(N * 2) as by:
+        ctx.gemv_quantized(bx, bq, by, fmt, 1, N, K)
+        got = by.to_numpy((1, N), np.float16)
+    want = oracle.gemv_quantized(X, Wq_rows, fmt, len(rows))
+    assert oracle.scaled_rms(got[:, rows], want) <= TOL_VS_ORACLE_F16
+    assert np.all(np.isfinite(got))
+    bq.close()
+
+
+# ---------------------------------------------------------------------------------------
+# Activations that stress the int16 staging: outliers, heavy tails, empty blocks, non-finite values
+# ---------------------------------------------------------------------------------------
+def _stress_rows(rng, K):
+    rows = {}
+    x = rng.standard_normal(K)
+    for f in (100.0, 1000.0):                      # one element f times its block-mates, in 16 blocks
+        y = x.copy()
+        for b in rng.choice(K // 32, 16, replace=False):
+            y[32 * b + rng.integers(0, 32)] *= f
+        rows[f"outlier{int(f)}"] = y
+    rows["student_t2"] = rng.standard_t(2, K)
+    z = x.copy()
+    z[64:96] = 0.0
+    z[K - 32:] = 0.0
+    rows["zero_blocks"] = z
+    rows["tiny"] = x * 1e-4
+    return rows
+
+
+@pytest.mark.parametrize("tag", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("variant", ["simt", "stream"])
+def test_outlier_activations_single_operation(tc, ctx, oracle, tag, variant):
+    fmt, N, K = Q[tag], 512, 4096
+    rng = np.random.default_rng(4242 + fmt)
+    Wq = oracle.quantize_weights(make_weights(rng, N, K), fmt)
+    try:
+        tc.set_gemv_variant(variant)
+        for name, row in _stress_rows(rng, K).items():
+            X32 = row.astype(np.float32)[None, :]
+            want = oracle.dequant_dot_f64(X32.astype(np.float64), Wq, fmt, N)
+            got = gpu_gemv(tc, ctx, X32, Wq, fmt, N, y_f32=True)
+            assert oracle.scaled_rms(got, want) <= TOL_F32, name
+            X16 = X32.astype(np.float16)
+            if np.all(np.isfinite(X16)):
+                want16 = oracle.dequant_dot_f64(X16.astype(np.float64), Wq, fmt, N)
+                got16 = gpu_gemv(tc, ctx, X16, Wq, fmt, N, y_f32=True)
+                assert oracle.scaled_rms(got16, want16) <= TOL_F32, name   # fp16 values are staged exactly enough
+                assert oracle.scaled_rms(gpu_gemv(tc, ctx, X16, Wq, fmt, N), want16) <= TOL_F16_ACT, name
+            gam = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+            wantf = oracle.fused_rmsnorm_gemv_quantized_f32(X32, gam, Wq, fmt, N, 1e-5)
+            gotf = gpu_gemv(tc, ctx, X32, Wq, fmt, N, y_f32=True, gamma=gam)
+            assert oracle.scaled_rms(gotf, wantf) <= TOL_F32, name
+    finally:
+        tc.set_gemv_variant("auto")
+
+
+def test_outlier_activations_persistent_launch(tc, ctx, oracle):
+    """The same rows through a recorded list (the persistent decode kernel), plain and fused."""
+    fmt, N, K = 0, 512, 4096
+    rng = np.random.default_rng(777)
+    Wq = oracle.quantize_weights(make_weights(rng, N, K), fmt)
+    gam = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    bw, bg = dev(ctx, Wq), dev(ctx, gam)
+    y1, y2 = ctx.buffer(N * 4), ctx.buffer(N * 4)
+    s = ctx.stream()
+    for name, row in _stress_rows(rng, K).items():
+        X32 = row.astype(np.float32)[None, :]
+        bx = dev(ctx, X32)
+        tc.gemv_quantized_ex(ctx, bx, bw, y1, fmt, 1, N, K, "f32", "f32", s)
+        tc.fused_rmsnorm_gemv_quantized_ex(ctx, bx, bg, bw, y2, fmt, 1, N, K, 1e-5, "f32", "f32", s)
+        s.sync()
+        assert "persistent" in tc.cuda_last_kernel_name()
+        want = oracle.dequant_dot_f64(X32.astype(np.float64), Wq, fmt, N)
+        assert oracle.scaled_rms(y1.to_numpy((1, N), np.float32), want) <= TOL_F32, name
+        wantf = oracle.fused_rmsnorm_gemv_quantized_f32(X32, gam, Wq, fmt, N, 1e-5)
+        assert oracle.scaled_rms(y2.to_numpy((1, N), np.float32), wantf) <= TOL_F32, name
+        bx.close()
+    s.close()
+    for b in (bw, bg, y1, y2):
+        b.close()
+    assert tc.take_device_error(ctx) == 0
+
+
+@pytest.mark.parametrize("bad", [np.nan, np.inf, -np.inf])
+def test_non_finite_activations_propagate(tc, ctx, oracle, bad):
+    """The reference multiplies and accumulates in fp32, so a NaN or an infinity in x makes every
+    result that uses it non-finite (lib/ops/quantized_cpu.cpp:193-228); the int16 staging must
+    not turn it into a plausible finite number."""
+    fmt, N, K = 0, 256, 1024
+    rng = np.random.default_rng(99)
+    Wq = oracle.quantize_weights(make_weights(rng, N, K), fmt)
+    X = rng.standard_normal((1, K)).astype(np.float32)
+    X[0, 517] = bad
+    want = oracle.gemv_quantized_f32(X, Wq, fmt, N)
+    assert not np.any(np.isfinite(want))
+    for variant in ("simt", "stream"):
+        try:
+            tc.set_gemv_variant(variant)
+            assert not np.any(np.isfinite(gpu_gemv(tc, ctx, X, Wq, fmt, N, y_f32=True))), variant
+            if np.isnan(bad):
+                X16 = X.astype(np.float16)
+                assert not np.any(np.isfinite(gpu_gemv(tc, ctx, X16, Wq, fmt, N).astype(np.float32))), variant
+        finally:
+            tc.set_gemv_variant("auto")
+    # recorded list -> persistent kernel; the second operation reads the first one's NaNs
+    bx, bw = dev(ctx, X), dev(ctx, Wq)
+    W2 = oracle.quantize_weights(make_weights(rng, 64, N), fmt)
+    bw2, y1, y2 = dev(ctx, W2), ctx.buffer(N * 4), ctx.buffer(64 * 4)
+    s = ctx.stream()
+    tc.gemv_quantized_ex(ctx, bx, bw, y1, fmt, 1, N, K, "f32", "f32", s)
+    tc.gemv_quantized_ex(ctx, y1, bw2, y2, fmt, 1, 64, N, "f32", "f32", s)
+    s.sync()
+    assert "persistent" in tc.cuda_last_kernel_name()
+    assert not np.any(np.isfinite(y1.to_numpy((1, N), np.float32)))
+    assert not np.any(np.isfinite(y2.to_numpy((1, 64), np.float32)))
+    s.close()
+    for b in (bx, bw, bw2, y1, y2):
+        b.close()
+    # a NaN must not linger in the kernel's scratch: the next list is clean
+    X[0, 517] = 0.5
+    got = gpu_gemv(tc, ctx, X, Wq, fmt, N, y_f32=True, stream=None)
+    assert np.all(np.isfinite(got))
+
+
+# ---------------------------------------------------------------------------------------
+# The operations between the GEMVs of a decode step
+# ---------------------------------------------------------------------------------------
+def _ulps16(a, b):
+    """Largest distance between two fp16 arrays in units in the last place (finite values)."""
+    ia = a.view(np.int16).astype(np.int32); ib = b.view(np.int16).astype(np.int32)
+    ia = np.where(ia < 0, -32768 - ia, ia); ib = np.where(ib < 0, -32768 - ib, ib)
+    return int(np.abs(ia - ib).max())
+
+
+@pytest.mark.parametrize("shape", [(1, 64), (3, 1000), (2, 4096), (1, 8192), (8, 4096)])
+def test_norm_forward_matches_oracle(tc, ctx, oracle, shape):
+    """fp32 arithmetic in the reference's order; the only freedom is the summation order of the
+    double-precision statistics, so results agree to the last fp16 place or one off."""
+    N, D = shape
+    rng = np.random.default_rng(N * 100 + D)
+    X = (rng.standard_normal((N, D)) * 1.5).astype(np.float16)
+    gam = (1 + 0.1 * rng.standard_normal(D)).astype(np.float16)
+    bet = (0.1 * rng.standard_normal(D)).astype(np.float16)
+    bx, bg, bb = dev(ctx, X), dev(ctx, gam), dev(ctx, bet)
+    by, bm, br = ctx.buffer(N * D * 2), ctx.buffer(N * 4), ctx.buffer(N * 4)
+    tc.rmsnorm_forward(ctx, bx, bg, by, br, N, D, 1e-5)
+    assert tc.last_backend() == tc.TC_BACKEND_CUDA
+    wy, wr = oracle.rmsnorm_forward(X, gam)
+    assert _ulps16(by.to_numpy((N, D), np.float16), wy) <= 1
+    assert np.allclose(br.to_numpy((N,), np.float32), wr, rtol=3e-7, atol=0)
+    tc.layernorm_forward(ctx, bx, bg, bb, by, bm, br, N, D, 1e-5)
+    wy, wm, wr = oracle.layernorm_forward(X, gam, bet)
+    assert _ulps16(by.to_numpy((N, D), np.float16), wy) <= 1
+    assert np.allclose(bm.to_numpy((N,), np.float32), wm, rtol=1e-6, atol=1e-9)
+    assert np.allclose(br.to_numpy((N,), np.float32), wr, rtol=3e-7, atol=0)
+    for b in (bx, bg, bb, by, bm, br):
+        b.close()
+
+
+def test_step_ops_match_reference_golden_on_gpu(tc, ctx):
+    g = np.load(os.path.join(GOLDEN, "step_ops.npz"))
+    gate, up = g["swiglu_gate"].view(np.float16), g["swiglu_up"].view(np.float16)
+    bg, bu, bo = dev(ctx, gate), dev(ctx, up), ctx.buffer(gate.size * 2)
+    tc.swiglu_forward(ctx, bg, bu, bo, gate.size)
+    assert _ulps16(bo.to_numpy((gate.size,), np.float16), g["swiglu_out"].view(np.float16)) <= 1   # expf differs in the last fp32 place
+    X = g["rope_X"].view(np.float16)
+    B, H, S, D = X.shape
+    bx, bc, bs = dev(ctx, X), dev(ctx, g["rope_cos"]), dev(ctx, g["rope_sin"])
+    tc.rope_forward(ctx, bx, bc, bs, B, H, S, D)
+    assert np.array_equal(bx.to_numpy(X.shape, np.uint16), g["rope_out"])          # no freedom at all: bit for bit
+    for key in sorted({k.rsplit("_", 1)[0] for k in g.files if k.startswith("norm_") and k.endswith("_X")}):
+        Xn, gam = g[key + "_X"].view(np.float16), g[key + "_gamma"].view(np.float16)
+        N, Dn = Xn.shape
+        b1, b2, b3, b4 = dev(ctx, Xn), dev(ctx, gam), ctx.buffer(N * Dn * 2), ctx.buffer(N * 4)
+        tc.rmsnorm_forward(ctx, b1, b2, b3, b4, N, Dn, 1e-5)
+        assert _ulps16(b3.to_numpy((N, Dn), np.float16), g[key + "_Yrms"].view(np.float16)) <= 1, key
+        for b in (b1, b2, b3, b4):
+            b.close()
+    for b in (bg, bu, bo, bx, bc, bs):
+        b.close()
+
+
+def test_swiglu_and_rope_bulk(tc, ctx, oracle):
+    rng = np.random.default_rng(808)
+    n = 11008 * 3
+    gate, up = (rng.standard_normal(n) * 3).astype(np.float16), rng.standard_normal(n).astype(np.float16)
+    bg, bu, bo = dev(ctx, gate), dev(ctx, up), ctx.buffer(n * 2)
+    tc.swiglu_forward(ctx, bg, bu, bo, n)
+    assert _ulps16(bo.to_numpy((n,), np.float16), oracle.swiglu_forward(gate, up)) <= 1
+    B, H, S, D = 1, 32, 3, 128
+    X = rng.standard_normal((B, H, S, D)).astype(np.float16)
+    ang = np.outer(np.arange(S) + 17, 10000.0 ** (-np.arange(D // 2) / (D // 2))).astype(np.float32)
+    bx, bc, bs = dev(ctx, X), dev(ctx, np.cos(ang)), dev(ctx, np.sin(ang))
+    tc.rope_forward(ctx, bx, bc, bs, B, H, S, D)
+    assert np.array_equal(bx.to_numpy(X.shape, np.uint16), oracle.rope_forward(X, np.cos(ang), np.sin(ang)).view(np.uint16))
+    for b in (bg, bu, bo, bx, bc, bs):
+        b.close()

@@ -151,3 +151,46 @@ def test_against_reference_backend_when_built(oracle):
             assert np.array_equal(
                 oracle.fused_rmsnorm_gemv_quantized(X, gam, wq, fmt, N).view(np.uint16),
                 R.fused_rmsnorm_gemv_quantized(X, gam, wq, fmt, N).view(np.uint16))
+
+
+def _step_inputs(rng, N, D):
+    X = (rng.standard_normal((N, D)) * 1.5).astype(np.float16)
+    g = (1 + 0.1 * rng.standard_normal(D)).astype(np.float16)
+    b = (0.1 * rng.standard_normal(D)).astype(np.float16)
+    return X, g, b
+
+
+def test_step_ops_match_reference_golden(oracle):
+    """RMSNorm / LayerNorm forward, SwiGLU and RoPE against outputs of the reference's CPU backend
+    (tests/golden/step_ops.npz, written by make_golden.py): bit for bit."""
+    g = np.load(os.path.join(GOLDEN, "step_ops.npz"))
+    for key in sorted({k.rsplit("_", 1)[0] for k in g.files if k.startswith("norm_") and k.endswith("_X")}):
+        X, gam, bet = (g[key + s].view(np.float16) for s in ("_X", "_gamma", "_beta"))
+        y, r = oracle.rmsnorm_forward(X, gam)
+        assert np.array_equal(y.view(np.uint16), g[key + "_Yrms"]) and np.array_equal(r, g[key + "_rstd_rms"]), key
+        y, m, r = oracle.layernorm_forward(X, gam, bet)
+        assert np.array_equal(y.view(np.uint16), g[key + "_Yln"]), key
+        assert np.array_equal(m, g[key + "_mean_ln"]) and np.array_equal(r, g[key + "_rstd_ln"]), key
+    out = oracle.swiglu_forward(g["swiglu_gate"].view(np.float16), g["swiglu_up"].view(np.float16))
+    assert np.array_equal(out.view(np.uint16), g["swiglu_out"])
+    out = oracle.rope_forward(g["rope_X"].view(np.float16), g["rope_cos"], g["rope_sin"])
+    assert np.array_equal(out.view(np.uint16), g["rope_out"])
+
+
+def test_step_ops_against_reference_backend_when_built(oracle):
+    if not oracle.ref_available():
+        pytest.skip("oracle/_ref not built (no reference checkout on this machine)")
+    R = oracle.RefLib()
+    rng = np.random.default_rng(21)
+    for (N, D) in ((1, 32), (4, 1000), (2, 8192)):
+        X, gam, bet = _step_inputs(rng, N, D)
+        a, b = oracle.rmsnorm_forward(X, gam), R.rmsnorm_forward(X, gam)
+        assert np.array_equal(a[0].view(np.uint16), b[0].view(np.uint16)) and np.array_equal(a[1], b[1])
+        a, b = oracle.layernorm_forward(X, gam, bet), R.layernorm_forward(X, gam, bet)
+        assert all(np.array_equal(np.asarray(p).view(np.uint8), np.asarray(q).view(np.uint8)) for p, q in zip(a, b))
+    gate, up = (rng.standard_normal(5000) * 6).astype(np.float16), rng.standard_normal(5000).astype(np.float16)
+    assert np.array_equal(oracle.swiglu_forward(gate, up).view(np.uint16), R.swiglu_forward(gate, up).view(np.uint16))
+    X = rng.standard_normal((1, 4, 7, 128)).astype(np.float16)
+    ang = rng.uniform(0, 6.28, (7, 64)).astype(np.float32)
+    assert np.array_equal(oracle.rope_forward(X, np.cos(ang), np.sin(ang)).view(np.uint16),
+                          R.rope_forward(X, np.cos(ang), np.sin(ang)).view(np.uint16))

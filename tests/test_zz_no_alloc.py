@@ -3,12 +3,14 @@
 Who it is for: callers that cannot afford an allocation on the decode path - a server that has
 handed all of its HBM to weights and KV cache at start-up, or a loop in which cudaMalloc's
 device-wide synchronisation must not happen.  The entry point keeps the persistent kernel's
-scratch (operation table, grid-barrier counter) in a fixed device array of the library image.
+scratch (operation table, tensor maps, grid-barrier counter, fp32 accumulators) in a fixed device
+array of the library image.
 
 The check: the same five-operation decode fragment is run through the existing per-operation
 raw entry points and through the new one, through the C ABI, twice in a row (the array keeps the
 previous call's contents, so the second call proves that it is re-initialised), and the
-outputs must agree within the tolerances of the other GPU tests.  The file sorts last so that a
+outputs must agree with the existing entry points' and with the oracle's values for the same
+fragment, within the tolerances of the other GPU tests.  The file sorts last so that a
 run that stops at the first failure has executed every other test before it."""
 import numpy as np
 import pytest
@@ -26,6 +28,19 @@ def _fragment(tc, ctx, oracle, seed):
     g16 = (1 + 0.1 * rng.standard_normal(d)).astype(np.float16)
     gam16, gam32 = B(g16), B(g16.astype(np.float32))
     return d, f, w, x, gam16, gam32
+
+
+def _oracle_values(oracle, ctx, d, f, w, x, gam16):
+    """The fragment on the CPU: q, k = fused(x); o = gemv(q) in fp32; g = fused_f32(o); y = gemv(g)."""
+    host = {n: b.to_numpy((b.nbytes,), np.uint8) for n, b in w.items()}
+    x16 = x.to_numpy((1, d), np.float16)
+    g16 = gam16.to_numpy((d,), np.float16)
+    q = oracle.fused_rmsnorm_gemv_quantized(x16, g16, host["q"], 0, d)
+    k = oracle.fused_rmsnorm_gemv_quantized(x16, g16, host["k"], 0, 256)
+    o = oracle.gemv_quantized_f32(q.astype(np.float32), host["o"], 0, d)
+    g = oracle.fused_rmsnorm_gemv_quantized_f32(o, g16.astype(np.float32), host["g"], 0, f).astype(np.float16)
+    y = oracle.gemv_quantized(g, host["dn"], 0, d)
+    return {"q": q.ravel(), "k": k.ravel(), "o": o.ravel(), "g": g.ravel(), "y": y.ravel()}
 
 
 def _outputs(ctx, d, f):
@@ -69,6 +84,7 @@ def test_static_scratch_decode_matches_existing_entry_points(tc, ctx, oracle):
 
     run_existing(ref)
     want = _read(ref, d, f)
+    cpu = _oracle_values(oracle, ctx, d, f, w, x, gam16)
     for call in range(2):                      # two calls in a row share the static array
         for b in new.values():                 # poison the outputs so that stale data cannot pass
             b.upload(np.full(b.nbytes, 0x7F, np.uint8))
@@ -80,6 +96,11 @@ def test_static_scratch_decode_matches_existing_entry_points(tc, ctx, oracle):
         assert oracle.scaled_rms(got["o"], want["o"]) <= 2e-3, call
         assert oracle.scaled_rms(got["g"], want["g"]) <= 2e-3, call
         assert oracle.scaled_rms(got["y"], want["y"]) <= 2e-3, call
+        # and against the CPU restatement of the reference, bars as in test_gpu_persistent.py
+        assert oracle.scaled_rms(got["q"], cpu["q"]) <= 3e-4, call
+        assert oracle.scaled_rms(got["k"], cpu["k"]) <= 3e-4, call
+        for n in ("o", "g", "y"):
+            assert oracle.scaled_rms(got[n], cpu[n]) <= 2e-3, (call, n)
     assert tc.take_device_error(ctx) == 0
 
 

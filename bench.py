@@ -32,6 +32,7 @@ if ROOT not in sys.path:
 import numpy as np  # noqa: E402
 
 METRIC = "synthetic 7B Q4_0 decode tok/s"
+TRAFFIC_RATIO = 1.0075   # DRAM bytes / algorithmic bytes of the persistent decode kernel (ncu, see profiles/)
 UNIT = "tok/s"
 
 
@@ -242,11 +243,11 @@ def run_reference_arm(args) -> dict:
     return {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": spt * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": workload_text(shape) + "; the reference's CPU kernels called through "
-                               "the reference library's tc_* ABI",
-                   "gemvs_per_token": shape.gemvs_per_token(), "weight_bytes_per_token": weight_b},
+        "config": {"workload": workload_text(shape),
+                   "gemvs_per_token": shape.gemvs_per_token(), "weight_bytes_per_token": weight_b,
+                   "api": "the reference's CPU kernels called through the reference library's tc_* ABI"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": probe.kind,
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -262,6 +263,150 @@ def cpu_baseline_leg(shape) -> dict:
     return {"value": 1.0 / spt, "unit": UNIT, "cores": 1, "kind": cpu.kind,
             "sample": f"one token: {shape.n_layers} of {shape.n_layers} layers + lm_head on one thread "
                       f"({per_sample:.1f} s)"}
+
+
+# ---------------------------------------------------------------------------------------
+# Single operations (BASELINE configs 1, 2 and 4, and the dense fused operations)
+# ---------------------------------------------------------------------------------------
+def gemv_cases(ctx, quick: bool = False) -> list[dict]:
+    """Per case: microseconds per GEMV with the weights streamed from HBM (the calls rotate over
+    enough distinct copies of the matrix to exceed twice the L2), algorithmic GB/s and its
+    fraction of the measured HBM peak.  Two ways of issuing the same calls:
+      stream  - recorded on a tc_stream, one tc_stream_sync (Q4_0, M = 1 lists run as one
+                persistent kernel; everything else replays a CUDA graph of per-operation kernels);
+      per_op  - the same with the persistent kernel switched off: one kernel per GEMV.
+    Algorithmic bytes per call: N*(K/32)*B + M*K*sx + M*N*sy (+ K*sx of gamma when fused)."""
+    import tensorcore_b200 as tc
+    from tensorcore_b200 import decode as D
+    peak, _ = measured_peaks()
+    out = []
+
+    def weights_copies(fmt, N, K):
+        nbytes = tc.quantized_size(fmt, N, K)
+        copies = max(2, min(64, int(2 * 126e6 // nbytes) + 1))
+        w16 = D.device_weights_fp16(N, K, 0xC0FFEE + N + K)
+        return [D.quantize_into(ctx, w16, fmt) for _ in range(copies)], nbytes
+
+    def quant_case(config, fmt, M, N, K, xd, yd, fused, iters):
+        ws, nbytes = weights_copies(fmt, N, K)
+        xs, ys = (4 if xd == "f32" else 2), (4 if yd == "f32" else 2)
+        rng = np.random.default_rng(M + N + K)
+        xdt = np.float32 if xd == "f32" else np.float16
+        x = ctx.buffer_from_array(rng.standard_normal((M, K)).astype(np.float32).astype(xdt))
+        g = ctx.buffer_from_array((1 + 0.1 * rng.standard_normal(K)).astype(np.float32).astype(xdt)) if fused else None
+        y = ctx.buffer(M * N * ys)
+        alg = nbytes + M * K * xs + M * N * ys + (K * xs if fused else 0)
+        rec = {"config": config, "fmt": "q4_0" if fmt == 0 else "q8_0", "M": M, "N": N, "K": K, "x": xd, "y": yd,
+               "fused_rmsnorm": bool(fused), "weight_copies": len(ws), "bytes": alg}
+        for mode in ("stream", "per_op"):
+            ms = D.gemv_bench(ctx, ws, x, y, fmt, M, N, K, iters, xd, yd, g, persistent=(mode == "stream"))
+            us = ms / iters * 1e3
+            rec[mode] = {"us": round(us, 3), "GBs": round(alg / us / 1e3, 1), "frac": round(alg / us / 1e3 / peak, 4),
+                         "kernel": tc.cuda_last_kernel_name()}
+            if mode == "stream" and "persistent" not in rec[mode]["kernel"]:
+                rec["per_op"] = rec["stream"]          # nothing to switch off: same launches
+                break
+        best = min(rec["stream"]["us"], rec["per_op"]["us"])
+        rec["tflops"] = round(2.0 * M * N * K / best / 1e6, 2)
+        for b in ws + [x, y] + ([g] if g else []):
+            b.close()
+        out.append(rec)
+
+    def dense_case(name, layernorm, M, N, K, iters):
+        import torch
+        nbytes = K * N * 2
+        copies = max(2, int(2 * 126e6 // nbytes) + 1)
+        gen = torch.Generator(device="cuda"); gen.manual_seed(0xD0 + N)
+        rng = np.random.default_rng(N + K)
+        ws = []
+        for _ in range(copies):
+            w = (torch.randn((K, N), generator=gen, device="cuda") * 0.02).to(torch.float16)
+            b = ctx.buffer(nbytes)
+            b.upload(w.cpu().numpy())
+            ws.append(b)
+        x = ctx.buffer_from_array(rng.standard_normal((M, K)).astype(np.float16))
+        g = ctx.buffer_from_array((1 + 0.1 * rng.standard_normal(K)).astype(np.float16))
+        bt = ctx.buffer_from_array((0.1 * rng.standard_normal(K)).astype(np.float16)) if layernorm else None
+        y = ctx.buffer(M * N * 2)
+        alg = nbytes + M * K * 2 + M * N * 2 + K * 2 * (2 if layernorm else 1)
+        ms = D.dense_bench(ctx, ws, x, g, bt, y, M, N, K, iters)
+        us = ms / iters * 1e3
+        out.append({"config": name, "fmt": "f16 W[K,N]", "M": M, "N": N, "K": K, "x": "f16", "y": "f16",
+                    "weight_copies": copies, "bytes": alg,
+                    "per_op": {"us": round(us, 3), "GBs": round(alg / us / 1e3, 1), "frac": round(alg / us / 1e3 / peak, 4),
+                               "kernel": tc.cuda_last_kernel_name()}})
+        for b in ws + [x, g, y] + ([bt] if bt else []):
+            b.close()
+
+    it = 100 if quick else 200
+    quant_case("config 1: Q4_0 4096x4096, fp32 x -> fp32 y", 0, 1, 4096, 4096, "f32", "f32", False, it)
+    quant_case("config 1 through the fp16 ABI", 0, 1, 4096, 4096, "f16", "f16", False, it)
+    for xd in ("f32", "f16"):
+        quant_case(f"config 2: Q8_0 11008x4096, {xd} x", 1, 1, 11008, 4096, xd, xd, False, it)
+        quant_case(f"config 2: fused RMSNorm + Q8_0 11008x4096, {xd} x", 1, 1, 11008, 4096, xd, xd, True, it)
+    for M in (1, 4, 8, 16, 32):
+        quant_case(f"config 4: Q4_0 14336x4096, M={M}, fp16 x -> fp32 y", 0, M, 14336, 4096, "f16", "f32", False, it // 2)
+    dense_case("tc_fused_rmsnorm_gemv, fp16 W 4096x11008", False, 1, 11008, 4096, it // 2)
+    dense_case("tc_fused_layernorm_gemv, fp16 W 4096x11008", True, 1, 11008, 4096, it // 2)
+    return out
+
+
+def cpu_single_gemv_baselines() -> list[dict]:
+    """The reference's CPU code as shipped (one thread) on configs 1 and 2: median of 3 calls."""
+    import oracle as O
+    if not O.ref_available():
+        return []
+    R = O.RefLib()
+    rng = np.random.default_rng(12)
+    res = []
+    for config, fmt, N, K in (("config 1: Q4_0 4096x4096", 0, 4096, 4096), ("config 2: Q8_0 11008x4096", 1, 11008, 4096)):
+        bb = 18 if fmt == 0 else 34
+        Wq = rng.integers(0, 256, N * (K // 32) * bb, dtype=np.uint8)
+        Wq.reshape(-1, bb)[:, 0:2] = np.frombuffer(np.float16(0.005).tobytes(), dtype=np.uint8)
+        X = rng.standard_normal((1, K)).astype(np.float16)
+        ts = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            R.gemv_quantized(X, Wq, fmt, N)
+            ts.append(time.perf_counter() - t0)
+        t = float(np.median(ts))
+        res.append({"config": config, "ms": round(t * 1e3, 2), "GBs": round(Wq.nbytes / t / 1e9, 3), "cores": 1,
+                    "kind": "reference", "sample": "whole call through the reference library's tc_gemv_quantized "
+                                                   "(includes its buffer set-up), median of 3"})
+    return res
+
+
+def llama70b_record(ctx, steps: int) -> dict:
+    """BASELINE config 5 on one GPU: the 70B-shape model (39.1 GB of Q4_0) quantised on the device,
+    decoded at batch 1 (one persistent launch per token) and batch 8 (tcgen05 kernels, CUDA graph)."""
+    import tensorcore_b200 as tc
+    from tensorcore_b200 import decode as D
+    shape = D.LLAMA_70B
+    peak, _ = measured_peaks()
+    t0 = time.perf_counter()
+    model = D.synthetic_model_on_device(ctx, shape, 0)
+    build_s = time.perf_counter() - t0
+    rec = {"workload": "llama-70b-shape Q4_0 decode weight stream: 80 layers x (q,o 8192x8192; k,v 1024x8192; "
+                       "gate,up 28672x8192; down 8192x28672) + lm_head 128256x8192, RMSNorm fused",
+           "weight_bytes_per_token": shape.weight_bytes(0), "build_s": round(build_s, 1)}
+    for M in (1, 8):
+        sess = D.DecodeSession(ctx, model, M=M)
+        rng = np.random.default_rng(D.X_SEED + M)
+        sess.x.upload(rng.standard_normal((M, shape.d_model)).astype(np.float16))
+        sess.run(3, fused_norms=True)
+        gpu_ms, _ = sess.run(steps, fused_norms=True)
+        logits = sess.logits.to_numpy((M, shape.vocab), np.float16)
+        if not np.all(np.isfinite(logits)) or tc.take_device_error(ctx) != 0:
+            raise SystemExit("70B run: non-finite logits or device error")
+        ms = gpu_ms / steps
+        wb = shape.weight_bytes(0)
+        rec[f"batch{M}"] = {"ms_per_step": round(ms, 4), "tok_s": round(M * 1e3 / ms, 2),
+                            "weight_GBs": round(wb / ms / 1e6, 1), "frac": round(wb / ms / 1e6 / peak, 4),
+                            "kernel": tc.cuda_last_kernel_name()}
+        sess.close()
+    for b in model.owner.values():
+        b.close()
+    return rec
 
 
 def run_single_gpu(args) -> dict:
@@ -303,7 +448,7 @@ def run_single_gpu(args) -> dict:
     launches = tc.launch_count() - launches0
     clocks = sampler.stop()
     logits = sess.logits.to_numpy((1, shape.vocab), np.float16)
-    if not np.all(np.isfinite(logits)) and not os.environ.get("TC_GEMV_DBG_SKIP"):
+    if not np.all(np.isfinite(logits)):
         raise SystemExit("non-finite logits")
     if tc.take_device_error(ctx) != 0:
         raise SystemExit("device-side error word set")
@@ -318,7 +463,7 @@ def run_single_gpu(args) -> dict:
     # the summation order of the shared-memory accumulators (fp16 rounding flips)
     a, b = hl.numpy().astype(np.float64), logits.astype(np.float64)
     drift = float(np.sqrt(np.mean((a - b) ** 2)) / max(np.sqrt(np.mean(b ** 2)), 1e-30))
-    if not drift <= 2e-2 and not os.environ.get("TC_GEMV_DBG_SKIP"):   # 225 chained fp16 GEMVs: rounding flips compound
+    if not drift <= 2e-2:   # 225 chained fp16 GEMVs: the accumulation order differs run to run and rounding flips compound
         raise SystemExit(f"e2e logits differ from resident-run logits (scaled rms {drift})")
 
     total_b, weight_b = algorithmic_bytes_per_token(shape)
@@ -330,11 +475,11 @@ def run_single_gpu(args) -> dict:
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "s16 x u4 -> s32 (dp2a), f32 scales", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "s16 x u4 -> s32 (dp2a), f32 scales", "data": "synthetic",
         "config": {
-            "workload": workload_text(shape) + "; GGUF v3 file loaded with "
-                        "tc_gguf_load_supported_tensors",
+            "workload": workload_text(shape),
             "gemvs_per_token": n_gemv, "weight_bytes_per_token": weight_b,
+            "model": "GGUF v3 file loaded with tc_gguf_load_supported_tensors",
             "l2": "3.7 GB of weights are streamed per step (126 MB L2): no flush needed",
             "api": "tc_gemv_quantized_async / tcx_fused_rmsnorm_gemv_quantized_ex on a tc_stream, "
                    "one tc_stream_sync per token",
@@ -342,9 +487,10 @@ def run_single_gpu(args) -> dict:
         },
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak,
-                     # DRAM bytes per launch: ncu (dram__bytes_read + write) on an 8-layer launch
-                     # of the same kernel was 1.0075 x its algorithmic bytes; scaled by bytes
-                     "traffic": 1.0075 * total_b / (launches / args.steps),
+                     # DRAM bytes per launch, modelled: ncu (dram__bytes_read + write) on an 8-layer
+                     # launch of this kernel, as a ratio to its algorithmic bytes, scaled by bytes
+                     "traffic": TRAFFIC_RATIO * total_b / (launches / args.steps),
+                     "traffic_kind": f"modelled: algorithmic bytes x {TRAFFIC_RATIO} (ncu capture of an 8-layer launch)",
                      "traffic_source": "profiles/bench_decode_7b_q4_0_persistent_launch.md",
                      "peak_kind": peak_kind,
                      # one persistent launch per token when the stream takes that path, else
@@ -361,10 +507,15 @@ def run_single_gpu(args) -> dict:
         "wall_ms_per_step": wall_ms / args.steps,
         "kernel": tc.cuda_last_kernel_name(),
     }
-    if not args.no_cpu_baseline:
-        out["cpu_baseline"] = cpu_baseline_leg(shape)
     sess.close()
     model.owner.close()
+    if not args.no_gemv:
+        out["gemv"] = gemv_cases(ctx, quick=args.steps < 50)
+    if not args.no_70b and not getattr(args, "layers", 0):
+        out["llama70b"] = llama70b_record(ctx, steps=max(5, min(30, args.steps // 5)))
+    if not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_baseline_leg(shape)
+        out["cpu_baseline"]["single_gemv"] = cpu_single_gemv_baselines()
     ctx.close()
     return out
 
@@ -376,6 +527,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gemv", action="store_true", help="skip the single-operation cases (configs 1, 2, 4)")
+    ap.add_argument("--no-70b", action="store_true", help="skip the 70B-shape record (config 5)")
     ap.add_argument("--layers", type=int, default=0,
                     help="profiling aid: run the same step on the first LAYERS layers + lm_head (a smaller "
                          "device footprint for ncu captures); the JSON line then names the reduced workload")

@@ -340,6 +340,10 @@ tc_status_t tcx_buffer_device_ptr(const tc_buffer* buf, void** out_dptr);
 tc_status_t tcx_stream_cuda_handle(const tc_stream* s, void** out_cuda_stream);
 /* Submit the operations recorded on the stream without waiting for them. */
 tc_status_t tcx_stream_flush(tc_stream* s);
+/* Recorded lists of Q4_0, M = 1 operations normally run as ONE persistent kernel per
+ * tc_stream_sync; enable = 0 makes this stream launch one kernel per operation instead (CUDA
+ * graph replay from the second identical list), e.g. to compare the two. */
+tc_status_t tcx_stream_set_persistent(tc_stream* s, int enable);
 
 /* Raw launches on caller-owned device memory.  Pointers are device addresses valid on the
  * context's device; `cuda_stream` is a cudaStream_t as void* (NULL = the legacy default

@@ -192,6 +192,7 @@ def _declare(L) -> None:
     sig("tcx_buffer_device_ptr", i, vp, POINTER(vp))
     sig("tcx_stream_cuda_handle", i, vp, POINTER(vp))
     sig("tcx_stream_flush", i, vp)
+    sig("tcx_stream_set_persistent", i, vp, i)
     sig("tcx_raw_quantize_weights", i, vp, vp, vp, i, i, i, vp)
     sig("tcx_raw_gemv_quantized", i, vp, vp, vp, vp, i, i, i, i, i, i, vp)
     sig("tcx_raw_fused_rmsnorm_gemv_quantized", i, vp, vp, vp, vp, vp, i, i, i, i, f, i, i, vp)

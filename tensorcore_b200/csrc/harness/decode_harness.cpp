@@ -171,13 +171,16 @@ int tch_session_run(tch_session* s, int tokens, int mode, int e2e, const void* h
 // Single-matrix benchmark: `iters` GEMVs recorded on one stream, rotating over `copies`
 // distinct weight buffers (so that with copies * bytes > L2 every launch streams from HBM),
 // one synchronisation at the end.  fused != 0 uses the RMSNorm-fused entry point.
+// persistent == 0: one kernel per operation (graph replay) even where the list would qualify for
+// the persistent decode kernel.
 int tch_gemv_bench(tc_context* ctx, tc_buffer** weights, int copies, tc_buffer* x,
                    tc_buffer* gamma, tc_buffer* y, int fmt, int M, int N, int K, int x_dtype,
-                   int y_dtype, int fused, int iters, float* gpu_ms) {
+                   int y_dtype, int fused, int iters, int persistent, float* gpu_ms) {
     if (!ctx || !weights || copies <= 0 || iters <= 0) return TC_ERR_INVALID_ARG;
     tc_stream* s = nullptr;
     int st = tc_stream_create(ctx, &s);
     if (st != TC_OK) return st;
+    tcx_stream_set_persistent(s, persistent);
     void* cs = nullptr;
     tcx_stream_cuda_handle(s, &cs);
     cudaStream_t stream = (cudaStream_t)cs;
@@ -204,6 +207,37 @@ int tch_gemv_bench(tc_context* ctx, tc_buffer** weights, int copies, tc_buffer* 
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
     tc_stream_destroy(ctx, s);
+    return st;
+}
+
+// The dense fused norm + GEMV operations (fp16 W[K,N]): `iters` raw launches back to back on one
+// CUDA stream, rotating over `copies` weight matrices.  beta == NULL: RMSNorm, else LayerNorm.
+int tch_dense_bench(tc_context* ctx, tc_buffer** weights, int copies, tc_buffer* x, tc_buffer* gamma,
+                    tc_buffer* beta, tc_buffer* y, int M, int N, int K, int iters, float* gpu_ms) {
+    if (!ctx || !weights || copies <= 0 || iters <= 0 || !x || !gamma || !y) return TC_ERR_INVALID_ARG;
+    cudaStream_t stream;
+    if (cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) != cudaSuccess) return TC_ERR_INTERNAL;
+    void *px, *pg, *pb = nullptr, *py;
+    tcx_buffer_device_ptr(x, &px); tcx_buffer_device_ptr(gamma, &pg); tcx_buffer_device_ptr(y, &py);
+    if (beta) tcx_buffer_device_ptr(beta, &pb);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    int st = TC_OK;
+    for (int rep = 0; rep < 2 && st == TC_OK; ++rep) {
+        if (rep == 1) cudaEventRecord(e0, stream);
+        for (int i = 0; i < iters && st == TC_OK; ++i) {
+            void* pw;
+            tcx_buffer_device_ptr(weights[i % copies], &pw);
+            st = tcx_raw_fused_norm_gemv_f16(ctx, px, pg, pb, pw, py, M, N, K, 1e-5f, stream);
+        }
+        if (rep == 1) cudaEventRecord(e1, stream);
+        if (cudaStreamSynchronize(stream) != cudaSuccess && st == TC_OK) st = TC_ERR_INTERNAL;
+    }
+    if (gpu_ms) { *gpu_ms = 0.f; if (st == TC_OK) cudaEventElapsedTime(gpu_ms, e0, e1); }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaStreamDestroy(stream);
     return st;
 }
 

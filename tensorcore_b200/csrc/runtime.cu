@@ -110,6 +110,7 @@ struct tc_stream {
     std::vector<RecordedOp> pending;
     std::unordered_map<uint64_t, CachedGraph> cache;
     DecodeSite site;
+    bool persistent = true;               // qualifying lists may run as one persistent launch
     std::vector<tcb::MegaOp> table;       // planning scratch, kept to avoid reallocation
     std::vector<tcb::DecodeSpan> spans;
     std::vector<tcb::GemvQArgs> args;
@@ -690,7 +691,7 @@ void reset_decode_site(DecodeSite& d) {
 cudaError_t submit_as_persistent_launch(tc_stream* s, int* launches, const char** name) {
     tc_context* ctx = s->owner;
     const size_t n = s->pending.size();
-    if (!ctx->mega_on || n < 2 || n > static_cast<size_t>(kMegaMaxOps)) return cudaErrorNotSupported;
+    if (!ctx->mega_on || !s->persistent || n < 2 || n > static_cast<size_t>(kMegaMaxOps)) return cudaErrorNotSupported;
     for (const RecordedOp& op : s->pending)
         if (op.kind != OP_GEMV_Q || op.a.fmt != tcb::FMT_Q4_0 || op.a.M != 1) return cudaErrorNotSupported;
     DecodeSite& d = s->site;
@@ -899,6 +900,12 @@ extern "C" tc_status_t tc_stream_sync(tc_stream* s) {
     if (st == TC_OK) st = check_device_error(s->owner);
     if (st != TC_OK) reset_decode_site(s->site);
     return st;
+}
+
+extern "C" tc_status_t tcx_stream_set_persistent(tc_stream* s, int enable) {
+    if (!s) return TC_ERR_INVALID_ARG;
+    s->persistent = enable != 0;
+    return TC_OK;
 }
 
 extern "C" tc_status_t tcx_stream_cuda_handle(const tc_stream* s, void** out) {

@@ -176,8 +176,11 @@ def harness() -> ctypes.CDLL:
         H.tch_session_run.restype = c_int
         H.tch_gemv_bench.argtypes = [c_void_p, POINTER(c_void_p), c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                     c_int, POINTER(c_float)]
+                                     c_int, c_int, POINTER(c_float)]
         H.tch_gemv_bench.restype = c_int
+        H.tch_dense_bench.argtypes = [c_void_p, POINTER(c_void_p), c_int, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_int, c_int, c_int, c_int, POINTER(c_float)]
+        H.tch_dense_bench.restype = c_int
         _harness = H
     return _harness
 
@@ -269,14 +272,28 @@ class DecodeSession:
 
 def gemv_bench(ctx: tc.Context, weights: list[tc.Buffer], x: tc.Buffer, y: tc.Buffer, fmt: int,
                M: int, N: int, K: int, iters: int, x_dtype="f16", y_dtype="f16",
-               gamma: tc.Buffer | None = None) -> float:
-    """Milliseconds (CUDA events) for `iters` back-to-back GEMVs rotating over `weights`."""
+               gamma: tc.Buffer | None = None, persistent: bool = True) -> float:
+    """Milliseconds (CUDA events) for `iters` back-to-back GEMVs rotating over `weights`,
+    recorded on one tc_stream.  persistent=False keeps one kernel per operation."""
     arr = (c_void_p * len(weights))(*[w.handle for w in weights])
     ms = c_float()
     st = harness().tch_gemv_bench(ctx.handle, ctypes.cast(arr, POINTER(c_void_p)), len(weights),
                                   x.handle, gamma.handle if gamma else None, y.handle, fmt, M, N,
                                   K, tc._dtype(x_dtype), tc._dtype(y_dtype), 1 if gamma else 0,
-                                  iters, byref(ms))
+                                  iters, 1 if persistent else 0, byref(ms))
+    if st != tc.TC_OK:
+        raise tc.TensorcoreError(st)
+    return ms.value
+
+
+def dense_bench(ctx: tc.Context, weights: list[tc.Buffer], x: tc.Buffer, gamma: tc.Buffer,
+                beta: tc.Buffer | None, y: tc.Buffer, M: int, N: int, K: int, iters: int) -> float:
+    """Milliseconds for `iters` back-to-back fused norm + dense fp16 GEMV launches."""
+    arr = (c_void_p * len(weights))(*[w.handle for w in weights])
+    ms = c_float()
+    st = harness().tch_dense_bench(ctx.handle, ctypes.cast(arr, POINTER(c_void_p)), len(weights), x.handle,
+                                   gamma.handle, beta.handle if beta else None, y.handle, M, N, K, iters,
+                                   byref(ms))
     if st != tc.TC_OK:
         raise tc.TensorcoreError(st)
     return ms.value

@@ -399,6 +399,40 @@ typedef struct {
 tc_status_t tcx_raw_decode_q4_static(tc_context* ctx, const tcx_decode_op* ops, int n_ops,
                                      void* cuda_stream);
 
+/* Tensor-parallel decode (no counterpart in the reference, which has no GPU collectives).
+ *
+ * One process per GPU.  Every rank records the SAME list of operations on its own shard of the
+ * weights: projections split by output rows (q/k/v, gate/up, lm_head) compute their own rows;
+ * projections split along K (o_proj, down_proj) compute partial sums over their K range.  An
+ * operation marked `peers` adds its results into the accumulators of EVERY rank inside the
+ * persistent decode kernel, with red.global.add over NVLink peer memory - that is the all-reduce
+ * of a K-split projection and, with `y_row0` / `y_rows` placing a rank's rows inside a longer
+ * vector, the all-gather of a row-split one.  The kernel's grid barriers span all ranks (every
+ * CTA arrives on every rank's counter), waits are bounded as everywhere else, and no collective
+ * library is involved.  A whole token is one launch per rank.
+ *
+ *  1. every rank: tcx_stream_tp_export(stream, pool_floats, handles) - allocates the stream's
+ *     accumulator pool (pool_floats must cover the list, see plan sizes in DESIGN.md; 1 Mi floats
+ *     covers the 70B shapes) and barrier counter and writes two CUDA IPC handles (128 bytes);
+ *  2. exchange the 128-byte records among the ranks by any host channel, in rank order;
+ *  3. every rank: tcx_stream_tp_connect(stream, n_ranks, rank, all_records);
+ *  4. per token, every rank: tcx_stream_decode_tp(stream, ops, n_ops) then tc_stream_sync(stream).
+ *
+ * The lists must have the same structure on every rank (same order, same dependencies, same
+ * `layout_rows`), so that accumulator offsets agree; `layout_rows` (the largest row count of the
+ * operation over the ranks) keeps them equal when row shards differ in size.  n_ranks == 1 (no
+ * connect call) runs the same list on one GPU. */
+typedef struct {
+    tcx_decode_op op;
+    int peers;         /* 1: results are summed into / placed in every rank's copy of Y */
+    int y_row0;        /* row of Y that this rank's row 0 maps to (gathered results), else 0 */
+    int y_rows;        /* rows of Y (0 = op.N) */
+    int layout_rows;   /* accumulators to reserve (0 = y_rows); identical on all ranks */
+} tcx_decode_tp_op;
+tc_status_t tcx_stream_tp_export(tc_stream* s, size_t pool_floats, void* handles_out_128_bytes);
+tc_status_t tcx_stream_tp_connect(tc_stream* s, int n_ranks, int rank, const void* all_records);
+tc_status_t tcx_stream_decode_tp(tc_stream* s, const tcx_decode_tp_op* ops, int n_ops);
+
 /* Kernel-variant override for A/B measurements: "auto" (default), "simt" (CUDA-core integer dot
  * products at any M), "stream" (the same arithmetic on the streaming kernel instead of the box
  * kernel), "tc" (tcgen05 kernel where it applies), "generic".  Returns TC_ERR_INVALID_ARG for an

@@ -93,6 +93,11 @@ class TCXDecodeOp(Structure):
                 ("eps", c_float)]
 
 
+class TCXDecodeTpOp(Structure):
+    _fields_ = [("op", TCXDecodeOp), ("peers", c_int), ("y_row0", c_int), ("y_rows", c_int),
+                ("layout_rows", c_int)]
+
+
 DECODE_STATIC_MAX_OPS = 256
 
 
@@ -193,6 +198,9 @@ def _declare(L) -> None:
     sig("tcx_stream_cuda_handle", i, vp, POINTER(vp))
     sig("tcx_stream_flush", i, vp)
     sig("tcx_stream_set_persistent", i, vp, i)
+    sig("tcx_stream_tp_export", i, vp, sz, vp)
+    sig("tcx_stream_tp_connect", i, vp, i, i, vp)
+    sig("tcx_stream_decode_tp", i, vp, POINTER(TCXDecodeTpOp), i)
     sig("tcx_raw_quantize_weights", i, vp, vp, vp, i, i, i, vp)
     sig("tcx_raw_gemv_quantized", i, vp, vp, vp, vp, i, i, i, i, i, i, vp)
     sig("tcx_raw_fused_rmsnorm_gemv_quantized", i, vp, vp, vp, vp, vp, i, i, i, i, f, i, i, vp)
@@ -475,6 +483,39 @@ def raw_decode_q4_static(ctx, ops, cuda_stream=0) -> None:
         arr[i].x_dtype, arr[i].y_dtype = _dtype(o.get("x_dtype", "f16")), _dtype(o.get("y_dtype", "f16"))
         arr[i].eps = float(o.get("eps", 1e-5))
     _check(lib().tcx_raw_decode_q4_static(_h(ctx), arr, len(ops), c_void_p(cuda_stream)))
+
+
+def stream_tp_export(stream, pool_floats: int) -> bytes:
+    """Allocates the stream's decode scratch and returns its 128-byte IPC record."""
+    buf = ctypes.create_string_buffer(128)
+    _check(lib().tcx_stream_tp_export(_h(stream), int(pool_floats), buf))
+    return buf.raw
+
+
+def stream_tp_connect(stream, n_ranks: int, rank: int, records: bytes) -> None:
+    """records: the ranks' 128-byte records concatenated in rank order."""
+    assert len(records) == 128 * n_ranks
+    _check(lib().tcx_stream_tp_connect(_h(stream), int(n_ranks), int(rank), ctypes.c_char_p(records)))
+
+
+def make_decode_tp_ops(ops):
+    """ctypes array for stream_decode_tp from a list of dicts (device addresses W, X, Y, optional
+    gamma; N, K, x_dtype, y_dtype, eps; optional peers, y_row0, y_rows, layout_rows)."""
+    arr = (TCXDecodeTpOp * len(ops))()
+    for i, o in enumerate(ops):
+        a = arr[i].op
+        a.W, a.X, a.Y = o["W"], o["X"], o["Y"]
+        a.gamma = o.get("gamma") or None
+        a.N, a.K = int(o["N"]), int(o["K"])
+        a.x_dtype, a.y_dtype = _dtype(o.get("x_dtype", "f16")), _dtype(o.get("y_dtype", "f16"))
+        a.eps = float(o.get("eps", 1e-5))
+        arr[i].peers, arr[i].y_row0 = int(o.get("peers", 0)), int(o.get("y_row0", 0))
+        arr[i].y_rows, arr[i].layout_rows = int(o.get("y_rows", 0)), int(o.get("layout_rows", 0))
+    return arr
+
+
+def stream_decode_tp(stream, arr) -> None:
+    _check(lib().tcx_stream_decode_tp(_h(stream), arr, len(arr)))
 
 
 def set_gemv_variant(name: str) -> None:

@@ -353,7 +353,7 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
     };
     for (int i = 0; i < ns; ++i) try_issue();
 
-    unsigned long long target = p.base;
+    unsigned long long target = p.base, ltarget = p.local_base;
     const unsigned long long per_barrier = static_cast<unsigned long long>(gridDim.x) * (multi ? p.n_ranks : 1);
     bool failed = false;
     int cur_b = 0;                                  // first operation of the current epoch
@@ -378,12 +378,16 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
             // reduction (no value comes back) and polls with acquire loads; the wait is bounded.
             // Tensor parallel: every CTA arrives on every rank's counter, so the barrier spans all
             // grids.
-            target += per_barrier;
+            // A barrier that only orders this rank's own data (results consumed on the rank that
+            // produced them) stays inside the rank: its own counter, GPU scope.
+            const bool global = multi && (tail || (flags & MOP_GBARRIER));
+            const bool local = multi && !global;
+            if (local) ltarget += gridDim.x; else target += per_barrier;
             if (tid == 0) {
-                if (multi) {
+                if (global) {
                     for (int r = 0; r < p.n_ranks; ++r) arrive_sys(p.peer_counter[r]);
                 } else {
-                    arrive_gpu(p.counter);
+                    arrive_gpu(local ? p.local_counter : p.counter);
                 }
             }
             // While the others arrive: result buffers of the epoch before the one that just ended
@@ -394,7 +398,8 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
             finalize_results(ops, prev_b, prev_e, p.pool, inv_grid, false);
             if (tid == 0) {
                 const long long t0 = clock64();
-                while ((multi ? poll_sys(p.counter) : poll_gpu(p.counter)) < target) {
+                while ((global ? poll_sys(p.counter) : poll_gpu(local ? p.local_counter : p.counter)) <
+                       (local ? ltarget : target)) {
                     if (clock64() - t0 > 2000000000LL) {
                         *abort_s = 1;
                         atomicOr(p.err, ERR_WAIT_TIMEOUT);
@@ -413,6 +418,19 @@ __global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_kernel(const D
             // the last epoch's results, and what the regular schedule would zero later
             finalize_results(ops, prev_b, prev_e, p.pool, inv_grid, true);
             zero_accumulators(ops, pp_b, pp_e, p.pool, inv_grid);
+            if (multi) {
+                // Another rank may start its next launch, and add into this rank's accumulators,
+                // as soon as it leaves this kernel: nobody leaves before everyone has zeroed.
+                __syncthreads();
+                target += per_barrier;
+                if (tid == 0) {
+                    for (int r = 0; r < p.n_ranks; ++r) arrive_sys(p.peer_counter[r]);
+                    const long long t0 = clock64();
+                    while (poll_sys(p.counter) < target) {
+                        if (clock64() - t0 > 2000000000LL) { atomicOr(p.err, ERR_WAIT_TIMEOUT); break; }
+                    }
+                }
+            }
             break;
         }
         const MegaOp& op = ops[o];
@@ -512,7 +530,7 @@ cudaError_t encode_decode_maps(const MegaOp* host_ops, int n_ops, void* host_map
 }
 
 cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, DecodeSpan* work,
-                        MegaOp* table, DecodePlan* plan, size_t pool_capacity_floats) {
+                        MegaOp* table, DecodePlan* plan, size_t pool_capacity_floats, int n_ranks) {
     if (!ops || !work || !table || !plan || n_ops <= 0) return cudaErrorInvalidValue;
     DecodeSpan* reads = work;                 // inputs read since the last barrier (x, gamma, W)
     DecodeSpan* writes = work + 3 * n_ops;    // results written since the last barrier
@@ -642,7 +660,8 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
         m.y_row0 = y_row0;
         m.y_rows = y_rows;
         m.acc_off = static_cast<uint32_t>(in_epoch);
-        in_epoch += (static_cast<size_t>(y_rows) + 31) & ~static_cast<size_t>(31);
+        const size_t layout = tp && tp[i].layout_rows > static_cast<int>(y_rows) ? static_cast<size_t>(tp[i].layout_rows) : y_rows;
+        in_epoch += (layout + 31) & ~static_cast<size_t>(31);
         m.ss_off = 0;
         if (a.gamma) {
             if (restage) {      // operations that share a staged row share its sums of squares
@@ -674,12 +693,16 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
     // A generation: accumulators first, then the sums of squares.  The two never share an
     // address: accumulators are zeroed before reuse, the sums are simply overwritten.
     const size_t gen = worst + ss_worst;
-    if (pool_capacity_floats && 3 * gen > pool_capacity_floats) return cudaErrorNotSupported;
+    // Tensor parallel: another rank may run one epoch ahead across a rank-local barrier and add into
+    // this rank's accumulators early; a fourth generation moves the zeroing of an accumulator in
+    // front of the last barrier that spans all ranks before its next use (see below).
+    const size_t gens = n_ranks > 1 ? 4 : 3;
+    if (pool_capacity_floats && gens * gen > pool_capacity_floats) return cudaErrorNotSupported;
     // Pass 2: place the accumulators and the sums of squares (generation = epoch mod 3).
     int barriers = 1;   // the trailing one
     for (int i = 0; i < n_ops; ++i) {
         MegaOp& m = table[i];
-        const uint32_t base = static_cast<uint32_t>((epoch_of[i].lo % 3) * gen);
+        const uint32_t base = static_cast<uint32_t>((epoch_of[i].lo % gens) * gen);
         m.acc_off += base;
         if (m.flags & MOP_FUSED) m.ss_off += base + static_cast<uint32_t>(worst);
         if (m.xacc_off >= 0) {
@@ -694,6 +717,44 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
         }
         if (m.flags & MOP_BARRIER) barriers += (m.flags & MOP_BARRIER2) ? 2 : 1;
     }
+    plan->global_barriers = 0;
+    plan->local_barriers = 0;
+    if (n_ranks > 1) {
+        // Which barriers span all ranks.  The one that ends an epoch with results added into the
+        // peers' accumulators must (the sums are complete only when every rank is done).  And such
+        // an epoch p needs one in front of it no further back than the end of p - 2, where its
+        // accumulators are zeroed on every rank: so that no rank adds before every rank has zeroed.
+        // (Before the first two epochs that is the barrier that ended the previous launch.)
+        const int n_epochs = epoch + 1;
+        // per epoch: has peers; barrier in front is global.  Kept in epoch_of[].hi of the first op.
+        int first_op_of_epoch = 0, prev_global_at = -1000;   // prev_global_at: last epoch e with a global barrier in front
+        bool prev_epoch_peers = false;
+        int e_cur = 0;
+        for (int i = 0; i <= n_ops; ++i) {
+            const bool boundary = i == n_ops || (i > 0 && (table[i].flags & MOP_BARRIER));
+            if (!boundary) continue;
+            // close epoch e_cur = [first_op_of_epoch, i)
+            bool peers = false;
+            for (int k = first_op_of_epoch; k < i; ++k) peers = peers || (table[k].flags & MOP_PEERS);
+            bool global_front = e_cur > 0 && prev_epoch_peers;
+            if (e_cur == 0) prev_global_at = 0;               // the previous launch ended with one
+            if (global_front) prev_global_at = e_cur;
+            if (peers && e_cur - prev_global_at > 1 && e_cur > 0) { global_front = true; prev_global_at = e_cur; }
+            if (e_cur > 0) {
+                if (global_front) table[first_op_of_epoch].flags |= MOP_GBARRIER;
+                const int rounds = (table[first_op_of_epoch].flags & MOP_BARRIER2) ? 2 : 1;
+                (global_front ? plan->global_barriers : plan->local_barriers) += rounds;
+                // an empty epoch (second round) sits between: it neither adds nor zeroes anything new
+            }
+            prev_epoch_peers = peers;
+            if (i < n_ops) {
+                e_cur = static_cast<int>(epoch_of[i].lo);
+                first_op_of_epoch = i;
+            }
+        }
+        (void)n_epochs;
+        plan->global_barriers += 2;     // the two trailing barriers
+    }
     for (int i = 0; i < n_ops;) {          // phases: runs that share their staged input, at most kMaxPhaseOps long
         int e = i + 1;
         while (e < n_ops && e - i < kMaxPhaseOps && !(table[e].flags & (MOP_BARRIER | MOP_RESTAGE))) ++e;
@@ -702,7 +763,7 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
     }
     plan->n_ops = n_ops;
     plan->barriers = barriers;
-    plan->pool_floats = 3 * gen;
+    plan->pool_floats = gens * gen;
     return cudaSuccess;
 }
 
@@ -735,6 +796,7 @@ cudaError_t launch_decode(const MegaOp* host_ops, const DecodePlan& plan, const 
     std::memset(&p, 0, sizeof(p));
     p.ops = dev.ops; p.maps = dev.maps; p.n_ops = n_ops; p.pool = dev.pool;
     p.counter = dev.counter; p.base = dev.base; p.err = env.err_word;
+    p.local_counter = dev.local_counter; p.local_base = dev.local_base;
     p.n_ranks = dev.n_ranks; p.rank = dev.rank;
     p.inv_grid = static_cast<uint32_t>(((1ull << 32) + grid - 1) / grid);
     for (int r = 0; r < dev.n_ranks; ++r) { p.peer_pool[r] = dev.peer_pool[r]; p.peer_counter[r] = dev.peer_counter[r]; }

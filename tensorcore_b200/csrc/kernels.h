@@ -82,6 +82,7 @@ enum : uint32_t {
     MOP_XACC_F16 = 32u, // activations taken from accumulators are rounded to fp16 first
     MOP_PEERS = 64u,    // partial sums are added into every rank's accumulators (tensor parallel)
     MOP_BARRIER2 = 128u, // with MOP_BARRIER: two barriers, i.e. one empty epoch, before this operation
+    MOP_GBARRIER = 512u, // tensor parallel: the barrier(s) before this operation span all ranks (else only this rank's grid)
 };
 constexpr int kDecodeMaxRanks = 8;
 struct DecodeParams {
@@ -91,6 +92,8 @@ struct DecodeParams {
     float* pool;                    // device memory: fp32 accumulators, all zero between launches
     unsigned long long* counter;    // device memory: grid-barrier arrival counter, never reset
     unsigned long long base;        // counter value all earlier launches add up to
+    unsigned long long* local_counter;  // tensor parallel: counter of the barriers that span this rank only
+    unsigned long long local_base;
     uint32_t* err;
     int ns;
     int off_sx, off_x, off_ring;
@@ -120,13 +123,19 @@ cudaError_t launch_dense_norm_gemv(const DenseNormGemvArgs& a, const LaunchEnv& 
 struct DecodeSpan { uintptr_t lo, hi; };
 struct DecodePlan {
     int n_ops = 0;
-    int barriers = 0;          // grid barriers the launch executes (the trailing one included)
+    int barriers = 0;          // grid barriers a single-GPU launch executes (the trailing one included)
+    int global_barriers = 0;   // tensor parallel: how many of the launch's barriers span all ranks (the two
+                               // trailing ones included); the other barriers - local_barriers - span one rank
+    int local_barriers = 0;
     size_t pool_floats = 0;    // accumulator pool the table addresses
 };
 // Tensor-parallel extras of one operation (all zero on one GPU).
 struct DecodeTpOp {
     int peers = 0;             // add the partial sums into every rank's accumulators
     int y_row0 = 0, y_rows = 0;   // placement of the N rows inside a longer gathered vector
+    int layout_rows = 0;       // accumulators reserved for this result (>= its rows; 0 = its rows): the
+                               // same value on every rank keeps the pool layout identical across ranks
+                               // when their row shards differ in size
 };
 // Builds the device table for `ops` (GemvQArgs with M == 1, Q4_0): barriers from pointer overlap,
 // accumulator placement, hand-over of results through the accumulators.  `work` is caller scratch
@@ -134,8 +143,10 @@ struct DecodeTpOp {
 // cudaErrorNotSupported: the list is outside the kernel's domain (shapes, alignment, an
 // operation that writes a later operation's weights, a partial overlap between a result and the
 // next epoch's input, more accumulators than pool_capacity_floats when that is non-zero).
+// n_ranks > 1 plans for tensor parallelism: four accumulator generations instead of three and a
+// choice per barrier between one that spans all ranks and one that spans this rank only.
 cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, DecodeSpan* work,
-                        MegaOp* table, DecodePlan* plan, size_t pool_capacity_floats);
+                        MegaOp* table, DecodePlan* plan, size_t pool_capacity_floats, int n_ranks = 1);
 // Device-side state of one launch site (a tc_stream, or the static scratch).
 struct DecodeDevice {
     const MegaOp* ops = nullptr;
@@ -143,6 +154,8 @@ struct DecodeDevice {
     float* pool = nullptr;
     unsigned long long* counter = nullptr;
     unsigned long long base = 0;
+    unsigned long long* local_counter = nullptr;
+    unsigned long long local_base = 0;
     int n_ranks = 1, rank = 0;
     float* peer_pool[kDecodeMaxRanks] = {};
     unsigned long long* peer_counter[kDecodeMaxRanks] = {};

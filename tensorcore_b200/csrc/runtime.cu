@@ -96,12 +96,15 @@ struct DecodeSite {
     size_t pool_floats = 0;
     unsigned long long* counter = nullptr;   // grid-barrier arrival counter
     unsigned long long base = 0;             // what all earlier launches add up to
+    unsigned long long local_base = 0;       // the same for the rank-local barriers of tensor-parallel launches
     int uploaded = 0;                        // table entries currently valid on the device
     tcb::DecodePlan plan;
-    // tensor parallel (tcx_stream_set_decode_peers): the other ranks' pools and counters
+    // tensor parallel (tcx_stream_tp_export / _connect): the other ranks' pools and counters,
+    // opened from their CUDA IPC handles
     int n_ranks = 1, rank = 0;
     float* peer_pool[tcb::kDecodeMaxRanks] = {};
     unsigned long long* peer_counter[tcb::kDecodeMaxRanks] = {};
+    std::vector<tcb::DecodeTpOp> tp_ops;
 };
 
 struct tc_stream {
@@ -668,6 +671,11 @@ constexpr int kMegaMaxOps = 1024;
 constexpr size_t kMegaFlagBytes = 256;
 
 void free_decode_site(DecodeSite& d) {
+    for (int r = 0; r < d.n_ranks; ++r) {
+        if (r == d.rank || d.n_ranks <= 1) continue;
+        if (d.peer_pool[r]) cudaIpcCloseMemHandle(d.peer_pool[r]);
+        if (d.peer_counter[r]) cudaIpcCloseMemHandle(d.peer_counter[r]);
+    }
     if (d.host) cudaFreeHost(d.host);
     if (d.maps_host) cudaFreeHost(d.maps_host);
     if (d.dev) cudaFree(d.dev);
@@ -680,9 +688,24 @@ void free_decode_site(DecodeSite& d) {
 // After a launch that gave up on a bounded wait the counter and the accumulators hold arbitrary
 // values: start over from zero.
 void reset_decode_site(DecodeSite& d) {
+    if (d.n_ranks > 1) return;   // tensor parallel: the ranks must agree on a restart (tcx_stream_tp_reset)
     if (d.counter) cudaMemset(d.counter, 0, kMegaFlagBytes);
     if (d.pool) cudaMemset(d.pool, 0, d.pool_floats * sizeof(float));
     d.base = 0;
+}
+
+bool alloc_decode_site_tables(DecodeSite& d) {
+    if (d.host) return true;
+    if (cudaHostAlloc(reinterpret_cast<void**>(&d.host), kMegaMaxOps * sizeof(tcb::MegaOp), cudaHostAllocDefault) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&d.dev), kMegaMaxOps * sizeof(tcb::MegaOp)) != cudaSuccess ||
+        cudaHostAlloc(reinterpret_cast<void**>(&d.maps_host), kMegaMaxOps * tcb::kDecodeMapBytes, cudaHostAllocDefault) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&d.maps_dev), kMegaMaxOps * tcb::kDecodeMapBytes) != cudaSuccess ||
+        (d.counter == nullptr && (cudaMalloc(reinterpret_cast<void**>(&d.counter), kMegaFlagBytes) != cudaSuccess ||
+                                  cudaMemset(d.counter, 0, kMegaFlagBytes) != cudaSuccess))) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return true;
 }
 
 // Tries to run the whole recorded list as ONE persistent launch (Q4_0, M = 1 lists: a decode
@@ -725,19 +748,9 @@ cudaError_t submit_as_persistent_launch(tc_stream* s, int* launches, const char*
     e = tcb::plan_decode(s->args.data(), nullptr, static_cast<int>(n), s->spans.data(),
                                      s->table.data(), &plan, 0);
     if (e != cudaSuccess) return cudaErrorNotSupported;
-    if (!d.host) {
-        if (cudaHostAlloc(reinterpret_cast<void**>(&d.host), kMegaMaxOps * sizeof(tcb::MegaOp),
-                          cudaHostAllocDefault) != cudaSuccess ||
-            cudaMalloc(reinterpret_cast<void**>(&d.dev), kMegaMaxOps * sizeof(tcb::MegaOp)) != cudaSuccess ||
-            cudaHostAlloc(reinterpret_cast<void**>(&d.maps_host), kMegaMaxOps * tcb::kDecodeMapBytes,
-                          cudaHostAllocDefault) != cudaSuccess ||
-            cudaMalloc(reinterpret_cast<void**>(&d.maps_dev), kMegaMaxOps * tcb::kDecodeMapBytes) != cudaSuccess ||
-            cudaMalloc(reinterpret_cast<void**>(&d.counter), kMegaFlagBytes) != cudaSuccess ||
-            cudaMemset(d.counter, 0, kMegaFlagBytes) != cudaSuccess) {
-            (void)cudaGetLastError();
-            free_decode_site(d);
-            return cudaErrorNotSupported;
-        }
+    if (!alloc_decode_site_tables(d)) {
+        free_decode_site(d);
+        return cudaErrorNotSupported;
     }
     if (plan.pool_floats > d.pool_floats) {
         // a larger accumulator pool: the stream's earlier launches must be done with the old one
@@ -900,6 +913,132 @@ extern "C" tc_status_t tc_stream_sync(tc_stream* s) {
     if (st == TC_OK) st = check_device_error(s->owner);
     if (st != TC_OK) reset_decode_site(s->site);
     return st;
+}
+
+// ---------------------------------------------------------------------------------------
+// Tensor-parallel decode: one process per GPU, every rank runs the same list on its shard and
+// row-parallel results are summed / row-sharded results gathered inside the persistent kernel by
+// adding into every rank's accumulators over NVLink (see include/tensorcore_b200.h).
+// ---------------------------------------------------------------------------------------
+extern "C" tc_status_t tcx_stream_tp_export(tc_stream* s, size_t pool_floats, void* handles_out) {
+    if (!s || !handles_out || pool_floats == 0) return TC_ERR_INVALID_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "two handles fill the 128-byte record");
+    DecodeSite& d = s->site;
+    if (d.pool || d.n_ranks > 1) return TC_ERR_INVALID_ARG;     // before the stream's first decode launch only
+    bind_device(s->owner);
+    if (cudaMalloc(reinterpret_cast<void**>(&d.pool), pool_floats * sizeof(float)) != cudaSuccess ||
+        cudaMemset(d.pool, 0, pool_floats * sizeof(float)) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&d.counter), kMegaFlagBytes) != cudaSuccess ||
+        cudaMemset(d.counter, 0, kMegaFlagBytes) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return TC_ERR_ALLOC;
+    }
+    d.pool_floats = pool_floats;
+    cudaIpcMemHandle_t* h = static_cast<cudaIpcMemHandle_t*>(handles_out);
+    if (cudaIpcGetMemHandle(&h[0], d.pool) != cudaSuccess || cudaIpcGetMemHandle(&h[1], d.counter) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return TC_ERR_INTERNAL;
+    }
+    return from_cuda(cudaDeviceSynchronize(), TC_ERR_INTERNAL);
+}
+
+extern "C" tc_status_t tcx_stream_tp_connect(tc_stream* s, int n_ranks, int rank, const void* all_handles) {
+    if (!s || !all_handles || n_ranks < 2 || n_ranks > tcb::kDecodeMaxRanks || rank < 0 || rank >= n_ranks)
+        return TC_ERR_INVALID_ARG;
+    DecodeSite& d = s->site;
+    if (!d.pool || !d.counter || d.n_ranks > 1) return TC_ERR_INVALID_ARG;
+    bind_device(s->owner);
+    const cudaIpcMemHandle_t* h = static_cast<const cudaIpcMemHandle_t*>(all_handles);
+    for (int r = 0; r < n_ranks; ++r) {
+        if (r == rank) {
+            d.peer_pool[r] = d.pool;
+            d.peer_counter[r] = d.counter;
+            continue;
+        }
+        void *pp = nullptr, *pc = nullptr;
+        if (cudaIpcOpenMemHandle(&pp, h[2 * r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess ||
+            cudaIpcOpenMemHandle(&pc, h[2 * r + 1], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return TC_ERR_INTERNAL;
+        }
+        d.peer_pool[r] = static_cast<float*>(pp);
+        d.peer_counter[r] = static_cast<unsigned long long*>(pc);
+    }
+    d.n_ranks = n_ranks;
+    d.rank = rank;
+    return TC_OK;
+}
+
+extern "C" tc_status_t tcx_stream_decode_tp(tc_stream* s, const tcx_decode_tp_op* ops, int n_ops) {
+    if (!s || !ops || n_ops <= 0) return TC_ERR_INVALID_ARG;
+    if (n_ops > kMegaMaxOps) return TC_ERR_INVALID_SHAPE;
+    tc_context* ctx = s->owner;
+    DecodeSite& d = s->site;
+    if (!d.pool || !d.counter) return TC_ERR_INVALID_ARG;     // tcx_stream_tp_export first
+    bind_device(ctx);
+    const size_t n = static_cast<size_t>(n_ops);
+    s->args.resize(n);
+    d.tp_ops.resize(n);
+    for (size_t i = 0; i < n; ++i) {
+        const tcx_decode_op& o = ops[i].op;
+        if (!o.W || !o.X || !o.Y || o.N <= 0 || o.K <= 0) return TC_ERR_INVALID_ARG;
+        if ((o.x_dtype != TC_DTYPE_F16 && o.x_dtype != TC_DTYPE_F32) || (o.y_dtype != TC_DTYPE_F16 && o.y_dtype != TC_DTYPE_F32))
+            return TC_ERR_UNSUPPORTED_DTYPE;
+        tcb::GemvQArgs a;
+        std::memset(&a, 0, sizeof(a));
+        a.W = static_cast<const uint8_t*>(o.W); a.X = o.X; a.Y = o.Y; a.gamma = o.gamma;
+        a.fmt = tcb::FMT_Q4_0; a.M = 1; a.N = o.N; a.K = o.K;
+        a.x_f32 = o.x_dtype == TC_DTYPE_F32; a.y_f32 = o.y_dtype == TC_DTYPE_F32; a.eps = o.eps;
+        s->args[i] = a;
+        tcb::DecodeTpOp t;
+        t.peers = ops[i].peers != 0 && d.n_ranks > 1;
+        t.y_row0 = ops[i].y_row0; t.y_rows = ops[i].y_rows; t.layout_rows = ops[i].layout_rows;
+        d.tp_ops[i] = t;
+    }
+    cudaError_t e = cudaSuccess;
+    const bool replay = d.uploaded == n_ops && s->planned.size() == n &&
+                        std::memcmp(s->planned.data(), s->args.data(), n * sizeof(tcb::GemvQArgs)) == 0;
+    if (!replay) {
+        s->planned.clear();
+        s->table.resize(n);
+        s->spans.resize(5 * n);
+        tcb::DecodePlan plan;
+        e = tcb::plan_decode(s->args.data(), d.tp_ops.data(), n_ops, s->spans.data(), s->table.data(), &plan,
+                             d.pool_floats, d.n_ranks);
+        if (e != cudaSuccess) { (void)cudaGetLastError(); return TC_ERR_INVALID_SHAPE; }
+        if (!alloc_decode_site_tables(d)) return TC_ERR_ALLOC;
+        e = cudaStreamSynchronize(s->s);
+        if (e != cudaSuccess) return from_cuda(e, TC_ERR_DISPATCH);
+        std::memcpy(d.host, s->table.data(), n * sizeof(tcb::MegaOp));
+        e = tcb::encode_decode_maps(d.host, n_ops, d.maps_host);
+        if (e != cudaSuccess) { d.uploaded = 0; (void)cudaGetLastError(); return TC_ERR_INVALID_SHAPE; }
+        e = cudaMemcpyAsync(d.dev, d.host, n * sizeof(tcb::MegaOp), cudaMemcpyHostToDevice, s->s);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(d.maps_dev, d.maps_host, n * tcb::kDecodeMapBytes, cudaMemcpyHostToDevice, s->s);
+        if (e != cudaSuccess) return from_cuda(e, TC_ERR_DISPATCH);
+        d.uploaded = n_ops;
+        d.plan = plan;
+        s->planned = s->args;
+    }
+    tcb::DecodeDevice dev;
+    dev.ops = d.dev; dev.maps = d.maps_dev; dev.pool = d.pool; dev.counter = d.counter; dev.base = d.base;
+    dev.n_ranks = d.n_ranks; dev.rank = d.rank;
+    dev.local_counter = d.counter + 16;      // the second half of the 256-byte counter allocation
+    dev.local_base = d.local_base;
+    for (int r = 0; r < d.n_ranks; ++r) { dev.peer_pool[r] = d.peer_pool[r]; dev.peer_counter[r] = d.peer_counter[r]; }
+    e = tcb::launch_decode(d.host, d.plan, dev, make_env(ctx, false), s->s);
+    if (e == cudaErrorNotSupported || e == cudaErrorCooperativeLaunchTooLarge) { (void)cudaGetLastError(); return TC_ERR_INVALID_SHAPE; }
+    if (e == cudaSuccess) {
+        if (d.n_ranks > 1) {
+            d.base += static_cast<unsigned long long>(d.plan.global_barriers) * ctx->sm_count * d.n_ranks;
+            d.local_base += static_cast<unsigned long long>(d.plan.local_barriers) * ctx->sm_count;
+        } else {
+            d.base += static_cast<unsigned long long>(d.plan.barriers) * ctx->sm_count;
+        }
+        g_launches.fetch_add(1);
+        t_last_kernel = d.n_ranks > 1 ? "q4_0_decode_persistent_tp_sm100" : "q4_0_decode_persistent_sm100";
+    }
+    return record("tcx_stream_decode_tp", from_cuda(e, TC_ERR_DISPATCH));
 }
 
 extern "C" tc_status_t tcx_stream_set_persistent(tc_stream* s, int enable) {

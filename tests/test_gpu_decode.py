@@ -66,3 +66,54 @@ def test_decode_session_matches_oracle_chain(tc, ctx, oracle, tmp_path, fmt, M):
     assert tc.take_device_error(ctx) == 0
     sess.close()
     model.owner.close()
+
+
+def test_tp_decoder_fused_backend_world1_matches_oracle_chain(tc, ctx, oracle):
+    """The tensor-parallel decoder's data flow (fp32 hidden states, K-split projections with fp32
+    results, logits 'gathered' into the full vector) on ONE GPU through the fused back end - one
+    persistent launch per token via tcx_stream_decode_tp - against the same chain on the CPU."""
+    import torch
+    from tensorcore_b200 import decode as D
+    from tensorcore_b200 import tp as TP
+    shape = D.tiny_shape()
+    device = torch.device("cuda", torch.cuda.current_device())
+
+    class Recording(TP.FusedBackend):
+        def weight(self, which, seed, rows, cols):
+            N, K = self.shape.proj_shape(which)
+            w = D.device_weights_fp16(N, K, seed, self.device)
+            if rows is not None:
+                w = w[rows[0]:rows[1]]
+            if cols is not None:
+                w = w[:, cols[0]:cols[1]]
+            self.host = getattr(self, "host", {})
+            ptr = super().weight(which, seed, rows, cols)
+            self.host[ptr] = oracle.quantize_weights(w.contiguous().cpu().numpy(), 0)
+            return ptr
+
+    be = Recording(ctx, shape, 0, device, TP.TPLink(ctx, None, 1, 0))
+    dec = TP.TPDecoder(TP.TPPlan(shape, 1, 0), be, 0)
+    dec.token()
+    be.commit()
+    rng = np.random.default_rng(D.X_SEED)
+    x = rng.standard_normal(shape.d_model).astype(np.float32)
+    # the same chain on the CPU
+    g = lambda t: t.cpu().numpy()
+    cur = x[None, :]
+    for l, lw in enumerate(dec.w):
+        q = oracle.fused_rmsnorm_gemv_quantized_f32(cur, g(lw["attn_norm"]), be.host[lw["attn_q"]], 0, shape.d_model).astype(np.float16)
+        o = oracle.gemv_quantized_f32(q.astype(np.float32), be.host[lw["attn_output"]], 0, shape.d_model)
+        gate = oracle.fused_rmsnorm_gemv_quantized_f32(o, g(lw["ffn_norm"]), be.host[lw["ffn_gate"]], 0, shape.d_ff).astype(np.float16)
+        cur = oracle.gemv_quantized_f32(gate.astype(np.float32), be.host[lw["ffn_down"]], 0, shape.d_model)
+    want = oracle.fused_rmsnorm_gemv_quantized_f32(cur, g(dec.out_norm), be.host[dec.lm_head], 0, shape.vocab).astype(np.float16)
+    for rep in range(3):
+        dec.x_in.copy_(torch.from_numpy(x))
+        torch.cuda.synchronize()
+        be.run()
+        be.sync()
+        assert "persistent" in tc.cuda_last_kernel_name()
+        got = dec.logits.cpu().numpy()[None, :]
+        assert oracle.scaled_rms(got, want) <= 2e-3, rep      # nine dependent GEMVs with fp16 hand-offs
+        assert oracle.scaled_rms(dec.h[(shape.n_layers - 1) & 1].cpu().numpy()[None, :], cur) <= 2e-3
+    assert tc.take_device_error(ctx) == 0
+    be.stream.close()

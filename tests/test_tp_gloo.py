@@ -68,7 +68,7 @@ class CpuBackend:
     def view(self, vec, a, b):
         return vec[a:b]
 
-    def gemv(self, x, w, y, N, K, gamma=None):
+    def gemv(self, x, w, y, N, K, gamma=None, layout=0):
         assert x.shape == (K,) and y.shape == (N,) and w.size == N * (K // 32) * 18
         xf = x.astype(np.float32).reshape(1, K)
         if gamma is None:

@@ -309,6 +309,25 @@ typedef struct {
 tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* desc, const tc_buffer* A, const tc_buffer* B,
                     tc_buffer* C);
 
+/* --- collectives (include/tensorcore/distributed.h:30-87; the reference implements them as a TCP
+ * ring between hosts, lib/distributed/distributed_cpu.cpp:202-347).  Here: NCCL between one
+ * process per GPU, on device buffers.  TC_DIST_RING and TC_DIST_GLOO both select it; the
+ * rendezvous URL "<anything>://host:port" names where rank 0 hands out NCCL's unique id.
+ * TC_ERR_UNSUPPORTED_FAMILY when no NCCL library can be loaded.  Element types fp16 and fp32. */
+typedef enum { TC_DIST_SINGLE = 0, TC_DIST_RING = 1, TC_DIST_GLOO = 2 } tc_dist_backend_t;
+typedef enum { TC_REDUCE_SUM = 0, TC_REDUCE_AVG = 1, TC_REDUCE_MAX = 2, TC_REDUCE_MIN = 3 } tc_reduce_op_t;
+typedef struct tc_dist_ctx tc_dist_ctx;
+tc_status_t tc_dist_init(tc_context* tc, tc_dist_backend_t backend, int world_size, int rank,
+                         const char* rendezvous_url, tc_dist_ctx** out);
+tc_status_t tc_dist_finalize(tc_dist_ctx* d);
+int tc_dist_world_size(const tc_dist_ctx* d);
+int tc_dist_rank(const tc_dist_ctx* d);
+tc_status_t tc_allreduce(tc_dist_ctx* d, tc_buffer* buf, size_t num_elements, tc_dtype_t dtype, tc_reduce_op_t op);
+tc_status_t tc_broadcast(tc_dist_ctx* d, tc_buffer* buf, size_t num_elements, tc_dtype_t dtype, int root);
+tc_status_t tc_allgather(tc_dist_ctx* d, const tc_buffer* in, tc_buffer* out, size_t num_elements_per_rank,
+                         tc_dtype_t dtype);
+tc_status_t tc_barrier(tc_dist_ctx* d);
+
 extern const int tensorcore_abi_version;            /* lib/c_api/c_api_cpu.c:15-16 */
 
 /* ===================================================================================== *
@@ -370,8 +389,8 @@ tc_status_t tcx_raw_fused_norm_gemv_f16(tc_context* ctx, const void* X, const vo
  * qualifying tc_stream list, but for callers that cannot tolerate an allocation on this path:
  * a server whose HBM is fully handed out to weights and KV cache at start-up, or a decode loop
  * where cudaMalloc's device-wide synchronisation must never occur.  The kernel's scratch (the
- * operation table, one TMA tensor map per operation and the grid-barrier counter) lives in a fixed
- * 48.25 KB device array inside the
+ * grid-barrier counter, the operation table, one TMA tensor map per operation and the fp32
+ * accumulators the results are summed in) lives in a fixed 1,972 KB device array inside the
  * library image, which every GPU that loads the library holds until the process exits; the call
  * performs no cudaMalloc / cudaFree and uses no allocating library routine.
  *
@@ -379,12 +398,17 @@ tc_status_t tcx_raw_fused_norm_gemv_f16(tc_context* ctx, const void* X, const vo
  *    addresses owned by the caller (inputs and outputs as for tcx_raw_gemv_quantized with M = 1;
  *    gamma != NULL adds the RMSNorm prologue).  K must be a multiple of 256, pointers 16-byte
  *    aligned.  Dependencies between operations are derived from pointer overlap.
- *  - Limit: n_ops <= TCX_DECODE_STATIC_MAX_OPS (256); more returns TC_ERR_INVALID_SHAPE, as does
+ *  - Limits: n_ops <= TCX_DECODE_STATIC_MAX_OPS (256) and a list whose accumulators fit the
+ *    array (491,520 floats; a list needs three times the result rows of its widest group of
+ *    operations that run side by side, e.g. 3 x 128,256 for a 128k-row output projection);
+ *    beyond either the call returns TC_ERR_INVALID_SHAPE and launches nothing, as it does for
  *    a list whose activations do not fit the kernel's shared memory.
  *  - The first call on a device looks up the array's device address; make that first call before
  *    starting any stream capture.
  *  - All calls on a device share the one array: the call clears the counter and overwrites the
- *    table itself, but two calls that overlap in time on the GPU (different streams) race.
+ *    table itself, but two calls that overlap in time on the GPU (different streams) race.  The
+ *    host-side bookkeeping (one record per device) is guarded by a mutex, so calls from several
+ *    threads are safe as long as their launches do not overlap on one GPU.
  *  - Asynchronous on `cuda_stream`, like the other tcx_raw_* launches. */
 typedef struct {
     const void* W;        /* Q4_0 blocks, [N][K/32] x 18 bytes */

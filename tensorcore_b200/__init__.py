@@ -159,6 +159,14 @@ def _declare(L) -> None:
     sig("tc_fused_rmsnorm_gemv_quantized", i, vp, vp, vp, vp, vp, i, i, i, i, f)
     sig("tc_fused_rmsnorm_gemv", i, vp, vp, vp, vp, vp, i, i, i, f)
     sig("tc_fused_layernorm_gemv", i, vp, vp, vp, vp, vp, vp, i, i, i, f)
+    sig("tc_dist_init", i, vp, i, i, i, c_char_p, POINTER(vp))
+    sig("tc_dist_finalize", i, vp)
+    sig("tc_dist_world_size", i, vp)
+    sig("tc_dist_rank", i, vp)
+    sig("tc_allreduce", i, vp, vp, sz, i, i)
+    sig("tc_broadcast", i, vp, vp, sz, i, i)
+    sig("tc_allgather", i, vp, vp, vp, sz, i)
+    sig("tc_barrier", i, vp)
     sig("tc_rmsnorm_forward", i, vp, vp, vp, vp, vp, i, i, f)
     sig("tc_layernorm_forward", i, vp, vp, vp, vp, vp, vp, vp, i, i, f)
     sig("tc_swiglu_forward", i, vp, vp, vp, vp, i)
@@ -409,6 +417,43 @@ def fused_rmsnorm_gemv(ctx, X, gamma, W, Y, M, N, K, eps=1e-5) -> None:
 def fused_layernorm_gemv(ctx, X, gamma, beta, W, Y, M, N, K, eps=1e-5) -> None:
     _check(lib().tc_fused_layernorm_gemv(_h(ctx), _h(X), _h(gamma), _h(beta), _h(W), _h(Y), int(M),
                                          int(N), int(K), float(eps)))
+
+
+TC_DIST_SINGLE, TC_DIST_RING, TC_DIST_GLOO = 0, 1, 2
+_REDUCE = {"sum": 0, "avg": 1, "max": 2, "min": 3}
+
+
+class DistContext:
+    """Mirror of the reference binding's DistContext: collectives among one process per GPU."""
+
+    def __init__(self, ctx, backend=TC_DIST_SINGLE, world_size=1, rank=0, rendezvous_url=None):
+        h = c_void_p()
+        _check(lib().tc_dist_init(_h(ctx), int(backend), int(world_size), int(rank),
+                                  rendezvous_url.encode() if rendezvous_url else None, byref(h)))
+        self.handle = h
+
+    def world_size(self) -> int:
+        return int(lib().tc_dist_world_size(self.handle))
+
+    def rank(self) -> int:
+        return int(lib().tc_dist_rank(self.handle))
+
+    def allreduce(self, buf, num_elements, dtype="f32", op="sum") -> None:
+        _check(lib().tc_allreduce(self.handle, _h(buf), int(num_elements), _dtype(dtype), _REDUCE[op]))
+
+    def broadcast(self, buf, num_elements, dtype="f32", root=0) -> None:
+        _check(lib().tc_broadcast(self.handle, _h(buf), int(num_elements), _dtype(dtype), int(root)))
+
+    def allgather(self, src, dst, num_elements_per_rank, dtype="f32") -> None:
+        _check(lib().tc_allgather(self.handle, _h(src), _h(dst), int(num_elements_per_rank), _dtype(dtype)))
+
+    def barrier(self) -> None:
+        _check(lib().tc_barrier(self.handle))
+
+    def close(self) -> None:
+        if self.handle is not None:
+            lib().tc_dist_finalize(self.handle)
+            self.handle = None
 
 
 def rmsnorm_forward(ctx, X, gamma, Y, rstd_out, N, D, eps=1e-5) -> None:

@@ -191,6 +191,18 @@ cudaError_t launch_rope(void* X, const float* cos_t, const float* sin_t, int bat
 cudaError_t launch_gemm_f16_rows(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
                                  int ldc, float alpha, float beta, cudaStream_t stream);
 
+// --- collectives over NCCL (dist_nccl.cpp); return 0, or -1 bad arguments, -2 NCCL not found,
+// -3 rendezvous failed, -4 NCCL / CUDA error ----------------------------------------------------
+struct DistComm;
+int dist_create(int world, int rank, const char* rendezvous_url, DistComm** out);
+void dist_destroy(DistComm* d);
+int dist_world(const DistComm* d);
+int dist_rank(const DistComm* d);
+int dist_allreduce(DistComm* d, void* buf, size_t count, int dtype, int op, cudaStream_t st);
+int dist_broadcast(DistComm* d, void* buf, size_t count, int dtype, int root, cudaStream_t st);
+int dist_allgather(DistComm* d, const void* in, void* out, size_t count_per_rank, int dtype, cudaStream_t st);
+int dist_barrier(DistComm* d, cudaStream_t st);
+
 // One-time per-device kernel attribute setup (max dynamic shared memory).
 cudaError_t init_kernels_for_device(int smem_optin);
 

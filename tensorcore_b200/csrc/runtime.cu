@@ -1401,6 +1401,116 @@ extern "C" tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* d, const tc_
 }
 
 // ---------------------------------------------------------------------------------------
+// Collectives (include/tensorcore/distributed.h:51-87) over NCCL, one process per GPU
+// ---------------------------------------------------------------------------------------
+struct tc_dist_ctx {
+    tc_context* ctx;
+    tcb::DistComm* comm;
+};
+
+namespace {
+tc_status_t dist_status(int rc) {
+    switch (rc) {
+        case 0: return TC_OK;
+        case -1: return TC_ERR_INVALID_ARG;
+        case -2: return TC_ERR_UNSUPPORTED_FAMILY;    // no NCCL library on this machine
+        case -3: return TC_ERR_DISPATCH;              // the ranks did not find each other
+        default: return TC_ERR_INTERNAL;
+    }
+}
+size_t dist_elem(tc_dtype_t t) { return t == TC_DTYPE_F16 ? 2 : (t == TC_DTYPE_F32 ? 4 : 0); }
+
+template <typename Launch>
+tc_status_t run_collective(tc_dist_ctx* d, const char* opname, StepIo* io, int n_io, Launch launch) {
+    tc_context* ctx = d->ctx;
+    for (int i = 0; i < n_io; ++i) {
+        const tc_status_t st = validate(ctx, io[i].b, io[i].bytes);
+        if (st != TC_OK) return st;
+    }
+    bind_device(ctx);
+    cudaStream_t s0 = ctx->stream0;
+    cudaError_t e = cudaSuccess;
+    for (int i = 0; i < n_io && e == cudaSuccess; ++i)
+        e = io[i].write ? prepare_output(ctx, io[i].b, s0) : prepare_input(ctx, io[i].b, io[i].bytes, s0);
+    if (e != cudaSuccess) return from_cuda(e, TC_ERR_DISPATCH);
+    const int rc = launch(s0);
+    if (rc != 0) return dist_status(rc);
+    for (int i = 0; i < n_io && e == cudaSuccess; ++i)
+        if (io[i].write) e = finish_output(io[i].b, io[i].bytes, s0);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s0);
+    return record(opname, from_cuda(e, TC_ERR_DISPATCH));
+}
+}  // namespace
+
+extern "C" tc_status_t tc_dist_init(tc_context* tc, tc_dist_backend_t backend, int world_size, int rank,
+                                    const char* rendezvous_url, tc_dist_ctx** out) {
+    if (!tc) return TC_ERR_NOT_INITIALIZED;
+    if (!out || world_size < 1 || rank < 0 || rank >= world_size) return TC_ERR_INVALID_ARG;
+    if (backend != TC_DIST_SINGLE && backend != TC_DIST_RING && backend != TC_DIST_GLOO) return TC_ERR_INVALID_ARG;
+    if (backend == TC_DIST_SINGLE && world_size != 1) return TC_ERR_INVALID_ARG;
+    if (world_size > 1 && !rendezvous_url) return TC_ERR_INVALID_ARG;
+    bind_device(tc);
+    tc_dist_ctx* d = new (std::nothrow) tc_dist_ctx();
+    if (!d) return TC_ERR_ALLOC;
+    d->ctx = tc;
+    d->comm = nullptr;
+    const int rc = tcb::dist_create(world_size, rank, rendezvous_url, &d->comm);
+    if (rc != 0) { delete d; return dist_status(rc); }
+    *out = d;
+    return TC_OK;
+}
+
+extern "C" tc_status_t tc_dist_finalize(tc_dist_ctx* d) {
+    if (!d) return TC_ERR_INVALID_ARG;
+    bind_device(d->ctx);
+    cudaStreamSynchronize(d->ctx->stream0);
+    tcb::dist_destroy(d->comm);
+    delete d;
+    return TC_OK;
+}
+
+extern "C" int tc_dist_world_size(const tc_dist_ctx* d) { return d ? tcb::dist_world(d->comm) : 0; }
+extern "C" int tc_dist_rank(const tc_dist_ctx* d) { return d ? tcb::dist_rank(d->comm) : 0; }
+
+extern "C" tc_status_t tc_allreduce(tc_dist_ctx* d, tc_buffer* buf, size_t num_elements, tc_dtype_t dtype,
+                                    tc_reduce_op_t op) {
+    if (!d || !buf || num_elements == 0) return TC_ERR_INVALID_ARG;
+    if (dist_elem(dtype) == 0) return TC_ERR_UNSUPPORTED_DTYPE;
+    StepIo io[] = {{buf, num_elements * dist_elem(dtype), false}, {buf, num_elements * dist_elem(dtype), true}};
+    return run_collective(d, "tc_allreduce", io, 2, [&](cudaStream_t st) {
+        return tcb::dist_allreduce(d->comm, buf->dptr, num_elements, static_cast<int>(dtype), static_cast<int>(op), st);
+    });
+}
+
+extern "C" tc_status_t tc_broadcast(tc_dist_ctx* d, tc_buffer* buf, size_t num_elements, tc_dtype_t dtype, int root) {
+    if (!d || !buf || num_elements == 0) return TC_ERR_INVALID_ARG;
+    if (dist_elem(dtype) == 0) return TC_ERR_UNSUPPORTED_DTYPE;
+    StepIo io[] = {{buf, num_elements * dist_elem(dtype), false}, {buf, num_elements * dist_elem(dtype), true}};
+    return run_collective(d, "tc_broadcast", io, 2, [&](cudaStream_t st) {
+        return tcb::dist_broadcast(d->comm, buf->dptr, num_elements, static_cast<int>(dtype), root, st);
+    });
+}
+
+extern "C" tc_status_t tc_allgather(tc_dist_ctx* d, const tc_buffer* in, tc_buffer* out,
+                                    size_t num_elements_per_rank, tc_dtype_t dtype) {
+    if (!d || !in || !out || num_elements_per_rank == 0) return TC_ERR_INVALID_ARG;
+    if (dist_elem(dtype) == 0) return TC_ERR_UNSUPPORTED_DTYPE;
+    const size_t per = num_elements_per_rank * dist_elem(dtype);
+    StepIo io[] = {{mut(in), per, false}, {out, per * static_cast<size_t>(tcb::dist_world(d->comm)), true}};
+    return run_collective(d, "tc_allgather", io, 2, [&](cudaStream_t st) {
+        return tcb::dist_allgather(d->comm, in->dptr, out->dptr, num_elements_per_rank, static_cast<int>(dtype), st);
+    });
+}
+
+extern "C" tc_status_t tc_barrier(tc_dist_ctx* d) {
+    if (!d) return TC_ERR_INVALID_ARG;
+    bind_device(d->ctx);
+    const int rc = tcb::dist_barrier(d->comm, d->ctx->stream0);
+    if (rc != 0) return dist_status(rc);
+    return from_cuda(cudaStreamSynchronize(d->ctx->stream0), TC_ERR_DISPATCH);
+}
+
+// ---------------------------------------------------------------------------------------
 // Raw device-pointer launches
 // ---------------------------------------------------------------------------------------
 extern "C" tc_status_t tcx_raw_quantize_weights(tc_context* ctx, const void* W_fp16,

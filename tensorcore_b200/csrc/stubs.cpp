@@ -11,13 +11,9 @@
 #define TCB_EXPORT extern "C" __attribute__((visibility("default")))
 
 TCB_EXPORT int tc_adamw_step(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_allgather(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_allreduce(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_attention_backward(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_attention_forward(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_attention_forward_async(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_barrier(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_broadcast(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_buffer_demote_async(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_buffer_get_tier(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_buffer_promote_async(void) { return TCB_UNSUPPORTED; }
@@ -30,8 +26,6 @@ TCB_EXPORT int tc_checkpoint_unregister(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_conv2d_backward_input(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_conv2d_backward_weight(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_conv2d_forward(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_dist_finalize(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_dist_init(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_diloco_add_parameter(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_diloco_apply_outer(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_diloco_finalize(void) { return TCB_UNSUPPORTED; }
@@ -62,8 +56,6 @@ TCB_EXPORT uint64_t tc_checkpoint_total_bytes_discarded(void) { return 0; }
 TCB_EXPORT uint64_t tc_diloco_inner_steps_completed(void) { return 0; }
 TCB_EXPORT uint64_t tc_diloco_outer_steps_completed(void) { return 0; }
 TCB_EXPORT int tc_checkpoint_is_resident(void) { return 0; }
-TCB_EXPORT int tc_dist_rank(void) { return 0; }
-TCB_EXPORT int tc_dist_world_size(void) { return 0; }
 TCB_EXPORT int tc_hip_device_count(void) { return 0; }
 TCB_EXPORT int tc_eshkol_device_family(void) { return 0; }
 TCB_EXPORT int tc_eshkol_device_supports_bf16(void) { return 0; }

@@ -25,7 +25,7 @@ def test_single_rank_collectives(tc, ctx):
     assert np.array_equal(bx.to_numpy(x.shape, np.float32), x)
     assert np.array_equal(by.to_numpy(x.shape, np.float32), x)
     with pytest.raises(tc.TensorcoreError):
-        d.allreduce(bx, x.size, "i8", "sum")
+        d.allreduce(bx, x.size, tc.TC_DTYPE_BF16, "sum")          # only fp16 and fp32 are carried
     with pytest.raises(tc.TensorcoreError):
         tc.DistContext(ctx, tc.TC_DIST_SINGLE, 2, 0)
     d.close()

@@ -71,8 +71,13 @@ struct MegaOp {
                         // factor, whose sums of squares are at this pool index ...
     int32_t xss_k;      // ... for a row of this many elements ...
     float xss_eps;      // ... and this epsilon
+    uint32_t expect;    // one GPU: partial sums that make a row of this operation complete (its boxes per row)
+    uint32_t xexpect;   // the same for the operation whose accumulators are read at xacc_off
+    uint32_t x_epoch;   // one GPU: 1 + the epoch of the latest operation of this list that wrote into X, when
+                        // X is read from memory (not from the accumulators of the epoch before); else 0
+    uint32_t pad;
 };
-static_assert(sizeof(MegaOp) == 80, "the device copies the table in 16-byte pieces");
+static_assert(sizeof(MegaOp) == 96, "the device copies the table in 16-byte pieces");
 enum : uint32_t {
     MOP_BARRIER = 1u,   // grid-wide barrier before this operation (it depends on earlier output)
     MOP_X_F32 = 2u,     // activations (and gamma) are fp32
@@ -98,6 +103,10 @@ struct DecodeParams {
     int ns;
     int off_sx, off_x, off_ring;
     int off_ops;                    // shared-memory copy of the operation table, or -1
+    int off_desc, off_phases;       // shared memory: box descriptors of the ring slots, per-phase records
+    int n_phases;                   // phases in the table (runs of operations that share their staged input)
+    int off_epochs, n_epochs;       // shared memory: first operation of every epoch; epochs in the table
+    int off_jscale, jscale_cap;     // shared memory: 1/rms factors of the operations of one epoch, and how many fit
     uint32_t inv_grid;              // ceil(2^32 / gridDim.x): divisions by the grid size as multiplies
     // tensor parallel: every barrier spans all ranks' grids; peer pointers are device addresses
     // of the other ranks' pools and counters, valid on this device
@@ -123,7 +132,9 @@ cudaError_t launch_dense_norm_gemv(const DenseNormGemvArgs& a, const LaunchEnv& 
 struct DecodeSpan { uintptr_t lo, hi; };
 struct DecodePlan {
     int n_ops = 0;
-    int barriers = 0;          // grid barriers a single-GPU launch executes (the trailing one included)
+    int max_epoch_ops = 0;     // operations of the longest epoch
+    int epochs = 0;            // epochs of the table (runs of operations between two barriers), empty ones included
+    int barriers = 0;          // arrivals of one CTA on the arrival counter during a single-GPU launch
     int global_barriers = 0;   // tensor parallel: how many of the launch's barriers span all ranks (the two
                                // trailing ones included); the other barriers - local_barriers - span one rank
     int local_barriers = 0;
@@ -176,7 +187,7 @@ cudaError_t encode_decode_maps(const MegaOp* host_ops, int n_ops, void* host_map
 // and kDecodeStaticPoolFloats accumulators; cudaErrorNotSupported beyond that or for operations
 // outside the kernel's domain (any other error comes from the CUDA runtime).  First use on a device looks up the array's device address.
 constexpr int kDecodeStaticMaxOps = 256;
-constexpr size_t kDecodeStaticPoolFloats = 3 * 160 * 1024;
+constexpr size_t kDecodeStaticPoolFloats = 12 * 136 * 1024;   // six generations of (sum, count) pairs
 cudaError_t launch_gemv_q4_decode_static(const GemvQArgs* ops, int n_ops, const LaunchEnv& env,
                                          cudaStream_t stream);
 

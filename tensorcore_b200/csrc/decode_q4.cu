@@ -51,8 +51,10 @@ constexpr uint32_t MOP_NO_STORE = 256u;  // internal: a later operation overwrit
 constexpr int kPhaseLenShift = 16;     // MegaOp::flags bits 16..18: operations in the phase that starts here
 constexpr int kDecodeMaxSlots = 64;    // ring slots: 16 consumer warps x 4 stages at most
 constexpr int kProducerWarps = 4;     // one per warp scheduler
-constexpr int kFlowGenerations = 6;   // accumulator generations of the one-GPU kernel (epoch mod 6)
-constexpr int kDecodeMaxThreads = (kMaxStreamWarps + kProducerWarps + 1) * 32;   // consumer, producer and housekeeping warps
+constexpr int kFlowGenerations = 12;  // accumulator generations of the one-GPU kernel (epoch mod 12)
+constexpr int kKeeperWarps = 4;       // housekeeping warps: they take the epochs in turn
+constexpr int kAuxWarps = kProducerWarps + kKeeperWarps;
+constexpr int kDecodeMaxThreads = (kMaxStreamWarps + kProducerWarps + kKeeperWarps) * 32;   // consumer, producer and housekeeping warps
 
 __device__ __forceinline__ void red_add_gpu(float* p, float v) {
     asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
@@ -193,7 +195,7 @@ __device__ __forceinline__ float rstd_from_flagged_slots(const float2* slots, in
 // in its slot.
 __device__ void stage_bands_flow(const MegaOp& op, const DecodeParams& p, uint8_t* smem, float* scratch,
                                  uint32_t band_lo, uint32_t band_hi, int nthreads, volatile int* abort_s) {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;     // the consumers are the CTA's first warps
     const int nwarps = nthreads >> 5;
     const uint32_t flags = op.flags;
     const bool fused = (flags & MOP_FUSED) != 0, f16 = !(flags & MOP_X_F32);
@@ -366,26 +368,27 @@ __device__ void produce_boxes(const DecodeParams& p, const MegaOp* ops, const Ph
 }
 
 // ---------------------------------------------------------------------------------------
-// The housekeeping warp.  Everything that is not on the path from one operation's last partial
-// sum to the next operation's first box happens here, behind the consumers:
-//   when the CTA's consumers have finished epoch e,
-//     1. the 1/rms factors of the fused operations of epoch e - 1 are worked out from their sums
-//        of squares and kept in shared memory;
-//     2. the CTA arrives on the launch's arrival counter (release: publishes what steps 3 and 5
-//        of the iteration before stored; nothing recent is outstanding, so this is quick);
-//     3. this CTA's slice of the results of epoch e - 1 goes to the result buffers (the counts
-//        say when a row is complete);
-//     4. it waits until every CTA has arrived for epoch e: nobody reads the accumulators of
-//        epoch e - 1 any more (while staging epoch e), nor its sums of squares (step 1);
-//     5. it zeroes its slice of those accumulators, and the sums of squares;
-//     6. it tells the consumers that epoch e + G - 2 may start - the accumulators come from a pool
-//        in G generations; those of epoch e + G - 2 were last used by epoch e - 2 and zeroed, by
-//        every CTA, before its arrival for epoch e - 1, hence before step 4 ended.  (G = 4 would
-//        do; with 6 this warp may lag two more epochs before a consumer has to wait for it.)
-//        It also publishes how many arrival rounds are complete: a phase whose input is a result
-//        buffer written by this launch (not the accumulators of the epoch before) waits for the
-//        round that made those stores visible.
-// So the counter is a grid barrier that nobody waits at: it trails the computation.
+// The housekeeping warps.  Everything that is not on the path from one operation's last partial
+// sum to the next operation's first box happens here, behind the consumers.  Four warps take the
+// epochs in turn, each with an arrival counter of its own, so that one iteration may last four
+// epochs.  An iteration, for epoch e, once the CTA's consumers have finished e:
+//     1. this CTA's slice of the results of epoch e - 1 goes to the result buffers: the counts
+//        say when a row is complete, the 1/rms factors of fused operations come from their sums
+//        of squares;
+//     2. the CTA arrives on the warp's arrival counter (release: publishes step 1 and the
+//        clearing of the iteration before) and
+//     3. waits until every CTA has arrived for epoch e: then nobody reads the accumulators of
+//        epoch e - 1 any more (they were read while staging epoch e), nor its sums of squares
+//        (staging, and step 1);
+//     4. it zeroes its slice of those accumulators, and the sums of squares;
+//     5. it notes that iteration e is done.
+// The accumulators come from a pool in G generations.  Those that epoch t uses were last used by
+// epoch t - G, cleared in iteration t - G + 1 and published by the same warp's next arrival, in
+// iteration t - G + 5: a consumer starts epoch t when that iteration is done (with G = 12 that
+// iteration began seven epochs earlier).  A phase whose input is a result buffer written by this
+// launch in epoch s (three epochs earlier or more; anything closer reads the accumulators) waits
+// for iteration s + 1 instead, which stored and published it.
+// So the counters are grid barriers that nobody waits at: they trail the computation.
 // ---------------------------------------------------------------------------------------
 __device__ void epoch_scales(const MegaOp* ops, int b, int e, const float2* pool2, float* jscale, int cap,
                              volatile int* abort_s) {
@@ -479,27 +482,38 @@ __device__ void zero_epoch(const MegaOp* ops, int b, int e, float2* pool2, uint3
 }
 
 __device__ void keep_house(const DecodeParams& p, const MegaOp* ops, const uint16_t* ep_op, int n_epochs,
-                           volatile int* ctl, float* jscale) {
+                           volatile int* ctl, float* jscale, int jp) {
     const int lane = threadIdx.x & 31;
     float2* pool2 = reinterpret_cast<float2*>(p.pool);
+    unsigned long long* counter = p.counter + 4 * jp;    // each housekeeping warp has its own, 32 bytes apart
     unsigned long long target = p.base;
-    // One more iteration than there are epochs: the last one finishes the last epoch.
-    for (int e = 0; e <= n_epochs; ++e) {
+    // One more iteration than there are epochs: the last one finishes the last epoch.  Every warp
+    // arrives equally often per launch (the host advances one base for all counters): a warp with
+    // an iteration less makes up for it with a bare arrival.
+    const int rounds = (n_epochs + kKeeperWarps) / kKeeperWarps;
+    for (int it = 0; it < rounds; ++it) {
+        const int e = jp + it * kKeeperWarps;
+        if (e > n_epochs) {
+            if (lane == 0) arrive_gpu(counter);
+            break;
+        }
         if (e < n_epochs && lane == 0) {
             const long long t0 = clock64();
             while (ctl[2] < e + 1) {                   // the consumers have finished epoch e
                 if (ctl[0] || clock64() - t0 > kWaitClocks) { ctl[0] = 1; break; }
+                __nanosleep(200);                      // leave the issue slots to the consumers
             }
         }
         __syncwarp();
         const int b = e > 0 ? ep_op[e - 1] : 0, en = e > 0 ? ep_op[e] : 0;     // operations of epoch e - 1
         epoch_scales(ops, b, en, pool2, jscale, p.jscale_cap, &ctl[0]);
-        target += gridDim.x;
-        if (lane == 0) arrive_gpu(p.counter);
         epoch_results(ops, b, en, pool2, p.inv_grid, jscale, p.jscale_cap, &ctl[0]);
+        target += gridDim.x;
+        __syncwarp();
         if (lane == 0) {
+            arrive_gpu(counter);
             const long long t0 = clock64();
-            while (poll_gpu(p.counter) < target) {
+            while (poll_gpu(counter) < target) {
                 if (ctl[0] || clock64() - t0 > kWaitClocks) { ctl[0] = 1; break; }
             }
         }
@@ -507,7 +521,7 @@ __device__ void keep_house(const DecodeParams& p, const MegaOp* ops, const uint1
         if (ctl[0]) break;
         zero_epoch(ops, b, en, pool2, p.inv_grid);
         __syncwarp();
-        if (lane == 0) { ctl[5] = e + 1; ctl[3] = e + kFlowGenerations - 2; }
+        if (lane == 0) ctl[8 + jp] = e;
     }
     if (ctl[0] && lane == 0) atomicOr(p.err, ERR_WAIT_TIMEOUT);
 }
@@ -517,8 +531,8 @@ __global__ void __launch_bounds__(kDecodeMaxThreads, 1) decode_q4_kernel(const D
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);                      // [kDecodeMaxSlots]
     uint64_t* empty = full + kDecodeMaxSlots;                                // [kDecodeMaxSlots]
     float* scratch = reinterpret_cast<float*>(smem + 16 * kDecodeMaxSlots);  // [32]
-    // [0] abort, [1] phases found, [2] epochs the consumers have finished, [3] epochs that may start,
-    // [4] the consumers' common view of [0], [5] arrival rounds that are complete
+    // [0] abort, [1] phases found, [2] epochs the consumers have finished, [4] the consumers' common
+    // view of [0], [8 + j] last iteration housekeeping warp j has completed
     volatile int* ctl = reinterpret_cast<volatile int*>(smem + 16 * kDecodeMaxSlots + 128);
     uint2* desc = reinterpret_cast<uint2*>(smem + p.off_desc);               // [kDecodeMaxSlots]
     PhaseRec* phases = reinterpret_cast<PhaseRec*>(smem + p.off_phases);
@@ -528,14 +542,14 @@ __global__ void __launch_bounds__(kDecodeMaxThreads, 1) decode_q4_kernel(const D
     const float2* sx2 = reinterpret_cast<const float2*>(smem + p.off_sx);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nwc = (blockDim.x >> 5) - kProducerWarps - 1, nct = nwc * 32;   // consumer warps / threads
+    const int nwc = (blockDim.x >> 5) - kProducerWarps - kKeeperWarps, nct = nwc * 32;   // consumer warps / threads
     const int ns = p.ns, n_ops = p.n_ops;
     const uint32_t inv_grid = p.inv_grid;
 
     if (tid == 0) {
         for (int i = 0; i < nwc * ns; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-        ctl[0] = 0; ctl[2] = 0; ctl[5] = 0;
-        ctl[3] = kFlowGenerations - 1;   // the pool is all zero: the first epochs need no clearing
+        ctl[0] = 0; ctl[2] = 0;
+        for (int j = 0; j < kKeeperWarps; ++j) ctl[8 + j] = -1;
         fence_barrier_init();
     }
     // The operation table is read at every hand-over: keep it in shared memory when it fits (a
@@ -626,7 +640,8 @@ __global__ void __launch_bounds__(kDecodeMaxThreads, 1) decode_q4_kernel(const D
     __syncthreads();
 
     if (warp >= nwc + kProducerWarps) {
-        keep_house(p, ops, ep_op, p.n_epochs, ctl, reinterpret_cast<float*>(smem + p.off_jscale));
+        const int jp = warp - nwc - kProducerWarps;
+        keep_house(p, ops, ep_op, p.n_epochs, ctl, reinterpret_cast<float*>(smem + p.off_jscale) + jp * p.jscale_cap, jp);
         return;
     }
     if (warp >= nwc) {
@@ -635,10 +650,11 @@ __global__ void __launch_bounds__(kDecodeMaxThreads, 1) decode_q4_kernel(const D
     }
 
     // ---- consumer warps ----
+    const int ctid = tid, cw = warp;     // the consumers are the CTA's first warps
     float2* pool2 = reinterpret_cast<float2*>(p.pool);
     bool failed = false;                            // this warp gave up on a wait
     int epoch = 0;                                  // the epoch of the current phase
-    uint32_t s = static_cast<uint32_t>(warp);       // this warp's next box in the CTA's sequence
+    uint32_t s = static_cast<uint32_t>(cw);       // this warp's next box in the CTA's sequence
     int cj = 0;                                     // its ring stage
     uint32_t cpar = 0;                              // parity of that stage's current use
     for (int ph = 0; ph < n_phases; ++ph) {
@@ -649,31 +665,36 @@ __global__ void __launch_bounds__(kDecodeMaxThreads, 1) decode_q4_kernel(const D
         // Everyone in the CTA is done with the previous phase: its staged activations may be replaced.
         // (Thread 0 samples the abort flag before the barrier, everyone reads the sample after it: the
         // flag can be raised at any moment, and the consumers must all leave at the same point.)
-        if (tid == 0) ctl[4] = ctl[0];
+        if (ctid == 0) ctl[4] = ctl[0];
         consumer_sync(nct);
         if (ctl[4]) break;
         if (rounds > 0) {
             epoch += rounds;
-            if (tid == 0) ctl[2] = epoch;    // the housekeeping warp takes over epochs < epoch
-            // The accumulators and the slots of this epoch belong to a generation that an earlier
-            // epoch used: wait until the housekeeping warp has seen every CTA clear them (it has,
-            // unless it lags several epochs behind).  No fence: the clearing was performed before
-            // the housekeeping warp could see the arrivals, and nothing below is issued before this
-            // loop ends.
-            if (ctl[3] < epoch) {
-                const long long t0 = clock64();
-                while (ctl[3] < epoch) {
-                    if (ctl[0] || clock64() - t0 > kWaitClocks) { ctl[0] = 1; break; }
+            if (ctid == 0) ctl[2] = epoch;    // the housekeeping warp takes over epochs < epoch
+            // The accumulators and the slots of this epoch belong to a generation that epoch - G
+            // used: wait until the housekeeping warp that cleared it has seen every CTA's clearing
+            // published (it has, unless it lags epochs behind).  No fence: the clearing was performed
+            // before that warp could see the arrivals, and nothing below is issued before this loop
+            // ends.
+            const int need = epoch - kFlowGenerations + 1 + kKeeperWarps;
+            if (need >= 0) {
+                volatile int* done = &ctl[8 + need % kKeeperWarps];
+                if (*done < need) {
+                    const long long t0 = clock64();
+                    while (*done < need) {
+                        if (ctl[0] || clock64() - t0 > kWaitClocks) { ctl[0] = 1; break; }
+                    }
                 }
             }
         }
         if (ops[o].x_epoch) {
-            // The input is a result buffer that an earlier epoch of this launch wrote: wait for the
-            // arrival round that published those stores.
-            const int need = static_cast<int>(ops[o].x_epoch) + 2;
-            if (ctl[5] < need) {
+            // The input is a result buffer that epoch x_epoch - 1 of this launch wrote: wait for the
+            // iteration that stored and published it.
+            const int need = static_cast<int>(ops[o].x_epoch);
+            volatile int* done = &ctl[8 + need % kKeeperWarps];
+            if (*done < need) {
                 const long long t0 = clock64();
-                while (ctl[5] < need) {
+                while (*done < need) {
                     if (ctl[0] || clock64() - t0 > kWaitClocks) { ctl[0] = 1; break; }
                 }
             }
@@ -685,7 +706,7 @@ __global__ void __launch_bounds__(kDecodeMaxThreads, 1) decode_q4_kernel(const D
         }
         const uint32_t send = rec.s0 + rec.n;
         while (s < send && !failed) {
-            const int slot = warp + nwc * cj;
+            const int slot = cw + nwc * cj;
             if (!mbar_wait_bounded(&full[slot], cpar)) { failed = true; break; }
             const uint2 d = desc[slot];
             uint32_t w[36];
@@ -713,7 +734,7 @@ __global__ void __launch_bounds__(kDecodeMaxThreads, 1) decode_q4_kernel(const D
     }
     // all boxes done: hand the last epoch to the housekeeping warp
     consumer_sync(nct);
-    if (tid == 0) ctl[2] = p.n_epochs;
+    if (ctid == 0) ctl[2] = p.n_epochs;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1414,8 +1435,9 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
     }
     plan->n_ops = n_ops;
     plan->epochs = barriers;
-    // one GPU: a CTA arrives once per epoch and once more at the end
-    plan->barriers = n_ranks > 1 ? barriers : barriers + 1;
+    // one GPU: each of a CTA's housekeeping warps arrives on its own counter for every kKeeperWarps-th
+    // epoch, and once more at the end
+    plan->barriers = n_ranks > 1 ? barriers : (barriers + kKeeperWarps) / kKeeperWarps;
     plan->pool_floats = gens * gen * per_acc;
     return cudaSuccess;
 }
@@ -1458,7 +1480,7 @@ cudaError_t launch_decode(const MegaOp* host_ops, const DecodePlan& plan, const 
     for (int r = 0; r < dev.n_ranks; ++r) { p.peer_pool[r] = dev.peer_pool[r]; p.peer_counter[r] = dev.peer_counter[r]; }
     int off;
     if (flow) {
-        off = 16 * kDecodeMaxSlots + 128 + 32;   // full / empty barriers, scratch, control words (8 ints)
+        off = 16 * kDecodeMaxSlots + 128 + 64;   // full / empty barriers, scratch, control words (16 ints)
         p.off_desc = off;
         off += 8 * kDecodeMaxSlots;
         p.off_phases = off;
@@ -1467,7 +1489,7 @@ cudaError_t launch_decode(const MegaOp* host_ops, const DecodePlan& plan, const 
         off += align_up((plan.epochs + 1) * 2, 16);
         p.off_jscale = off;
         p.jscale_cap = plan.max_epoch_ops < 256 ? plan.max_epoch_ops : 256;
-        off += align_up(p.jscale_cap * 4, 16);
+        off += align_up(kKeeperWarps * p.jscale_cap * 4, 16);
     } else {
         off = 8 * kMaxStreamWarps * 4 + 8 * kMaxStreamWarps + 16;   // barriers, scratch, abort flag
         off = align_up(off, 16);
@@ -1496,9 +1518,9 @@ cudaError_t launch_decode(const MegaOp* host_ops, const DecodePlan& plan, const 
     if (!flow)
         return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(tpk::decode_q4_tp_kernel), dim3(grid),
                                            dim3(warps * 32), args, smem, stream);
-    // `warps` consumer warps, the producer warps and the housekeeping warp
+    // `warps` consumer warps, the producer warps and the housekeeping warps
     return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(decode_q4_kernel), dim3(grid),
-                                       dim3((warps + kProducerWarps + 1) * 32), args, smem, stream);
+                                       dim3((warps + kProducerWarps + kKeeperWarps) * 32), args, smem, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1610,6 +1632,8 @@ cudaError_t launch_gemv_q4_decode_static(const GemvQArgs* ops, int n_ops, const 
     dev.pool = reinterpret_cast<float*>(scratch + kStaticPoolOffset);
     dev.counter = reinterpret_cast<unsigned long long*>(scratch);
     dev.base = 0;
+    dev.local_counter = dev.counter + 16;     // the second arrival counter, in the same 256 bytes
+    dev.local_base = 0;
     return launch_decode(table, plan, dev, env, stream);
 }
 

@@ -171,6 +171,20 @@ struct DecodeDevice {
     float* peer_pool[kDecodeMaxRanks] = {};
     unsigned long long* peer_counter[kDecodeMaxRanks] = {};
 };
+// What a completed launch has added to the site's arrival counters.  One GPU: every housekeeping
+// warp of a CTA arrives plan.barriers times on a counter of its own (they sit 32 bytes apart in
+// the counter allocation and share one base).  Tensor parallel: the barriers that span all ranks,
+// and those that span one rank.
+inline void decode_advance(const DecodePlan& plan, int sm_count, int n_ranks, unsigned long long* base,
+                           unsigned long long* local_base) {
+    const unsigned long long g = static_cast<unsigned long long>(sm_count);
+    if (n_ranks > 1) {
+        *base += static_cast<unsigned long long>(plan.global_barriers) * g * static_cast<unsigned long long>(n_ranks);
+        *local_base += static_cast<unsigned long long>(plan.local_barriers) * g;
+    } else {
+        *base += static_cast<unsigned long long>(plan.barriers) * g;
+    }
+}
 // Launches the table (already uploaded to dev.ops with its tensor maps in dev.maps).
 // cudaErrorNotSupported when the list does not fit the kernel's shared memory.
 cudaError_t launch_decode(const MegaOp* host_ops, const DecodePlan& plan, const DecodeDevice& dev,
@@ -187,7 +201,7 @@ cudaError_t encode_decode_maps(const MegaOp* host_ops, int n_ops, void* host_map
 // and kDecodeStaticPoolFloats accumulators; cudaErrorNotSupported beyond that or for operations
 // outside the kernel's domain (any other error comes from the CUDA runtime).  First use on a device looks up the array's device address.
 constexpr int kDecodeStaticMaxOps = 256;
-constexpr size_t kDecodeStaticPoolFloats = 12 * 136 * 1024;   // six generations of (sum, count) pairs
+constexpr size_t kDecodeStaticPoolFloats = 24 * 136 * 1024;   // twelve generations of (sum, count) pairs
 cudaError_t launch_gemv_q4_decode_static(const GemvQArgs* ops, int n_ops, const LaunchEnv& env,
                                          cudaStream_t stream);
 

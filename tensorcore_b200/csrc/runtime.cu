@@ -692,6 +692,7 @@ void reset_decode_site(DecodeSite& d) {
     if (d.counter) cudaMemset(d.counter, 0, kMegaFlagBytes);
     if (d.pool) cudaMemset(d.pool, 0, d.pool_floats * sizeof(float));
     d.base = 0;
+    d.local_base = 0;
 }
 
 bool alloc_decode_site_tables(DecodeSite& d) {
@@ -729,9 +730,10 @@ cudaError_t submit_as_persistent_launch(tc_stream* s, int* launches, const char*
     if (replay) {
         tcb::DecodeDevice dev;
         dev.ops = d.dev; dev.maps = d.maps_dev; dev.pool = d.pool; dev.counter = d.counter; dev.base = d.base;
+        dev.local_counter = d.counter + 16; dev.local_base = d.local_base;
         e = tcb::launch_decode(d.host, d.plan, dev, make_env(ctx, false), s->s);
         if (e == cudaSuccess) {
-            d.base += static_cast<unsigned long long>(d.plan.barriers) * ctx->sm_count;
+            tcb::decode_advance(d.plan, ctx->sm_count, 1, &d.base, &d.local_base);
             *launches += 1;
             *name = "q4_0_decode_persistent_sm100";
             return e;
@@ -788,11 +790,12 @@ cudaError_t submit_as_persistent_launch(tc_stream* s, int* launches, const char*
     d.plan = plan;
     tcb::DecodeDevice dev;
     dev.ops = d.dev; dev.maps = d.maps_dev; dev.pool = d.pool; dev.counter = d.counter; dev.base = d.base;
+    dev.local_counter = d.counter + 16; dev.local_base = d.local_base;
     e = tcb::launch_decode(d.host, plan, dev, make_env(ctx, false), s->s);
     if (e == cudaErrorCooperativeLaunchTooLarge) { (void)cudaGetLastError(); return cudaErrorNotSupported; }
     if (e == cudaErrorNotSupported) return e;
     if (e == cudaSuccess) {
-        d.base += static_cast<unsigned long long>(plan.barriers) * ctx->sm_count;
+        tcb::decode_advance(plan, ctx->sm_count, 1, &d.base, &d.local_base);
         *launches += 1;
         *name = "q4_0_decode_persistent_sm100";
         s->planned = s->args;
@@ -1029,12 +1032,7 @@ extern "C" tc_status_t tcx_stream_decode_tp(tc_stream* s, const tcx_decode_tp_op
     e = tcb::launch_decode(d.host, d.plan, dev, make_env(ctx, false), s->s);
     if (e == cudaErrorNotSupported || e == cudaErrorCooperativeLaunchTooLarge) { (void)cudaGetLastError(); return TC_ERR_INVALID_SHAPE; }
     if (e == cudaSuccess) {
-        if (d.n_ranks > 1) {
-            d.base += static_cast<unsigned long long>(d.plan.global_barriers) * ctx->sm_count * d.n_ranks;
-            d.local_base += static_cast<unsigned long long>(d.plan.local_barriers) * ctx->sm_count;
-        } else {
-            d.base += static_cast<unsigned long long>(d.plan.barriers) * ctx->sm_count;
-        }
+        tcb::decode_advance(d.plan, ctx->sm_count, d.n_ranks, &d.base, &d.local_base);
         g_launches.fetch_add(1);
         t_last_kernel = d.n_ranks > 1 ? "q4_0_decode_persistent_tp_sm100" : "q4_0_decode_persistent_sm100";
     }

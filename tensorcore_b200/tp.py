@@ -277,7 +277,7 @@ class TPLink:
     Every fused decoder of the process launches on it (the kernel's table is re-planned when the
     operation list changes; pool and counter carry over)."""
 
-    def __init__(self, ctx, dist, world: int, rank: int, pool_floats: int = 1 << 21):
+    def __init__(self, ctx, dist, world: int, rank: int, pool_floats: int = 3 << 20):
         import tensorcore_b200 as tc
         self.world, self.rank = world, rank
         self.stream = ctx.stream()

@@ -335,9 +335,9 @@ __device__ void produce_boxes(const DecodeParams& p, const MegaOp* ops, const Ph
                     // the consumer has copied the slot's previous box into registers
                     const uint32_t par = (use - 1u) & 1u;
                     if (!mbar_try_wait(&empty[slot], par)) {
-                        const long long t0 = clock64();
-                        while (!mbar_try_wait(&empty[slot], par)) {
-                            if (*abort_s || clock64() - t0 > kWaitClocks) { good = false; break; }
+                        int tries = 0;
+                        while (!mbar_try_wait_parked(&empty[slot], par, 1000000u)) {      // up to a millisecond each
+                            if (*abort_s || ++tries > 1000) { good = false; break; }
                         }
                     }
                 }

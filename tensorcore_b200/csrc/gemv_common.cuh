@@ -83,14 +83,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ~2e9 clocks (about a second) and reports false.
+// The same test, but the hardware may park the thread for up to `ns` nanoseconds while the phase is
+// incomplete (it wakes as soon as the phase completes): a waiting warp then takes no issue slots
+// from the warps that share its scheduler.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after about a second and reports false.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > 2000000000LL) return false;
-    }
-    return true;
+    for (int i = 0; i < 1000; ++i)
+        if (mbar_try_wait_parked(bar, parity, 1000000u)) return true;     // up to a millisecond each
+    return false;
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes,
                                          uint64_t* bar) {

@@ -32,7 +32,7 @@ if ROOT not in sys.path:
 import numpy as np  # noqa: E402
 
 METRIC = "synthetic 7B Q4_0 decode tok/s"
-TRAFFIC_RATIO = 1.0087
+TRAFFIC_RATIO = 1.0087   # DRAM bytes / algorithmic bytes of the persistent decode kernel (ncu, see profiles/)
 UNIT = "tok/s"
 
 

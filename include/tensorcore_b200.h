@@ -452,6 +452,8 @@ typedef struct {
     int y_row0;        /* row of Y that this rank's row 0 maps to (gathered results), else 0 */
     int y_rows;        /* rows of Y (0 = op.N) */
     int layout_rows;   /* accumulators to reserve (0 = y_rows); identical on all ranks */
+    int expect;        /* partial sums that complete a row, over all ranks: the sum of op.K / 256 over the
+                          ranks that add to the same rows (0 = op.K / 256: only this rank adds to them) */
 } tcx_decode_tp_op;
 tc_status_t tcx_stream_tp_export(tc_stream* s, size_t pool_floats, void* handles_out_128_bytes);
 tc_status_t tcx_stream_tp_connect(tc_stream* s, int n_ranks, int rank, const void* all_records);

@@ -95,7 +95,7 @@ class TCXDecodeOp(Structure):
 
 class TCXDecodeTpOp(Structure):
     _fields_ = [("op", TCXDecodeOp), ("peers", c_int), ("y_row0", c_int), ("y_rows", c_int),
-                ("layout_rows", c_int)]
+                ("layout_rows", c_int), ("expect", c_int)]
 
 
 DECODE_STATIC_MAX_OPS = 256
@@ -545,7 +545,7 @@ def stream_tp_connect(stream, n_ranks: int, rank: int, records: bytes) -> None:
 
 def make_decode_tp_ops(ops):
     """ctypes array for stream_decode_tp from a list of dicts (device addresses W, X, Y, optional
-    gamma; N, K, x_dtype, y_dtype, eps; optional peers, y_row0, y_rows, layout_rows)."""
+    gamma; N, K, x_dtype, y_dtype, eps; optional peers, y_row0, y_rows, layout_rows, expect)."""
     arr = (TCXDecodeTpOp * len(ops))()
     for i, o in enumerate(ops):
         a = arr[i].op
@@ -556,6 +556,7 @@ def make_decode_tp_ops(ops):
         a.eps = float(o.get("eps", 1e-5))
         arr[i].peers, arr[i].y_row0 = int(o.get("peers", 0)), int(o.get("y_row0", 0))
         arr[i].y_rows, arr[i].layout_rows = int(o.get("y_rows", 0)), int(o.get("layout_rows", 0))
+        arr[i].expect = int(o.get("expect", 0))
     return arr
 
 

@@ -151,16 +151,24 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void red_add_pair(float2* p, float v) {
     asm volatile("red.relaxed.gpu.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(v), "f"(1.0f) : "memory");
 }
-// Two accumulators with their counts, straight from L2.
-__device__ __forceinline__ float4 ld_pairs(const float2* p) {
+__device__ __forceinline__ void red_add_pair_sys(float2* p, float v) {     // into another GPU's pool as well
+    asm volatile("red.relaxed.sys.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(v), "f"(1.0f) : "memory");
+}
+// Two accumulators with their counts, straight from L2.  `sys`: other GPUs add to them too.
+__device__ __forceinline__ float4 ld_pairs(const float2* p, bool sys) {
     float4 v;
-    asm volatile("ld.relaxed.gpu.global.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    if (sys)
+        asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    else
+        asm volatile("ld.relaxed.gpu.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ float2 ld_pair(const float2* p) {
+__device__ __forceinline__ float2 ld_pair(const float2* p, bool sys = false) {
     float2 v;
-    asm volatile("ld.relaxed.gpu.global.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
+    if (sys) asm volatile("ld.relaxed.sys.global.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
+    else asm volatile("ld.relaxed.gpu.global.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
     return v;
 }
 constexpr long long kWaitClocks = 2000000000LL;    // about a second: every wait gives up after this
@@ -229,7 +237,7 @@ __device__ void stage_bands_flow(const MegaOp& op, const DecodeParams& p, uint8_
                     const long long t0 = clock64();
                     while (!done) {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) a[e] = ld_pairs(src + 2 * e);
+                        for (int e = 0; e < 4; ++e) a[e] = ld_pairs(src + 2 * e, p.n_ranks > 1);
                         done = true;
 #pragma unroll
                         for (int e = 0; e < 4; ++e) done = done && a[e].y == want && a[e].w == want;
@@ -301,7 +309,7 @@ __device__ __forceinline__ bool locate_box(const PhaseRec* phases, int n_phases,
     b.y = static_cast<int>(rb * 32u);
     const uint32_t left = static_cast<uint32_t>(op.N) - rb * 32u;
     b.d0 = op.acc_off + op.y_row0 + rb * 32u;
-    b.d1 = kg | ((left < 32u ? left : 32u) << 16);
+    b.d1 = kg | ((left < 32u ? left : 32u) << 16) | ((op.flags & MOP_PEERS) ? (1u << 24) : 0u);
     return true;
 }
 
@@ -428,7 +436,7 @@ __device__ void epoch_scales(const MegaOp* ops, int b, int e, const float2* pool
 }
 
 __device__ void epoch_results(const MegaOp* ops, int b, int e, const float2* pool2, uint32_t inv_grid,
-                              const float* jscale, int cap, volatile int* abort_s) {
+                              const float* jscale, int cap, volatile int* abort_s, bool sys) {
     const int lane = threadIdx.x & 31;
     constexpr int kRowsAtOnce = 8;
     for (int k = b; k < e; ++k) {
@@ -442,19 +450,21 @@ __device__ void epoch_results(const MegaOp* ops, int b, int e, const float2* poo
         const float scale = k - b < cap ? jscale[k - b]
                                         : ((flags & MOP_FUSED) ? rstd_from_flagged_slots(pool2 + op.ss_off, op.K, op.eps, abort_s) : 1.0f);
         const uint32_t r0 = op.y_row0, r1 = op.y_row0 + static_cast<uint32_t>(op.N);
+        const bool all_rows = sys && (flags & MOP_PEERS);
         void* Y = op.Y;
         for (uint32_t i0 = lo + lane; i0 < hi; i0 += 32u * kRowsAtOnce) {
             float2 v[kRowsAtOnce];
 #pragma unroll
             for (int u = 0; u < kRowsAtOnce; ++u) {
                 const uint32_t i = i0 + 32u * u;
-                if (i < hi) v[u] = ld_pair(acc + i);
+                if (i < hi) v[u] = ld_pair(acc + i, sys);
             }
 #pragma unroll
             for (int u = 0; u < kRowsAtOnce; ++u) {
                 const uint32_t i = i0 + 32u * u;
                 if (i >= hi) break;
-                const float need = (i >= r0 && i < r1) ? want : 0.f;     // rows outside this operation's part get nothing
+                // rows outside this operation's part get nothing - unless the other ranks fill them
+                const float need = (all_rows || (i >= r0 && i < r1)) ? want : 0.f;
                 if (v[u].y != need) {
                     const long long t0 = clock64();
                     while ((v[u] = ld_pair(acc + i)).y != need) {
@@ -485,8 +495,20 @@ __device__ void keep_house(const DecodeParams& p, const MegaOp* ops, const uint1
                            volatile int* ctl, float* jscale, int jp) {
     const int lane = threadIdx.x & 31;
     float2* pool2 = reinterpret_cast<float2*>(p.pool);
+    const bool multi = p.n_ranks > 1;
     unsigned long long* counter = p.counter + 4 * jp;    // each housekeeping warp has its own, 32 bytes apart
     unsigned long long target = p.base;
+    const unsigned long long per_round = static_cast<unsigned long long>(gridDim.x) * (multi ? p.n_ranks : 1);
+    // Tensor parallel: a CTA arrives on the counter of every rank, so a round is complete when the
+    // CTAs of all ranks have arrived - other ranks add into this rank's accumulators, and must not
+    // before it has cleared them.
+    auto arrive = [&]() {
+        if (multi) {
+            for (int r = 0; r < p.n_ranks; ++r) arrive_sys(p.peer_counter[r] + 4 * jp);
+        } else {
+            arrive_gpu(counter);
+        }
+    };
     // One more iteration than there are epochs: the last one finishes the last epoch.  Every warp
     // arrives equally often per launch (the host advances one base for all counters): a warp with
     // an iteration less makes up for it with a bare arrival.
@@ -494,7 +516,8 @@ __device__ void keep_house(const DecodeParams& p, const MegaOp* ops, const uint1
     for (int it = 0; it < rounds; ++it) {
         const int e = jp + it * kKeeperWarps;
         if (e > n_epochs) {
-            if (lane == 0) arrive_gpu(counter);
+            if (lane == 0) arrive();
+            target += per_round;
             break;
         }
         if (e < n_epochs && lane == 0) {
@@ -507,13 +530,13 @@ __device__ void keep_house(const DecodeParams& p, const MegaOp* ops, const uint1
         __syncwarp();
         const int b = e > 0 ? ep_op[e - 1] : 0, en = e > 0 ? ep_op[e] : 0;     // operations of epoch e - 1
         epoch_scales(ops, b, en, pool2, jscale, p.jscale_cap, &ctl[0]);
-        epoch_results(ops, b, en, pool2, p.inv_grid, jscale, p.jscale_cap, &ctl[0]);
-        target += gridDim.x;
+        epoch_results(ops, b, en, pool2, p.inv_grid, jscale, p.jscale_cap, &ctl[0], multi);
+        target += per_round;
         __syncwarp();
         if (lane == 0) {
-            arrive_gpu(counter);
+            arrive();
             const long long t0 = clock64();
-            while (poll_gpu(counter) < target) {
+            while ((multi ? poll_sys(counter) : poll_gpu(counter)) < target) {
                 if (ctl[0] || clock64() - t0 > kWaitClocks) { ctl[0] = 1; break; }
             }
         }
@@ -522,6 +545,20 @@ __device__ void keep_house(const DecodeParams& p, const MegaOp* ops, const uint1
         zero_epoch(ops, b, en, pool2, p.inv_grid);
         __syncwarp();
         if (lane == 0) ctl[8 + jp] = e;
+    }
+    if (multi && !ctl[0]) {
+        // Another rank may start its next launch, and add into this rank's accumulators, as soon as
+        // it leaves this kernel: nobody leaves before everyone has cleared everything.
+        target += per_round;
+        __syncwarp();
+        if (lane == 0) {
+            arrive();
+            const long long t0 = clock64();
+            while (poll_sys(counter) < target) {
+                if (ctl[0] || clock64() - t0 > kWaitClocks) { ctl[0] = 1; break; }
+            }
+        }
+        __syncwarp();
     }
     if (ctl[0] && lane == 0) atomicOr(p.err, ERR_WAIT_TIMEOUT);
 }
@@ -725,7 +762,14 @@ __global__ void __launch_bounds__(kDecodeMaxThreads, 1) decode_q4_kernel(const D
             s += static_cast<uint32_t>(nwc);
             float out[1] = {0.f};
             group_dot_i16<FMT_Q4_0, 1, true>(w, xs, sx2, static_cast<int>(d.y & 0xffffu), 0, 0, 0, out);
-            if (static_cast<uint32_t>(lane) < (d.y >> 16)) red_add_pair(pool2 + d.x + lane, out[0]);
+            if (static_cast<uint32_t>(lane) < ((d.y >> 16) & 63u)) {
+                if (d.y >> 24) {     // tensor parallel: into every rank's accumulators
+                    for (int r = 0; r < p.n_ranks; ++r)
+                        red_add_pair_sys(reinterpret_cast<float2*>(p.peer_pool[r]) + d.x + lane, out[0]);
+                } else {
+                    red_add_pair(pool2 + d.x + lane, out[0]);
+                }
+            }
         }
         if (__any_sync(0xffffffffu, failed)) {
             failed = true;
@@ -736,423 +780,6 @@ __global__ void __launch_bounds__(kDecodeMaxThreads, 1) decode_q4_kernel(const D
     consumer_sync(nct);
     if (ctid == 0) ctl[2] = p.n_epochs;
 }
-
-// ---------------------------------------------------------------------------------------
-// Tensor parallel (more than one rank): the same boxes, phases and accumulators, but every warp
-// issues its own copies and epochs are separated by grid barriers, which span all ranks where
-// results cross ranks: an operation marked MOP_PEERS adds its partial sums into the accumulators
-// of every rank over NVLink peer memory.
-// ---------------------------------------------------------------------------------------
-namespace tpk {
-struct Phase {
-    int o, oe;                          // operations [o, oe): they share their input, hence K
-    uint32_t rbase[kMaxPhaseOps + 1];   // prefix sums of the operations' row-block counts
-    uint32_t gpr;                       // groups per row
-    uint32_t c0, c1;                    // this CTA's boxes
-};
-
-__device__ __forceinline__ void make_phase(const MegaOp* ops, int n_ops, int o, uint32_t inv_grid, Phase& ph) {
-    // plan_decode leaves the number of operations of the phase that starts at o in the flags
-    const int oe = o + static_cast<int>((ops[o].flags >> kPhaseLenShift) & 7u);
-    ph.o = o;
-    ph.oe = oe;
-    uint32_t r = 0;
-#pragma unroll
-    for (int k = 0; k < kMaxPhaseOps; ++k) {
-        ph.rbase[k] = r;
-        if (o + k < oe) r += static_cast<uint32_t>((ops[o + k].N + 31) >> 5);
-    }
-    ph.rbase[kMaxPhaseOps] = r;
-    ph.gpr = static_cast<uint32_t>(ops[o].K) >> 8;
-    const uint32_t u = r * ph.gpr;   // the launcher refuses lists with u * gridDim >= 2^32
-    ph.c0 = grid_share(u, blockIdx.x, inv_grid);
-    ph.c1 = blockIdx.x + 1 == gridDim.x ? u : grid_share(u, blockIdx.x + 1, inv_grid);
-}
-
-// Position of a box in its phase: band, row block of the phase's concatenated operations, group
-// inside the band.  Full bands hold 4R boxes (R row blocks), a last narrower band R * (gpr % 4).
-struct Cursor { uint32_t u, band, r, kgi; };
-
-__device__ __forceinline__ void cursor_set(const Phase& ph, uint32_t u, Cursor& c) {
-    const uint32_t R = ph.rbase[kMaxPhaseOps], full = ph.gpr / kBandGroups, per = R * kBandGroups;
-    c.u = u;
-    uint32_t band = div_u32(u, per);
-    if (band >= full) {
-        band = full;
-        const uint32_t w = ph.gpr % kBandGroups, off = u - full * per;   // callers keep u below R * gpr, so w > 0 here
-        c.r = w == 3 ? div_u32(off, 3) : (w == 2 ? off >> 1 : off);
-        c.kgi = off - c.r * w;
-    } else {
-        const uint32_t off = u - band * per;
-        c.r = off / kBandGroups;
-        c.kgi = off % kBandGroups;
-    }
-    c.band = band;
-}
-// Next box of the same warp: `step` (the warp count, a multiple of 4) boxes further, u < limit.
-__device__ __forceinline__ void cursor_advance(const Phase& ph, uint32_t step, uint32_t limit, Cursor& c) {
-    c.u += step;
-    if (c.u >= limit) return;
-    if (c.band < ph.gpr / kBandGroups) {
-        c.r += step / kBandGroups;
-        if (c.r < ph.rbase[kMaxPhaseOps]) return;
-    }
-    cursor_set(ph, c.u, c);
-}
-// Band of box u.
-__device__ __forceinline__ uint32_t band_of(const Phase& ph, uint32_t u) {
-    const uint32_t band = div_u32(u, ph.rbase[kMaxPhaseOps] * kBandGroups), full = ph.gpr / kBandGroups;
-    return band < full ? band : full;
-}
-// Row block r of the phase -> operation (index within the phase) and its row block.
-__device__ __forceinline__ void row_block(const Phase& ph, uint32_t r, int& k, uint32_t& rb) {
-    k = 0;
-    uint32_t base = 0;
-#pragma unroll
-    for (int j = 1; j < kMaxPhaseOps; ++j)
-        if (j < ph.oe - ph.o && r >= ph.rbase[j]) { k = j; base = ph.rbase[j]; }
-    rb = r - base;
-}
-
-// This CTA's share of a vector of n rows.
-__device__ __forceinline__ void cta_slice(uint32_t n, uint32_t inv_grid, uint32_t& lo, uint32_t& hi) {
-    lo = grid_share(n, blockIdx.x, inv_grid);          // plan_decode keeps n below 2^24: no overflow
-    hi = blockIdx.x + 1 == gridDim.x ? n : grid_share(n, blockIdx.x + 1, inv_grid);
-}
-
-// 1 / sqrt(mean square + eps) from a warp's per-lane share of the sums of squares.  One routine
-// for every reader, so that they all get the same bits.
-__device__ __forceinline__ float rstd_from_lane_part(float t, int K, float eps) {
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    return rsqrtf(t / static_cast<float>(K) + eps);
-}
-// The same from the per-band sums of a row of K elements in the pool.  Called by whole warps.
-__device__ __forceinline__ float rstd_from_slots(const float* slots, int K, float eps) {
-    const int nbands = ((K >> 8) + kBandGroups - 1) / kBandGroups, l = threadIdx.x & 31;
-    return rstd_from_lane_part(l < nbands ? __ldcg(slots + l) : 0.f, K, eps);
-}
-
-// Writes this CTA's slice of the result buffers of operations [b, e), whose accumulators are
-// complete, applying the 1/rms factor their staging pass left out; optionally zeroes the slice.
-// A group of four warps takes one operation (a CTA's slice is a few dozen rows), so the
-// operations of an epoch are finished side by side, each with one round trip to L2.
-__device__ void finalize_results(const MegaOp* ops, int b, int e, float* pool, uint32_t inv_grid, bool zero_too) {
-    const int tid = threadIdx.x, grp = tid >> 7, tg = tid & 127, ngrp = blockDim.x >> 7;
-    for (int k = b + grp; k < e; k += ngrp) {
-        const MegaOp& op = ops[k];
-        const uint32_t flags = op.flags;
-        uint32_t lo, hi;
-        cta_slice(op.y_rows, inv_grid, lo, hi);
-        float* acc = pool + op.acc_off;
-        const uint32_t first = lo + tg;
-        if ((flags & MOP_NO_STORE) && !zero_too) continue;
-        const float v0 = first < hi ? __ldcg(acc + first) : 0.f;     // in flight together with the sums
-        const float scale = (flags & MOP_FUSED) ? rstd_from_slots(pool + op.ss_off, op.K, op.eps) : 1.0f;
-        void* Y = op.Y;
-        for (uint32_t i = first; i < hi; i += 128) {
-            const float v = (i == first ? v0 : __ldcg(acc + i)) * scale;
-            if (!(flags & MOP_NO_STORE)) {
-                if (flags & MOP_Y_F32) static_cast<float*>(Y)[i] = v;
-                else static_cast<__half*>(Y)[i] = __float2half_rn(v);
-            }
-            if (zero_too) acc[i] = 0.f;
-        }
-    }
-}
-
-__device__ void zero_accumulators(const MegaOp* ops, int b, int e, float* pool, uint32_t inv_grid) {
-    const int tid = threadIdx.x, grp = tid >> 7, tg = tid & 127, ngrp = blockDim.x >> 7;
-    for (int k = b + grp; k < e; k += ngrp) {
-        uint32_t lo, hi;
-        cta_slice(ops[k].y_rows, inv_grid, lo, hi);
-        float* acc = pool + ops[k].acc_off;
-        for (uint32_t i = lo + tg; i < hi; i += 128) acc[i] = 0.f;
-    }
-}
-
-// Stages bands [band_lo, band_hi] of the input of `op` (the head of a phase) as int16 with one
-// scale per 32 elements, at their natural positions in the shared-memory row.  Four warps take
-// one band (32 chunks of 8 elements each per group), so up to four bands are staged at a time.
-// Fused RMSNorm: quantises x * gamma and stores each band's sum of squares to its slot.
-__device__ void stage_bands(const MegaOp& op, const DecodeParams& p, uint8_t* smem, float* scratch,
-                            uint32_t band_lo, uint32_t band_hi) {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nwarps = blockDim.x >> 5;
-    const uint32_t flags = op.flags;
-    const bool fused = (flags & MOP_FUSED) != 0, f16 = !(flags & MOP_X_F32);
-    const bool from_acc = op.xacc_off >= 0, round16 = (flags & MOP_XACC_F16) != 0;
-    const int K = op.K, nb = K >> 5, gpr = K >> 8;
-    const bool pow2 = (from_acc ? round16 : f16) && !fused;
-    const void* X = from_acc ? static_cast<const void*>(p.pool + op.xacc_off) : op.X;
-    const int xkind = from_acc ? 1 : (f16 ? 0 : 1), gkind = f16 ? 0 : 1;
-    uint4* dst = reinterpret_cast<uint4*>(smem + p.off_x);
-    float2* sx2 = reinterpret_cast<float2*>(smem + p.off_sx);
-    const uint32_t per_pass = static_cast<uint32_t>(nwarps) / 4;
-    for (uint32_t b0 = band_lo; b0 <= band_hi; b0 += per_pass) {
-        const uint32_t band = b0 + static_cast<uint32_t>(warp >> 2);
-        const bool mine = band <= band_hi;
-        const int g0 = static_cast<int>(band) * kBandGroups;
-        const int width = mine ? min(kBandGroups, gpr - g0) : 0;          // groups in this band
-        float ssq = 0.f;
-        for (int c = (warp & 3) * 32 + lane; c - lane < width * 32; c += 128) {   // warp-uniform trip count
-            const bool live = c < width * 32;
-            const int i = g0 * 32 + c;                                    // chunk index in the row
-            float v[8], g[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) { v[e] = 0.f; g[e] = 1.f; }
-            if (live) {
-                load8<true>(X, xkind, 8 * static_cast<size_t>(i), v);
-                if (fused) load8<false>(op.gamma, gkind, 8 * static_cast<size_t>(i), g);
-            }
-            if (from_acc) {
-                // what the producer's result buffer will hold: the accumulator scaled by the
-                // producer's own 1/rms (when its prologue was fused) and rounded to its type;
-                // the sums of squares are fetched while the loads above are in flight
-                const float xs = op.xss_off >= 0 ? rstd_from_slots(p.pool + op.xss_off, op.xss_k, op.xss_eps) : 1.0f;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    v[e] *= xs;
-                    if (round16) v[e] = __half2float(__float2half_rn(v[e]));
-                }
-            }
-            if (fused) {
-                ssq += sumsq8(v);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], g[e]);
-            }
-            quantise_chunk<true>(v, live, i, 0, 8, pow2, gpr, nb, dst, sx2);
-        }
-        if (fused) {
-            for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-            if (lane == 0) scratch[warp] = ssq;
-        }
-        __syncthreads();
-        if (fused && tid < static_cast<int>(per_pass) && b0 + tid <= band_hi) {
-            const float* s4 = scratch + 4 * tid;
-            p.pool[op.ss_off + b0 + tid] = (s4[0] + s4[1]) + (s4[2] + s4[3]);
-        }
-        if (b0 + per_pass <= band_hi) __syncthreads();    // the partial sums are reused by the next pass
-    }
-}
-
-__global__ void __launch_bounds__(kMaxStreamThreads, 1) decode_q4_tp_kernel(const DecodeParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                               // [nwarps*ns]
-    float* scratch = reinterpret_cast<float*>(smem + 8 * kMaxStreamWarps * 4);        // after barriers
-    volatile int* abort_s = reinterpret_cast<volatile int*>(smem + 8 * kMaxStreamWarps * 4 +
-                                                            8 * kMaxStreamWarps);
-    uint8_t* ring = smem + p.off_ring;
-    const uint8_t* xs = smem + p.off_x;
-    const float2* sx2 = reinterpret_cast<const float2*>(smem + p.off_sx);
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nwarps = blockDim.x >> 5, nthreads = blockDim.x;
-    const int ns = p.ns, n_ops = p.n_ops;
-    const bool multi = p.n_ranks > 1;
-    const uint32_t inv_grid = p.inv_grid;
-
-    if (tid == 0) {
-        for (int i = 0; i < nwarps * ns; ++i) mbar_init(&bars[i], 1);
-        *abort_s = 0;
-        fence_barrier_init();
-    }
-    // The operation table is read by every thread at every box: keep it in shared memory when it
-    // fits (a global read costs an L2 round trip).
-    const MegaOp* ops = p.ops;
-    if (p.off_ops >= 0) {
-        uint4* dst = reinterpret_cast<uint4*>(smem + p.off_ops);
-        const uint4* src = reinterpret_cast<const uint4*>(p.ops);
-        for (int i = tid; i < n_ops * static_cast<int>(sizeof(MegaOp) / 16); i += nthreads) dst[i] = src[i];
-        ops = reinterpret_cast<const MegaOp*>(smem + p.off_ops);
-    }
-    __syncthreads();
-
-    // ---- per-warp weight stream: the issue cursor runs ahead of the consume cursor ----
-    const uint8_t* maps = static_cast<const uint8_t*>(p.maps);   // one 128-byte tensor map per operation
-    Phase pi;
-    Cursor ci;
-    make_phase(ops, n_ops, 0, inv_grid, pi);
-    ci.u = pi.c0 + warp;
-    if (ci.u < pi.c1) cursor_set(pi, ci.u, ci);
-    int islot = 0, cslot = 0;            // ring slots of the next issue / next consume
-    uint32_t cphase = 0;                 // parity of the consume slot's current use
-    int inflight = 0;
-    auto try_issue = [&]() {
-        while (pi.o < n_ops && ci.u >= pi.c1) {
-            if (pi.oe >= n_ops) { pi.o = n_ops; break; }
-            make_phase(ops, n_ops, pi.oe, inv_grid, pi);
-            ci.u = pi.c0 + warp;
-            if (ci.u < pi.c1) cursor_set(pi, ci.u, ci);
-        }
-        if (pi.o >= n_ops || inflight >= ns) return;
-        if (lane == 0) {
-            int k;
-            uint32_t rb;
-            row_block(pi, ci.r, k, rb);
-            uint64_t* bar = &bars[warp * ns + islot];
-            fence_proxy_async();
-            mbar_expect_tx(bar, kBoxBytes);
-            sm100::tensor_load_2d(ring + static_cast<size_t>(warp * ns + islot) * kBoxBytes,
-                                  maps + static_cast<size_t>(pi.o + k) * kDecodeMapBytes,
-                                  static_cast<int>((ci.band * kBandGroups + ci.kgi) * 144),
-                                  static_cast<int>(rb * 32), bar);
-        }
-        cursor_advance(pi, nwarps, pi.c1, ci);
-        ++inflight;
-        if (++islot == ns) islot = 0;
-    };
-    for (int i = 0; i < ns; ++i) try_issue();
-
-    unsigned long long target = p.base, ltarget = p.local_base;
-    const unsigned long long per_barrier = static_cast<unsigned long long>(gridDim.x) * (multi ? p.n_ranks : 1);
-    bool failed = false;
-    int cur_b = 0;                                  // first operation of the current epoch
-    int prev_b = 0, prev_e = 0, pp_b = 0, pp_e = 0; // the two epochs before it
-    Phase pc;
-    Cursor cc;
-    for (int o = 0; o <= n_ops && !failed;) {
-        const bool tail = o == n_ops;               // trailing epoch: barrier and clean-up only
-        const uint32_t flags = tail ? MOP_BARRIER : ops[o].flags;
-        if (!tail) make_phase(ops, n_ops, o, inv_grid, pc);
-        const int rounds = (flags & MOP_BARRIER) ? ((flags & MOP_BARRIER2) ? 2 : 1) : 0;
-        // Everyone in the CTA is done with the previous phase: its staged activations may be
-        // replaced, and thread 0's arrival below covers every warp's accumulator updates.
-        if (rounds == 0) __syncthreads();
-        for (int round = 0; round < rounds; ++round) {
-            // Accumulators last read two epochs ago (staging) and one epoch ago (result buffers):
-            // zero this CTA's slices before arriving, so that the barrier publishes the zeros.
-            zero_accumulators(ops, pp_b, pp_e, p.pool, inv_grid);
-            __syncthreads();
-            // One 64-bit arrival counter that is never reset: a barrier is complete when the
-            // counter reaches the running target.  One thread per CTA arrives with a release
-            // reduction (no value comes back) and polls with acquire loads; the wait is bounded.
-            // Tensor parallel: every CTA arrives on every rank's counter, so the barrier spans all
-            // grids.
-            // A barrier that only orders this rank's own data (results consumed on the rank that
-            // produced them) stays inside the rank: its own counter, GPU scope.
-            const bool global = multi && (tail || (flags & MOP_GBARRIER));
-            const bool local = multi && !global;
-            if (local) ltarget += gridDim.x; else target += per_barrier;
-            if (tid == 0) {
-                if (global) {
-                    for (int r = 0; r < p.n_ranks; ++r) arrive_sys(p.peer_counter[r]);
-                } else {
-                    arrive_gpu(local ? p.local_counter : p.counter);
-                }
-            }
-            // While the others arrive: result buffers of the epoch before the one that just ended
-            // (its accumulators were completed by the previous barrier).  These stores are
-            // published by the NEXT barrier, so a buffer can be read three epochs after it was
-            // produced; readers one epoch after take the accumulators, and the host puts an empty
-            // epoch (a second barrier) in front of a reader two epochs after.
-            finalize_results(ops, prev_b, prev_e, p.pool, inv_grid, false);
-            if (tid == 0) {
-                const long long t0 = clock64();
-                while ((global ? poll_sys(p.counter) : poll_gpu(local ? p.local_counter : p.counter)) <
-                       (local ? ltarget : target)) {
-                    if (clock64() - t0 > 2000000000LL) {
-                        *abort_s = 1;
-                        atomicOr(p.err, ERR_WAIT_TIMEOUT);
-                        break;
-                    }
-                }
-            }
-            __syncthreads();
-            if (*abort_s) { failed = true; break; }
-            pp_b = prev_b; pp_e = prev_e;
-            prev_b = cur_b; prev_e = o;
-            cur_b = o;
-        }
-        if (failed) break;
-        if (tail) {
-            // the last epoch's results, and what the regular schedule would zero later
-            finalize_results(ops, prev_b, prev_e, p.pool, inv_grid, true);
-            zero_accumulators(ops, pp_b, pp_e, p.pool, inv_grid);
-            if (multi) {
-                // Another rank may start its next launch, and add into this rank's accumulators,
-                // as soon as it leaves this kernel: nobody leaves before everyone has zeroed.
-                __syncthreads();
-                target += per_barrier;
-                if (tid == 0) {
-                    for (int r = 0; r < p.n_ranks; ++r) arrive_sys(p.peer_counter[r]);
-                    const long long t0 = clock64();
-                    while (poll_sys(p.counter) < target) {
-                        if (clock64() - t0 > 2000000000LL) { atomicOr(p.err, ERR_WAIT_TIMEOUT); break; }
-                    }
-                }
-            }
-            break;
-        }
-        const MegaOp& op = ops[o];
-        cc.u = pc.c0 + warp;
-        if (cc.u < pc.c1) cursor_set(pc, cc.u, cc);      // ahead of the staging pass, whose loads hide it
-        if (pc.c0 < pc.c1) {
-            stage_bands(op, p, smem, scratch, band_of(pc, pc.c0), band_of(pc, pc.c1 - 1));
-        } else {
-            __syncthreads();   // keeps the barrier count of stage_bands (one per phase at least)
-        }
-        {   // The next phase's RMSNorm weights are a first-touch read from HBM on its critical
-            // path: one CTA pulls them into L2 a phase ahead.
-            const int nx = pc.oe;
-            if (nx < n_ops && (ops[nx].flags & MOP_FUSED) &&
-                static_cast<int>(blockIdx.x) == nx % static_cast<int>(gridDim.x)) {
-                const int bytes = ops[nx].K * ((ops[nx].flags & MOP_X_F32) ? 4 : 2);
-                const uint8_t* g = static_cast<const uint8_t*>(ops[nx].gamma);
-                for (int b = tid * 128; b < bytes; b += nthreads * 128) prefetch_l2(g + b);
-            }
-        }
-
-        while (cc.u < pc.c1) {
-            uint64_t* bar = &bars[warp * ns + cslot];
-            if (!mbar_wait_bounded(bar, cphase)) { failed = true; break; }
-            int k;
-            uint32_t rb;
-            row_block(pc, cc.r, k, rb);
-            const int kg = static_cast<int>(cc.band * kBandGroups + cc.kgi);
-            uint32_t w[36];
-            {
-                const uint4* src = reinterpret_cast<const uint4*>(
-                    ring + static_cast<size_t>(warp * ns + cslot) * kBoxBytes + static_cast<size_t>(lane) * 144);
-#pragma unroll
-                for (int v = 0; v < 9; ++v) {
-                    const uint4 t = src[v];
-                    w[4 * v + 0] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
-                }
-            }
-            __syncwarp();
-            --inflight;
-            if (++cslot == ns) { cslot = 0; cphase ^= 1u; }
-            try_issue();                           // refill: this or a later phase's weights
-            const MegaOp& opk = ops[pc.o + k];
-            const int K = opk.K;
-            float out[1] = {0.f};
-            group_dot_i16<FMT_Q4_0, 1, true>(w, xs, sx2, kg, K >> 8, K, K >> 5, out);
-            const uint32_t row = rb * 32 + lane;
-            if (row < static_cast<uint32_t>(opk.N)) {
-                const size_t at = static_cast<size_t>(opk.acc_off) + opk.y_row0 + row;
-                if (opk.flags & MOP_PEERS) {
-                    for (int r = 0; r < p.n_ranks; ++r) red_add_sys(p.peer_pool[r] + at, out[0]);
-                } else {
-                    red_add_gpu(p.pool + at, out[0]);
-                }
-            }
-            cursor_advance(pc, nwarps, pc.c1, cc);
-        }
-        if (__any_sync(0xffffffffu, failed)) failed = true;
-        if (failed) {
-            if (lane == 0) { *abort_s = 1; atomicOr(p.err, ERR_WAIT_TIMEOUT); }
-        }
-        o = pc.oe;
-    }
-    if (failed) {
-        // let copies that are still in flight land before the CTA's shared memory is released
-        for (int i = 0; i < inflight; ++i) {
-            (void)mbar_wait_bounded(&bars[warp * ns + cslot], cphase);
-            if (++cslot == ns) { cslot = 0; cphase ^= 1u; }
-        }
-    }
-}
-}  // namespace tpk
 
 inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
 inline bool spans_overlap(DecodeSpan a, DecodeSpan b) { return a.lo < b.hi && b.lo < a.hi; }
@@ -1165,9 +792,7 @@ inline bool span_hits(const DecodeSpan* v, int n, DecodeSpan r) {
 }  // namespace
 
 cudaError_t init_decode_kernel(int smem_optin) {
-    cudaError_t e = cudaFuncSetAttribute(decode_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(tpk::decode_q4_tp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+    return cudaFuncSetAttribute(decode_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
 }
 
 cudaError_t encode_decode_maps(const MegaOp* host_ops, int n_ops, void* host_maps) {
@@ -1353,15 +978,12 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
     // A generation: accumulators first, then the sums of squares.  The two never share an
     // address: accumulators are zeroed before reuse, the sums are simply overwritten.
     const size_t gen = worst + ss_worst;
-    // Tensor parallel: another rank may run one epoch ahead across a rank-local barrier and add into
-    // this rank's accumulators early; a fourth generation moves the zeroing of an accumulator in
-    // front of the last barrier that spans all ranks before its next use (see below).
-    // One GPU: the accumulators of an epoch are cleared two epochs later by a warp that trails the
-    // computation, the clearing is confirmed an epoch after that, and more generations than that
-    // needs let the trailing warp lag without holding anybody up; every accumulator is a pair
-    // (sum, number of partial sums added).
-    const size_t gens = n_ranks > 1 ? 4 : kFlowGenerations;
-    const size_t per_acc = n_ranks > 1 ? 1 : 2;
+    // The accumulators of an epoch are cleared by a warp that trails the computation, and the
+    // clearing is confirmed some epochs after that; more generations than that needs let the
+    // trailing warps lag without holding anybody up.  Every accumulator is a pair (sum, number of
+    // partial sums added).
+    const size_t gens = kFlowGenerations;
+    const size_t per_acc = 2;
     if (pool_capacity_floats && gens * gen * per_acc > pool_capacity_floats) return cudaErrorNotSupported;
     // Pass 2: place the accumulators and the sums of squares (generation = epoch mod 3).
     int barriers = 1;   // the trailing one
@@ -1371,11 +993,12 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
         const uint32_t base = static_cast<uint32_t>((epoch_of[i].lo % gens) * gen);
         m.acc_off += base;
         if (m.flags & MOP_FUSED) m.ss_off += base + static_cast<uint32_t>(worst);
-        m.expect = static_cast<uint32_t>(m.K / 256);   // partial sums per row: one per box
+        // partial sums per row: one per box; summed over the ranks when they split K among them
+        m.expect = tp && tp[i].expect > 0 ? static_cast<uint32_t>(tp[i].expect) : static_cast<uint32_t>(m.K / 256);
         m.xexpect = 0;
         if (m.xacc_off >= 0) {
             const MegaOp& pr = table[m.xacc_off];      // earlier in the list: already placed
-            m.xexpect = static_cast<uint32_t>(pr.K / 256);
+            m.xexpect = pr.expect;
             m.xacc_off = static_cast<int32_t>(pr.acc_off + static_cast<uint32_t>(m.xss_k));
             m.xss_k = 0;
             if (pr.flags & MOP_FUSED) {
@@ -1389,44 +1012,6 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
         max_epoch_ops = run_ops > max_epoch_ops ? run_ops : max_epoch_ops;
     }
     plan->max_epoch_ops = max_epoch_ops;
-    plan->global_barriers = 0;
-    plan->local_barriers = 0;
-    if (n_ranks > 1) {
-        // Which barriers span all ranks.  The one that ends an epoch with results added into the
-        // peers' accumulators must (the sums are complete only when every rank is done).  And such
-        // an epoch p needs one in front of it no further back than the end of p - 2, where its
-        // accumulators are zeroed on every rank: so that no rank adds before every rank has zeroed.
-        // (Before the first two epochs that is the barrier that ended the previous launch.)
-        const int n_epochs = epoch + 1;
-        // per epoch: has peers; barrier in front is global.  Kept in epoch_of[].hi of the first op.
-        int first_op_of_epoch = 0, prev_global_at = -1000;   // prev_global_at: last epoch e with a global barrier in front
-        bool prev_epoch_peers = false;
-        int e_cur = 0;
-        for (int i = 0; i <= n_ops; ++i) {
-            const bool boundary = i == n_ops || (i > 0 && (table[i].flags & MOP_BARRIER));
-            if (!boundary) continue;
-            // close epoch e_cur = [first_op_of_epoch, i)
-            bool peers = false;
-            for (int k = first_op_of_epoch; k < i; ++k) peers = peers || (table[k].flags & MOP_PEERS);
-            bool global_front = e_cur > 0 && prev_epoch_peers;
-            if (e_cur == 0) prev_global_at = 0;               // the previous launch ended with one
-            if (global_front) prev_global_at = e_cur;
-            if (peers && e_cur - prev_global_at > 1 && e_cur > 0) { global_front = true; prev_global_at = e_cur; }
-            if (e_cur > 0) {
-                if (global_front) table[first_op_of_epoch].flags |= MOP_GBARRIER;
-                const int rounds = (table[first_op_of_epoch].flags & MOP_BARRIER2) ? 2 : 1;
-                (global_front ? plan->global_barriers : plan->local_barriers) += rounds;
-                // an empty epoch (second round) sits between: it neither adds nor zeroes anything new
-            }
-            prev_epoch_peers = peers;
-            if (i < n_ops) {
-                e_cur = static_cast<int>(epoch_of[i].lo);
-                first_op_of_epoch = i;
-            }
-        }
-        (void)n_epochs;
-        plan->global_barriers += 2;     // the two trailing barriers
-    }
     for (int i = 0; i < n_ops;) {          // phases: runs that share their staged input, at most kMaxPhaseOps long
         int e = i + 1;
         while (e < n_ops && e - i < kMaxPhaseOps && !(table[e].flags & (MOP_BARRIER | MOP_RESTAGE))) ++e;
@@ -1435,9 +1020,9 @@ cudaError_t plan_decode(const GemvQArgs* ops, const DecodeTpOp* tp, int n_ops, D
     }
     plan->n_ops = n_ops;
     plan->epochs = barriers;
-    // one GPU: each of a CTA's housekeeping warps arrives on its own counter for every kKeeperWarps-th
-    // epoch, and once more at the end
-    plan->barriers = n_ranks > 1 ? barriers : (barriers + kKeeperWarps) / kKeeperWarps;
+    // each of a CTA's housekeeping warps arrives on its own counter for every kKeeperWarps-th epoch and
+    // once more at the end; tensor parallel: and a last time, so that no rank leaves early
+    plan->barriers = (barriers + kKeeperWarps) / kKeeperWarps + (n_ranks > 1 ? 1 : 0);
     plan->pool_floats = gens * gen * per_acc;
     return cudaSuccess;
 }
@@ -1467,33 +1052,25 @@ cudaError_t launch_decode(const MegaOp* host_ops, const DecodePlan& plan, const 
         }
     }
     const int optin = env.smem_optin > 0 ? env.smem_optin : 232448;
-    const bool flow = dev.n_ranks == 1;
     DecodeParams p;
     std::memset(&p, 0, sizeof(p));
     p.ops = dev.ops; p.maps = dev.maps; p.n_ops = n_ops; p.pool = dev.pool;
     p.counter = dev.counter; p.base = dev.base; p.err = env.err_word;
-    p.local_counter = dev.local_counter; p.local_base = dev.local_base;
     p.n_ranks = dev.n_ranks; p.rank = dev.rank;
     p.n_phases = n_phases;
     p.n_epochs = plan.epochs;
     p.inv_grid = static_cast<uint32_t>(((1ull << 32) + grid - 1) / grid);
     for (int r = 0; r < dev.n_ranks; ++r) { p.peer_pool[r] = dev.peer_pool[r]; p.peer_counter[r] = dev.peer_counter[r]; }
-    int off;
-    if (flow) {
-        off = 16 * kDecodeMaxSlots + 128 + 64;   // full / empty barriers, scratch, control words (16 ints)
-        p.off_desc = off;
-        off += 8 * kDecodeMaxSlots;
-        p.off_phases = off;
-        off += align_up(n_phases * static_cast<int>(sizeof(PhaseRec)), 16);
-        p.off_epochs = off;
-        off += align_up((plan.epochs + 1) * 2, 16);
-        p.off_jscale = off;
-        p.jscale_cap = plan.max_epoch_ops < 256 ? plan.max_epoch_ops : 256;
-        off += align_up(kKeeperWarps * p.jscale_cap * 4, 16);
-    } else {
-        off = 8 * kMaxStreamWarps * 4 + 8 * kMaxStreamWarps + 16;   // barriers, scratch, abort flag
-        off = align_up(off, 16);
-    }
+    int off = 16 * kDecodeMaxSlots + 128 + 64;   // full / empty barriers, scratch, control words (16 ints)
+    p.off_desc = off;
+    off += 8 * kDecodeMaxSlots;
+    p.off_phases = off;
+    off += align_up(n_phases * static_cast<int>(sizeof(PhaseRec)), 16);
+    p.off_epochs = off;
+    off += align_up((plan.epochs + 1) * 2, 16);
+    p.off_jscale = off;
+    p.jscale_cap = plan.max_epoch_ops < 256 ? plan.max_epoch_ops : 256;
+    off += align_up(kKeeperWarps * p.jscale_cap * 4, 16);
     p.off_sx = off;
     off += align_up((k_max / 32) * 8, 16);
     off = align_up(off, 128);
@@ -1515,9 +1092,6 @@ cudaError_t launch_decode(const MegaOp* host_ops, const DecodePlan& plan, const 
     p.ns = ns;
     const size_t smem = static_cast<size_t>(off) + static_cast<size_t>(warps) * ns * kBoxBytes;
     void* args[] = {&p};
-    if (!flow)
-        return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(tpk::decode_q4_tp_kernel), dim3(grid),
-                                           dim3(warps * 32), args, smem, stream);
     // `warps` consumer warps, the producer warps and the housekeeping warps
     return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(decode_q4_kernel), dim3(grid),
                                        dim3((warps + kProducerWarps + kKeeperWarps) * 32), args, smem, stream);
@@ -1632,8 +1206,6 @@ cudaError_t launch_gemv_q4_decode_static(const GemvQArgs* ops, int n_ops, const 
     dev.pool = reinterpret_cast<float*>(scratch + kStaticPoolOffset);
     dev.counter = reinterpret_cast<unsigned long long*>(scratch);
     dev.base = 0;
-    dev.local_counter = dev.counter + 16;     // the second arrival counter, in the same 256 bytes
-    dev.local_base = 0;
     return launch_decode(table, plan, dev, env, stream);
 }
 

@@ -87,7 +87,6 @@ enum : uint32_t {
     MOP_XACC_F16 = 32u, // activations taken from accumulators are rounded to fp16 first
     MOP_PEERS = 64u,    // partial sums are added into every rank's accumulators (tensor parallel)
     MOP_BARRIER2 = 128u, // with MOP_BARRIER: two barriers, i.e. one empty epoch, before this operation
-    MOP_GBARRIER = 512u, // tensor parallel: the barrier(s) before this operation span all ranks (else only this rank's grid)
 };
 constexpr int kDecodeMaxRanks = 8;
 struct DecodeParams {
@@ -97,8 +96,6 @@ struct DecodeParams {
     float* pool;                    // device memory: fp32 accumulators, all zero between launches
     unsigned long long* counter;    // device memory: grid-barrier arrival counter, never reset
     unsigned long long base;        // counter value all earlier launches add up to
-    unsigned long long* local_counter;  // tensor parallel: counter of the barriers that span this rank only
-    unsigned long long local_base;
     uint32_t* err;
     int ns;
     int off_sx, off_x, off_ring;
@@ -135,15 +132,14 @@ struct DecodePlan {
     int max_epoch_ops = 0;     // operations of the longest epoch
     int epochs = 0;            // epochs of the table (runs of operations between two barriers), empty ones included
     int barriers = 0;          // arrivals of one CTA on the arrival counter during a single-GPU launch
-    int global_barriers = 0;   // tensor parallel: how many of the launch's barriers span all ranks (the two
-                               // trailing ones included); the other barriers - local_barriers - span one rank
-    int local_barriers = 0;
     size_t pool_floats = 0;    // accumulator pool the table addresses
 };
 // Tensor-parallel extras of one operation (all zero on one GPU).
 struct DecodeTpOp {
     int peers = 0;             // add the partial sums into every rank's accumulators
     int y_row0 = 0, y_rows = 0;   // placement of the N rows inside a longer gathered vector
+    int expect = 0;            // partial sums that complete a row of the result, over all ranks (0 = K / 256):
+                               // ranks that split K among them each add K_rank / 256 per row
     int layout_rows = 0;       // accumulators reserved for this result (>= its rows; 0 = its rows): the
                                // same value on every rank keeps the pool layout identical across ranks
                                // when their row shards differ in size
@@ -165,25 +161,16 @@ struct DecodeDevice {
     float* pool = nullptr;
     unsigned long long* counter = nullptr;
     unsigned long long base = 0;
-    unsigned long long* local_counter = nullptr;
-    unsigned long long local_base = 0;
     int n_ranks = 1, rank = 0;
     float* peer_pool[kDecodeMaxRanks] = {};
     unsigned long long* peer_counter[kDecodeMaxRanks] = {};
 };
-// What a completed launch has added to the site's arrival counters.  One GPU: every housekeeping
-// warp of a CTA arrives plan.barriers times on a counter of its own (they sit 32 bytes apart in
-// the counter allocation and share one base).  Tensor parallel: the barriers that span all ranks,
-// and those that span one rank.
-inline void decode_advance(const DecodePlan& plan, int sm_count, int n_ranks, unsigned long long* base,
-                           unsigned long long* local_base) {
-    const unsigned long long g = static_cast<unsigned long long>(sm_count);
-    if (n_ranks > 1) {
-        *base += static_cast<unsigned long long>(plan.global_barriers) * g * static_cast<unsigned long long>(n_ranks);
-        *local_base += static_cast<unsigned long long>(plan.local_barriers) * g;
-    } else {
-        *base += static_cast<unsigned long long>(plan.barriers) * g;
-    }
+// What a completed launch has added to the site's arrival counters: every housekeeping warp of a
+// CTA arrives plan.barriers times on a counter of its own (they sit 32 bytes apart in the counter
+// allocation and share one base); tensor parallel: on that counter of every rank.
+inline void decode_advance(const DecodePlan& plan, int sm_count, int n_ranks, unsigned long long* base) {
+    *base += static_cast<unsigned long long>(plan.barriers) * static_cast<unsigned long long>(sm_count) *
+             static_cast<unsigned long long>(n_ranks > 1 ? n_ranks : 1);
 }
 // Launches the table (already uploaded to dev.ops with its tensor maps in dev.maps).
 // cudaErrorNotSupported when the list does not fit the kernel's shared memory.

@@ -96,7 +96,6 @@ struct DecodeSite {
     size_t pool_floats = 0;
     unsigned long long* counter = nullptr;   // grid-barrier arrival counter
     unsigned long long base = 0;             // what all earlier launches add up to
-    unsigned long long local_base = 0;       // the same for the rank-local barriers of tensor-parallel launches
     int uploaded = 0;                        // table entries currently valid on the device
     tcb::DecodePlan plan;
     // tensor parallel (tcx_stream_tp_export / _connect): the other ranks' pools and counters,
@@ -692,7 +691,6 @@ void reset_decode_site(DecodeSite& d) {
     if (d.counter) cudaMemset(d.counter, 0, kMegaFlagBytes);
     if (d.pool) cudaMemset(d.pool, 0, d.pool_floats * sizeof(float));
     d.base = 0;
-    d.local_base = 0;
 }
 
 bool alloc_decode_site_tables(DecodeSite& d) {
@@ -730,10 +728,9 @@ cudaError_t submit_as_persistent_launch(tc_stream* s, int* launches, const char*
     if (replay) {
         tcb::DecodeDevice dev;
         dev.ops = d.dev; dev.maps = d.maps_dev; dev.pool = d.pool; dev.counter = d.counter; dev.base = d.base;
-        dev.local_counter = d.counter + 16; dev.local_base = d.local_base;
         e = tcb::launch_decode(d.host, d.plan, dev, make_env(ctx, false), s->s);
         if (e == cudaSuccess) {
-            tcb::decode_advance(d.plan, ctx->sm_count, 1, &d.base, &d.local_base);
+            tcb::decode_advance(d.plan, ctx->sm_count, 1, &d.base);
             *launches += 1;
             *name = "q4_0_decode_persistent_sm100";
             return e;
@@ -790,12 +787,11 @@ cudaError_t submit_as_persistent_launch(tc_stream* s, int* launches, const char*
     d.plan = plan;
     tcb::DecodeDevice dev;
     dev.ops = d.dev; dev.maps = d.maps_dev; dev.pool = d.pool; dev.counter = d.counter; dev.base = d.base;
-    dev.local_counter = d.counter + 16; dev.local_base = d.local_base;
     e = tcb::launch_decode(d.host, plan, dev, make_env(ctx, false), s->s);
     if (e == cudaErrorCooperativeLaunchTooLarge) { (void)cudaGetLastError(); return cudaErrorNotSupported; }
     if (e == cudaErrorNotSupported) return e;
     if (e == cudaSuccess) {
-        tcb::decode_advance(plan, ctx->sm_count, 1, &d.base, &d.local_base);
+        tcb::decode_advance(plan, ctx->sm_count, 1, &d.base);
         *launches += 1;
         *name = "q4_0_decode_persistent_sm100";
         s->planned = s->args;
@@ -996,6 +992,7 @@ extern "C" tc_status_t tcx_stream_decode_tp(tc_stream* s, const tcx_decode_tp_op
         tcb::DecodeTpOp t;
         t.peers = ops[i].peers != 0 && d.n_ranks > 1;
         t.y_row0 = ops[i].y_row0; t.y_rows = ops[i].y_rows; t.layout_rows = ops[i].layout_rows;
+        t.expect = ops[i].expect;
         d.tp_ops[i] = t;
     }
     cudaError_t e = cudaSuccess;
@@ -1026,13 +1023,11 @@ extern "C" tc_status_t tcx_stream_decode_tp(tc_stream* s, const tcx_decode_tp_op
     tcb::DecodeDevice dev;
     dev.ops = d.dev; dev.maps = d.maps_dev; dev.pool = d.pool; dev.counter = d.counter; dev.base = d.base;
     dev.n_ranks = d.n_ranks; dev.rank = d.rank;
-    dev.local_counter = d.counter + 16;      // the second half of the 256-byte counter allocation
-    dev.local_base = d.local_base;
     for (int r = 0; r < d.n_ranks; ++r) { dev.peer_pool[r] = d.peer_pool[r]; dev.peer_counter[r] = d.peer_counter[r]; }
     e = tcb::launch_decode(d.host, d.plan, dev, make_env(ctx, false), s->s);
     if (e == cudaErrorNotSupported || e == cudaErrorCooperativeLaunchTooLarge) { (void)cudaGetLastError(); return TC_ERR_INVALID_SHAPE; }
     if (e == cudaSuccess) {
-        tcb::decode_advance(d.plan, ctx->sm_count, d.n_ranks, &d.base, &d.local_base);
+        tcb::decode_advance(d.plan, ctx->sm_count, d.n_ranks, &d.base);
         g_launches.fetch_add(1);
         t_last_kernel = d.n_ranks > 1 ? "q4_0_decode_persistent_tp_sm100" : "q4_0_decode_persistent_sm100";
     }

@@ -277,9 +277,9 @@ class TPLink:
     Every fused decoder of the process launches on it (the kernel's table is re-planned when the
     operation list changes; pool and counter carry over)."""
 
-    def __init__(self, ctx, dist, world: int, rank: int, pool_floats: int = 3 << 20):
+    def __init__(self, ctx, dist, world: int, rank: int, pool_floats: int = 4 << 20):
         import tensorcore_b200 as tc
-        self.world, self.rank = world, rank
+        self.world, self.rank, self.dist = world, rank, dist
         self.stream = ctx.stream()
         record = tc.stream_tp_export(self.stream, pool_floats)
         if world > 1:
@@ -296,6 +296,7 @@ class FusedBackend(CudaBackend):
         super().__init__(ctx, shape, fmt, device)
         self.world, self.rank = link.world, link.rank
         self.ops = []
+        self.link = link
         self.stream = link.stream
         self.arr = None
 
@@ -316,7 +317,9 @@ class FusedBackend(CudaBackend):
         raise ValueError("no recorded operation produced this vector")
 
     def all_reduce(self, vec):
-        self._producer(vec.data_ptr())["peers"] = 1
+        op = self._producer(vec.data_ptr())
+        op["peers"] = 1
+        op["sum"] = True          # every rank adds its K range's partial sums to all rows
         self.collectives += 1
 
     def all_gather(self, dst, src):
@@ -326,6 +329,14 @@ class FusedBackend(CudaBackend):
         self.collectives += 1
 
     def commit(self) -> None:
+        # A summed result is complete when the partial sums of every rank's K range have arrived:
+        # one per 256 input elements and row, so the ranks add up their counts once, here.
+        sums = [op for op in self.ops if op.get("sum")]
+        if sums and self.world > 1:
+            counts = self.torch.tensor([op["K"] // 256 for op in sums], dtype=self.torch.int64, device=self.device)
+            self.link.dist.all_reduce(counts)
+            for op, c in zip(sums, counts.tolist()):
+                op["expect"] = int(c)
         self.arr = self.tc.make_decode_tp_ops(self.ops)
 
     def run(self) -> None:

@@ -68,6 +68,9 @@ __device__ __forceinline__ void arrive_gpu(unsigned long long* p) {
 __device__ __forceinline__ void arrive_sys(unsigned long long* p) {
     asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(1ULL) : "memory");
 }
+__device__ __forceinline__ void arrive_relaxed_sys(unsigned long long* p) {
+    asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(1ULL) : "memory");
+}
 __device__ __forceinline__ unsigned long long poll_gpu(const unsigned long long* p) {
     unsigned long long v;
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -504,7 +507,10 @@ __device__ void keep_house(const DecodeParams& p, const MegaOp* ops, const uint1
     // before it has cleared them.
     auto arrive = [&]() {
         if (multi) {
-            for (int r = 0; r < p.n_ranks; ++r) arrive_sys(p.peer_counter[r] + 4 * jp);
+            // one fence for all ranks' counters (a release per counter would wait for the system-wide
+            // fence once per rank)
+            __threadfence_system();
+            for (int r = 0; r < p.n_ranks; ++r) arrive_relaxed_sys(p.peer_counter[r] + 4 * jp);
         } else {
             arrive_gpu(counter);
         }

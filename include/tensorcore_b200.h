@@ -389,23 +389,24 @@ tc_status_t tcx_raw_fused_norm_gemv_f16(tc_context* ctx, const void* X, const vo
  * qualifying tc_stream list, but for callers that cannot tolerate an allocation on this path:
  * a server whose HBM is fully handed out to weights and KV cache at start-up, or a decode loop
  * where cudaMalloc's device-wide synchronisation must never occur.  The kernel's scratch (the
- * grid-barrier counter, the operation table, one TMA tensor map per operation and the fp32
- * accumulators the results are summed in) lives in a fixed 1,972 KB device array inside the
- * library image, which every GPU that loads the library holds until the process exits; the call
- * performs no cudaMalloc / cudaFree and uses no allocating library routine.
+ * arrival counters, the operation table, one TMA tensor map per operation and the accumulators
+ * the results are summed in) lives in a fixed 13,112 KB device array inside the library image,
+ * which every GPU that loads the library holds until the process exits; the call performs no
+ * cudaMalloc / cudaFree and uses no allocating library routine.
  *
  *  - `ops`: host array of `n_ops` operations in execution order; all pointers inside are device
  *    addresses owned by the caller (inputs and outputs as for tcx_raw_gemv_quantized with M = 1;
  *    gamma != NULL adds the RMSNorm prologue).  K must be a multiple of 256, pointers 16-byte
  *    aligned.  Dependencies between operations are derived from pointer overlap.
  *  - Limits: n_ops <= TCX_DECODE_STATIC_MAX_OPS (256) and a list whose accumulators fit the
- *    array (491,520 floats; a list needs three times the result rows of its widest group of
- *    operations that run side by side, e.g. 3 x 128,256 for a 128k-row output projection);
- *    beyond either the call returns TC_ERR_INVALID_SHAPE and launches nothing, as it does for
- *    a list whose activations do not fit the kernel's shared memory.
+ *    array: the widest group of operations that run side by side may have 139,264 result rows
+ *    together (a 128k-row output projection fits; the array holds twelve generations of
+ *    (sum, count) pairs of that many rows); beyond either the call returns TC_ERR_INVALID_SHAPE
+ *    and launches nothing, as it does for a list whose activations do not fit the kernel's
+ *    shared memory.
  *  - The first call on a device looks up the array's device address; make that first call before
  *    starting any stream capture.
- *  - All calls on a device share the one array: the call clears the counter and overwrites the
+ *  - All calls on a device share the one array: the call clears the counters and overwrites the
  *    table itself, but two calls that overlap in time on the GPU (different streams) race.  The
  *    host-side bookkeeping (one record per device) is guarded by a mutex, so calls from several
  *    threads are safe as long as their launches do not overlap on one GPU.
@@ -428,16 +429,20 @@ tc_status_t tcx_raw_decode_q4_static(tc_context* ctx, const tcx_decode_op* ops, 
  * One process per GPU.  Every rank records the SAME list of operations on its own shard of the
  * weights: projections split by output rows (q/k/v, gate/up, lm_head) compute their own rows;
  * projections split along K (o_proj, down_proj) compute partial sums over their K range.  An
- * operation marked `peers` adds its results into the accumulators of EVERY rank inside the
- * persistent decode kernel, with red.global.add over NVLink peer memory - that is the all-reduce
- * of a K-split projection and, with `y_row0` / `y_rows` placing a rank's rows inside a longer
- * vector, the all-gather of a row-split one.  The kernel's grid barriers span all ranks (every
- * CTA arrives on every rank's counter), waits are bounded as everywhere else, and no collective
- * library is involved.  A whole token is one launch per rank.
+ * operation marked `peers` adds its partial sums into the accumulators of EVERY rank inside the
+ * persistent decode kernel, with vector reductions over NVLink peer memory that carry the sum and
+ * a count - that is the all-reduce of a K-split projection and, with `y_row0` / `y_rows` placing
+ * a rank's rows inside a longer vector, the all-gather of a row-split one.  The next operation
+ * starts on a rank as soon as the counts of its input rows say that every rank's partial sums are
+ * there: no barrier lies between two operations.  (An arrival counter that spans all ranks trails
+ * the computation by a few operations and tells when accumulators may be reused; its waits are
+ * bounded as everywhere else.)  No collective library is involved.  A whole token is one launch
+ * per rank.
  *
  *  1. every rank: tcx_stream_tp_export(stream, pool_floats, handles) - allocates the stream's
- *     accumulator pool (pool_floats must cover the list, see plan sizes in DESIGN.md; 1 Mi floats
- *     covers the 70B shapes) and barrier counter and writes two CUDA IPC handles (128 bytes);
+ *     accumulator pool (24 floats per result row of the widest group of operations that run
+ *     side by side; 4 Mi floats cover the 70B shapes) and arrival counters and writes two CUDA IPC
+ *     handles (128 bytes);
  *  2. exchange the 128-byte records among the ranks by any host channel, in rank order;
  *  3. every rank: tcx_stream_tp_connect(stream, n_ranks, rank, all_records);
  *  4. per token, every rank: tcx_stream_decode_tp(stream, ops, n_ops) then tc_stream_sync(stream).

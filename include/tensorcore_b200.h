@@ -309,6 +309,30 @@ typedef struct {
 tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* desc, const tc_buffer* A, const tc_buffer* B,
                     tc_buffer* C);
 
+/* include/tensorcore/attention.h:24-69 (arithmetic: lib/ops/attention_cpu.cpp:131-277).  fp16 Q
+ * [batch, heads, seq_q, head_dim], K and V [batch, kv_heads, seq_kv, head_dim], O like Q, optional
+ * fp32 LSE [batch, heads, seq_q]; softmax in fp32.  Causal mask (key index > query index), sliding
+ * window, ALiBi and grouped-query heads as in the reference.  Here: the forward pass as a
+ * streaming kernel per query row - the attention of a decode step (seq_q of one or a few rows over
+ * a long K/V cache); head_dim <= 128 (TC_ERR_INVALID_SHAPE above).  The recorded form runs at once,
+ * as the reference's CPU backend does.  tc_attention_backward stays a placeholder. */
+typedef struct {
+    int32_t batch, heads, seq_q, seq_kv, head_dim;
+    tc_dtype_t io_dtype;      /* TC_DTYPE_F16 */
+    tc_dtype_t accum_dtype;   /* TC_DTYPE_F32 */
+    float softmax_scale;      /* <= 0: 1 / sqrt(head_dim) */
+    bool causal;
+    bool return_lse;
+    int32_t kv_heads;         /* 0: heads */
+    int32_t window_size;      /* 0: none */
+    const float* alibi_slopes; /* host array of `heads` floats, or NULL */
+} tc_attention_desc;
+tc_status_t tc_attention_forward(tc_context* ctx, const tc_attention_desc* desc, const tc_buffer* Q,
+                                 const tc_buffer* K, const tc_buffer* V, tc_buffer* O, tc_buffer* LSE);
+tc_status_t tc_attention_forward_async(tc_context* ctx, const tc_attention_desc* desc, const tc_buffer* Q,
+                                       const tc_buffer* K, const tc_buffer* V, tc_buffer* O, tc_buffer* LSE,
+                                       tc_stream* stream);
+
 /* --- collectives (include/tensorcore/distributed.h:30-87; the reference implements them as a TCP
  * ring between hosts, lib/distributed/distributed_cpu.cpp:202-347).  Here: NCCL between one
  * process per GPU, on device buffers.  TC_DIST_RING and TC_DIST_GLOO both select it; the

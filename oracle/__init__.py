@@ -207,6 +207,24 @@ def rope_forward(X_f16, cos_t, sin_t):
     return X.view(np.float16)
 
 
+def attention_forward(Q_f16, K_f16, V_f16, softmax_scale=0.0, causal=True, window=0, alibi_slopes=None,
+                      return_lse=False, dot_order=1):
+    """Q [B,Hq,Sq,D], K/V [B,Hkv,Sk,D] fp16 -> O [B,Hq,Sq,D] fp16 (and LSE [B,Hq,Sq] fp32).
+    dot_order 1 is the order of the reference's AVX2 dot product, 0 that of its scalar one."""
+    Q = np.ascontiguousarray(Q_f16).view(np.uint16)
+    K = np.ascontiguousarray(K_f16).view(np.uint16)
+    V = np.ascontiguousarray(V_f16).view(np.uint16)
+    B, Hq, Sq, D = Q.shape
+    _, Hkv, Sk, _ = K.shape
+    O = np.empty((B, Hq, Sq, D), np.uint16)
+    L = np.empty((B, Hq, Sq), np.float32) if return_lse else None
+    sl = None if alibi_slopes is None else np.ascontiguousarray(alibi_slopes, dtype=np.float32)
+    _call(lib().orc_attention_forward, _p(Q), _p(K), _p(V), _p(O), _p(L) if L is not None else None,
+          c_int(B), c_int(Hq), c_int(Hkv), c_int(Sq), c_int(Sk), c_int(D), c_float(softmax_scale),
+          c_int(1 if causal else 0), c_int(window), _p(sl) if sl is not None else None, c_int(dot_order))
+    return (O.view(np.float16), L) if return_lse else O.view(np.float16)
+
+
 def dequant_dot_f64(X: np.ndarray, Wq: np.ndarray, fmt: int, N: int) -> np.ndarray:
     X = np.ascontiguousarray(X, dtype=np.float64)
     M, K = X.shape
@@ -409,6 +427,39 @@ class RefLib:
         out = self._read(px, nx, np.uint16).reshape(B, H, S, D).view(np.float16)
         self._free(hx, hc, hs)
         return out
+
+
+    def attention_forward(self, Q_f16, K_f16, V_f16, softmax_scale=0.0, causal=True, window=0,
+                          alibi_slopes=None, return_lse=False):
+        import ctypes
+
+        class Desc(ctypes.Structure):     # include/tensorcore/attention.h:24-52
+            _fields_ = [("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("seq_q", ctypes.c_int32),
+                        ("seq_kv", ctypes.c_int32), ("head_dim", ctypes.c_int32), ("io_dtype", ctypes.c_int),
+                        ("accum_dtype", ctypes.c_int), ("softmax_scale", ctypes.c_float), ("causal", ctypes.c_bool),
+                        ("return_lse", ctypes.c_bool), ("kv_heads", ctypes.c_int32), ("window_size", ctypes.c_int32),
+                        ("alibi_slopes", ctypes.c_void_p)]
+
+        Q = np.ascontiguousarray(Q_f16).view(np.uint16)
+        K = np.ascontiguousarray(K_f16).view(np.uint16)
+        V = np.ascontiguousarray(V_f16).view(np.uint16)
+        B, Hq, Sq, D = Q.shape
+        _, Hkv, Sk, _ = K.shape
+        sl = None if alibi_slopes is None else np.ascontiguousarray(alibi_slopes, dtype=np.float32)
+        d = Desc(B, Hq, Sq, Sk, D, 0, 2, softmax_scale, bool(causal), bool(return_lse), Hkv, window,
+                 sl.ctypes.data if sl is not None else None)
+        self.L.tc_attention_forward.argtypes = [c_void_p] * 7
+        hq, _, _ = self._buf(Q)
+        hk, _, _ = self._buf(K)
+        hv, _, _ = self._buf(V)
+        ho, po, no = self._buf(Q.size * 2)
+        hl, pl, nl = self._buf(B * Hq * Sq * 4) if return_lse else (None, None, 0)
+        st = self.L.tc_attention_forward(self.ctx, ctypes.byref(d), hq, hk, hv, ho, hl)
+        assert st == 0, st
+        out = self._read(po, no, np.uint16).reshape(B, Hq, Sq, D).view(np.float16)
+        lse = self._read(pl, nl, np.float32).reshape(B, Hq, Sq) if return_lse else None
+        self._free(hq, hk, hv, ho, *( [hl] if hl else []))
+        return (out, lse) if return_lse else out
 
 
 def ref_available() -> bool:

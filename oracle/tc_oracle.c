@@ -395,6 +395,93 @@ int orc_rope_forward(uint16_t* X, const float* cos_t, const float* sin_t, int ba
     return 0;
 }
 
+/* lib/ops/attention_cpu.cpp:62-83 (dot_order 1: eight running sums updated with fused multiply-adds,
+ * then folded 8 -> 4 -> 2 -> 1, the tail added element by element) and :100-106 (dot_order 0: one
+ * running sum, multiply then add).  The reference picks the first on x86 CPUs with AVX2, F16C and FMA. */
+static float attn_dot(const uint16_t* a, const uint16_t* b, int n, int dot_order) {
+    if (dot_order == 0) {
+        float acc = 0.0f;
+        for (int i = 0; i < n; ++i) acc += orc_f16_to_f32(a[i]) * orc_f16_to_f32(b[i]);
+        return acc;
+    }
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int i = 0;
+    for (; i + 7 < n; i += 8)
+        for (int k = 0; k < 8; ++k) acc[k] = fmaf(orc_f16_to_f32(a[i + k]), orc_f16_to_f32(b[i + k]), acc[k]);
+    float s4[4];
+    for (int k = 0; k < 4; ++k) s4[k] = acc[k] + acc[k + 4];
+    const float s2a = s4[0] + s4[2], s2b = s4[1] + s4[3];
+    float result = s2a + s2b;
+    for (; i < n; ++i) result += orc_f16_to_f32(a[i]) * orc_f16_to_f32(b[i]);
+    return result;
+}
+
+/* lib/ops/attention_cpu.cpp:131-277: Q [B,Hq,Sq,D], K/V [B,Hkv,Sk,D], O [B,Hq,Sq,D] fp16, LSE
+ * [B,Hq,Sq] fp32 or NULL.  Tiles of 32 query rows x 32 keys with a running maximum, denominator and
+ * unnormalised output per row (:57-58, :185-255); mask order causal, window, then ALiBi (:203-214). */
+int orc_attention_forward(const uint16_t* Q, const uint16_t* K, const uint16_t* V, uint16_t* O, float* LSE,
+                          int B, int Hq, int Hkv, int Sq, int Sk, int D, float softmax_scale, int causal,
+                          int window, const float* alibi_slopes, int dot_order) {
+    if (!Q || !K || !V || !O || B <= 0 || Hq <= 0 || Sq <= 0 || Sk <= 0 || D <= 0) return -1;
+    if (Hkv <= 0) Hkv = Hq;
+    if (Hq % Hkv != 0) return -1;
+    enum { BR = 32, BC = 32 };
+    const int per = Hq / Hkv;
+    const float scale = softmax_scale > 0 ? softmax_scale : 1.0f / sqrtf((float)D);
+    float* o_state = (float*)malloc(sizeof(float) * BR * (size_t)D);
+    if (!o_state) return -2;
+    float m_state[BR], l_state[BR], s_tile[BR * BC];
+    for (long bh = 0; bh < (long)B * Hq; ++bh) {
+        const int b = (int)(bh / Hq), h = (int)(bh % Hq), hkv = h / per;
+        const uint16_t* Qbh = Q + ((size_t)b * Hq + h) * Sq * D;
+        const uint16_t* Kbh = K + ((size_t)b * Hkv + hkv) * Sk * D;
+        const uint16_t* Vbh = V + ((size_t)b * Hkv + hkv) * Sk * D;
+        uint16_t* Obh = O + ((size_t)b * Hq + h) * Sq * D;
+        float* Lbh = LSE ? LSE + ((size_t)b * Hq + h) * Sq : NULL;
+        for (int qb = 0; qb < Sq; qb += BR) {
+            const int br = Sq - qb < BR ? Sq - qb : BR;
+            for (int r = 0; r < br; ++r) { m_state[r] = -INFINITY; l_state[r] = 0.0f; }
+            memset(o_state, 0, sizeof(float) * (size_t)br * D);
+            for (int kb = 0; kb < Sk; kb += BC) {
+                const int bc = Sk - kb < BC ? Sk - kb : BC;
+                for (int r = 0; r < br; ++r)
+                    for (int cidx = 0; cidx < bc; ++cidx) {
+                        float sc = attn_dot(Qbh + (size_t)(qb + r) * D, Kbh + (size_t)(kb + cidx) * D, D, dot_order) * scale;
+                        if (causal && (kb + cidx) > (qb + r)) sc = -INFINITY;
+                        if (window > 0 && (qb + r) - (kb + cidx) > window) sc = -INFINITY;
+                        if (alibi_slopes) sc -= alibi_slopes[h] * (float)((qb + r) - (kb + cidx));
+                        s_tile[r * BC + cidx] = sc;
+                    }
+                for (int r = 0; r < br; ++r) {
+                    float m_new = m_state[r];
+                    for (int cidx = 0; cidx < bc; ++cidx)
+                        if (s_tile[r * BC + cidx] > m_new) m_new = s_tile[r * BC + cidx];
+                    if (!isfinite(m_new)) m_new = m_state[r];
+                    const float scale_old = (m_state[r] == -INFINITY) ? 0.0f : expf(m_state[r] - m_new);
+                    float l_new = l_state[r] * scale_old;
+                    for (int d = 0; d < D; ++d) o_state[r * D + d] *= scale_old;
+                    for (int cidx = 0; cidx < bc; ++cidx) {
+                        const float p = expf(s_tile[r * BC + cidx] - m_new);
+                        if (!isfinite(p)) continue;
+                        l_new += p;
+                        const uint16_t* Vrow = Vbh + (size_t)(kb + cidx) * D;
+                        for (int d = 0; d < D; ++d) o_state[r * D + d] += p * orc_f16_to_f32(Vrow[d]);
+                    }
+                    m_state[r] = m_new;
+                    l_state[r] = l_new;
+                }
+            }
+            for (int r = 0; r < br; ++r) {
+                const float inv_l = l_state[r] != 0.0f ? 1.0f / l_state[r] : 0.0f;
+                for (int d = 0; d < D; ++d) Obh[(size_t)(qb + r) * D + d] = orc_f32_to_f16(o_state[r * D + d] * inv_l);
+                if (Lbh) Lbh[qb + r] = m_state[r] + logf(l_state[r] > 1e-30f ? l_state[r] : 1e-30f);
+            }
+        }
+    }
+    free(o_state);
+    return 0;
+}
+
 int orc_dequantize(const uint8_t* Wq, float* out, int fmt, int N, int K) {
     const unsigned bb = block_bytes(fmt);
     if (!Wq || !out || N <= 0 || K <= 0 || (K % 32) != 0 || bb == 0) return -1;

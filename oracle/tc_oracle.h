@@ -71,6 +71,9 @@ int orc_layernorm_forward(const uint16_t* X, const uint16_t* gamma, const uint16
 int orc_swiglu_forward(const uint16_t* gate, const uint16_t* up, uint16_t* out, int n);
 int orc_rope_forward(uint16_t* X, const float* cos_t, const float* sin_t, int batch, int heads,
                      int seq, int head_dim);
+int orc_attention_forward(const uint16_t* Q, const uint16_t* K, const uint16_t* V, uint16_t* O, float* LSE,
+                          int B, int Hq, int Hkv, int Sq, int Sk, int D, float softmax_scale, int causal,
+                          int window, const float* alibi_slopes, int dot_order);
 
 /* Double-precision dequantise-and-dot of the stored blocks against X given as double,
  * the yardstick of tests/test_quantized.c:48-94.  Y is [M,N] double. */

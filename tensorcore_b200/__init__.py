@@ -171,6 +171,8 @@ def _declare(L) -> None:
     sig("tc_layernorm_forward", i, vp, vp, vp, vp, vp, vp, vp, i, i, f)
     sig("tc_swiglu_forward", i, vp, vp, vp, vp, i)
     sig("tc_rope_forward", i, vp, vp, vp, vp, i, i, i, i)
+    sig("tc_attention_forward", i, vp, vp, vp, vp, vp, vp, vp)
+    sig("tc_attention_forward_async", i, vp, vp, vp, vp, vp, vp, vp, vp)
     # GGUF
     sig("tc_gguf_open", i, c_char_p, POINTER(vp))
     sig("tc_gguf_close", None, vp)
@@ -240,7 +242,7 @@ def _quant(fmt) -> int:
 
 def _dtype(d) -> int:
     if isinstance(d, str):
-        return {"f16": TC_DTYPE_F16, "f32": TC_DTYPE_F32}[d.lower()]
+        return {"f16": TC_DTYPE_F16, "bf16": TC_DTYPE_BF16, "f32": TC_DTYPE_F32}[d.lower()]
     return int(d)
 
 
@@ -472,6 +474,48 @@ def swiglu_forward(ctx, gate, up, out, n) -> None:
 def rope_forward(ctx, X, cos_t, sin_t, batch, heads, seq, head_dim) -> None:
     _check(lib().tc_rope_forward(_h(ctx), _h(X), _h(cos_t), _h(sin_t), int(batch), int(heads), int(seq),
                                  int(head_dim)))
+
+
+class TCAttentionDesc(Structure):     # tc_attention_desc
+    _fields_ = [("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("seq_q", ctypes.c_int32),
+                ("seq_kv", ctypes.c_int32), ("head_dim", ctypes.c_int32), ("io_dtype", c_int),
+                ("accum_dtype", c_int), ("softmax_scale", c_float), ("causal", ctypes.c_bool),
+                ("return_lse", ctypes.c_bool), ("kv_heads", ctypes.c_int32), ("window_size", ctypes.c_int32),
+                ("alibi_slopes", c_void_p)]
+
+
+def _attention_desc(batch, heads, seq_q, seq_kv, head_dim, dtype, accum, softmax_scale, causal, return_lse,
+                    kv_heads, window_size, alibi_slopes):
+    slopes = None
+    if alibi_slopes is not None:
+        slopes = (c_float * int(heads))(*[float(v) for v in alibi_slopes])
+    d = TCAttentionDesc(int(batch), int(heads), int(seq_q), int(seq_kv), int(head_dim), _dtype(dtype), _dtype(accum),
+                        float(softmax_scale or 0.0), bool(causal), bool(return_lse), int(kv_heads), int(window_size),
+                        ctypes.cast(slopes, c_void_p) if slopes is not None else None)
+    return d, slopes
+
+
+def attention_forward(ctx, Q, K, V, O, batch, heads, seq_q, seq_kv, head_dim, LSE=None, dtype="f16", accum="f32",
+                      softmax_scale=None, causal=True, return_lse=False, kv_heads=0, window_size=0,
+                      alibi_slopes=None) -> None:
+    """Scaled-dot-product attention forward (same arguments as the reference binding)."""
+    return_lse = bool(return_lse or LSE is not None)
+    desc, slopes = _attention_desc(batch, heads, seq_q, seq_kv, head_dim, dtype, accum, softmax_scale, causal,
+                                   return_lse, kv_heads, window_size, alibi_slopes)
+    _check(lib().tc_attention_forward(_h(ctx), byref(desc), _h(Q), _h(K), _h(V), _h(O),
+                                      _h(LSE) if LSE is not None else None))
+    _ = slopes
+
+
+def attention_forward_async(ctx, Q, K, V, O, batch, heads, seq_q, seq_kv, head_dim, stream, LSE=None, dtype="f16",
+                            accum="f32", softmax_scale=None, causal=True, return_lse=False, kv_heads=0,
+                            window_size=0, alibi_slopes=None) -> None:
+    return_lse = bool(return_lse or LSE is not None)
+    desc, slopes = _attention_desc(batch, heads, seq_q, seq_kv, head_dim, dtype, accum, softmax_scale, causal,
+                                   return_lse, kv_heads, window_size, alibi_slopes)
+    _check(lib().tc_attention_forward_async(_h(ctx), byref(desc), _h(Q), _h(K), _h(V), _h(O),
+                                            _h(LSE) if LSE is not None else None, _h(stream)))
+    _ = slopes
 
 
 def gemv_quantized_ex(ctx, X, W_quant, Y, fmt, M, N, K, x_dtype="f16", y_dtype="f16",

@@ -203,6 +203,16 @@ cudaError_t launch_rope(void* X, const float* cos_t, const float* sin_t, int bat
 cudaError_t launch_gemm_f16_rows(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
                                  int ldc, float alpha, float beta, cudaStream_t stream);
 
+// --- attention forward for decode (attention.cu); fp16 data, fp32 softmax ----------------------------
+// Floats of scratch the launch needs for (rows = B * Hq * Sq) query rows, and into how many key
+// chunks it will cut a row (1 = no scratch).
+size_t attention_scratch_floats(int rows, int Sk, int D, int sm_count, int* chunks_out);
+// cudaErrorNotSupported: head_dim above 128.  slopes_dev: ALiBi slopes on the device, or null.
+cudaError_t launch_attention_forward(const void* Q, const void* K, const void* V, void* O, float* LSE,
+                                     float* scratch, const float* slopes_dev, int B, int Hq, int Hkv, int Sq,
+                                     int Sk, int D, float scale, bool causal, int window, int sm_count,
+                                     cudaStream_t stream, int* launches);
+
 // --- collectives over NCCL (dist_nccl.cpp); return 0, or -1 bad arguments, -2 NCCL not found,
 // -3 rendezvous failed, -4 NCCL / CUDA error ----------------------------------------------------
 struct DistComm;

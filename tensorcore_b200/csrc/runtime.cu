@@ -51,6 +51,8 @@ struct tc_context {
     uint32_t* err_host;   // pinned, mapped
     uint32_t* err_dev;
     bool mega_on;         // route qualifying recorded lists to the persistent decode kernel
+    float* attn_scratch;  // partial softmax states of tc_attention_forward, grown on demand
+    size_t attn_scratch_floats;
 };
 
 struct tc_buffer {
@@ -266,6 +268,9 @@ tc_status_t setup_device(tc_context* ctx, int device) {
 void teardown_device(tc_context* ctx) {
     if (ctx->stream0) cudaStreamDestroy(ctx->stream0);
     if (ctx->err_host) cudaFreeHost(ctx->err_host);
+    if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
+    ctx->attn_scratch = nullptr;
+    ctx->attn_scratch_floats = 0;
     ctx->stream0 = nullptr;
     ctx->err_host = nullptr;
     ctx->err_dev = nullptr;
@@ -350,6 +355,8 @@ extern "C" tc_status_t tc_init(tc_context** out_ctx) {
     ctx->stream0 = nullptr;
     ctx->err_host = nullptr;
     ctx->err_dev = nullptr;
+    ctx->attn_scratch = nullptr;
+    ctx->attn_scratch_floats = 0;
     if (const char* v = std::getenv("TC_GEMV_VARIANT")) (void)tcx_set_gemv_variant(v);
     ctx->mega_on = env_flag("TC_MEGA", true);
     ctx->pdl = env_flag("TC_PDL", true);
@@ -1366,6 +1373,71 @@ extern "C" tc_status_t tc_rope_forward(tc_context* ctx, tc_buffer* X, const tc_b
         return tcb::launch_rope(X->dptr, static_cast<const float*>(cos_t->dptr),
                                 static_cast<const float*>(sin_t->dptr), batch, heads, seq, head_dim, st);
     });
+}
+
+// Attention forward for decode (include/tensorcore/attention.h:54-69; checks in the order of
+// lib/ops/attention_cpu.cpp:138-151).  Any seq_q is accepted, but the kernel is a streaming pass
+// per query row: it is meant for the one to few rows of a decode step.
+extern "C" tc_status_t tc_attention_forward(tc_context* ctx, const tc_attention_desc* d, const tc_buffer* Q,
+                                            const tc_buffer* K, const tc_buffer* V, tc_buffer* O, tc_buffer* LSE) {
+    if (!ctx) return TC_ERR_NOT_INITIALIZED;
+    if (!d || !Q || !K || !V || !O) return TC_ERR_INVALID_ARG;
+    if (d->batch <= 0 || d->heads <= 0 || d->seq_q <= 0 || d->seq_kv <= 0 || d->head_dim <= 0) return TC_ERR_INVALID_ARG;
+    if (d->io_dtype != TC_DTYPE_F16 || d->accum_dtype != TC_DTYPE_F32) return TC_ERR_UNSUPPORTED_DTYPE;
+    if (d->return_lse && !LSE) return TC_ERR_INVALID_ARG;
+    const int Hkv = d->kv_heads > 0 ? d->kv_heads : d->heads;
+    if (Hkv <= 0 || d->heads % Hkv != 0) return TC_ERR_INVALID_ARG;
+    if (d->head_dim > 128) return TC_ERR_INVALID_SHAPE;
+    const int B = d->batch, Hq = d->heads, Sq = d->seq_q, Sk = d->seq_kv, D = d->head_dim;
+    const float scale = d->softmax_scale > 0 ? d->softmax_scale : 1.0f / std::sqrt(static_cast<float>(D));
+    const size_t qb = static_cast<size_t>(B) * Hq * Sq * D * 2, kb = static_cast<size_t>(B) * Hkv * Sk * D * 2;
+    const size_t lb = static_cast<size_t>(B) * Hq * Sq * 4;
+    StepIo io[6] = {{mut(Q), qb, false}, {mut(K), kb, false}, {mut(V), kb, false}, {O, qb, true}, {LSE, lb, true}, {nullptr, 0, false}};
+    const int n_io = LSE ? 5 : 4;
+    bind_device(ctx);
+    // scratch for the partial softmax states of a row's key chunks, and the ALiBi slopes
+    int chunks = 1;
+    const long long rows = static_cast<long long>(B) * Hq * Sq;
+    if (rows > 0x7fffffffLL) return TC_ERR_INVALID_SHAPE;
+    size_t want = tcb::attention_scratch_floats(static_cast<int>(rows), Sk, D, ctx->sm_count, &chunks);
+    const size_t slope_at = want;
+    if (d->alibi_slopes) want += static_cast<size_t>(Hq);
+    if (want > ctx->attn_scratch_floats) {
+        cudaStreamSynchronize(ctx->stream0);
+        if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
+        ctx->attn_scratch = nullptr;
+        ctx->attn_scratch_floats = 0;
+        if (cudaMalloc(reinterpret_cast<void**>(&ctx->attn_scratch), want * sizeof(float)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return record("tc_attention_forward", TC_ERR_ALLOC);
+        }
+        ctx->attn_scratch_floats = want;
+    }
+    float* slopes_dev = nullptr;
+    if (d->alibi_slopes) {
+        slopes_dev = ctx->attn_scratch + slope_at;
+        // a small copy from caller memory: staged by the runtime before the call returns
+        if (cudaMemcpyAsync(slopes_dev, d->alibi_slopes, static_cast<size_t>(Hq) * sizeof(float),
+                            cudaMemcpyHostToDevice, ctx->stream0) != cudaSuccess)
+            return record("tc_attention_forward", TC_ERR_DISPATCH);
+    }
+    int launched = 0;
+    const tc_status_t st = run_step_op(ctx, "tc_attention_forward", "attention_decode_sm100", io, n_io, [&](cudaStream_t s0) {
+        return tcb::launch_attention_forward(Q->dptr, K->dptr, V->dptr, O->dptr,
+                                             LSE ? static_cast<float*>(LSE->dptr) : nullptr,
+                                             chunks > 1 ? ctx->attn_scratch : nullptr, slopes_dev, B, Hq, Hkv, Sq, Sk,
+                                             D, scale, d->causal, d->window_size, ctx->sm_count, s0, &launched);
+    });
+    if (launched > 1) g_launches.fetch_add(static_cast<uint64_t>(launched - 1));
+    return st;
+}
+
+// The recorded form runs at once, as the reference's CPU backend does (attention_cpu.cpp:280-291).
+extern "C" tc_status_t tc_attention_forward_async(tc_context* ctx, const tc_attention_desc* d, const tc_buffer* Q,
+                                                  const tc_buffer* K, const tc_buffer* V, tc_buffer* O,
+                                                  tc_buffer* LSE, tc_stream* stream) {
+    if (!stream) return TC_ERR_INVALID_ARG;
+    return tc_attention_forward(ctx, d, Q, K, V, O, LSE);
 }
 
 extern "C" tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* d, const tc_buffer* A,

@@ -12,8 +12,6 @@
 
 TCB_EXPORT int tc_adamw_step(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_attention_backward(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_attention_forward(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_attention_forward_async(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_buffer_demote_async(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_buffer_get_tier(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_buffer_promote_async(void) { return TCB_UNSUPPORTED; }

@@ -84,6 +84,21 @@ def main() -> None:
     step["rope_X"], step["rope_cos"], step["rope_sin"] = X.view(np.uint16), np.cos(ang), np.sin(ang)
     step["rope_out"] = R.rope_forward(X, np.cos(ang), np.sin(ang)).view(np.uint16)
     np.savez_compressed(os.path.join(OUT, "step_ops.npz"), **step)
+    # attention forward: decode rows (seq_q = 1) and a few short prefill shapes
+    att = {}
+    cases = [("dec_mha", 1, 4, 4, 1, 300, 64, False, 0, False), ("dec_gqa_alibi", 1, 8, 2, 1, 400, 128, False, 0, True),
+             ("causal_gqa", 1, 4, 2, 5, 77, 128, True, 0, False), ("window_alibi", 1, 2, 2, 40, 70, 64, True, 16, True),
+             ("odd_dim", 1, 3, 3, 1, 65, 40, False, 0, False)]
+    for name, B, Hq, Hkv, Sq, Sk, D, causal, window, alibi in cases:
+        Q = rng.standard_normal((B, Hq, Sq, D)).astype(np.float16)
+        K = rng.standard_normal((B, Hkv, Sk, D)).astype(np.float16)
+        V = rng.standard_normal((B, Hkv, Sk, D)).astype(np.float16)
+        sl = (0.05 * rng.random(Hq)).astype(np.float32) if alibi else np.zeros(0, np.float32)
+        Oa, La = R.attention_forward(Q, K, V, 0.0, causal, window, sl if alibi else None, True)
+        att[name + "_Q"], att[name + "_K"], att[name + "_V"] = Q.view(np.uint16), K.view(np.uint16), V.view(np.uint16)
+        att[name + "_slopes"], att[name + "_cfg"] = sl, np.array([int(causal), window], np.int32)
+        att[name + "_O"], att[name + "_LSE"] = Oa.view(np.uint16), La
+    np.savez_compressed(os.path.join(OUT, "attention.npz"), **att)
     print("wrote", sorted(os.listdir(OUT)))
 
 

@@ -574,3 +574,64 @@ def test_swiglu_and_rope_bulk(tc, ctx, oracle):
     assert np.array_equal(bx.to_numpy(X.shape, np.uint16), oracle.rope_forward(X, np.cos(ang), np.sin(ang)).view(np.uint16))
     for b in (bg, bu, bo, bx, bc, bs):
         b.close()
+
+
+# ---- attention forward (decode rows and a few short prefill shapes) ---------------------------
+def _run_attention(tc, ctx, Q, K, V, causal, window, slopes, want_lse):
+    B, Hq, Sq, D = Q.shape
+    _, Hkv, Sk, _ = K.shape
+    bq, bk, bv = ctx.buffer_from_array(Q), ctx.buffer_from_array(K), ctx.buffer_from_array(V)
+    bo = ctx.buffer(Q.nbytes)
+    bl = ctx.buffer(B * Hq * Sq * 4) if want_lse else None
+    tc.attention_forward(ctx, bq, bk, bv, bo, B, Hq, Sq, Sk, D, LSE=bl, causal=causal, kv_heads=Hkv,
+                         window_size=window, alibi_slopes=slopes)
+    assert tc.last_backend() == tc.TC_BACKEND_CUDA
+    O = bo.to_numpy(Q.shape, np.float16)
+    L = bl.to_numpy((B, Hq, Sq), np.float32) if want_lse else None
+    for b in (bq, bk, bv, bo) + ((bl,) if bl else ()):
+        b.close()
+    return O, L
+
+
+def test_attention_forward_golden_vectors(tc, ctx):
+    """Against what the reference's CPU backend produced (tests/golden/attention.npz).  Bar: the
+    reference's own for this operation, max abs error below 1e-3 on outputs of order one
+    (tests/test_attention_correctness.c:254-262); log-sum-exp within 1e-4."""
+    g = np.load(os.path.join(GOLDEN, "attention.npz"))
+    for name in sorted(k[:-2] for k in g.files if k.endswith("_Q")):
+        Q, K, V = (g[name + s].view(np.float16) for s in ("_Q", "_K", "_V"))
+        causal, window = (int(v) for v in g[name + "_cfg"])
+        sl = g[name + "_slopes"] if g[name + "_slopes"].size else None
+        O, L = _run_attention(tc, ctx, Q, K, V, bool(causal), window, sl, True)
+        err = np.abs(O.astype(np.float32) - g[name + "_O"].view(np.float16).astype(np.float32)).max()
+        assert err < 1e-3, (name, err)
+        assert np.abs(L - g[name + "_LSE"]).max() < 1e-4, name
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sk,D", [(1, 32, 32, 2048, 128), (1, 32, 8, 4096, 128), (4, 8, 8, 1000, 64),
+                                            (1, 2, 1, 33, 80)])
+def test_attention_decode_row_matches_oracle(tc, ctx, oracle, B, Hq, Hkv, Sk, D):
+    """One query row per head over a long K/V cache - the call of a decode step; the key range is
+    cut into chunks that are merged by a second kernel."""
+    rng = np.random.default_rng(Sk + D)
+    Q = rng.standard_normal((B, Hq, 1, D)).astype(np.float16)
+    K = rng.standard_normal((B, Hkv, Sk, D)).astype(np.float16)
+    V = rng.standard_normal((B, Hkv, Sk, D)).astype(np.float16)
+    O, L = _run_attention(tc, ctx, Q, K, V, False, 0, None, True)
+    Oo, Lo = oracle.attention_forward(Q, K, V, 0.0, False, 0, None, True)
+    assert np.abs(O.astype(np.float32) - Oo.astype(np.float32)).max() < 1e-3
+    assert np.abs(L - Lo).max() < 1e-4
+
+
+def test_attention_argument_checks(tc, ctx):
+    b = ctx.buffer(4096)
+    with pytest.raises(tc.TensorcoreError) as e:
+        tc.attention_forward(ctx, b, b, b, b, 1, 1, 1, 8, 256)           # head_dim above 128
+    assert e.value.status == tc.TC_ERR_INVALID_SHAPE
+    with pytest.raises(tc.TensorcoreError) as e:
+        tc.attention_forward(ctx, b, b, b, b, 1, 3, 1, 8, 64, kv_heads=2)  # kv_heads does not divide heads
+    assert e.value.status == tc.TC_ERR_INVALID_ARG
+    with pytest.raises(tc.TensorcoreError) as e:
+        tc.attention_forward(ctx, b, b, b, b, 1, 1, 1, 8, 64, dtype="bf16")
+    assert e.value.status == tc.TC_ERR_UNSUPPORTED_DTYPE
+    b.close()

@@ -194,3 +194,40 @@ def test_step_ops_against_reference_backend_when_built(oracle):
     ang = rng.uniform(0, 6.28, (7, 64)).astype(np.float32)
     assert np.array_equal(oracle.rope_forward(X, np.cos(ang), np.sin(ang)).view(np.uint16),
                           R.rope_forward(X, np.cos(ang), np.sin(ang)).view(np.uint16))
+
+
+def _attention_cases(g):
+    return sorted(k[:-2] for k in g.files if k.endswith("_Q"))
+
+
+def test_attention_forward_matches_reference_golden_vectors(oracle):
+    """lib/ops/attention_cpu.cpp:131-277 as run by the reference's CPU backend
+    (tests/golden/attention.npz, written by make_golden.py on an AVX2 machine, hence dot_order 1):
+    outputs and log-sum-exps bit for bit - decode rows, grouped-query heads, causal mask, sliding
+    window, ALiBi, a head_dim that is not a multiple of 8."""
+    g = np.load(os.path.join(GOLDEN, "attention.npz"))
+    for name in _attention_cases(g):
+        Q, K, V = (g[name + s].view(np.float16) for s in ("_Q", "_K", "_V"))
+        causal, window = (int(v) for v in g[name + "_cfg"])
+        sl = g[name + "_slopes"] if g[name + "_slopes"].size else None
+        O, L = oracle.attention_forward(Q, K, V, 0.0, bool(causal), window, sl, True, dot_order=1)
+        assert np.array_equal(O.view(np.uint16), g[name + "_O"]), name
+        assert np.array_equal(L, g[name + "_LSE"]), name
+        # the scalar dot-product order differs only in rounding
+        O0 = oracle.attention_forward(Q, K, V, 0.0, bool(causal), window, sl, False, dot_order=0)
+        assert np.abs(O0.astype(np.float32) - O.astype(np.float32)).max() < 2e-3, name
+
+
+def test_attention_forward_against_fp64_softmax(oracle):
+    """The tolerance the reference's own test uses against an fp64 reference
+    (tests/test_attention_correctness.c:254-262): max abs error below 1e-3."""
+    rng = np.random.default_rng(12)
+    B, Hq, Hkv, Sq, Sk, D = 1, 4, 2, 3, 130, 64
+    Q, K, V = (rng.standard_normal(s).astype(np.float16) for s in ((B, Hq, Sq, D), (B, Hkv, Sk, D), (B, Hkv, Sk, D)))
+    O = oracle.attention_forward(Q, K, V, 0.0, True, 0, None, False).astype(np.float64)
+    for h in range(Hq):
+        for i in range(Sq):
+            s = (K[0, h // 2].astype(np.float64) @ Q[0, h, i].astype(np.float64)) / np.sqrt(D)
+            s[np.arange(Sk) > i] = -np.inf
+            p = np.exp(s - s.max()); p /= p.sum()
+            assert np.abs(p @ V[0, h // 2].astype(np.float64) - O[0, h, i]).max() < 1e-3

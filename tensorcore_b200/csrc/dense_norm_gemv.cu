@@ -3,10 +3,22 @@
 //
 // The normalised row is rounded to fp16 before the product (as the reference's CPU path does)
 // and products are accumulated in fp32 with the mixed-precision FMA.  HBM-bound: W is read
-// once, 2 bytes per weight.  A CTA owns a strip of 32 columns (64-byte row segments) and all of
-// K; its 256 threads are 64 k-lanes x 4 column chunks of 16 bytes, each thread keeps several
-// independent 128-bit loads in flight.  The norm statistics are recomputed per CTA (K values
-// from L2), which is cheaper than a separate kernel and an fp16 round trip.
+// once, 2 bytes per weight.
+//
+// Main kernel (dense_norm_gemv_split_kernel): W is cut into tiles of 256 columns (512-byte row
+// segments: a warp copies one, 16 bytes per lane) by a K range chosen so that there are about
+// four tiles per SM - the hardware spreads them evenly, and three CTAs per SM keep 144 KB of
+// copies in flight.  A CTA starts the asynchronous copies of its first stages (cp.async into a
+// four-stage ring in shared memory; a thread reads back exactly the pieces it copied, so the
+// ring needs no barrier), works out the row statistics meanwhile (K values from L2; cheaper than
+// a separate kernel and an fp16 round trip), normalises its K range into shared memory, streams
+// its tile and leaves its partial sums in scratch;
+// the CTA that finishes a column strip last adds the strip's partial sums in K order - the result
+// does not depend on which CTA that is - and writes fp16 Y.  The scratch (partial sums and one
+// ticket counter per strip, which the last CTA resets) belongs to the stream the call runs on.
+//
+// Without scratch, for N not a multiple of 8 or an unaligned W: a CTA owns a strip of 32 columns
+// and all of K (dense_norm_gemv_kernel), or one thread owns a column (scalar kernel).
 #include "kernels.h"
 
 #include <cuda_fp16.h>
@@ -173,6 +185,165 @@ __global__ void __launch_bounds__(kDThreads) dense_norm_gemv_kernel(const DenseP
     }
 }
 
+// Statistics of row m for the split kernel: mean (LayerNorm) and 1/std or 1/rms, the reference's
+// arithmetic (double-precision sums, lib/ops/training_cpu.cpp:799-935).
+__device__ void row_stats(const DenseParams& p, int m, double* scratch, float& mean, float& rstd) {
+    const int tid = threadIdx.x, K = p.K;
+    const __half* xr = p.X + static_cast<size_t>(m) * K;
+    mean = 0.f;
+    if (p.beta != nullptr) {
+        double s = 0.0;
+        for (int k = tid; k < K; k += kDThreads) s += static_cast<double>(__half2float(xr[k]));
+        s = dblock_sum(s, scratch);
+        mean = static_cast<float>(s / K);
+    }
+    double ss = 0.0;
+    for (int k = tid; k < K; k += kDThreads) {
+        const float c = __fsub_rn(__half2float(xr[k]), mean);
+        ss += static_cast<double>(c) * static_cast<double>(c);
+    }
+    ss = dblock_sum(ss, scratch);
+    rstd = 1.0f / sqrtf(static_cast<float>(ss / K) + p.eps);
+}
+
+constexpr int kSplitCols = 256;          // columns of a tile: 512 contiguous bytes per row, one warp-wide copy
+constexpr int kRowGroups = kDThreads / 32;   // 8: a warp per row
+constexpr int kStageRows = 32;           // rows of W per ring stage: 16 KB
+constexpr int kStages = 4;               // ring depth: three stages (48 KB) in flight per CTA
+constexpr int kStageBytes = kStageRows * kSplitCols * 2;
+
+struct SplitParams {
+    DenseParams d;
+    float* partial;      // [chunks][M][N]
+    int* counters;       // [strips], zero between launches
+    int kc;              // K rows per tile (a multiple of kStageRows)
+    int chunks;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool live) {
+    // zero-fills when the row lies beyond the tile
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(live ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int MB>
+__global__ void __launch_bounds__(kDThreads) dense_norm_gemv_split_kernel(const SplitParams sp) {
+    extern __shared__ __align__(128) uint8_t dsm[];
+    double* scratch = reinterpret_cast<double*>(dsm);                 // kDWarps doubles
+    int* ticket_s = reinterpret_cast<int*>(dsm + 64);
+    uint8_t* ring = dsm + 128;                                        // kStages x 16 KB; reused for the reduction
+    float* red = reinterpret_cast<float*>(ring);                      // [8][MB][256] floats <= 32 KB
+    __half* xn = reinterpret_cast<__half*>(ring + kStages * kStageBytes);   // [MB][kc]
+    const DenseParams& p = sp.d;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int strip = blockIdx.x, chunk = blockIdx.y;
+    const int k0 = chunk * sp.kc, k1 = min(p.K, k0 + sp.kc);
+
+    // A thread copies, and later reads back, its own 16-byte pieces: rows (tid >> 5) + 8 * j of a
+    // stage, columns 8 * (tid & 31) .. + 7 of the strip.  So the ring needs no barrier: a copy
+    // group's completion is all a thread waits for.
+    const int hl = tid & 31, r0 = tid >> 5;
+    const int col = strip * kSplitCols + hl * 8;
+    const bool active = col < p.N;
+    const __half* wcol = p.W + (active ? col : 0);
+    const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
+    const int n_stages = (k1 - k0 + kStageRows - 1) / kStageRows;
+    auto issue = [&](int st) {
+        if (st < n_stages) {
+            const uint32_t dst = ring_s + (st % kStages) * kStageBytes + r0 * (kSplitCols * 2) + hl * 16;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int k = k0 + st * kStageRows + r0 + kRowGroups * j;
+                cp_async16(dst + j * kRowGroups * (kSplitCols * 2), wcol + static_cast<size_t>(k < k1 ? k : k0) * p.N, active && k < k1);
+            }
+        }
+        cp_async_commit();
+    };
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int st = 0; st < kStages - 1; ++st) issue(st);      // the weights do not depend on the statistics
+
+    for (int m = 0; m < MB; ++m) {
+        float mean, rstd;
+        row_stats(p, m, scratch, mean, rstd);
+        const __half* xr = p.X + static_cast<size_t>(m) * p.K;
+        for (int k = k0 + tid; k < k1; k += kDThreads) {
+            const float xv = __half2float(xr[k]), gv = __half2float(p.gamma[k]);
+            float o;
+            if (p.beta != nullptr) {
+                const float bv = __half2float(p.beta[k]);
+                o = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(xv, mean), rstd), gv), bv);
+            } else {
+                o = __fmul_rn(__fmul_rn(xv, rstd), gv);
+            }
+            xn[m * sp.kc + (k - k0)] = __float2half_rn(o);
+        }
+    }
+    __syncthreads();
+
+    float acc[MB][8];
+#pragma unroll
+    for (int m = 0; m < MB; ++m)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[m][e] = 0.f;
+    for (int st = 0; st < n_stages; ++st) {
+        issue(st + kStages - 1);
+        cp_async_wait<kStages - 1>();
+        const uint8_t* src = ring + (st % kStages) * kStageBytes + r0 * (kSplitCols * 2) + hl * 16;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int kk = st * kStageRows + r0 + kRowGroups * j;     // row within the tile
+            if (k0 + kk >= k1) break;
+            const uint4 wv = *reinterpret_cast<const uint4*>(src + j * kRowGroups * (kSplitCols * 2));
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int m = 0; m < MB; ++m) {
+                const uint16_t xb = __half_as_ushort(xn[m * sp.kc + kk]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    acc[m][2 * e] = fma_h16(xb, static_cast<uint16_t>(ww[e]), acc[m][2 * e]);
+                    acc[m][2 * e + 1] = fma_h16(xb, static_cast<uint16_t>(ww[e] >> 16), acc[m][2 * e + 1]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();         // every thread is done with the ring: it now holds the partial sums
+    // 8 row groups per column: through shared memory, added in a fixed order
+#pragma unroll
+    for (int m = 0; m < MB; ++m)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) red[(r0 * MB + m) * kSplitCols + hl * 8 + e] = acc[m][e];
+    __syncthreads();
+    for (int i = tid; i < MB * kSplitCols; i += kDThreads) {
+        const int m = i / kSplitCols, c = i - m * kSplitCols;
+        float v = 0.f;
+#pragma unroll
+        for (int g = 0; g < kRowGroups; ++g) v += red[(g * MB + m) * kSplitCols + c];
+        const int n = strip * kSplitCols + c;
+        if (n < p.N) sp.partial[(static_cast<size_t>(chunk) * p.M + m) * p.N + n] = v;
+    }
+    // The last CTA of the strip adds the K ranges in order and writes the result.
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) *ticket_s = atomicAdd(&sp.counters[strip], 1);
+    __syncthreads();
+    if (*ticket_s != sp.chunks - 1) return;
+    __threadfence();
+    for (int i = tid; i < MB * kSplitCols; i += kDThreads) {
+        const int m = i / kSplitCols, c = i - m * kSplitCols;
+        const int n = strip * kSplitCols + c;
+        if (n >= p.N) continue;
+        float v = 0.f;
+        for (int ch = 0; ch < sp.chunks; ++ch)
+            v += __ldcg(sp.partial + (static_cast<size_t>(ch) * p.M + m) * p.N + n);
+        p.Y[static_cast<size_t>(m) * p.N + n] = __float2half_rn(v);
+    }
+    if (tid == 0) sp.counters[strip] = 0;      // ready for the next launch on this stream
+}
+
 // Fallback for N % 8 != 0 or unaligned W: one thread per column, scalar loads (still
 // coalesced across the warp).
 template <int MB>
@@ -232,7 +403,53 @@ cudaError_t launch_dense_mb(const DenseParams& p, bool vec, int smem_optin, cuda
     return cudaLaunchKernelEx(&cfg, dense_norm_gemv_scalar_kernel<MB>, p);
 }
 
+template <int MB>
+cudaError_t launch_dense_split(const SplitParams& sp, int strips, int smem_optin, cudaStream_t st, bool pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(kDThreads);
+    cfg.gridDim = dim3(strips, sp.chunks);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    cfg.dynamicSmemBytes = 128 + kStages * kStageBytes + static_cast<size_t>(MB) * sp.kc * 2;
+    if (static_cast<int>(cfg.dynamicSmemBytes) > smem_optin) return cudaErrorInvalidValue;
+    cudaError_t e = cudaFuncSetAttribute(dense_norm_gemv_split_kernel<MB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(cfg.dynamicSmemBytes));
+    if (e != cudaSuccess) return e;
+    return cudaLaunchKernelEx(&cfg, dense_norm_gemv_split_kernel<MB>, sp);
+}
+
+// Tiles of the split kernel for one launch of up to kDMaxMB rows.
+void dense_split_shape(int N, int K, int sm_count, int* strips, int* chunks, int* kc) {
+    // about four tiles per SM (three CTAs are resident per SM; more, shorter tiles measured slower:
+    // every tile pays for the row statistics and for a fence before its ticket), K ranges of whole
+    // ring stages
+    const int st = (N + kSplitCols - 1) / kSplitCols;
+    int ch = (4 * sm_count + st - 1) / st;
+    const int most = (K + 2 * kStageRows - 1) / (2 * kStageRows);
+    if (ch > most) ch = most;
+    if (ch < 1) ch = 1;
+    int rows = (K + ch - 1) / ch;
+    rows = (rows + kStageRows - 1) / kStageRows * kStageRows;
+    *strips = st;
+    *kc = rows;
+    *chunks = (K + rows - 1) / rows;
+}
+
 }  // namespace
+
+void dense_norm_gemv_scratch(int M, int N, int K, int sm_count, size_t* floats, size_t* ints) {
+    int strips, chunks, kc;
+    dense_split_shape(N, K, sm_count, &strips, &chunks, &kc);
+    const int mb = M < kDMaxMB ? M : kDMaxMB;
+    *floats = static_cast<size_t>(chunks) * mb * N;
+    *ints = static_cast<size_t>(strips);
+}
 
 cudaError_t launch_dense_norm_gemv(const DenseNormGemvArgs& a, const LaunchEnv& env,
                                    cudaStream_t stream, int* launches, const char** name) {
@@ -240,6 +457,9 @@ cudaError_t launch_dense_norm_gemv(const DenseNormGemvArgs& a, const LaunchEnv& 
     const int optin = env.smem_optin > 0 ? env.smem_optin : 48 * 1024;
     cudaError_t err = cudaSuccess;
     int count = 0;
+    size_t need_f = 0, need_i = 0;
+    dense_norm_gemv_scratch(a.M, a.N, a.K, env.sm_count > 0 ? env.sm_count : 148, &need_f, &need_i);
+    const bool split = vec && a.scratch && a.counters && a.scratch_floats >= need_f && a.counters_n >= need_i;
     for (int m0 = 0; m0 < a.M && err == cudaSuccess; m0 += kDMaxMB) {
         const int mb = (a.M - m0) < kDMaxMB ? (a.M - m0) : kDMaxMB;
         DenseParams p;
@@ -249,6 +469,22 @@ cudaError_t launch_dense_norm_gemv(const DenseNormGemvArgs& a, const LaunchEnv& 
         p.W = static_cast<const __half*>(a.W);
         p.Y = static_cast<__half*>(a.Y) + static_cast<size_t>(m0) * a.N;
         p.M = mb; p.N = a.N; p.K = a.K; p.eps = a.eps;
+        if (split) {
+            SplitParams sp;
+            sp.d = p;
+            sp.partial = a.scratch;
+            sp.counters = a.counters;
+            int strips = 0;
+            dense_split_shape(a.N, a.K, env.sm_count > 0 ? env.sm_count : 148, &strips, &sp.chunks, &sp.kc);
+            switch (mb) {
+                case 1: err = launch_dense_split<1>(sp, strips, optin, stream, env.pdl); break;
+                case 2: err = launch_dense_split<2>(sp, strips, optin, stream, env.pdl); break;
+                case 3: err = launch_dense_split<3>(sp, strips, optin, stream, env.pdl); break;
+                default: err = launch_dense_split<4>(sp, strips, optin, stream, env.pdl); break;
+            }
+            ++count;
+            continue;
+        }
         switch (mb) {
             case 1: err = launch_dense_mb<1>(p, vec, optin, stream, env.pdl); break;
             case 2: err = launch_dense_mb<2>(p, vec, optin, stream, env.pdl); break;
@@ -258,7 +494,8 @@ cudaError_t launch_dense_norm_gemv(const DenseNormGemvArgs& a, const LaunchEnv& 
         ++count;
     }
     if (launches) *launches += count;
-    if (name) *name = a.beta ? "layernorm_gemv_f16_sm100" : "rmsnorm_gemv_f16_sm100";
+    if (name) *name = a.beta ? (split ? "layernorm_gemv_f16_split_sm100" : "layernorm_gemv_f16_sm100")
+                             : (split ? "rmsnorm_gemv_f16_split_sm100" : "rmsnorm_gemv_f16_sm100");
     return err;
 }
 

@@ -44,7 +44,15 @@ struct DenseNormGemvArgs {
     void* Y = nullptr;            // [M,N] fp16
     int M = 0, N = 0, K = 0;
     float eps = 0.f;
+    // scratch of the stream the call runs on (dense_norm_gemv_scratch says how much): partial sums
+    // and one ticket counter per column strip, all zero between launches; without it a slower
+    // kernel that needs none is used
+    float* scratch = nullptr;
+    size_t scratch_floats = 0;
+    int* counters = nullptr;
+    size_t counters_n = 0;
 };
+void dense_norm_gemv_scratch(int M, int N, int K, int sm_count, size_t* floats, size_t* ints);
 
 // ---------------------------------------------------------------------------------------
 // Persistent decode launch (decode_q4.cu): a list of Q4_0, M = 1 GEMVs as one cooperative kernel.

@@ -184,6 +184,56 @@ tc_status_t validate(tc_context* ctx, const tc_buffer* b, size_t min_bytes) {
 bool staged(const tc_buffer* b) { return b->kind == BUF_WRAP_HOST || b->kind == BUF_HOST_SHADOW; }
 bool managed(const tc_buffer* b) { return b->kind == BUF_MANAGED || b->kind == BUF_WRAP_MANAGED; }
 
+// Scratch of the dense fused GEMV (partial sums of the K ranges, one ticket counter per column
+// strip), one per CUDA stream: calls on a stream are ordered, calls on different streams must not
+// share it.  Grown on demand, freed when the context goes.
+struct DenseScratch { float* f = nullptr; size_t nf = 0; int* c = nullptr; size_t nc = 0; };
+std::mutex g_dense_mutex;
+std::unordered_map<cudaStream_t, DenseScratch> g_dense;
+
+void dense_scratch_for(tc_context* ctx, cudaStream_t st, tcb::DenseNormGemvArgs* a) {
+    size_t nf = 0, nc = 0;
+    tcb::dense_norm_gemv_scratch(a->M, a->N, a->K, ctx->sm_count, &nf, &nc);
+    std::lock_guard<std::mutex> lock(g_dense_mutex);
+    if (g_dense.size() > 32 && g_dense.find(st) == g_dense.end()) {
+        // many short-lived streams: start over rather than keep scratch for streams that are gone
+        cudaDeviceSynchronize();
+        for (auto& kv : g_dense) {
+            if (kv.second.f) cudaFree(kv.second.f);
+            if (kv.second.c) cudaFree(kv.second.c);
+        }
+        g_dense.clear();
+    }
+    DenseScratch& d = g_dense[st];
+    if (d.nf < nf || d.nc < nc) {
+        cudaStreamSynchronize(st);        // an earlier call on this stream may still use the old one
+        if (d.f) cudaFree(d.f);
+        if (d.c) cudaFree(d.c);
+        d = DenseScratch();
+        const size_t wf = nf + nf / 2, wc = nc * 2;
+        if (cudaMalloc(reinterpret_cast<void**>(&d.f), wf * sizeof(float)) != cudaSuccess ||
+            cudaMalloc(reinterpret_cast<void**>(&d.c), wc * sizeof(int)) != cudaSuccess ||
+            cudaMemset(d.c, 0, wc * sizeof(int)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            if (d.f) cudaFree(d.f);
+            if (d.c) cudaFree(d.c);
+            d = DenseScratch();
+            return;                        // the launcher falls back to the kernel that needs none
+        }
+        d.nf = wf;
+        d.nc = wc;
+    }
+    a->scratch = d.f; a->scratch_floats = d.nf; a->counters = d.c; a->counters_n = d.nc;
+}
+void free_dense_scratch() {
+    std::lock_guard<std::mutex> lock(g_dense_mutex);
+    for (auto& kv : g_dense) {
+        if (kv.second.f) cudaFree(kv.second.f);
+        if (kv.second.c) cudaFree(kv.second.c);
+    }
+    g_dense.clear();
+}
+
 LaunchEnv make_env(tc_context* ctx, bool allow_pdl) {
     LaunchEnv e;
     e.sm_count = ctx->sm_count;
@@ -269,6 +319,7 @@ void teardown_device(tc_context* ctx) {
     if (ctx->stream0) cudaStreamDestroy(ctx->stream0);
     if (ctx->err_host) cudaFreeHost(ctx->err_host);
     if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
+    free_dense_scratch();
     ctx->attn_scratch = nullptr;
     ctx->attn_scratch_floats = 0;
     ctx->stream0 = nullptr;
@@ -1266,8 +1317,10 @@ static tc_status_t dense_common(tc_context* ctx, const tc_buffer* X, const tc_bu
     a.Y = Y->dptr; a.M = M; a.N = N; a.K = K; a.eps = eps;
     int launches = 0;
     const char* name = "none";
-    if (e == cudaSuccess)
+    if (e == cudaSuccess) {
+        dense_scratch_for(ctx, s0, &a);
         e = tcb::launch_dense_norm_gemv(a, make_env(ctx, false), s0, &launches, &name);
+    }
     if (e == cudaSuccess) e = finish_output(Y, yb, s0);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s0);
     g_launches.fetch_add(static_cast<uint64_t>(launches));
@@ -1405,6 +1458,7 @@ extern "C" tc_status_t tc_attention_forward(tc_context* ctx, const tc_attention_
     if (want > ctx->attn_scratch_floats) {
         cudaStreamSynchronize(ctx->stream0);
         if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
+    free_dense_scratch();
         ctx->attn_scratch = nullptr;
         ctx->attn_scratch_floats = 0;
         if (cudaMalloc(reinterpret_cast<void**>(&ctx->attn_scratch), want * sizeof(float)) != cudaSuccess) {
@@ -1645,6 +1699,7 @@ extern "C" tc_status_t tcx_raw_fused_norm_gemv_f16(tc_context* ctx, const void* 
     a.M = M; a.N = N; a.K = K; a.eps = eps;
     int launches = 0;
     const char* name = "none";
+    dense_scratch_for(ctx, static_cast<cudaStream_t>(cuda_stream), &a);
     const cudaError_t e = tcb::launch_dense_norm_gemv(a, make_env(ctx, true),
                                                       static_cast<cudaStream_t>(cuda_stream),
                                                       &launches, &name);

@@ -338,6 +338,26 @@ def gemv_cases(ctx, quick: bool = False) -> list[dict]:
         for b in ws + [x, g, y] + ([bt] if bt else []):
             b.close()
 
+    def attention_case(name, B, H, Hkv, Sk, Dh, iters):
+        """Decode attention: one query row per head over a K/V cache of Sk positions.  Algorithmic
+        bytes: K and V of every kv head once (2 * B * Hkv * Sk * Dh * 2) + Q and O."""
+        kv_bytes = B * Hkv * Sk * Dh * 2
+        copies = max(2, int(2 * 126e6 // (2 * kv_bytes)) + 1)
+        rng = np.random.default_rng(Sk + Dh)
+        ks = [ctx.buffer_from_array(rng.standard_normal((B, Hkv, Sk, Dh)).astype(np.float16)) for _ in range(copies)]
+        vs = [ctx.buffer_from_array(rng.standard_normal((B, Hkv, Sk, Dh)).astype(np.float16)) for _ in range(copies)]
+        q = ctx.buffer_from_array(rng.standard_normal((B, H, 1, Dh)).astype(np.float16))
+        o = ctx.buffer(B * H * Dh * 2)
+        alg = 2 * kv_bytes + 2 * B * H * Dh * 2
+        ms = D.attention_bench(ctx, q, ks, vs, o, B, H, Hkv, Sk, Dh, iters)
+        us = ms / iters * 1e3
+        out.append({"config": name, "fmt": "f16 K/V", "batch": B, "heads": H, "kv_heads": Hkv, "seq_kv": Sk, "head_dim": Dh,
+                    "kv_copies": copies, "bytes": alg,
+                    "per_op": {"us": round(us, 3), "GBs": round(alg / us / 1e3, 1), "frac": round(alg / us / 1e3 / peak, 4),
+                               "kernel": tc.cuda_last_kernel_name()}})
+        for b in ks + vs + [q, o]:
+            b.close()
+
     it = 100 if quick else 200
     quant_case("config 1: Q4_0 4096x4096, fp32 x -> fp32 y", 0, 1, 4096, 4096, "f32", "f32", False, it)
     quant_case("config 1 through the fp16 ABI", 0, 1, 4096, 4096, "f16", "f16", False, it)
@@ -348,6 +368,8 @@ def gemv_cases(ctx, quick: bool = False) -> list[dict]:
         quant_case(f"config 4: Q4_0 14336x4096, M={M}, fp16 x -> fp32 y", 0, M, 14336, 4096, "f16", "f32", False, it // 2)
     dense_case("tc_fused_rmsnorm_gemv, fp16 W 4096x11008", False, 1, 11008, 4096, it // 2)
     dense_case("tc_fused_layernorm_gemv, fp16 W 4096x11008", True, 1, 11008, 4096, it // 2)
+    attention_case("tc_attention_forward, decode row: 32 heads x 128, 4096 keys (7B shape)", 1, 32, 32, 4096, 128, it // 2)
+    attention_case("tc_attention_forward, decode row: 64 heads / 8 kv heads x 128, 8192 keys (70B shape)", 1, 64, 8, 8192, 128, it // 2)
     return out
 
 

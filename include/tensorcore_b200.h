@@ -402,6 +402,12 @@ tc_status_t tcx_raw_fused_rmsnorm_gemv_quantized(tc_context* ctx, const void* X,
                                                  tc_quant_t fmt, int M, int N, int K, float eps,
                                                  tc_dtype_t x_dtype, tc_dtype_t y_dtype,
                                                  void* cuda_stream);
+/* tc_attention_forward on raw device pointers, asynchronous on `cuda_stream` (desc->alibi_slopes must
+ * be NULL).  The scratch that holds the partial softmax states of a row's key chunks belongs to the
+ * context: do not let two of these launches overlap on different streams. */
+tc_status_t tcx_raw_attention_forward(tc_context* ctx, const tc_attention_desc* desc, const void* Q,
+                                      const void* K, const void* V, void* O, void* LSE /* or NULL */,
+                                      void* cuda_stream);
 tc_status_t tcx_raw_fused_norm_gemv_f16(tc_context* ctx, const void* X, const void* gamma,
                                         const void* beta /* NULL = RMSNorm */, const void* W,
                                         void* Y, int M, int N, int K, float eps,

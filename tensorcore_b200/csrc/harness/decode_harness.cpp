@@ -241,4 +241,39 @@ int tch_dense_bench(tc_context* ctx, tc_buffer** weights, int copies, tc_buffer*
     return st;
 }
 
+// Decode attention: `iters` launches of one query row per head over `copies` distinct K/V caches
+// (so that they stream from HBM), event-timed on one stream.
+int tch_attention_bench(tc_context* ctx, tc_buffer* q, tc_buffer** ks, tc_buffer** vs, int copies, tc_buffer* o,
+                        int batch, int heads, int kv_heads, int seq_kv, int head_dim, int iters, float* gpu_ms) {
+    if (!ctx || !q || !ks || !vs || !o || copies <= 0 || iters <= 0) return TC_ERR_INVALID_ARG;
+    cudaStream_t stream;
+    if (cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) != cudaSuccess) return TC_ERR_INTERNAL;
+    tc_attention_desc d;
+    std::memset(&d, 0, sizeof(d));
+    d.batch = batch; d.heads = heads; d.seq_q = 1; d.seq_kv = seq_kv; d.head_dim = head_dim;
+    d.io_dtype = TC_DTYPE_F16; d.accum_dtype = TC_DTYPE_F32; d.kv_heads = kv_heads;
+    void *pq, *po;
+    tcx_buffer_device_ptr(q, &pq); tcx_buffer_device_ptr(o, &po);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    int st = TC_OK;
+    for (int rep = 0; rep < 2 && st == TC_OK; ++rep) {
+        if (rep == 1) cudaEventRecord(e0, stream);
+        for (int i = 0; i < iters && st == TC_OK; ++i) {
+            void *pk, *pv;
+            tcx_buffer_device_ptr(ks[i % copies], &pk);
+            tcx_buffer_device_ptr(vs[i % copies], &pv);
+            st = tcx_raw_attention_forward(ctx, &d, pq, pk, pv, po, nullptr, stream);
+        }
+        if (rep == 1) cudaEventRecord(e1, stream);
+        if (cudaStreamSynchronize(stream) != cudaSuccess && st == TC_OK) st = TC_ERR_INTERNAL;
+    }
+    if (gpu_ms) { *gpu_ms = 0.f; if (st == TC_OK) cudaEventElapsedTime(gpu_ms, e0, e1); }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaStreamDestroy(stream);
+    return st;
+}
+
 }  // extern "C"

@@ -1486,6 +1486,48 @@ extern "C" tc_status_t tc_attention_forward(tc_context* ctx, const tc_attention_
     return st;
 }
 
+// The same on raw device pointers, asynchronous on the caller's stream (no ALiBi: its slopes would
+// have to be staged from host memory).  The scratch for the key chunks belongs to the context:
+// launches on different streams must not overlap.
+extern "C" tc_status_t tcx_raw_attention_forward(tc_context* ctx, const tc_attention_desc* d, const void* Q,
+                                                 const void* K, const void* V, void* O, void* LSE,
+                                                 void* cuda_stream) {
+    if (!ctx) return TC_ERR_NOT_INITIALIZED;
+    if (!d || !Q || !K || !V || !O) return TC_ERR_INVALID_ARG;
+    if (d->batch <= 0 || d->heads <= 0 || d->seq_q <= 0 || d->seq_kv <= 0 || d->head_dim <= 0) return TC_ERR_INVALID_ARG;
+    if (d->io_dtype != TC_DTYPE_F16 || d->accum_dtype != TC_DTYPE_F32) return TC_ERR_UNSUPPORTED_DTYPE;
+    if (d->alibi_slopes) return TC_ERR_UNSUPPORTED_FAMILY;
+    const int Hkv = d->kv_heads > 0 ? d->kv_heads : d->heads;
+    if (Hkv <= 0 || d->heads % Hkv != 0) return TC_ERR_INVALID_ARG;
+    if (d->head_dim > 128) return TC_ERR_INVALID_SHAPE;
+    const long long rows = static_cast<long long>(d->batch) * d->heads * d->seq_q;
+    if (rows > 0x7fffffffLL) return TC_ERR_INVALID_SHAPE;
+    bind_device(ctx);
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    int chunks = 1;
+    const size_t want = tcb::attention_scratch_floats(static_cast<int>(rows), d->seq_kv, d->head_dim, ctx->sm_count, &chunks);
+    if (want > ctx->attn_scratch_floats) {
+        cudaDeviceSynchronize();
+        if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
+        ctx->attn_scratch = nullptr;
+        ctx->attn_scratch_floats = 0;
+        if (cudaMalloc(reinterpret_cast<void**>(&ctx->attn_scratch), want * sizeof(float)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return record("tcx_raw_attention_forward", TC_ERR_ALLOC);
+        }
+        ctx->attn_scratch_floats = want;
+    }
+    const float scale = d->softmax_scale > 0 ? d->softmax_scale : 1.0f / std::sqrt(static_cast<float>(d->head_dim));
+    int launched = 0;
+    const cudaError_t e = tcb::launch_attention_forward(Q, K, V, O, static_cast<float*>(LSE),
+                                                        chunks > 1 ? ctx->attn_scratch : nullptr, nullptr, d->batch,
+                                                        d->heads, Hkv, d->seq_q, d->seq_kv, d->head_dim, scale, d->causal,
+                                                        d->window_size, ctx->sm_count, st, &launched);
+    g_launches.fetch_add(static_cast<uint64_t>(launched));
+    t_last_kernel = "attention_decode_sm100";
+    return record("tcx_raw_attention_forward", from_cuda(e, TC_ERR_DISPATCH));
+}
+
 // The recorded form runs at once, as the reference's CPU backend does (attention_cpu.cpp:280-291).
 extern "C" tc_status_t tc_attention_forward_async(tc_context* ctx, const tc_attention_desc* d, const tc_buffer* Q,
                                                   const tc_buffer* K, const tc_buffer* V, tc_buffer* O,

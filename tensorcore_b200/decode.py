@@ -181,6 +181,9 @@ def harness() -> ctypes.CDLL:
         H.tch_dense_bench.argtypes = [c_void_p, POINTER(c_void_p), c_int, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_int, c_int, c_int, c_int, POINTER(c_float)]
         H.tch_dense_bench.restype = c_int
+        H.tch_attention_bench.argtypes = [c_void_p, c_void_p, POINTER(c_void_p), POINTER(c_void_p), c_int, c_void_p,
+                                          c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_float)]
+        H.tch_attention_bench.restype = c_int
         _harness = H
     return _harness
 
@@ -294,6 +297,20 @@ def dense_bench(ctx: tc.Context, weights: list[tc.Buffer], x: tc.Buffer, gamma: 
     st = harness().tch_dense_bench(ctx.handle, ctypes.cast(arr, POINTER(c_void_p)), len(weights), x.handle,
                                    gamma.handle, beta.handle if beta else None, y.handle, M, N, K, iters,
                                    byref(ms))
+    if st != tc.TC_OK:
+        raise tc.TensorcoreError(st)
+    return ms.value
+
+
+def attention_bench(ctx: tc.Context, q: tc.Buffer, ks: list[tc.Buffer], vs: list[tc.Buffer], o: tc.Buffer, batch: int,
+                    heads: int, kv_heads: int, seq_kv: int, head_dim: int, iters: int) -> float:
+    """Milliseconds for `iters` back-to-back decode-attention launches (one query row per head)."""
+    ka = (c_void_p * len(ks))(*[b.handle for b in ks])
+    va = (c_void_p * len(vs))(*[b.handle for b in vs])
+    ms = c_float()
+    st = harness().tch_attention_bench(ctx.handle, q.handle, ctypes.cast(ka, POINTER(c_void_p)),
+                                       ctypes.cast(va, POINTER(c_void_p)), len(ks), o.handle, batch, heads, kv_heads,
+                                       seq_kv, head_dim, iters, byref(ms))
     if st != tc.TC_OK:
         raise tc.TensorcoreError(st)
     return ms.value

@@ -635,3 +635,22 @@ def test_attention_argument_checks(tc, ctx):
         tc.attention_forward(ctx, b, b, b, b, 1, 1, 1, 8, 64, dtype="bf16")
     assert e.value.status == tc.TC_ERR_UNSUPPORTED_DTYPE
     b.close()
+
+
+def test_raw_attention_entry_matches_oracle(tc, ctx, oracle):
+    """tcx_raw_attention_forward (device pointers, asynchronous on a stream), as the timing harness
+    drives it: the output of the last launch against the oracle."""
+    from tensorcore_b200 import decode as D
+    rng = np.random.default_rng(77)
+    B, H, Hkv, Sk, Dh = 1, 16, 4, 1500, 128
+    Q = rng.standard_normal((B, H, 1, Dh)).astype(np.float16)
+    Ks = [rng.standard_normal((B, Hkv, Sk, Dh)).astype(np.float16) for _ in range(2)]
+    Vs = [rng.standard_normal((B, Hkv, Sk, Dh)).astype(np.float16) for _ in range(2)]
+    bq, bo = ctx.buffer_from_array(Q), ctx.buffer(Q.nbytes)
+    bks, bvs = [ctx.buffer_from_array(k) for k in Ks], [ctx.buffer_from_array(v) for v in Vs]
+    D.attention_bench(ctx, bq, bks, bvs, bo, B, H, Hkv, Sk, Dh, 4)       # launches use copies 0, 1, 0, 1
+    O = bo.to_numpy(Q.shape, np.float16)
+    Oo = oracle.attention_forward(Q, Ks[1], Vs[1], 0.0, False, 0, None, False)
+    assert np.abs(O.astype(np.float32) - Oo.astype(np.float32)).max() < 1e-3
+    for b in [bq, bo] + bks + bvs:
+        b.close()

@@ -1,37 +1,37 @@
 // Persistent decode kernel for sm_100a: a whole recorded list of Q4_0, M = 1 GEMVs - one decode
-// token - in ONE cooperative launch, one CTA per SM.
+// token - in ONE cooperative launch, one CTA per SM; tensor parallel: one such launch per rank.
 //
 // Work.  An operation Y[N] = dequant(W[N,K]) . x[K] is cut into boxes of 32 weight rows x one
 // 8-block group (144 bytes per row, 256 weights per row), each fetched by one tiled TMA copy
-// through a per-operation tensor map.  Operations that share their input and need no barrier
+// through a per-operation tensor map.  Operations that share their input and need no ordering
 // between them (q/k/v, gate/up) form a phase.  The boxes of a phase are numbered band-major - a
 // band is four consecutive groups, i.e. 1024 input elements and 576 contiguous bytes of every
 // row - then by row block, then by group inside the band, and dealt evenly to the CTAs (CTA c
-// owns boxes [U*c/G, U*(c+1)/G)) and within a CTA round-robin to its warps.  So every SM streams
-// the same number of bytes whatever N is, four consecutive warps fetch one contiguous piece of
-// 32 rows, and a CTA needs only the one or two bands of the input that its boxes touch.
-// A lane owns one ROW of a box: all lanes of a warp read the same int16 activations from shared
-// memory (one broadcast per load) and the lane's partial dot product is added with one
-// red.global.add.f32 to the operation's fp32 accumulators in global memory (L2 atomics; the K
-// split of a row over boxes, warps, CTAs and - tensor parallel - GPUs all ends in the same
-// accumulator).
+// owns boxes [U*c/G, U*(c+1)/G)).  So every SM streams the same number of bytes whatever N is, and
+// a CTA needs only the one or two bands of the input that its boxes touch.
 //
-// Epochs.  Operations that read what an earlier one wrote are separated by a grid-wide barrier
-// (one never-reset 64-bit arrival counter, release / acquire, bounded spin).  After the barrier
-// a CTA stages ITS bands of the input straight from the producer's accumulators (L2-coherent
-// loads, scaled and rounded to the producer's result type), quantised to int16 with one scale per
-// 32 elements.  RMSNorm prologue: the row x*gamma is quantised without the 1/rms factor, which
-// needs the whole row; instead the CTAs that stage a band leave the band's sum of squares in a
-// slot beside the accumulators, and whoever reads the accumulators one epoch later (the next
-// staging pass, or the pass that writes the result buffer) multiplies by 1/sqrt(mean square +
-// eps) computed from the slots.  Result buffers are written while a CTA waits at the NEXT barrier
-// (each CTA converts a 1/G slice), accumulators are zeroed one epoch after that; they come from a
-// pool in three generations (epoch mod 3), and a trailing barrier finishes the last epoch, so the
-// pool is all zero again when the kernel ends.
+// Three kinds of warps.  Producer warps walk the CTA's box sequence over all phases and keep a ring
+// of boxes in shared memory full (weights do not depend on activations: the ring refills while the
+// consumers are between two phases).  Consumer warps take a box each: a lane owns one ROW of the
+// box, all lanes read the same int16 activations from shared memory (one broadcast per load), and
+// the lane adds its partial dot product, together with a count of one, to the operation's
+// accumulator pair in global memory with ONE vector reduction (L2 atomics; the K split of a row
+// over boxes, warps, CTAs and - tensor parallel - GPUs all ends in the same pair).  Housekeeping
+// warps follow behind: result buffers, clearing, and an arrival counter that nobody waits at.
 //
-// Every warp keeps its ring of boxes full ACROSS phases and barriers: weights do not depend on
-// activations, so HBM keeps streaming while a CTA waits and re-stages.  (The host refuses lists
-// in which an operation writes a later operation's weights.)
+// Epochs without barriers.  Operations that read what an earlier one wrote belong to different
+// epochs.  A CTA that starts an epoch stages ITS bands of the input straight from the producer's
+// accumulator pairs (L2-coherent loads, scaled and rounded to the producer's result type),
+// quantised to int16 with one scale per 32 elements, and simply repeats the load until every
+// pair's count says that all of the row's partial sums have arrived.  RMSNorm prologue: the row
+// x*gamma is quantised without the 1/rms factor, which needs the whole row; instead the CTAs that
+// stage a band leave the band's sum of squares, with a flag, in a slot beside the accumulators,
+// and whoever reads the accumulators next (the next staging pass, or the housekeeping warp that
+// writes the result buffer) multiplies by 1/sqrt(mean square + eps) computed from the slots.  The
+// accumulators come from a pool in twelve generations (epoch mod 12) and are all zero again when
+// the kernel ends.
+//
+// Every wait is bounded (about a second), sets an error bit and lets the kernel end.
 #include "gemv_common.cuh"
 #include "tensor_map.h"
 
@@ -56,17 +56,8 @@ constexpr int kKeeperWarps = 4;       // housekeeping warps: they take the epoch
 constexpr int kAuxWarps = kProducerWarps + kKeeperWarps;
 constexpr int kDecodeMaxThreads = (kMaxStreamWarps + kProducerWarps + kKeeperWarps) * 32;   // consumer, producer and housekeeping warps
 
-__device__ __forceinline__ void red_add_gpu(float* p, float v) {
-    asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
-}
-__device__ __forceinline__ void red_add_sys(float* p, float v) {
-    asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
-}
 __device__ __forceinline__ void arrive_gpu(unsigned long long* p) {
     asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(1ULL) : "memory");
-}
-__device__ __forceinline__ void arrive_sys(unsigned long long* p) {
-    asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(1ULL) : "memory");
 }
 __device__ __forceinline__ void arrive_relaxed_sys(unsigned long long* p) {
     asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(1ULL) : "memory");

@@ -212,9 +212,8 @@ cudaError_t launch_gemm_f16_rows(const void* A, const void* B, void* C, int M, i
                                  int ldc, float alpha, float beta, cudaStream_t stream);
 
 // --- attention forward for decode (attention.cu); fp16 data, fp32 softmax ----------------------------
-// Floats of scratch the launch needs for (rows = B * Hq * Sq) query rows, and into how many key
-// chunks it will cut a row (1 = no scratch).
-size_t attention_scratch_floats(int rows, int Sk, int D, int sm_count, int* chunks_out);
+// Floats of scratch the launch needs, and into how many key chunks it will cut a row (1 = no scratch).
+size_t attention_scratch_floats(int B, int Hq, int Hkv, int Sq, int Sk, int D, int sm_count, int* chunks_out);
 // cudaErrorNotSupported: head_dim above 128.  slopes_dev: ALiBi slopes on the device, or null.
 cudaError_t launch_attention_forward(const void* Q, const void* K, const void* V, void* O, float* LSE,
                                      float* scratch, const float* slopes_dev, int B, int Hq, int Hkv, int Sq,

@@ -1452,7 +1452,7 @@ extern "C" tc_status_t tc_attention_forward(tc_context* ctx, const tc_attention_
     int chunks = 1;
     const long long rows = static_cast<long long>(B) * Hq * Sq;
     if (rows > 0x7fffffffLL) return TC_ERR_INVALID_SHAPE;
-    size_t want = tcb::attention_scratch_floats(static_cast<int>(rows), Sk, D, ctx->sm_count, &chunks);
+    size_t want = tcb::attention_scratch_floats(B, Hq, Hkv, Sq, Sk, D, ctx->sm_count, &chunks);
     const size_t slope_at = want;
     if (d->alibi_slopes) want += static_cast<size_t>(Hq);
     if (want > ctx->attn_scratch_floats) {
@@ -1505,7 +1505,8 @@ extern "C" tc_status_t tcx_raw_attention_forward(tc_context* ctx, const tc_atten
     bind_device(ctx);
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     int chunks = 1;
-    const size_t want = tcb::attention_scratch_floats(static_cast<int>(rows), d->seq_kv, d->head_dim, ctx->sm_count, &chunks);
+    const size_t want = tcb::attention_scratch_floats(d->batch, d->heads, Hkv, d->seq_q, d->seq_kv, d->head_dim,
+                                                       ctx->sm_count, &chunks);
     if (want > ctx->attn_scratch_floats) {
         cudaDeviceSynchronize();
         if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);

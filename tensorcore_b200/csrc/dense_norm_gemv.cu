@@ -297,14 +297,19 @@ __global__ void __launch_bounds__(kDThreads) dense_norm_gemv_split_kernel(const 
             const int kk = st * kStageRows + r0 + kRowGroups * j;     // row within the tile
             if (k0 + kk >= k1) break;
             const uint4 wv = *reinterpret_cast<const uint4*>(src + j * kRowGroups * (kSplitCols * 2));
-            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+            // fp16 x fp16 products are exact in fp32, so converting both sides first and using the
+            // fp32 FMA gives the same bits as the mixed-precision FMA, with one conversion per pair
+            const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+            float2 wf[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) wf[e] = __half22float2(wh[e]);
 #pragma unroll
             for (int m = 0; m < MB; ++m) {
-                const uint16_t xb = __half_as_ushort(xn[m * sp.kc + kk]);
+                const float xf = __half2float(xn[m * sp.kc + kk]);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    acc[m][2 * e] = fma_h16(xb, static_cast<uint16_t>(ww[e]), acc[m][2 * e]);
-                    acc[m][2 * e + 1] = fma_h16(xb, static_cast<uint16_t>(ww[e] >> 16), acc[m][2 * e + 1]);
+                    acc[m][2 * e] = fmaf(xf, wf[e].x, acc[m][2 * e]);
+                    acc[m][2 * e + 1] = fmaf(xf, wf[e].y, acc[m][2 * e + 1]);
                 }
             }
         }

@@ -95,3 +95,31 @@ def test_long_list_and_wide_rows(tc, ctx, oracle):
         assert oracle.scaled_rms(by2.to_numpy((1, N2), np.float32), want2) <= 1e-4
     assert tc.take_device_error(ctx) == 0
     s.close()
+
+
+@pytest.mark.parametrize("K", [256, 512, 768, 1280, 1536, 2816])
+def test_narrow_and_ragged_bands(tc, ctx, oracle, K):
+    """K ranges as tensor parallelism cuts them: fewer than four groups (one narrow band), and a
+    last band of one, two or three groups after full ones; a chain of two operations so that the
+    second takes its input from the first one's accumulators."""
+    rng = np.random.default_rng(K)
+    N = 2 * K                                   # the second operation reads all of the first one's rows
+    W1 = oracle.quantize_weights((rng.standard_normal((N, K)) * 0.05).astype(np.float16), 0)
+    W2 = oracle.quantize_weights((rng.standard_normal((300, N)) * 0.05).astype(np.float16), 0) if N % 256 == 0 else None
+    X = rng.standard_normal((1, K)).astype(np.float16)
+    bx, bw1 = ctx.buffer_from_array(X), ctx.buffer_from_array(W1)
+    y1 = ctx.buffer(N * 2)
+    s = ctx.stream()
+    bw2 = ctx.buffer_from_array(W2)
+    y2 = ctx.buffer(300 * 2)
+    for rep in range(2):
+        ctx.gemv_quantized_async(bx, bw1, y1, 0, 1, N, K, s)
+        ctx.gemv_quantized_async(y1, bw2, y2, 0, 1, 300, N, s)
+        s.sync()
+        assert "persistent" in tc.cuda_last_kernel_name()
+        r1 = oracle.gemv_quantized(X, W1, 0, N)
+        assert oracle.scaled_rms(y1.to_numpy((1, N), np.float16), r1) <= 3e-4
+        r2 = oracle.gemv_quantized(r1, W2, 0, 300)
+        assert oracle.scaled_rms(y2.to_numpy((1, 300), np.float16), r2) <= 2e-3
+    assert tc.take_device_error(ctx) == 0
+    s.close()

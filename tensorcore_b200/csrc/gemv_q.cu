@@ -606,13 +606,27 @@ cudaError_t launch_gemv_q(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t
     // It rounds dequantised weights to fp16, which only the fp16-activation bound allows.
     const bool want_tc = env.variant == VARIANT_TC ||
                          (env.variant == VARIANT_AUTO && a.M >= kTcMinBatch);
-    if (want_tc && a.fmt == FMT_Q4_0 && !a.x_f32 && !fuse) {
+    // The fused RMSNorm form takes it too, behind a pass that normalises the rows into the stream's
+    // scratch as fp16 (one more rounding, inside the same bound).
+    const size_t slab_rows = a.M < 32 ? a.M : 32;
+    const size_t norm_need = slab_rows * static_cast<size_t>(a.K) * 2 + slab_rows * 4;
+    const bool fuse_tc = fuse && a.norm_scratch && a.norm_scratch_bytes >= norm_need && a.K % 256 == 0;
+    if (want_tc && a.fmt == FMT_Q4_0 && !a.x_f32 && (!fuse || fuse_tc)) {
         bool done = true;
         for (int m0 = 0; m0 < a.M; m0 += 32) {
             GemvQArgs s = a;
             s.M = (a.M - m0) < 32 ? (a.M - m0) : 32;
             s.X = static_cast<const uint8_t*>(a.X) + static_cast<size_t>(m0) * a.K * xsz;
             s.Y = static_cast<uint8_t*>(a.Y) + static_cast<size_t>(m0) * a.N * ysz;
+            if (fuse) {
+                float* rstd = reinterpret_cast<float*>(static_cast<uint8_t*>(a.norm_scratch) + slab_rows * static_cast<size_t>(a.K) * 2);
+                const cudaError_t ne = launch_norm_forward(s.X, a.gamma, nullptr, a.norm_scratch, nullptr, rstd, s.M, a.K,
+                                                           a.eps, stream);
+                if (ne != cudaSuccess) { err = ne; break; }
+                ++count;
+                s.X = a.norm_scratch;
+                s.gamma = nullptr;
+            }
             const cudaError_t te = launch_gemv_q4_tc(s, env, stream, &used);
             if (te == cudaErrorNotSupported && m0 == 0) { done = false; break; }
             if (te != cudaSuccess) { err = te; break; }

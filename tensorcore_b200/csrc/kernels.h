@@ -34,6 +34,11 @@ struct GemvQArgs {
     int fmt = 0, M = 0, N = 0, K = 0;
     bool x_f32 = false, y_f32 = false;
     float eps = 0.f;
+    // scratch of the stream the call runs on, for the batched fused form (M >= 5, fp16): room for
+    // min(M, 32) normalised rows of K halves and as many floats; without it that form takes the
+    // integer dot-product kernels, four rows per pass
+    void* norm_scratch = nullptr;
+    size_t norm_scratch_bytes = 0;
 };
 
 struct DenseNormGemvArgs {

@@ -187,7 +187,7 @@ bool managed(const tc_buffer* b) { return b->kind == BUF_MANAGED || b->kind == B
 // Scratch of the dense fused GEMV (partial sums of the K ranges, one ticket counter per column
 // strip), one per CUDA stream: calls on a stream are ordered, calls on different streams must not
 // share it.  Grown on demand, freed when the context goes.
-struct DenseScratch { float* f = nullptr; size_t nf = 0; int* c = nullptr; size_t nc = 0; };
+struct DenseScratch { float* f = nullptr; size_t nf = 0; int* c = nullptr; size_t nc = 0; void* norm = nullptr; size_t norm_bytes = 0; };
 std::mutex g_dense_mutex;
 std::unordered_map<cudaStream_t, DenseScratch> g_dense;
 
@@ -201,6 +201,7 @@ void dense_scratch_for(tc_context* ctx, cudaStream_t st, tcb::DenseNormGemvArgs*
         for (auto& kv : g_dense) {
             if (kv.second.f) cudaFree(kv.second.f);
             if (kv.second.c) cudaFree(kv.second.c);
+            if (kv.second.norm) cudaFree(kv.second.norm);
         }
         g_dense.clear();
     }
@@ -209,7 +210,7 @@ void dense_scratch_for(tc_context* ctx, cudaStream_t st, tcb::DenseNormGemvArgs*
         cudaStreamSynchronize(st);        // an earlier call on this stream may still use the old one
         if (d.f) cudaFree(d.f);
         if (d.c) cudaFree(d.c);
-        d = DenseScratch();
+        d.f = nullptr; d.c = nullptr; d.nf = 0; d.nc = 0;
         const size_t wf = nf + nf / 2, wc = nc * 2;
         if (cudaMalloc(reinterpret_cast<void**>(&d.f), wf * sizeof(float)) != cudaSuccess ||
             cudaMalloc(reinterpret_cast<void**>(&d.c), wc * sizeof(int)) != cudaSuccess ||
@@ -217,7 +218,7 @@ void dense_scratch_for(tc_context* ctx, cudaStream_t st, tcb::DenseNormGemvArgs*
             (void)cudaGetLastError();
             if (d.f) cudaFree(d.f);
             if (d.c) cudaFree(d.c);
-            d = DenseScratch();
+            d.f = nullptr; d.c = nullptr; d.nf = 0; d.nc = 0;
             return;                        // the launcher falls back to the kernel that needs none
         }
         d.nf = wf;
@@ -225,11 +226,39 @@ void dense_scratch_for(tc_context* ctx, cudaStream_t st, tcb::DenseNormGemvArgs*
     }
     a->scratch = d.f; a->scratch_floats = d.nf; a->counters = d.c; a->counters_n = d.nc;
 }
+// Room for the normalised rows of the batched fused RMSNorm GEMV (the tensor-core kernel reads them as
+// plain fp16 activations).
+size_t norm_scratch_need(const tcb::GemvQArgs& a) {
+    if (!a.gamma || a.x_f32 || a.fmt != 0 || a.M < 5 || a.K % 256 != 0) return 0;
+    const size_t rows = a.M < 32 ? a.M : 32;
+    return rows * static_cast<size_t>(a.K) * 2 + rows * 4;
+}
+void norm_scratch_for(cudaStream_t st, size_t need, tcb::GemvQArgs* a) {
+    if (need == 0) return;
+    std::lock_guard<std::mutex> lock(g_dense_mutex);
+    DenseScratch& d = g_dense[st];
+    if (d.norm_bytes < need) {
+        cudaStreamSynchronize(st);        // an earlier call on this stream may still use the old one
+        if (d.norm) cudaFree(d.norm);
+        d.norm = nullptr;
+        d.norm_bytes = 0;
+        const size_t want = need > (1u << 20) ? need + need / 2 : (1u << 20);
+        if (cudaMalloc(&d.norm, want) != cudaSuccess) {
+            (void)cudaGetLastError();
+            d.norm = nullptr;
+            return;                        // the launcher then uses the kernels that need no scratch
+        }
+        d.norm_bytes = want;
+    }
+    a->norm_scratch = d.norm;
+    a->norm_scratch_bytes = d.norm_bytes;
+}
 void free_dense_scratch() {
     std::lock_guard<std::mutex> lock(g_dense_mutex);
     for (auto& kv : g_dense) {
         if (kv.second.f) cudaFree(kv.second.f);
         if (kv.second.c) cudaFree(kv.second.c);
+        if (kv.second.norm) cudaFree(kv.second.norm);
     }
     g_dense.clear();
 }
@@ -866,7 +895,18 @@ tc_status_t submit_pending(tc_stream* s) {
     bind_device(ctx);
     bool any_staged = false;
     uint64_t sig = 1469598103934665603ull;
+    tcb::GemvQArgs scratch_of;          // the stream's scratch for normalised rows, sized for the widest operation
+    {
+        size_t need = 0;
+        for (const RecordedOp& op : s->pending) {
+            const size_t n = norm_scratch_need(op.a);
+            need = n > need ? n : need;
+        }
+        norm_scratch_for(s->s, need, &scratch_of);
+    }
     for (RecordedOp& op : s->pending) {
+        op.a.norm_scratch = scratch_of.norm_scratch;
+        op.a.norm_scratch_bytes = scratch_of.norm_scratch_bytes;
         // Device addresses are resolved now, not when the operation was recorded: a first
         // tc_buffer_map between the two moves a buffer to managed storage.
         op.a.X = op.X->dptr;
@@ -1221,6 +1261,7 @@ tc_status_t gemv_common(const GemvCall& c, tc_stream* stream, const char* opname
     if (e == cudaSuccess) e = prepare_output(ctx, op.Y, s0);
     int launches = 0;
     const char* name = "none";
+    if (e == cudaSuccess) norm_scratch_for(s0, norm_scratch_need(op.a), &op.a);
     if (e == cudaSuccess) e = launch_recorded(ctx, op, s0, false, &launches, &name);
     if (e == cudaSuccess) e = finish_output(op.Y, yb, s0);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s0);

@@ -105,7 +105,8 @@ def test_batched_agrees_with_the_streaming_kernel(tc, ctx, oracle, split_env):
 
 
 def test_domain(tc, ctx, oracle, split_env):
-    """fp32 activations, the fused RMSNorm form, Q8_0, small M and K % 256 != 0 stay off it."""
+    """fp32 activations, Q8_0, small M and K % 256 != 0 stay off it; the fused RMSNorm form takes it
+    behind a normalisation pass."""
     rng = np.random.default_rng(3)
     N, K, M = 256, 512, 16
     W = (rng.standard_normal((N, K)) * 0.02).astype(np.float16)
@@ -126,4 +127,31 @@ def test_domain(tc, ctx, oracle, split_env):
         ctx.gemv_quantized(x16, w4, y, 0, M, N, K)
         names["m16"] = tc.cuda_last_kernel_name()
     assert "tcgen05" in names.pop("m16")
+    assert "tcgen05" in names.pop("fused")
     assert all("tcgen05" not in n for n in names.values()), names
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 1024, 2048), (16, 4096, 4096), (32, 512, 8192), (40, 300, 1024)])
+def test_fused_rmsnorm_batched_matches_oracle(tc, ctx, oracle, M, N, K):
+    """Fused RMSNorm + Q4_0 GEMV with fp16 activations and M >= 5: rows normalised to fp16 in the
+    stream's scratch, then the tensor-core kernel.  Bar: the 2e-3 of fp16 activations."""
+    rng = np.random.default_rng(M * 7 + N)
+    W = (rng.standard_normal((N, K)) * 0.02).astype(np.float16)
+    X = (rng.standard_normal((M, K)) * 1.5).astype(np.float16)
+    gam = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    Wq = oracle.quantize_weights(W, 0)
+    want = oracle.fused_rmsnorm_gemv_quantized(X, gam, Wq, 0, N)
+    with ctx.buffer_from_array(Wq) as w4, ctx.buffer_from_array(X) as bx, ctx.buffer_from_array(gam) as bg, \
+            ctx.buffer(M * N * 2) as by:
+        ctx.fused_rmsnorm_gemv_quantized(bx, bg, w4, by, 0, M, N, K, 1e-5)
+        assert "tcgen05" in tc.cuda_last_kernel_name()
+        got = by.to_numpy((M, N), np.float16)
+        assert oracle.scaled_rms(got, want) <= TOL
+        # the same recorded on a stream (twice: the second submission may replay a captured graph)
+        s = ctx.stream()
+        for _ in range(3):
+            ctx.gemv_quantized_async(bx, w4, by, 0, M, N, K, s)
+            tc.fused_rmsnorm_gemv_quantized_ex(ctx, bx, bg, w4, by, 0, M, N, K, 1e-5, "f16", "f16", s)
+            s.sync()
+            assert oracle.scaled_rms(by.to_numpy((M, N), np.float16), want) <= TOL
+        s.close()

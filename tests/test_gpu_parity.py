@@ -213,7 +213,10 @@ def test_fused_rmsnorm_gemv_quantized(tc, ctx, oracle, tag, shape):
     gam = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32).astype(np.float16)
     got = gpu_gemv(tc, ctx, X, Wq, fmt, N, gamma=gam)
     want = oracle.fused_rmsnorm_gemv_quantized(X, gam, Wq, fmt, N, 1e-5)
-    assert oracle.scaled_rms(got, want) <= TOL_VS_ORACLE_F16
+    # Q4_0 with five or more fp16 rows runs on the tensor-core kernel (rows normalised to fp16, weights
+    # dequantised to fp16): the 2e-3 bound of fp16 activations applies there, as in test_gpu_batched.py
+    batched = fmt == 0 and M >= 5 and K % 256 == 0
+    assert oracle.scaled_rms(got, want) <= (TOL_F16_ACT if batched else TOL_VS_ORACLE_F16)
     # fp32 form
     Xf = rng.standard_normal((M, K)).astype(np.float32)
     gf = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)

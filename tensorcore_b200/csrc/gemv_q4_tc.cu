@@ -31,7 +31,9 @@
 // Accuracy: products are exact in fp32 inside the MMA, accumulation is fp32; the only extra
 // rounding against the reference's fp32 dequant-dot is the fp16 rounding of (q-8)*d, a scaled
 // RMS error of about 2e-4 - inside the 2e-3 bound that applies to fp16 activations, outside the
-// 1e-4 bound of fp32 activations, which therefore never take this path.
+// 1e-4 bound of fp32 activations, which therefore never take this path.  The fused RMSNorm form
+// reaches this kernel with its rows already normalised and rounded to fp16 by a separate pass
+// (one more rounding of the same size, same bound).
 #include "kernels.h"
 #include "sm100_prims.cuh"
 #include "tensor_map.h"

@@ -562,6 +562,8 @@ def main() -> None:
             print(json.dumps(run_reference_arm(args)), flush=True)
         return
     if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        # stdout carries the one JSON line and nothing else: NCCL's version banner goes to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         from tensorcore_b200 import tp
         out = tp.run_bench(args)
         if rank == 0 and out is not None:

@@ -195,6 +195,7 @@ __device__ __forceinline__ float rstd_from_flagged_slots(const float2* slots, in
 // the completed value and the knowledge that it is complete come in the same load, no barrier in
 // between.  Fused RMSNorm: quantises x * gamma and leaves each band's sum of squares, with a flag,
 // in its slot.
+template <bool SYS>
 __device__ void stage_bands_flow(const MegaOp& op, const DecodeParams& p, uint8_t* smem, float* scratch,
                                  uint32_t band_lo, uint32_t band_hi, int nthreads, volatile int* abort_s) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;     // the consumers are the CTA's first warps
@@ -231,7 +232,7 @@ __device__ void stage_bands_flow(const MegaOp& op, const DecodeParams& p, uint8_
                     const long long t0 = clock64();
                     while (!done) {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) a[e] = ld_pairs(src + 2 * e, p.n_ranks > 1);
+                        for (int e = 0; e < 4; ++e) a[e] = ld_pairs(src + 2 * e, SYS);
                         done = true;
 #pragma unroll
                         for (int e = 0; e < 4; ++e) done = done && a[e].y == want && a[e].w == want;
@@ -485,11 +486,12 @@ __device__ void zero_epoch(const MegaOp* ops, int b, int e, float2* pool2, uint3
     }
 }
 
+template <bool MULTI>
 __device__ void keep_house(const DecodeParams& p, const MegaOp* ops, const uint16_t* ep_op, int n_epochs,
                            volatile int* ctl, float* jscale, int jp) {
     const int lane = threadIdx.x & 31;
     float2* pool2 = reinterpret_cast<float2*>(p.pool);
-    const bool multi = p.n_ranks > 1;
+    constexpr bool multi = MULTI;
     unsigned long long* counter = p.counter + 4 * jp;    // each housekeeping warp has its own, 32 bytes apart
     unsigned long long target = p.base;
     const unsigned long long per_round = static_cast<unsigned long long>(gridDim.x) * (multi ? p.n_ranks : 1);
@@ -560,6 +562,9 @@ __device__ void keep_house(const DecodeParams& p, const MegaOp* ops, const uint1
     if (ctl[0] && lane == 0) atomicOr(p.err, ERR_WAIT_TIMEOUT);
 }
 
+// MULTI: tensor parallel (results may be added into other ranks' accumulators, system-scope loads and
+// arrival rounds); the one-GPU instance carries none of that in its loops.
+template <bool MULTI>
 __global__ void __launch_bounds__(kDecodeMaxThreads, 1) decode_q4_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);                      // [kDecodeMaxSlots]
@@ -675,7 +680,7 @@ __global__ void __launch_bounds__(kDecodeMaxThreads, 1) decode_q4_kernel(const D
 
     if (warp >= nwc + kProducerWarps) {
         const int jp = warp - nwc - kProducerWarps;
-        keep_house(p, ops, ep_op, p.n_epochs, ctl, reinterpret_cast<float*>(smem + p.off_jscale) + jp * p.jscale_cap, jp);
+        keep_house<MULTI>(p, ops, ep_op, p.n_epochs, ctl, reinterpret_cast<float*>(smem + p.off_jscale) + jp * p.jscale_cap, jp);
         return;
     }
     if (warp >= nwc) {
@@ -734,7 +739,7 @@ __global__ void __launch_bounds__(kDecodeMaxThreads, 1) decode_q4_kernel(const D
             }
         }
         if (rec.n) {
-            stage_bands_flow(ops[o], p, smem, scratch, rec.band_lo, rec.band_hi, nct, &ctl[0]);
+            stage_bands_flow<MULTI>(ops[o], p, smem, scratch, rec.band_lo, rec.band_hi, nct, &ctl[0]);
         } else {
             consumer_sync(nct);   // keeps the barrier count of stage_bands (one per phase at least)
         }
@@ -760,7 +765,7 @@ __global__ void __launch_bounds__(kDecodeMaxThreads, 1) decode_q4_kernel(const D
             float out[1] = {0.f};
             group_dot_i16<FMT_Q4_0, 1, true>(w, xs, sx2, static_cast<int>(d.y & 0xffffu), 0, 0, 0, out);
             if (static_cast<uint32_t>(lane) < ((d.y >> 16) & 63u)) {
-                if (d.y >> 24) {     // tensor parallel: into every rank's accumulators
+                if (MULTI && (d.y >> 24)) {     // tensor parallel: into every rank's accumulators
                     for (int r = 0; r < p.n_ranks; ++r)
                         red_add_pair_sys(reinterpret_cast<float2*>(p.peer_pool[r]) + d.x + lane, out[0]);
                 } else {
@@ -789,7 +794,9 @@ inline bool span_hits(const DecodeSpan* v, int n, DecodeSpan r) {
 }  // namespace
 
 cudaError_t init_decode_kernel(int smem_optin) {
-    return cudaFuncSetAttribute(decode_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+    cudaError_t e = cudaFuncSetAttribute(decode_q4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(decode_q4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
 }
 
 cudaError_t encode_decode_maps(const MegaOp* host_ops, int n_ops, void* host_maps) {
@@ -1090,7 +1097,9 @@ cudaError_t launch_decode(const MegaOp* host_ops, const DecodePlan& plan, const 
     const size_t smem = static_cast<size_t>(off) + static_cast<size_t>(warps) * ns * kBoxBytes;
     void* args[] = {&p};
     // `warps` consumer warps, the producer warps and the housekeeping warps
-    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(decode_q4_kernel), dim3(grid),
+    const void* kernel = dev.n_ranks > 1 ? reinterpret_cast<const void*>(decode_q4_kernel<true>)
+                                         : reinterpret_cast<const void*>(decode_q4_kernel<false>);
+    return cudaLaunchCooperativeKernel(kernel, dim3(grid),
                                        dim3((warps + kProducerWarps + kKeeperWarps) * 32), args, smem, stream);
 }
 

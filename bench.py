@@ -562,8 +562,10 @@ def main() -> None:
             print(json.dumps(run_reference_arm(args)), flush=True)
         return
     if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
-        # stdout carries the one JSON line and nothing else: NCCL's version banner goes to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        # stdout carries the one JSON line and nothing else: at NCCL_DEBUG=VERSION the library prints
+        # its version banner there
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         from tensorcore_b200 import tp
         out = tp.run_bench(args)
         if rank == 0 and out is not None:

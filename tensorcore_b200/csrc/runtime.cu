@@ -1746,6 +1746,7 @@ static tc_status_t raw_gemv(tc_context* ctx, const void* X, const void* gamma, b
     a.X = X; a.Y = Y; a.gamma = fused ? gamma : nullptr;
     a.fmt = static_cast<int>(fmt); a.M = M; a.N = N; a.K = K;
     a.x_f32 = xd == TC_DTYPE_F32; a.y_f32 = yd == TC_DTYPE_F32; a.eps = eps;
+    norm_scratch_for(static_cast<cudaStream_t>(cuda_stream), norm_scratch_need(a), &a);
     int launches = 0;
     const char* name = "none";
     const cudaError_t e = tcb::launch_gemv_q(a, make_env(ctx, true),

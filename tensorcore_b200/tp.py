@@ -352,6 +352,113 @@ class FusedBackend(CudaBackend):
         return self.torch.cuda.ExternalStream(h.value, device=self.device)
 
 
+class BatchedStep:
+    """One decode step for `batch` rows on the shard a TPDecoder already holds: one kernel per
+    projection on a torch stream with fp16 activations (five rows or more take the tensor-core
+    kernel), the partial sums of the K-split projections all-reduced in fp32 by NCCL and rounded
+    to fp16 for the next projection, the per-rank logits gathered as [rank][row][vocab / ranks].
+    The step is captured once into a CUDA graph (eager launches if the capture is refused)."""
+
+    def __init__(self, dec: TPDecoder, ctx, dist, device, batch: int, collectives: bool = True):
+        import torch
+
+        import tensorcore_b200 as tc
+        self.torch, self.tc, self.dist = torch, tc, dist
+        self.dec, self.ctx, self.device, self.M = dec, ctx, device, int(batch)
+        self.world = dec.plan.world
+        self.collectives = collectives and self.world > 1
+        s, plan, M = dec.plan.shape, dec.plan, self.M
+        f16, f32 = torch.float16, torch.float32
+        def z(n, dt):
+            return torch.zeros(M, n, dtype=dt, device=device)
+        self.x_in = z(s.d_model, f16)
+        self.cur = z(s.d_model, f16)
+        self.sum32 = z(s.d_model, f32)
+        loc = lambda which: z(plan.col(which)[1] - plan.col(which)[0], f16)
+        self.q, self.k, self.v = loc("attn_q"), loc("attn_k"), loc("attn_v")
+        self.g, self.u = loc("ffn_gate"), loc("ffn_up")
+        self.l_loc = z(s.vocab // self.world, f16)
+        self.logits_ranked = torch.zeros(self.world, M, s.vocab // self.world, dtype=f16, device=device)
+        self.gam = [{k: lw[k].to(f16) for k in ("attn_norm", "ffn_norm")} for lw in dec.w]
+        self.out_gam = dec.out_norm.to(f16)
+        self.stream = torch.cuda.Stream(device)
+        self.graph = None
+        self.launches = 0
+
+    def _gemv(self, x, w, y, N, K, gamma=None):
+        tc, st = self.tc, self.torch.cuda.current_stream().cuda_stream
+        yd = "f32" if y.dtype == self.torch.float32 else "f16"
+        if gamma is None:
+            tc.raw_gemv_quantized(self.ctx, x.data_ptr(), w, y.data_ptr(), 0, self.M, N, K, "f16", yd, st)
+        else:
+            tc.raw_fused_rmsnorm_gemv_quantized(self.ctx, x.data_ptr(), gamma.data_ptr(), w, y.data_ptr(), 0,
+                                                self.M, N, K, 1e-5, "f16", yd, st)
+        self.launches += 1
+
+    def _reduce(self):
+        if self.collectives:
+            self.dist.all_reduce(self.sum32)
+        self.cur.copy_(self.sum32)            # fp32 -> fp16 for the next projection
+
+    def _step(self):
+        dec, s, plan = self.dec, self.dec.plan.shape, self.dec.plan
+        d = s.d_model
+        self.launches = 0                     # kernels of this library in one step
+        self.cur.copy_(self.x_in)
+        for lw, gm in zip(dec.w, self.gam):
+            for p, y in (("attn_q", self.q), ("attn_k", self.k), ("attn_v", self.v)):
+                n0, n1 = plan.col(p)
+                self._gemv(self.cur, lw[p], y, n1 - n0, d, gamma=gm["attn_norm"])
+            k0, k1 = plan.kslice("attn_output")
+            self._gemv(self.q, lw["attn_output"], self.sum32, d, k1 - k0)     # q stands in for the attention mix
+            self._reduce()
+            for p, y in (("ffn_gate", self.g), ("ffn_up", self.u)):
+                n0, n1 = plan.col(p)
+                self._gemv(self.cur, lw[p], y, n1 - n0, d, gamma=gm["ffn_norm"])
+            k0, k1 = plan.kslice("ffn_down")
+            self._gemv(self.g, lw["ffn_down"], self.sum32, d, k1 - k0)        # gate stands in for SwiGLU
+            self._reduce()
+        n0, n1 = plan.col("output")
+        self._gemv(self.cur, dec.lm_head, self.l_loc, n1 - n0, d, gamma=self.out_gam)
+        if self.collectives:
+            self.dist.all_gather_into_tensor(self.logits_ranked, self.l_loc)
+        else:
+            self.logits_ranked[0].copy_(self.l_loc)
+
+    def prepare(self, use_graph: bool = True) -> None:
+        torch = self.torch
+        with torch.cuda.stream(self.stream):
+            for _ in range(2):                # scratch of this stream and NCCL's channels exist before capture
+                self._step()
+        self.stream.synchronize()
+        if not use_graph:
+            return
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self.stream):
+                self._step()
+            self.graph = g
+        except Exception:                     # refused capture: eager launches, same kernels
+            self.graph = None
+            torch.cuda.synchronize()
+
+    def run(self) -> None:
+        with self.torch.cuda.stream(self.stream):
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self._step()
+
+    def logits(self):
+        """[batch][vocab]"""
+        P, M, n = self.logits_ranked.shape
+        return self.logits_ranked.permute(1, 0, 2).reshape(M, P * n)
+
+
+def batch_input(shape: LlamaShape, batch: int) -> np.ndarray:
+    return np.random.default_rng(X_SEED + 1000 + batch).standard_normal((batch, shape.d_model)).astype(np.float16)
+
+
 def _exchange_records(dist, record: bytes, world: int) -> bytes:
     if world == 1:
         return record
@@ -360,9 +467,10 @@ def _exchange_records(dist, record: bytes, world: int) -> bytes:
     return b"".join(got)
 
 
-def _reference_logits(ctx, shape, device, x, solo: TPLink):
+def _reference_logits(ctx, shape, device, x, solo: TPLink, xb=None):
     """The same token on ONE GPU through the same data flow (world size 1): what the ranks'
-    gathered logits are compared with."""
+    gathered logits are compared with.  With `xb` ([batch][d_model] fp16) also the batched step's
+    logits from the same weights; returns (logits, batched logits or None)."""
     import torch
     be = FusedBackend(ctx, shape, 0, device, solo)
     dec = TPDecoder(TPPlan(shape, 1, 0), be, 0)
@@ -373,9 +481,19 @@ def _reference_logits(ctx, shape, device, x, solo: TPLink):
     be.run()
     be.sync()
     out = dec.logits.clone()
+    outb = None
+    if xb is not None:
+        step = BatchedStep(dec, ctx, None, device, xb.shape[0], collectives=False)
+        step.x_in.copy_(torch.from_numpy(xb))
+        torch.cuda.synchronize()
+        step.prepare(use_graph=False)
+        step.run()
+        torch.cuda.synchronize()
+        outb = step.logits().clone()
+        del step
     del dec, be
     torch.cuda.empty_cache()
-    return out
+    return out, outb
 
 
 def _logit_distance(dist, torch, logits, device, rank, reference) -> float:
@@ -392,9 +510,24 @@ def _logit_distance(dist, torch, logits, device, rank, reference) -> float:
     return float(worst.item())
 
 
-def shallow_parity(shape, dist, torch, ctx, device, link: TPLink, solo) -> float:
+def _batched_distance(dist, torch, dec, ctx, device, rank, xb, reference_b, use_graph=True):
+    """Runs the batched step once on this rank's shard; (scaled-rms distance of its logits from
+    the one-GPU batched logits, max over ranks; the prepared step)."""
+    step = BatchedStep(dec, ctx, dist, device, xb.shape[0])
+    step.x_in.copy_(torch.from_numpy(xb))
+    torch.cuda.synchronize()
+    dist.barrier()
+    step.prepare(use_graph)
+    step.run()
+    step.stream.synchronize()
+    d = _logit_distance(dist, torch, step.logits().contiguous(), device, rank, reference_b)
+    return d, step
+
+
+def shallow_parity(shape, dist, torch, ctx, device, link: TPLink, solo, batch: int = 0):
     """The first two layers + lm_head of `shape` (nine dependent GEMVs), sharded over the ranks,
-    against the same model on one GPU: scaled rms of the logits, max over ranks."""
+    against the same model on one GPU: scaled rms of the logits, max over ranks - for the one-row
+    persistent launch and, with `batch`, for the batched step (second value, else None)."""
     import dataclasses
     small = dataclasses.replace(shape, name=shape.name + "-2layers", n_layers=2)
     rank, world = link.rank, link.world
@@ -403,16 +536,26 @@ def shallow_parity(shape, dist, torch, ctx, device, link: TPLink, solo) -> float
     dec.token()
     be.commit()
     x = np.random.default_rng(X_SEED).standard_normal(small.d_model).astype(np.float32)
+    xb = batch_input(small, batch) if batch else None
     dec.x_in.copy_(torch.from_numpy(x))
     torch.cuda.synchronize()
     dist.barrier()
     be.run()
     be.sync()
-    d = _logit_distance(dist, torch, dec.logits, device, rank, lambda: _reference_logits(ctx, small, device, x, solo))
+    ref = {}
+    def reference(which):
+        if not ref:
+            ref["one"], ref["batch"] = _reference_logits(ctx, small, device, x, solo, xb)
+        return ref[which]
+    d = _logit_distance(dist, torch, dec.logits, device, rank, lambda: reference("one"))
+    db = None
+    if batch:
+        db, step = _batched_distance(dist, torch, dec, ctx, device, rank, xb, lambda: reference("batch"))
+        del step
     dist.barrier()
     del dec, be
     torch.cuda.empty_cache()
-    return d
+    return d, db
 
 
 def _timed(dist, torch, be, dec, steps, device, hx=None, hl=None):
@@ -442,7 +585,23 @@ def _timed(dist, torch, be, dec, steps, device, hx=None, hl=None):
     return float(v[0].item()), float(v[1].item())
 
 
-def _run_model(args, shape, dist, torch, tc, ctx, device, link: TPLink, solo, local, check: bool):
+def _timed_batched(dist, torch, step, steps, device):
+    """max-over-ranks GPU ms for `steps` batched steps."""
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(step.stream)
+    for _ in range(steps):
+        step.run()
+    e1.record(step.stream)
+    step.stream.synchronize()
+    dist.barrier()
+    v = torch.tensor([e0.elapsed_time(e1)], device=device, dtype=torch.float64)
+    dist.all_reduce(v, op=dist.ReduceOp.MAX)
+    return float(v[0].item())
+
+
+def _run_model(args, shape, dist, torch, tc, ctx, device, link: TPLink, solo, local, check: bool, batch: int = 0):
     """Builds the rank's shard, checks the gathered logits against a one-GPU run of the same
     token, times `args.steps` tokens.  Returns a dict on every rank."""
     from bench import ClockSampler
@@ -463,14 +622,19 @@ def _run_model(args, shape, dist, torch, tc, ctx, device, link: TPLink, solo, lo
         be.run()
     be.sync()
     parity = None
+    xb = batch_input(shape, batch) if batch else None
+    ref = {}
+    def reference(which):
+        if not ref:
+            ref["one"], ref["batch"] = _reference_logits(ctx, shape, device, x, solo, xb)
+        return ref[which]
     if check:
         # Whole model: the ranks' gathered logits against a one-GPU run of the same token.  Over
         # hundreds of dependent GEMVs with fp16 hand-offs a different (equally valid) summation
         # order flips fp16 roundings and the flips compound, so the bar is the one the one-GPU
         # benchmark uses between two of its own runs; the stated 2e-3 is checked on a two-layer
         # model by shallow_parity().
-        parity = _logit_distance(dist, torch, dec.logits, device, rank,
-                                 lambda: _reference_logits(ctx, shape, device, x, solo))
+        parity = _logit_distance(dist, torch, dec.logits, device, rank, lambda: reference("one"))
         if not parity <= 2e-2:
             raise SystemExit(f"tensor-parallel logits differ from the one-GPU logits: scaled rms {parity}")
     for _ in range(max(3, args.warmup)):
@@ -491,6 +655,31 @@ def _run_model(args, shape, dist, torch, tc, ctx, device, link: TPLink, solo, lo
     res = {"gpu_ms": gpu_ms, "e2e_s": e2e_s, "clocks": clocks, "parity": parity,
            "launches_per_token": 1, "collectives_per_token": dec.collectives_per_token(),
            "gemvs_per_token": dec.gemvs_per_token(), "weight_bytes_per_rank": plan.weight_bytes_local(0)}
+    if batch:
+        # The same shard, `batch` rows per step: per-projection kernels + NCCL, one CUDA graph per step.
+        if check:
+            bpar, step = _batched_distance(dist, torch, dec, ctx, device, rank, xb, lambda: reference("batch"))
+            if not bpar <= 2e-2:
+                raise SystemExit(f"batched tensor-parallel logits differ from the one-GPU logits: scaled rms {bpar}")
+        else:
+            bpar = None
+            step = BatchedStep(dec, ctx, dist, device, batch)
+            step.x_in.copy_(torch.from_numpy(xb))
+            step.prepare()
+        bsteps = max(3, args.steps // 3)
+        for _ in range(3):
+            step.run()
+        step.stream.synchronize()
+        bms = _timed_batched(dist, torch, step, bsteps, device) / bsteps
+        bfinite = bool(torch.isfinite(step.logits().float()).all().item())
+        berr = tc.take_device_error(ctx)
+        bflag = torch.tensor([0 if (bfinite and not berr) else 1], device=device)
+        dist.all_reduce(bflag)
+        if int(bflag.item()):
+            raise SystemExit(f"invalid batched run on some rank: finite={bfinite} device_error={berr}")
+        res["batch"] = {"rows": batch, "ms_per_step": bms, "parity": bpar, "graph": step.graph is not None,
+                        "kernels_per_step": step.launches, "steps": bsteps}
+        del step
     del dec, be
     torch.cuda.empty_cache()
     return res
@@ -519,15 +708,17 @@ def run_bench(args):
     link = TPLink(ctx, dist, world, rank)
     solo = TPLink(ctx, dist, 1, 0) if rank == 0 else None      # rank 0's one-GPU runs of the same tokens
     shape = D.LLAMA_7B
-    shallow = shallow_parity(shape, dist, torch, ctx, device, link, solo)
+    shallow, shallow_b = shallow_parity(shape, dist, torch, ctx, device, link, solo, batch=8)
     if not shallow <= 2e-3:
         raise SystemExit(f"tensor-parallel logits of the two-layer model differ from one GPU: scaled rms {shallow}")
-    r7 = _run_model(args, shape, dist, torch, tc, ctx, device, link, solo, local, check=True)
+    if not shallow_b <= 2e-3:
+        raise SystemExit(f"batched tensor-parallel logits of the two-layer model differ from one GPU: scaled rms {shallow_b}")
+    r7 = _run_model(args, shape, dist, torch, tc, ctx, device, link, solo, local, check=True, batch=8)
     r70 = None
     if not args.no_70b:
         sub = type(args)(**vars(args))
         sub.steps = max(5, min(30, args.steps // 5))
-        r70 = _run_model(sub, D.LLAMA_70B, dist, torch, tc, ctx, device, link, solo, local, check=True)
+        r70 = _run_model(sub, D.LLAMA_70B, dist, torch, tc, ctx, device, link, solo, local, check=True, batch=8)
         r70["steps"] = sub.steps
     dist.barrier()
     out = None
@@ -566,6 +757,18 @@ def run_bench(args):
             "tp_parity_full_depth": r7["parity"],
             "clocks": r7["clocks"],
         }
+        def batch_record(r, weight_bytes):
+            b = r["batch"]
+            ms = b["ms_per_step"]
+            return {"rows": b["rows"], "ms_per_step": round(ms, 4), "tok_s": round(b["rows"] * 1e3 / ms, 1),
+                    "weight_GBs": round(weight_bytes / ms / 1e6, 1),
+                    "frac": round(weight_bytes / ms / 1e6 / (peak * world), 4), "tp_parity": b["parity"],
+                    "cuda_graph": b["graph"], "kernels_per_step": b["kernels_per_step"],
+                    "collectives_per_step": r["collectives_per_token"],
+                    "path": "one kernel per projection (tcgen05 kernel for 5+ rows) + NCCL all-reduce of the "
+                            "K-split projections' fp32 partial sums"}
+        out["batch8"] = batch_record(r7, weight_b)
+        out["tp_parity_batch8"] = shallow_b
         if r70 is not None:
             s70 = D.LLAMA_70B
             ms70 = r70["gpu_ms"] / r70["steps"]
@@ -575,6 +778,7 @@ def run_bench(args):
                                           "frac": round(wb / ms70 / 1e6 / (peak * world), 4),
                                           "tp_parity": r70["parity"],
                                           "weight_bytes_per_rank": r70["weight_bytes_per_rank"]},
+                               "batch8": batch_record(r70, wb),
                                "weight_bytes_per_token": wb}
     return out
 

@@ -117,3 +117,53 @@ def test_tp_decoder_fused_backend_world1_matches_oracle_chain(tc, ctx, oracle):
         assert oracle.scaled_rms(dec.h[(shape.n_layers - 1) & 1].cpu().numpy()[None, :], cur) <= 2e-3
     assert tc.take_device_error(ctx) == 0
     be.stream.close()
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_batched_step_world1_matches_oracle_chain(tc, ctx, oracle, use_graph):
+    """The batched decode step of the tensor-parallel bench (eight rows, one kernel per projection,
+    fp32 partial sums rounded to fp16 between projections) on ONE GPU against the same chain on the
+    CPU; launched eagerly and replayed from a captured CUDA graph."""
+    import torch
+    from tensorcore_b200 import decode as D
+    from tensorcore_b200 import tp as TP
+    shape = D.tiny_shape()
+    device = torch.device("cuda", torch.cuda.current_device())
+
+    class Recording(TP.FusedBackend):
+        def weight(self, which, seed, rows, cols):
+            N, K = self.shape.proj_shape(which)
+            w = D.device_weights_fp16(N, K, seed, self.device)
+            self.host = getattr(self, "host", {})
+            ptr = super().weight(which, seed, rows, cols)
+            self.host[ptr] = oracle.quantize_weights(w.contiguous().cpu().numpy(), 0)
+            return ptr
+
+    be = Recording(ctx, shape, 0, device, TP.TPLink(ctx, None, 1, 0))
+    dec = TP.TPDecoder(TP.TPPlan(shape, 1, 0), be, 0)
+    M = 8
+    xb = TP.batch_input(shape, M)
+    g = lambda t: t.cpu().numpy()
+    f32 = lambda a: a.astype(np.float32)
+    cur = xb
+    for lw in dec.w:
+        q = oracle.fused_rmsnorm_gemv_quantized_f32(f32(cur), g(lw["attn_norm"]), be.host[lw["attn_q"]], 0, shape.d_model).astype(np.float16)
+        cur = oracle.gemv_quantized_f32(f32(q), be.host[lw["attn_output"]], 0, shape.d_model).astype(np.float16)
+        gate = oracle.fused_rmsnorm_gemv_quantized_f32(f32(cur), g(lw["ffn_norm"]), be.host[lw["ffn_gate"]], 0, shape.d_ff).astype(np.float16)
+        cur = oracle.gemv_quantized_f32(f32(gate), be.host[lw["ffn_down"]], 0, shape.d_model).astype(np.float16)
+    want = oracle.fused_rmsnorm_gemv_quantized_f32(f32(cur), g(dec.out_norm), be.host[dec.lm_head], 0, shape.vocab).astype(np.float16)
+
+    step = TP.BatchedStep(dec, ctx, None, device, M, collectives=False)
+    step.x_in.copy_(torch.from_numpy(xb))
+    torch.cuda.synchronize()
+    step.prepare(use_graph)
+    assert (step.graph is not None) == use_graph
+    for rep in range(3):
+        step.run()
+        step.stream.synchronize()
+        got = step.logits().cpu().numpy()
+        assert got.shape == want.shape
+        assert oracle.scaled_rms(got, want) <= 2e-3, rep
+    assert step.launches == 7 * shape.n_layers + 1
+    assert tc.take_device_error(ctx) == 0
+    be.stream.close()

@@ -564,7 +564,7 @@ def main() -> None:
     if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
         # stdout carries the one JSON line and nothing else: at NCCL_DEBUG=VERSION the library prints
         # its version banner there
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":     # unset: a system nccl.conf may say so
             os.environ["NCCL_DEBUG"] = "WARN"
         from tensorcore_b200 import tp
         out = tp.run_bench(args)

@@ -358,6 +358,33 @@ def gemv_cases(ctx, quick: bool = False) -> list[dict]:
         for b in ks + vs + [q, o]:
             b.close()
 
+    def gemm_case(name, M, N, K, iters):
+        """tc_gemm, fp16 in and out, fp32 accumulation, through the buffer API (each call returns
+        after the device is done, as the reference's does): host clock around the calls, against the
+        measured dense bf16 peak."""
+        rng = np.random.default_rng(M + N + K)
+        a = ctx.buffer_from_array(rng.standard_normal((M, K)).astype(np.float16))
+        b = ctx.buffer_from_array((rng.standard_normal((K, N)) * 0.05).astype(np.float16))
+        c = ctx.buffer(M * N * 2)
+        for _ in range(3):
+            tc.gemm(ctx, a, b, c, M, N, K)
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            tc.gemm(ctx, a, b, c, M, N, K)
+        us = (time.perf_counter() - t0) / iters * 1e6
+        tflops = 2.0 * M * N * K / us / 1e6
+        tpeak = None
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                tpeak = float(json.load(f)["bf16_tflops"])
+        except Exception:
+            tpeak = 1590.0
+        out.append({"config": name, "fmt": "f16", "M": M, "N": N, "K": K,
+                    "per_op": {"us": round(us, 2), "tflops": round(tflops, 1), "frac_tensor": round(tflops / tpeak, 4),
+                               "kernel": tc.cuda_last_kernel_name()}})
+        for x in (a, b, c):
+            x.close()
+
     it = 100 if quick else 200
     quant_case("config 1: Q4_0 4096x4096, fp32 x -> fp32 y", 0, 1, 4096, 4096, "f32", "f32", False, it)
     quant_case("config 1 through the fp16 ABI", 0, 1, 4096, 4096, "f16", "f16", False, it)
@@ -370,6 +397,8 @@ def gemv_cases(ctx, quick: bool = False) -> list[dict]:
     dense_case("tc_fused_layernorm_gemv, fp16 W 4096x11008", True, 1, 11008, 4096, it // 2)
     attention_case("tc_attention_forward, decode row: 32 heads x 128, 4096 keys (7B shape)", 1, 32, 32, 4096, 128, it // 2)
     attention_case("tc_attention_forward, decode row: 64 heads / 8 kv heads x 128, 8192 keys (70B shape)", 1, 64, 8, 8192, 128, it // 2)
+    gemm_case("tc_gemm fp16 4096 x 4096 x 4096", 4096, 4096, 4096, 20)
+    gemm_case("tc_gemm fp16 512 x 11008 x 4096 (a prefill block against a 7B projection)", 512, 11008, 4096, 20)
     return out
 
 

@@ -154,6 +154,21 @@ def fused_rmsnorm_gemv(X_f16, gamma_f16, W_f16, eps=1e-5) -> np.ndarray:
     return Y.view(np.float16)
 
 
+def gemm_f16(A_f16, B_f16, transpose_b=False, alpha=1.0, beta=0.0, C_f16=None, ref_narrowing=False) -> np.ndarray:
+    """alpha * A . op(B) + beta * C in the reference's order (lib/ops/gemm_cpu.cpp:544-568), stored with
+    IEEE round-to-nearest-even or, ref_narrowing, with the reference GEMM's own narrowing (:142-160)."""
+    A = np.ascontiguousarray(A_f16).view(np.uint16)
+    B = np.ascontiguousarray(B_f16).view(np.uint16)
+    M, K = A.shape
+    N = B.shape[0] if transpose_b else B.shape[1]
+    C = (np.zeros((M, N), dtype=np.uint16) if C_f16 is None
+         else np.ascontiguousarray(C_f16).view(np.uint16).copy())
+    _call(lib().orc_gemm_f16, _p(A), _p(B), _p(C), c_int(M), c_int(N), c_int(K), c_int(K),
+          c_int(B.shape[1]), c_int(N), c_int(1 if transpose_b else 0), c_float(alpha), c_float(beta),
+          c_int(1 if ref_narrowing else 0))
+    return C.view(np.float16)
+
+
 def fused_layernorm_gemv(X_f16, gamma_f16, beta_f16, W_f16, eps=1e-5) -> np.ndarray:
     X = np.ascontiguousarray(X_f16).view(np.uint16)
     g = np.ascontiguousarray(gamma_f16).view(np.uint16)
@@ -311,6 +326,28 @@ class RefLib:
         assert st == 0, st
         out = self._read(pq, nq, np.uint8)
         self._free(hw, hq)
+        return out
+
+    def gemm_f16(self, A_f16, B_f16, transpose_b=False, alpha=1.0, beta=0.0, C_f16=None) -> np.ndarray:
+        """tc_gemm of the reference's CPU backend (include/tensorcore/gemm.h:16-50), fp16 in and out."""
+        class Desc(ctypes.Structure):
+            _fields_ = [("M", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32), ("a", c_int), ("b", c_int),
+                        ("c", c_int), ("acc", c_int), ("ta", ctypes.c_bool), ("tb", ctypes.c_bool), ("alpha", c_float),
+                        ("beta", c_float), ("lda", ctypes.c_int32), ("ldb", ctypes.c_int32), ("ldc", ctypes.c_int32)]
+        A = np.ascontiguousarray(A_f16).view(np.uint16)
+        B = np.ascontiguousarray(B_f16).view(np.uint16)
+        M, K = A.shape
+        N = B.shape[0] if transpose_b else B.shape[1]
+        C = np.zeros((M, N), dtype=np.uint16) if C_f16 is None else np.ascontiguousarray(C_f16).view(np.uint16)
+        ha, _, _ = self._buf(A)
+        hb, _, _ = self._buf(B)
+        hc, pc, nc = self._buf(C)
+        d = Desc(M, N, K, 0, 0, 0, 2, False, bool(transpose_b), float(alpha), float(beta), 0, 0, 0)   # F16 = 0, F32 = 2
+        self.L.tc_gemm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+        st = self.L.tc_gemm(self.ctx, ctypes.byref(d), ha, hb, hc)
+        assert st == 0, st
+        out = self._read(pc, nc, np.uint16).reshape(M, N).view(np.float16)
+        self._free(ha, hb, hc)
         return out
 
     def gemv_quantized(self, X_f16, Wq, fmt, N) -> np.ndarray:

@@ -282,6 +282,53 @@ int orc_fused_rmsnorm_gemv(const uint16_t* X, const uint16_t* gamma, const uint1
     return 0;
 }
 
+/* The narrowing the reference's GEMM uses for its result (lib/ops/gemm_cpu.cpp:142-160), which is
+ * not the IEEE one of the quantized path: it adds the first dropped bit (ties go up, not to even)
+ * and ORs the sum into the exponent field, so a mantissa that carries out lands in the exponent
+ * only when the exponent's low bit was 0 (1.9998 becomes 1.0, not 2.0).  Kept for pinning the loop
+ * below against the reference bit for bit; parity targets use the IEEE narrowing. */
+static uint16_t gemm_ref_f32_to_f16(float x) {
+    union { float f; uint32_t u; } v = {x};
+    const uint32_t f = v.u;
+    const uint32_t sign = (f >> 16) & 0x8000u;
+    int32_t exp = (int32_t)((f >> 23) & 0xFF) - 127 + 15;
+    uint32_t mant = f & 0x7FFFFFu;
+    if (exp <= 0) {
+        if (exp < -10) return (uint16_t)sign;
+        mant |= 0x800000u;
+        const uint32_t shift = (uint32_t)(14 - exp);
+        const uint32_t round = (mant >> (shift - 1)) & 1u;
+        return (uint16_t)(sign | ((mant >> shift) + round));
+    }
+    if (exp >= 31) return (uint16_t)(sign | 0x7C00u | (mant ? 0x200u : 0u));
+    const uint32_t round = (mant >> 12) & 1u;
+    return (uint16_t)(sign | ((uint32_t)exp << 10) | ((mant >> 13) + round));
+}
+
+/* lib/ops/gemm_cpu.cpp:544-568 (the binary16 case): row-major A [M,K] (lda), B [K,N] or, transposed,
+ * [N,K] (ldb), C [M,N] (ldc); the products are added in k order in fp32;
+ * C = fp16(alpha * sum + beta * C), C not read when beta is 0.  ref_narrowing: 0 = IEEE
+ * round-to-nearest-even, 1 = the reference GEMM's own narrowing (see above). */
+int orc_gemm_f16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N, int K,
+                 int lda, int ldb, int ldc, int transpose_b, float alpha, float beta, int ref_narrowing) {
+    if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return -1;
+    for (int m = 0; m < M; ++m) {
+        for (int n = 0; n < N; ++n) {
+            float sum = 0.0f;
+            for (int k = 0; k < K; ++k) {
+                const uint16_t av = A[(size_t)m * lda + k];
+                const uint16_t bv = transpose_b ? B[(size_t)n * ldb + k] : B[(size_t)k * ldb + n];
+                sum += orc_f16_to_f32(av) * orc_f16_to_f32(bv);
+            }
+            const size_t idx = (size_t)m * ldc + n;
+            const float prev = (beta == 0.0f) ? 0.0f : orc_f16_to_f32(C[idx]);
+            const float out = alpha * sum + beta * prev;
+            C[idx] = ref_narrowing ? gemm_ref_f32_to_f16(out) : orc_f32_to_f16(out);
+        }
+    }
+    return 0;
+}
+
 /* lib/ops/training_cpu.cpp:858-935: mean in double then narrowed to fp32; centred second
  * moment in double; rstd = 1/sqrtf(float(var)+eps); row = fp16(((x-mean)*rstd)*gamma + beta). */
 int orc_fused_layernorm_gemv(const uint16_t* X, const uint16_t* gamma, const uint16_t* beta,

@@ -476,6 +476,21 @@ def rope_forward(ctx, X, cos_t, sin_t, batch, heads, seq, head_dim) -> None:
                                  int(head_dim)))
 
 
+class TCGemmDesc(Structure):          # tc_gemm_desc
+    _fields_ = [("M", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32), ("a_dtype", c_int),
+                ("b_dtype", c_int), ("c_dtype", c_int), ("accum_dtype", c_int), ("transpose_a", ctypes.c_bool),
+                ("transpose_b", ctypes.c_bool), ("alpha", c_float), ("beta", c_float), ("lda", ctypes.c_int32),
+                ("ldb", ctypes.c_int32), ("ldc", ctypes.c_int32)]
+
+
+def gemm(ctx, A, B, C, M, N, K, dtype="f16", accum="f32", transpose_a=False, transpose_b=False, alpha=1.0,
+         beta=0.0, lda=0, ldb=0, ldc=0) -> None:
+    """C = alpha * op(A) . op(B) + beta * C, row-major (tc_gemm; same arguments as the reference binding)."""
+    d = TCGemmDesc(int(M), int(N), int(K), _dtype(dtype), _dtype(dtype), _dtype(dtype), _dtype(accum),
+                   bool(transpose_a), bool(transpose_b), float(alpha), float(beta), int(lda), int(ldb), int(ldc))
+    _check(lib().tc_gemm(_h(ctx), byref(d), _h(A), _h(B), _h(C)))
+
+
 class TCAttentionDesc(Structure):     # tc_attention_desc
     _fields_ = [("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("seq_q", ctypes.c_int32),
                 ("seq_kv", ctypes.c_int32), ("head_dim", ctypes.c_int32), ("io_dtype", c_int),

@@ -576,6 +576,7 @@ cudaError_t set_smem(K kernel, int bytes) {
 
 cudaError_t init_gemv_kernels(int smem_optin) {
     cudaError_t e = init_tc_kernels(smem_optin);
+    if (e == cudaSuccess) e = init_gemm_tc_kernel(smem_optin);
     if (e != cudaSuccess) return e;
     e = init_decode_kernel(smem_optin);
     if (e != cudaSuccess) return e;

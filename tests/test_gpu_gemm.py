@@ -1,0 +1,88 @@
+"""GPU: tc_gemm (fp16 storage, fp32 accumulation) against the oracle's restatement of the
+reference's CPU loop (lib/ops/gemm_cpu.cpp:544-568), through the C ABI.
+
+The reference adds the K products in k order in fp32; the tensor-core kernel adds them in the
+MMA's order, the few-row kernel with fused multiply-adds.  Both keep fp32 sums, so results differ
+from the oracle by fp32 rounding of the sum and, after the fp16 store, by an occasional last-place
+flip: the bar is a scaled RMS of 3e-4 (one flipped element in a thousand is 1.5e-5)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL = 3e-4
+
+
+def _run(tc, ctx, A, B, tb, alpha=1.0, beta=0.0, C0=None, lda=0, ldb=0, ldc=0, M=None, N=None, K=None):
+    M = M if M is not None else A.shape[0]
+    K = K if K is not None else A.shape[1]
+    N = N if N is not None else (B.shape[0] if tb else B.shape[1])
+    a, b = ctx.buffer_from_array(A), ctx.buffer_from_array(B)
+    c_host = np.zeros((M, ldc or N), dtype=np.float16) if C0 is None else C0.copy()
+    c = ctx.buffer_from_array(c_host)
+    tc.gemm(ctx, a, b, c, M, N, K, transpose_b=tb, alpha=alpha, beta=beta, lda=lda, ldb=ldb, ldc=ldc)
+    out = c.to_numpy(c_host.shape, np.float16)
+    return out, tc.cuda_last_kernel_name()
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (256, 384, 512), (100, 72, 136), (513, 1000, 1024),
+                                   (32, 4096, 4096), (130, 264, 8)])
+@pytest.mark.parametrize("tb", [False, True])
+def test_tensor_core_gemm_matches_oracle(tc, ctx, oracle, shape, tb):
+    M, N, K = shape
+    rng = np.random.default_rng(M * 7 + N * 3 + K + int(tb))
+    A = rng.standard_normal((M, K)).astype(np.float16)
+    B = (rng.standard_normal((N, K) if tb else (K, N)) * 0.05).astype(np.float16)
+    got, kernel = _run(tc, ctx, A, B, tb)
+    assert kernel == "gemm_f16_tcgen05_sm100"
+    want = oracle.gemm_f16(A, B, tb)
+    assert np.isfinite(got.astype(np.float32)).all()
+    assert oracle.scaled_rms(got, want) <= TOL
+    assert tc.take_device_error(ctx) == 0
+
+
+def test_alpha_beta_and_leading_dimensions(tc, ctx, oracle):
+    rng = np.random.default_rng(5)
+    M, N, K = 200, 136, 320
+    A = rng.standard_normal((M, K)).astype(np.float16)
+    B = (rng.standard_normal((K, N)) * 0.05).astype(np.float16)
+    C0 = rng.standard_normal((M, N)).astype(np.float16)
+    got, kernel = _run(tc, ctx, A, B, False, alpha=0.5, beta=1.5, C0=C0)
+    assert kernel == "gemm_f16_tcgen05_sm100"
+    assert oracle.scaled_rms(got, oracle.gemm_f16(A, B, False, 0.5, 1.5, C0)) <= TOL
+    # sub-matrices of wider arrays: lda, ldb, ldc larger than the extents; the rest of C stays untouched
+    Aw = rng.standard_normal((M, K + 24)).astype(np.float16)
+    Bw = (rng.standard_normal((K, N + 40)) * 0.05).astype(np.float16)
+    Cw = rng.standard_normal((M, N + 8)).astype(np.float16)
+    got, _ = _run(tc, ctx, Aw, Bw, False, C0=Cw, lda=K + 24, ldb=N + 40, ldc=N + 8, M=M, N=N, K=K)
+    want = oracle.gemm_f16(Aw[:, :K], Bw[:, :N], False)
+    assert oracle.scaled_rms(got[:, :N], want) <= TOL
+    assert np.array_equal(got[:, N:].view(np.uint16), Cw[:, N:].view(np.uint16))
+
+
+def test_few_rows_and_shapes_outside_the_tiled_copies(tc, ctx, oracle):
+    """Up to four rows (a decode step) take the row kernel; so does a shape whose K is not a multiple
+    of 8, which the tiled copies cannot describe."""
+    rng = np.random.default_rng(6)
+    for (M, N, K) in ((1, 1000, 4096), (4, 512, 1024), (40, 96, 100)):
+        A = rng.standard_normal((M, K)).astype(np.float16)
+        B = (rng.standard_normal((K, N)) * 0.05).astype(np.float16)
+        got, kernel = _run(tc, ctx, A, B, False)
+        assert kernel == "gemm_f16_rows_sm100", (M, N, K)
+        assert oracle.scaled_rms(got, oracle.gemm_f16(A, B, False)) <= TOL
+
+
+def test_argument_checks(tc, ctx):
+    a = ctx.buffer(64 * 64 * 2)
+    with pytest.raises(tc.TensorcoreError) as e:
+        tc.gemm(ctx, a, a, a, 64, 64, 64, dtype="f32", accum="f32")
+    assert e.value.status == tc.TC_ERR_UNSUPPORTED_DTYPE
+    with pytest.raises(tc.TensorcoreError) as e:
+        tc.gemm(ctx, a, a, a, 64, 64, 64, transpose_a=True)
+    assert e.value.status == tc.TC_ERR_UNSUPPORTED_FAMILY
+    with pytest.raises(tc.TensorcoreError) as e:
+        tc.gemm(ctx, a, a, a, 64, 64, 64, lda=32)
+    assert e.value.status == tc.TC_ERR_INVALID_ARG
+    with pytest.raises(tc.TensorcoreError) as e:
+        tc.gemm(ctx, a, a, a, 128, 64, 64)          # A would need 128 x 64 halves
+    assert e.value.status != tc.TC_OK

@@ -196,6 +196,32 @@ def test_step_ops_against_reference_backend_when_built(oracle):
                           R.rope_forward(X, np.cos(ang), np.sin(ang)).view(np.uint16))
 
 
+def test_gemm_against_reference_backend_when_built(oracle):
+    """orc_gemm_f16 restates lib/ops/gemm_cpu.cpp:544-568; bit for bit against the reference's CPU
+    tc_gemm, B as given and transposed, with alpha and beta - with the reference GEMM's own narrowing
+    (ties up, a carry out of the mantissa lost when the exponent is odd).  With the IEEE narrowing,
+    which parity targets use, only such elements differ."""
+    if not oracle.ref_available():
+        pytest.skip("oracle/_ref not built (no reference checkout on this machine)")
+    R = oracle.RefLib()
+    rng = np.random.default_rng(33)
+    differing = total = 0
+    for (M, N, K) in ((1, 8, 8), (5, 24, 72), (33, 40, 256), (33, 40, 64)):
+        A = rng.standard_normal((M, K)).astype(np.float16)
+        B = rng.standard_normal((K, N)).astype(np.float16)
+        C0 = rng.standard_normal((M, N)).astype(np.float16)
+        for tb in (False, True):
+            Bx = np.ascontiguousarray(B.T) if tb else B
+            for alpha, beta in ((1.0, 0.0), (0.5, 0.0), (0.5, 1.5)):
+                b = R.gemm_f16(A, Bx, tb, alpha, beta, C0)
+                a = oracle.gemm_f16(A, Bx, tb, alpha, beta, C0, ref_narrowing=True)
+                assert np.array_equal(a.view(np.uint16), b.view(np.uint16)), (M, N, K, tb, alpha, beta)
+                ieee = oracle.gemm_f16(A, Bx, tb, alpha, beta, C0)
+                differing += int(np.count_nonzero(ieee.view(np.uint16) != b.view(np.uint16)))
+                total += ieee.size
+    assert differing <= total // 200          # ties and lost carries are rare
+
+
 def _attention_cases(g):
     return sorted(k[:-2] for k in g.files if k.endswith("_Q"))
 

@@ -216,8 +216,7 @@ cudaError_t launch_rope(void* X, const float* cos_t, const float* sin_t, int bat
 cudaError_t launch_gemm_f16_rows(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
                                  int ldc, float alpha, float beta, cudaStream_t stream);
 // The same product on the tensor cores (gemm_f16_tc.cu), B as given ([K][N]) or transposed ([N][K]).
-// cudaErrorNotSupported when K, lda, ldb (and N for B as given) are not multiples of 8 or a base is not
-// 16-byte aligned.
+// cudaErrorNotSupported when lda or ldb is not a multiple of 8 elements or a base is not 16-byte aligned.
 cudaError_t init_gemm_tc_kernel(int smem_optin);
 cudaError_t launch_gemm_f16_tc(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                                bool transpose_b, float alpha, float beta, const LaunchEnv& env, cudaStream_t stream);

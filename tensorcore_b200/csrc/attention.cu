@@ -240,8 +240,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_decode_kernel(const
 // that loads value row 2c (+1) already has that key's probability: no broadcast.  A lane
 // accumulates its eight output elements over the keys of its half; the two halves are added at
 // the end.  G query heads that share the K/V head are processed together (G <= 4).
+// The kernel is bound by how many warps an SM keeps in flight (a step is a chain of round trips and
+// shuffles), so the one- and two-head instances are held to 96 / 128 registers for five / four CTAs
+// per SM at the price of a few spilled words (32 heads x 4096 keys: 36.9 -> 30.8 us; batch 8 x 2048
+// keys: 99.5 -> 83.9 us); the four-head instance was slower that way (233 registers, two CTAs).
 template <int G>
-__global__ void __launch_bounds__(kAttnWarps * 32) attention_decode128_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kAttnWarps * 32, G == 1 ? 5 : (G == 2 ? 4 : 1)) attention_decode128_kernel(const AttnParams p) {
     constexpr int D = 128;
     __shared__ float o_s[kAttnWarps][G][D];
     __shared__ float m_s[kAttnWarps][G], l_s[kAttnWarps][G];

@@ -456,11 +456,13 @@ cudaError_t launch_group(int group, dim3 grid, cudaStream_t stream, const AttnPa
     return cudaGetLastError();
 }
 
-// Query heads one CTA takes together: those that share a K/V head, four at most (a multiple of four
-// shares in two or more CTAs, which find the cache in L2).
+// Query heads one CTA takes together: two of those that share a K/V head (the other pairs of the same
+// K/V head run in other CTAs and find the cache in L2).  Four at a time was measured slower (64 heads on
+// 8 K/V heads x 8192 keys: 47.3 against 41.3 us): the four-head instance needs 233 registers, two CTAs
+// per SM; one at a time re-reads the cache eight times (73.5 us).
 int attention_group(int Hq, int Hkv) {
     const int per = Hq / Hkv;
-    return per % 4 == 0 ? 4 : (per % 2 == 0 ? 2 : 1);
+    return per % 2 == 0 ? 2 : 1;
 }
 
 }  // namespace

@@ -26,8 +26,6 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
-#include <cstdlib>
-
 namespace tcb {
 namespace {
 
@@ -257,8 +255,7 @@ cudaError_t launch_gemm_f16_tc(const void* A, const void* B, void* C, int M, int
     p.b_kmajor = transpose_b ? 1 : 0;
     // 256-wide tiles halve the re-reads of A and the number of MMA instructions; measured faster than 128-wide
     // ones whenever N fills them (4096^3: 1119 against 769 TFLOP/s; 512 x 11008 x 4096: 629 against 523).
-    bool wide = N >= 256;
-    if (const char* s = std::getenv("TC_GEMM_TILE_N")) wide = std::atoi(s) == 256;
+    const bool wide = N >= 256;
     return wide ? launch_tile<256>(p, A, B, lda, ldb, transpose_b, env, stream)
                 : launch_tile<128>(p, A, B, lda, ldb, transpose_b, env, stream);
 }

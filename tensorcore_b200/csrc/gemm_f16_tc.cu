@@ -3,8 +3,10 @@
 // dequantised weights use (include/tensorcore/gemm.h:16-58; arithmetic lib/ops/gemm_cpu.cpp:544-568,
 // which adds the products in k order; here the tensor core's order, same fp32 accumulation).
 //
-//   * A CTA computes a 128 x BN tile of C (BN = 128 or 256) over the whole K, 64 at a time, through
-//     a ring of four stages (16 KB of A + BN * 128 bytes of B each).
+//   * One CTA per SM walks the 128 x BN tiles of C (BN = 128 or 256), each over the whole K, 64 at a
+//     time, through a ring of four stages (16 KB of A + BN * 128 bytes of B each) that keeps running
+//     across tiles; two accumulators in tensor memory, so that one tile is read out and stored while
+//     the next one's MMAs run.
 //   * Operands reach shared memory by tiled TMA copies of 128-byte rows written with the 128-byte
 //     swizzle, the layout the MMA's shared-memory descriptors read directly:
 //       - A ([M][K]) and a transposed B ([N][K]) are K-major: a box of 64 k x 128 (or BN) rows;
@@ -49,7 +51,9 @@ struct GemmParams {
 struct GemmBars {
     uint64_t full[kStages];
     uint64_t empty[kStages];
-    uint64_t d_full;
+    uint64_t acc_full[2];     // MMA issuer -> epilogue warps, per accumulator
+    uint64_t acc_empty[2];    // epilogue warps -> MMA issuer
+    uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -70,18 +74,22 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
     uint8_t* a_ring = smem + kGemmBarBytes;
     uint8_t* b_ring = a_ring + kStages * kAStage;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
     const int ksteps = (p.K + kBK - 1) / kBK;
+    // Tiles of C, numbered column-block-major (the CTAs running at the same time share a block of B's
+    // columns and walk down A); CTA c takes tiles c, c + gridDim.x, ...
+    const int tiles_m = (p.M + kBM - 1) / kBM, tiles_n = (p.N + BN - 1) / BN;
+    const int n_tiles = tiles_m * tiles_n;
 
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) { bar_init(&bars->full[i], 1); bar_init(&bars->empty[i], 1); }
-        bar_init(&bars->d_full, 1);
+        for (int i = 0; i < 2; ++i) { bar_init(&bars->acc_full[i], 1); bar_init(&bars->acc_empty[i], 4); }
+        bar_init(&bars->drain, 1);
         bars->abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&amap);
         prefetch_tensormap(&bmap);
     }
-    if (warp == 1) tmem_alloc(&bars->tmem_base, BN);
+    if (warp == 1) tmem_alloc(&bars->tmem_base, 2 * BN);     // two accumulators: a tile's epilogue overlaps the next tile's MMAs
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -91,48 +99,62 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
     if (warp == 0) {
         if (lane == 0) {
             int issued = 0;
-            for (int ks = 0; ks < ksteps; ++ks) {
-                const int s = ks % kStages;
-                const uint32_t par = static_cast<uint32_t>(ks / kStages) & 1u;
-                if (!bar_wait(&bars->empty[s], par ^ 1u, abort_flag)) { failed = true; break; }
-                bar_expect_tx(&bars->full[s], kAStage + kBStage);
-                tensor_load_2d(a_ring + s * kAStage, &amap, ks * kBK, m0, &bars->full[s]);
-                if (p.b_kmajor) {
-                    tensor_load_2d(b_ring + s * kBStage, &bmap, ks * kBK, n0, &bars->full[s]);
-                } else {
+            for (int t = blockIdx.x; t < n_tiles && !failed; t += gridDim.x) {
+                const int m0 = (t % tiles_m) * kBM, n0 = (t / tiles_m) * BN;
+                for (int ks = 0; ks < ksteps; ++ks, ++issued) {
+                    const int s = issued % kStages;
+                    const uint32_t par = static_cast<uint32_t>(issued / kStages) & 1u;
+                    if (!bar_wait(&bars->empty[s], par ^ 1u, abort_flag)) { failed = true; break; }
+                    bar_expect_tx(&bars->full[s], kAStage + kBStage);
+                    tensor_load_2d(a_ring + s * kAStage, &amap, ks * kBK, m0, &bars->full[s]);
+                    if (p.b_kmajor) {
+                        tensor_load_2d(b_ring + s * kBStage, &bmap, ks * kBK, n0, &bars->full[s]);
+                    } else {
 #pragma unroll
-                    for (int c = 0; c < BN / 64; ++c)
-                        tensor_load_2d(b_ring + s * kBStage + c * 8192, &bmap, n0 + 64 * c, ks * kBK, &bars->full[s]);
+                        for (int c = 0; c < BN / 64; ++c)
+                            tensor_load_2d(b_ring + s * kBStage + c * 8192, &bmap, n0 + 64 * c, ks * kBK, &bars->full[s]);
+                    }
                 }
-                ++issued;
             }
             if (failed || *abort_flag) {
                 // Let copies already in flight land before the CTA's shared memory is released.
                 const int first = issued > kStages ? issued - kStages : 0;
-                for (int ks = first; ks < issued; ++ks)
-                    bar_wait(&bars->full[ks % kStages], static_cast<uint32_t>(ks / kStages) & 1u, nullptr, 100000000LL);
+                for (int c = first; c < issued; ++c)
+                    bar_wait(&bars->full[c % kStages], static_cast<uint32_t>(c / kStages) & 1u, nullptr, 100000000LL);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = idesc_f16_f32(kBM, BN) | (p.b_kmajor ? 0u : (1u << 16));   // bit 16: B is MN-major
-            for (int ks = 0; ks < ksteps && !failed; ++ks) {
-                const int s = ks % kStages;
-                const uint32_t par = static_cast<uint32_t>(ks / kStages) & 1u;
-                if (!bar_wait(&bars->full[s], par, abort_flag)) { failed = true; break; }
+            int used = 0, it = 0;
+            for (int t = blockIdx.x; t < n_tiles && !failed; t += gridDim.x, ++it) {
+                const int acc = it & 1;
+                // the accumulator's previous tile (two tiles ago) has been read out
+                if (!bar_wait(&bars->acc_empty[acc], (static_cast<uint32_t>(it >> 1) & 1u) ^ 1u, abort_flag)) { failed = true; break; }
                 tc_fence_after_sync();
-                const uint32_t a_addr = s_u32(a_ring + s * kAStage), b_addr = s_u32(b_ring + s * kBStage);
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                for (int ks = 0; ks < ksteps; ++ks, ++used) {
+                    const int s = used % kStages;
+                    const uint32_t par = static_cast<uint32_t>(used / kStages) & 1u;
+                    if (!bar_wait(&bars->full[s], par, abort_flag)) { failed = true; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = s_u32(a_ring + s * kAStage), b_addr = s_u32(b_ring + s * kBStage);
 #pragma unroll
-                for (int j = 0; j < kBK / 16; ++j) {
-                    const uint64_t adesc = smem_desc(a_addr + j * 32, 16u, 1024u, kSwizzle128);
-                    const uint64_t bdesc = p.b_kmajor ? smem_desc(b_addr + j * 32, 16u, 1024u, kSwizzle128)
-                                                      : smem_desc(b_addr + j * 2048, 8192u, 1024u, kSwizzle128);
-                    mma_f16_ss(tmem_base, adesc, bdesc, idesc, (ks > 0 || j > 0) ? 1u : 0u);
+                    for (int j = 0; j < kBK / 16; ++j) {
+                        const uint64_t adesc = smem_desc(a_addr + j * 32, 16u, 1024u, kSwizzle128);
+                        const uint64_t bdesc = p.b_kmajor ? smem_desc(b_addr + j * 32, 16u, 1024u, kSwizzle128)
+                                                          : smem_desc(b_addr + j * 2048, 8192u, 1024u, kSwizzle128);
+                        mma_f16_ss(d_tmem, adesc, bdesc, idesc, (ks > 0 || j > 0) ? 1u : 0u);
+                    }
+                    mma_commit(&bars->empty[s]);
                 }
-                mma_commit(&bars->empty[s]);
+                if (!failed) mma_commit(&bars->acc_full[acc]);
             }
-            mma_commit(&bars->d_full);
-            if (failed || *abort_flag) bar_wait(&bars->d_full, 0, nullptr, 100000000LL);
+            if (failed || *abort_flag) {
+                // every MMA issued so far has completed before the tensor memory is released
+                mma_commit(&bars->drain);
+                bar_wait(&bars->drain, 0, nullptr, 100000000LL);
+            }
         }
     }
     if (failed) {
@@ -143,16 +165,23 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
 
     if (warp >= 2) {
         const int quad = warp & 3;                          // the TMEM lanes this warp may read
-        const int row = m0 + quad * 32 + lane;
-        const bool ok = bar_wait_warp(&bars->d_full, 0, abort_flag) && __all_sync(0xffffffffu, !*abort_flag);
-        if (!ok && lane == 0 && !*abort_flag) {
-            *abort_flag = 1;
-            if (p.err) atomicOr(p.err, ERR_WAIT_TIMEOUT);
-        }
-        tc_fence_after_sync();
-        if (ok) {
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-            const bool vec = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) && p.beta == 0.f;
+        const bool vec = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) && p.beta == 0.f;
+        int it = 0;
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++it) {
+            const int m0 = (t % tiles_m) * kBM, n0 = (t / tiles_m) * BN;
+            const int acc = it & 1;
+            const int row = m0 + quad * 32 + lane;
+            const bool ok = bar_wait_warp(&bars->acc_full[acc], static_cast<uint32_t>(it >> 1) & 1u, abort_flag) &&
+                            __all_sync(0xffffffffu, !*abort_flag);
+            if (!ok) {
+                if (lane == 0 && !*abort_flag) {
+                    *abort_flag = 1;
+                    if (p.err) atomicOr(p.err, ERR_WAIT_TIMEOUT);
+                }
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t v[16];
@@ -181,13 +210,17 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
                     }
                 }
             }
+            // the accumulator may take the tile after next
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) bar_arrive(&bars->acc_empty[acc]);
         }
-        tc_fence_before_sync();
     }
+    tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, BN);
+        tmem_dealloc(tmem_base, 2 * BN);
     }
 }
 
@@ -228,7 +261,9 @@ cudaError_t launch_tile(const GemmParams& p, const void* A, const void* B, int l
         ? encode_rows_sw128(&bmap, B, static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.K), static_cast<uint64_t>(ldb), BN)
         : encode_rows_sw128(&bmap, B, static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.N), static_cast<uint64_t>(ldb), kBK);
     if (!okb) return cudaErrorNotSupported;
-    const dim3 grid((p.N + BN - 1) / BN, (p.M + kBM - 1) / kBM);
+    const long tiles = static_cast<long>((p.N + BN - 1) / BN) * ((p.M + kBM - 1) / kBM);
+    const long sms = env.sm_count > 0 ? env.sm_count : 148;
+    const dim3 grid(static_cast<unsigned>(tiles < sms ? tiles : sms));     // one CTA per SM walks the tiles
     gemm_f16_tc_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(p, amap, bmap);
     return cudaGetLastError();
 }

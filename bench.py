@@ -591,12 +591,23 @@ def main() -> None:
             print(json.dumps(run_reference_arm(args)), flush=True)
         return
     if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
-        # stdout carries the one JSON line and nothing else: at NCCL_DEBUG=VERSION the library prints
-        # its version banner there
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":     # unset: a system nccl.conf may say so
-            os.environ["NCCL_DEBUG"] = "WARN"
-        from tensorcore_b200 import tp
-        out = tp.run_bench(args)
+        # stdout carries the one JSON line and nothing else: libraries that print to it while the ranks
+        # set up (NCCL's version banner) are pointed at stderr until the line is ready.
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            from tensorcore_b200 import tp
+            out = tp.run_bench(args)
+        finally:
+            sys.stdout.flush()
+            try:
+                import ctypes
+                ctypes.CDLL(None).fflush(None)       # whatever C code left in stdio's buffer goes to stderr too
+            except Exception:
+                pass
+            os.dup2(saved, 1)
+            os.close(saved)
         if rank == 0 and out is not None:
             print(json.dumps(out), flush=True)
         sys.stdout.flush()

@@ -465,6 +465,26 @@ cudaError_t launch_dense_norm_gemv(const DenseNormGemvArgs& a, const LaunchEnv& 
     size_t need_f = 0, need_i = 0;
     dense_norm_gemv_scratch(a.M, a.N, a.K, env.sm_count > 0 ? env.sm_count : 148, &need_f, &need_i);
     const bool split = vec && a.scratch && a.counters && a.scratch_floats >= need_f && a.counters_n >= need_i;
+    // Five rows or more: the kernels below would read W once per four rows.  Instead the rows are
+    // normalised once into the stream's scratch (fp16, as the reference rounds them before its GEMM,
+    // lib/ops/training_cpu.cpp:799-935) and multiplied by W on the tensor cores: W is read once.
+    const size_t rows_bytes = static_cast<size_t>(a.M) * a.K * 2;
+    if (a.M >= 5 && a.norm_scratch && a.norm_scratch_bytes >= rows_bytes + static_cast<size_t>(a.M) * 8) {
+        float* stats = reinterpret_cast<float*>(static_cast<uint8_t*>(a.norm_scratch) + rows_bytes);
+        cudaError_t e = launch_norm_forward(a.X, a.gamma, a.beta, a.norm_scratch, stats, stats + a.M, a.M, a.K, a.eps, stream);
+        if (e == cudaSuccess) {
+            e = launch_gemm_f16_tc(a.norm_scratch, a.W, a.Y, a.M, a.N, a.K, a.K, a.N, a.N, false, 1.0f, 0.0f, env, stream);
+            if (e == cudaSuccess) {
+                if (launches) *launches += 2;
+                if (name) *name = a.beta ? "layernorm_rows_gemm_tcgen05_sm100" : "rmsnorm_rows_gemm_tcgen05_sm100";
+                return cudaSuccess;
+            }
+            if (e != cudaErrorNotSupported) return e;
+            (void)cudaGetLastError();      // shapes the tiled copies cannot describe: the kernels below
+        } else {
+            return e;
+        }
+    }
     for (int m0 = 0; m0 < a.M && err == cudaSuccess; m0 += kDMaxMB) {
         const int mb = (a.M - m0) < kDMaxMB ? (a.M - m0) : kDMaxMB;
         DenseParams p;

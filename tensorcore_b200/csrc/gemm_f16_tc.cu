@@ -290,7 +290,9 @@ cudaError_t launch_gemm_f16_tc(const void* A, const void* B, void* C, int M, int
     p.b_kmajor = transpose_b ? 1 : 0;
     // 256-wide tiles halve the re-reads of A and the number of MMA instructions; measured faster than 128-wide
     // ones whenever N fills them (4096^3: 1119 against 769 TFLOP/s; 512 x 11008 x 4096: 629 against 523).
-    const bool wide = N >= 256;
+    const long sms = env.sm_count > 0 ? env.sm_count : 148;
+    const long tiles256 = static_cast<long>((M + kBM - 1) / kBM) * ((N + 255) / 256);
+    const bool wide = N >= 256 && tiles256 >= sms;      // few rows of A: narrower tiles spread over more SMs
     return wide ? launch_tile<256>(p, A, B, lda, ldb, transpose_b, env, stream)
                 : launch_tile<128>(p, A, B, lda, ldb, transpose_b, env, stream);
 }

@@ -49,6 +49,10 @@ struct DenseNormGemvArgs {
     void* Y = nullptr;            // [M,N] fp16
     int M = 0, N = 0, K = 0;
     float eps = 0.f;
+    // scratch of the stream for five rows or more: M normalised rows of K halves + 2 M floats; with it
+    // the rows are normalised once and multiplied on the tensor cores, W read once
+    void* norm_scratch = nullptr;
+    size_t norm_scratch_bytes = 0;
     // scratch of the stream the call runs on (dense_norm_gemv_scratch says how much): partial sums
     // and one ticket counter per column strip, all zero between launches; without it a slower
     // kernel that needs none is used

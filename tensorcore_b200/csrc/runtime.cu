@@ -253,6 +253,14 @@ void norm_scratch_for(cudaStream_t st, size_t need, tcb::GemvQArgs* a) {
     a->norm_scratch = d.norm;
     a->norm_scratch_bytes = d.norm_bytes;
 }
+// Room for the normalised rows of a dense fused norm + GEMV call with five rows or more.
+void dense_norm_rows_for(cudaStream_t st, tcb::DenseNormGemvArgs* a) {
+    if (a->M < 5) return;
+    tcb::GemvQArgs tmp;
+    norm_scratch_for(st, static_cast<size_t>(a->M) * a->K * 2 + static_cast<size_t>(a->M) * 8, &tmp);
+    a->norm_scratch = tmp.norm_scratch;
+    a->norm_scratch_bytes = tmp.norm_scratch_bytes;
+}
 void free_dense_scratch() {
     std::lock_guard<std::mutex> lock(g_dense_mutex);
     for (auto& kv : g_dense) {
@@ -1360,6 +1368,7 @@ static tc_status_t dense_common(tc_context* ctx, const tc_buffer* X, const tc_bu
     const char* name = "none";
     if (e == cudaSuccess) {
         dense_scratch_for(ctx, s0, &a);
+        dense_norm_rows_for(s0, &a);
         e = tcb::launch_dense_norm_gemv(a, make_env(ctx, false), s0, &launches, &name);
     }
     if (e == cudaSuccess) e = finish_output(Y, yb, s0);
@@ -1798,6 +1807,7 @@ extern "C" tc_status_t tcx_raw_fused_norm_gemv_f16(tc_context* ctx, const void* 
     int launches = 0;
     const char* name = "none";
     dense_scratch_for(ctx, static_cast<cudaStream_t>(cuda_stream), &a);
+    dense_norm_rows_for(static_cast<cudaStream_t>(cuda_stream), &a);
     const cudaError_t e = tcb::launch_dense_norm_gemv(a, make_env(ctx, true),
                                                       static_cast<cudaStream_t>(cuda_stream),
                                                       &launches, &name);

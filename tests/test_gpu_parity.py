@@ -269,6 +269,30 @@ def test_dense_fused_norm_gemv(tc, ctx, oracle, shape):
     assert oracle.scaled_rms(got_l, want_l) <= TOL_VS_ORACLE_F16
 
 
+@pytest.mark.parametrize("shape", [(8, 1024, 4096), (32, 2048, 1024), (40, 264, 520), (7, 77, 100)])
+def test_dense_fused_norm_gemv_batched(tc, ctx, oracle, shape):
+    """Five rows or more: the rows are normalised once (fp16, as the reference rounds them before
+    its GEMM) and multiplied on the tensor cores; shapes the tiled copies cannot describe (N not a
+    multiple of 8) keep the four-rows-at-a-time kernels."""
+    M, N, K = shape
+    rng = np.random.default_rng(M * 5 + N + K)
+    X = rng.standard_normal((M, K)).astype(np.float16)
+    gam = (1 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    bet = (0.1 * rng.standard_normal(K)).astype(np.float16)
+    W = (rng.standard_normal((K, N)) * 0.02).astype(np.float16)
+    got_r = gpu_dense(tc, ctx, X, gam, None, W)
+    name_r = tc.cuda_last_kernel_name()
+    got_l = gpu_dense(tc, ctx, X, gam, bet, W)
+    name_l = tc.cuda_last_kernel_name()
+    if N % 8 == 0:
+        assert name_r == "rmsnorm_rows_gemm_tcgen05_sm100" and name_l == "layernorm_rows_gemm_tcgen05_sm100"
+    else:
+        assert "tcgen05" not in name_r and "tcgen05" not in name_l
+    assert oracle.scaled_rms(got_r, oracle.fused_rmsnorm_gemv(X, gam, W, 1e-5)) <= TOL_VS_ORACLE_F16
+    assert oracle.scaled_rms(got_l, oracle.fused_layernorm_gemv(X, gam, bet, W, 1e-5)) <= TOL_VS_ORACLE_F16
+    assert tc.take_device_error(ctx) == 0
+
+
 def test_dense_fused_matches_reference_golden(tc, ctx, oracle):
     g = np.load(os.path.join(GOLDEN, "dense_fused.npz"))
     for key in sorted({k.rsplit("_", 1)[0] for k in g.files}):

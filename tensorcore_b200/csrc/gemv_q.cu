@@ -612,6 +612,34 @@ cudaError_t launch_gemv_q(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t
     const size_t slab_rows = a.M < 32 ? a.M : 32;
     const size_t norm_need = slab_rows * static_cast<size_t>(a.K) * 2 + slab_rows * 4;
     const bool fuse_tc = fuse && a.norm_scratch && a.norm_scratch_bytes >= norm_need && a.K % 256 == 0;
+    // Prefill-sized calls: the weights are dequantised once into the stream's scratch (fp16, the same
+    // rounding as the kernel below applies on the fly) and multiplied on the tensor cores as a GEMM
+    // with B transposed; Q8_0 too.  fp16 activations and results only (the rounding of the weights is
+    // inside their bound, not inside the fp32 one).
+    if (env.variant == VARIANT_AUTO && a.M >= gemm_min_rows(a.fmt) && !a.x_f32 && !a.y_f32 && a.dequant_scratch &&
+        a.dequant_scratch_bytes >= static_cast<size_t>(a.N) * a.K * 2 && a.K % 32 == 0 &&
+        (!fuse || (a.norm_scratch && a.norm_scratch_bytes >= static_cast<size_t>(a.M) * a.K * 2 + static_cast<size_t>(a.M) * 4))) {
+        cudaError_t e = launch_dequantize(a.W, a.dequant_scratch, a.fmt, a.N, a.K, stream);
+        const void* x = a.X;
+        int n_launch = 1;
+        if (e == cudaSuccess && fuse) {
+            float* rstd = reinterpret_cast<float*>(static_cast<uint8_t*>(a.norm_scratch) + static_cast<size_t>(a.M) * a.K * 2);
+            e = launch_norm_forward(a.X, a.gamma, nullptr, a.norm_scratch, nullptr, rstd, a.M, a.K, a.eps, stream);
+            x = a.norm_scratch;
+            ++n_launch;
+        }
+        if (e == cudaSuccess) {
+            e = launch_gemm_f16_tc(x, a.dequant_scratch, a.Y, a.M, a.N, a.K, a.K, a.K, a.N, true, 1.0f, 0.0f, env, stream);
+            ++n_launch;
+        }
+        if (e == cudaSuccess) {
+            if (launches) *launches += n_launch;
+            if (name) *name = a.fmt == FMT_Q4_0 ? "q4_0_dequant_gemm_tcgen05_sm100" : "q8_0_dequant_gemm_tcgen05_sm100";
+            return cudaSuccess;
+        }
+        if (e != cudaErrorNotSupported) return e;
+        (void)cudaGetLastError();
+    }
     if (want_tc && a.fmt == FMT_Q4_0 && !a.x_f32 && (!fuse || fuse_tc)) {
         bool done = true;
         for (int m0 = 0; m0 < a.M; m0 += 32) {

@@ -187,7 +187,8 @@ bool managed(const tc_buffer* b) { return b->kind == BUF_MANAGED || b->kind == B
 // Scratch of the dense fused GEMV (partial sums of the K ranges, one ticket counter per column
 // strip), one per CUDA stream: calls on a stream are ordered, calls on different streams must not
 // share it.  Grown on demand, freed when the context goes.
-struct DenseScratch { float* f = nullptr; size_t nf = 0; int* c = nullptr; size_t nc = 0; void* norm = nullptr; size_t norm_bytes = 0; };
+struct DenseScratch { float* f = nullptr; size_t nf = 0; int* c = nullptr; size_t nc = 0; void* norm = nullptr; size_t norm_bytes = 0;
+                      void* dq = nullptr; size_t dq_bytes = 0; };
 std::mutex g_dense_mutex;
 std::unordered_map<cudaStream_t, DenseScratch> g_dense;
 
@@ -202,6 +203,7 @@ void dense_scratch_for(tc_context* ctx, cudaStream_t st, tcb::DenseNormGemvArgs*
             if (kv.second.f) cudaFree(kv.second.f);
             if (kv.second.c) cudaFree(kv.second.c);
             if (kv.second.norm) cudaFree(kv.second.norm);
+            if (kv.second.dq) cudaFree(kv.second.dq);
         }
         g_dense.clear();
     }
@@ -228,8 +230,15 @@ void dense_scratch_for(tc_context* ctx, cudaStream_t st, tcb::DenseNormGemvArgs*
 }
 // Room for the normalised rows of the batched fused RMSNorm GEMV (the tensor-core kernel reads them as
 // plain fp16 activations).
+// Whether the call is prefill-sized: its weights are dequantised once and multiplied as a GEMM.
+bool dequant_gemm_wanted(const tcb::GemvQArgs& a) {
+    return a.M >= tcb::gemm_min_rows(a.fmt) && !a.x_f32 && !a.y_f32 && a.K % 32 == 0 &&
+           static_cast<size_t>(a.N) * a.K * 2 <= (static_cast<size_t>(3) << 29);      // at most 1.5 GB of scratch
+}
 size_t norm_scratch_need(const tcb::GemvQArgs& a) {
-    if (!a.gamma || a.x_f32 || a.fmt != 0 || a.M < 5 || a.K % 256 != 0) return 0;
+    if (!a.gamma || a.x_f32) return 0;
+    if (dequant_gemm_wanted(a)) return static_cast<size_t>(a.M) * a.K * 2 + static_cast<size_t>(a.M) * 4;
+    if (a.fmt != 0 || a.M < 5 || a.K % 256 != 0) return 0;
     const size_t rows = a.M < 32 ? a.M : 32;
     return rows * static_cast<size_t>(a.K) * 2 + rows * 4;
 }
@@ -261,12 +270,37 @@ void dense_norm_rows_for(cudaStream_t st, tcb::DenseNormGemvArgs* a) {
     a->norm_scratch = tmp.norm_scratch;
     a->norm_scratch_bytes = tmp.norm_scratch_bytes;
 }
+// Room for the weights as fp16 of a prefill-sized quantized GEMV on this stream (grown on demand; a
+// call that finds none keeps the kernels that stream the blocks).
+void dequant_scratch_for(cudaStream_t st, size_t need, tcb::GemvQArgs* a) {
+    if (need == 0) return;
+    std::lock_guard<std::mutex> lock(g_dense_mutex);
+    DenseScratch& d = g_dense[st];
+    if (d.dq_bytes < need) {
+        cudaStreamSynchronize(st);        // an earlier call on this stream may still use the old one
+        if (d.dq) cudaFree(d.dq);
+        d.dq = nullptr;
+        d.dq_bytes = 0;
+        if (cudaMalloc(&d.dq, need) != cudaSuccess) {
+            (void)cudaGetLastError();
+            d.dq = nullptr;
+            return;
+        }
+        d.dq_bytes = need;
+    }
+    a->dequant_scratch = d.dq;
+    a->dequant_scratch_bytes = d.dq_bytes;
+}
+size_t dequant_scratch_need(const tcb::GemvQArgs& a) {
+    return dequant_gemm_wanted(a) ? static_cast<size_t>(a.N) * a.K * 2 : 0;
+}
 void free_dense_scratch() {
     std::lock_guard<std::mutex> lock(g_dense_mutex);
     for (auto& kv : g_dense) {
         if (kv.second.f) cudaFree(kv.second.f);
         if (kv.second.c) cudaFree(kv.second.c);
         if (kv.second.norm) cudaFree(kv.second.norm);
+        if (kv.second.dq) cudaFree(kv.second.dq);
     }
     g_dense.clear();
 }
@@ -905,16 +939,21 @@ tc_status_t submit_pending(tc_stream* s) {
     uint64_t sig = 1469598103934665603ull;
     tcb::GemvQArgs scratch_of;          // the stream's scratch for normalised rows, sized for the widest operation
     {
-        size_t need = 0;
+        size_t need = 0, dq = 0;
         for (const RecordedOp& op : s->pending) {
             const size_t n = norm_scratch_need(op.a);
             need = n > need ? n : need;
+            const size_t q = dequant_scratch_need(op.a);
+            dq = q > dq ? q : dq;
         }
         norm_scratch_for(s->s, need, &scratch_of);
+        dequant_scratch_for(s->s, dq, &scratch_of);
     }
     for (RecordedOp& op : s->pending) {
         op.a.norm_scratch = scratch_of.norm_scratch;
         op.a.norm_scratch_bytes = scratch_of.norm_scratch_bytes;
+        op.a.dequant_scratch = scratch_of.dequant_scratch;
+        op.a.dequant_scratch_bytes = scratch_of.dequant_scratch_bytes;
         // Device addresses are resolved now, not when the operation was recorded: a first
         // tc_buffer_map between the two moves a buffer to managed storage.
         op.a.X = op.X->dptr;
@@ -1270,6 +1309,7 @@ tc_status_t gemv_common(const GemvCall& c, tc_stream* stream, const char* opname
     int launches = 0;
     const char* name = "none";
     if (e == cudaSuccess) norm_scratch_for(s0, norm_scratch_need(op.a), &op.a);
+    if (e == cudaSuccess) dequant_scratch_for(s0, dequant_scratch_need(op.a), &op.a);
     if (e == cudaSuccess) e = launch_recorded(ctx, op, s0, false, &launches, &name);
     if (e == cudaSuccess) e = finish_output(op.Y, yb, s0);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s0);
@@ -1769,6 +1809,7 @@ static tc_status_t raw_gemv(tc_context* ctx, const void* X, const void* gamma, b
     a.fmt = static_cast<int>(fmt); a.M = M; a.N = N; a.K = K;
     a.x_f32 = xd == TC_DTYPE_F32; a.y_f32 = yd == TC_DTYPE_F32; a.eps = eps;
     norm_scratch_for(static_cast<cudaStream_t>(cuda_stream), norm_scratch_need(a), &a);
+    dequant_scratch_for(static_cast<cudaStream_t>(cuda_stream), dequant_scratch_need(a), &a);
     int launches = 0;
     const char* name = "none";
     const cudaError_t e = tcb::launch_gemv_q(a, make_env(ctx, true),

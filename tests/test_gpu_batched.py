@@ -155,3 +155,37 @@ def test_fused_rmsnorm_batched_matches_oracle(tc, ctx, oracle, M, N, K):
             s.sync()
             assert oracle.scaled_rms(by.to_numpy((M, N), np.float16), want) <= TOL
         s.close()
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+@pytest.mark.parametrize("shape", [(1024, 512, 128), (520, 1056, 200), (4096, 4096, 512)])
+def test_prefill_sized_calls_dequantise_once_and_use_the_gemm(tc, ctx, oracle, fmt, shape):
+    """96 activation rows or more with fp16 results: the weights are dequantised once to fp16 in the
+    stream's scratch and multiplied on the tensor cores (Q4_0 and Q8_0, plain and fused RMSNorm);
+    same bar as the batched kernel, against the fp64 dequantise-and-dot."""
+    N, K, M = shape
+    rng = np.random.default_rng(N + K * 3 + M * 7 + fmt)
+    W = (rng.standard_normal((N, K)) * 0.02).astype(np.float32).astype(np.float16)
+    X = rng.standard_normal((M, K)).astype(np.float16)
+    gam = (1 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    Wq = oracle.quantize_weights(W, fmt)
+    want = oracle.dequant_dot_f64(X.astype(np.float64), Wq, fmt, N)
+    with ctx.buffer_from_array(X) as bx, ctx.buffer_from_array(Wq) as bw, ctx.buffer_from_array(gam) as bg, \
+            ctx.buffer(M * N * 2) as by:
+        ctx.gemv_quantized(bx, bw, by, fmt, M, N, K)
+        name = tc.cuda_last_kernel_name()
+        got = by.to_numpy((M, N), np.float16).astype(np.float64)
+        assert name == ("q4_0" if fmt == 0 else "q8_0") + "_dequant_gemm_tcgen05_sm100"
+        assert oracle.scaled_rms(got, want) <= TOL
+        # fused RMSNorm form, on a few rows against the oracle's fp32 chain
+        ctx.fused_rmsnorm_gemv_quantized(bx, bg, bw, by, fmt, M, N, K, 1e-5)
+        assert tc.cuda_last_kernel_name() == name
+        gotf = by.to_numpy((M, N), np.float16)
+        rows = [0, M // 2, M - 1]
+        wantf = oracle.fused_rmsnorm_gemv_quantized_f32(X[rows].astype(np.float32), gam.astype(np.float32), Wq, fmt, N)
+        assert oracle.scaled_rms(gotf[rows], wantf) <= TOL
+        # fp32 results keep the kernels that stream the blocks
+        with ctx.buffer(M * N * 4) as by32:
+            tc.gemv_quantized_ex(ctx, bx, bw, by32, fmt, M, N, K, "f16", "f32", None)
+            assert "dequant_gemm" not in tc.cuda_last_kernel_name()
+    assert tc.take_device_error(ctx) == 0

@@ -302,14 +302,15 @@ tc_status_t tc_rope_forward(tc_context* ctx, tc_buffer* X, const tc_buffer* cos_
 tc_status_t tc_swiglu_forward(tc_context* ctx, const tc_buffer* gate, const tc_buffer* up, tc_buffer* out,
                               int n);
 
-/* include/tensorcore/gemm.h:16-58 (arithmetic: lib/ops/gemm_cpu.cpp:544-568).  Here: fp16 x fp16 ->
- * fp16 with fp32 accumulation, row-major, B as given ([K,N]) or transposed ([N,K]), alpha, beta and
- * leading dimensions - on the tensor cores (tcgen05) when lda and ldb are multiples of 8 elements
- * and A and B are 16-byte aligned; up to four rows of A (a decode step: what
- * tests/test_fused_norm_gemv.c compares the fused operations against) and untransposed operands
- * outside that take a row kernel that adds in the reference's k order.  The result is narrowed
- * with IEEE round-to-nearest-even.  Every other descriptor answers TC_ERR_UNSUPPORTED_DTYPE
- * (dtypes) or TC_ERR_UNSUPPORTED_FAMILY (transpose_a). */
+/* include/tensorcore/gemm.h:16-58 (arithmetic: lib/ops/gemm_cpu.cpp:544-568).  Here: binary16 or
+ * bfloat16 operands and result (all three the same) with fp32 accumulation, row-major, B as given
+ * ([K,N]) or transposed ([N,K]), alpha, beta and leading dimensions - on the tensor cores (tcgen05)
+ * when lda and ldb are multiples of 8 elements and A and B are 16-byte aligned; binary16 with up to
+ * four rows of A (a decode step: what tests/test_fused_norm_gemv.c compares the fused operations
+ * against) or untransposed operands outside that take a row kernel that adds in the reference's k
+ * order.  The result is narrowed with round-to-nearest-even.  Every other descriptor answers
+ * TC_ERR_UNSUPPORTED_DTYPE (dtypes) or TC_ERR_UNSUPPORTED_FAMILY (transpose_a, bfloat16 operands
+ * the tiled copies cannot describe). */
 typedef struct {
     int32_t M, N, K;
     tc_dtype_t a_dtype, b_dtype, c_dtype, accum_dtype;

@@ -169,6 +169,29 @@ def gemm_f16(A_f16, B_f16, transpose_b=False, alpha=1.0, beta=0.0, C_f16=None, r
     return C.view(np.float16)
 
 
+def to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """float32 -> bfloat16 bit patterns (uint16), round to nearest even."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def from_bf16_bits(b: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def gemm_bf16(A_bits, B_bits, transpose_b=False, alpha=1.0, beta=0.0, C_bits=None) -> np.ndarray:
+    """The bfloat16 case of gemm_f16 (lib/ops/gemm_cpu.cpp:544-568, conversions :217-230); operands and
+    result are bfloat16 bit patterns (uint16)."""
+    A = np.ascontiguousarray(A_bits, dtype=np.uint16)
+    B = np.ascontiguousarray(B_bits, dtype=np.uint16)
+    M, K = A.shape
+    N = B.shape[0] if transpose_b else B.shape[1]
+    C = np.zeros((M, N), dtype=np.uint16) if C_bits is None else np.ascontiguousarray(C_bits, dtype=np.uint16).copy()
+    _call(lib().orc_gemm_bf16, _p(A), _p(B), _p(C), c_int(M), c_int(N), c_int(K), c_int(K),
+          c_int(B.shape[1]), c_int(N), c_int(1 if transpose_b else 0), c_float(alpha), c_float(beta))
+    return C
+
+
 def fused_layernorm_gemv(X_f16, gamma_f16, beta_f16, W_f16, eps=1e-5) -> np.ndarray:
     X = np.ascontiguousarray(X_f16).view(np.uint16)
     g = np.ascontiguousarray(gamma_f16).view(np.uint16)
@@ -328,7 +351,7 @@ class RefLib:
         self._free(hw, hq)
         return out
 
-    def gemm_f16(self, A_f16, B_f16, transpose_b=False, alpha=1.0, beta=0.0, C_f16=None) -> np.ndarray:
+    def gemm_f16(self, A_f16, B_f16, transpose_b=False, alpha=1.0, beta=0.0, C_f16=None, dtype=0) -> np.ndarray:
         """tc_gemm of the reference's CPU backend (include/tensorcore/gemm.h:16-50), fp16 in and out."""
         class Desc(ctypes.Structure):
             _fields_ = [("M", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32), ("a", c_int), ("b", c_int),
@@ -342,7 +365,7 @@ class RefLib:
         ha, _, _ = self._buf(A)
         hb, _, _ = self._buf(B)
         hc, pc, nc = self._buf(C)
-        d = Desc(M, N, K, 0, 0, 0, 2, False, bool(transpose_b), float(alpha), float(beta), 0, 0, 0)   # F16 = 0, F32 = 2
+        d = Desc(M, N, K, dtype, dtype, dtype, 2, False, bool(transpose_b), float(alpha), float(beta), 0, 0, 0)   # F16 = 0, BF16 = 1, F32 = 2
         self.L.tc_gemm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
         st = self.L.tc_gemm(self.ctx, ctypes.byref(d), ha, hb, hc)
         assert st == 0, st

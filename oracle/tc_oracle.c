@@ -309,6 +309,37 @@ static uint16_t gemm_ref_f32_to_f16(float x) {
  * [N,K] (ldb), C [M,N] (ldc); the products are added in k order in fp32;
  * C = fp16(alpha * sum + beta * C), C not read when beta is 0.  ref_narrowing: 0 = IEEE
  * round-to-nearest-even, 1 = the reference GEMM's own narrowing (see above). */
+/* The bfloat16 case of the same loop: widening is a shift, narrowing round-to-nearest-even on the
+ * dropped 16 bits (lib/ops/gemm_cpu.cpp:217-230). */
+static float gemm_bf16_to_f32(uint16_t b) {
+    union { uint32_t u; float f; } v = { (uint32_t)b << 16 };
+    return v.f;
+}
+static uint16_t gemm_f32_to_bf16(float f) {
+    union { float f; uint32_t u; } v = { f };
+    const uint32_t lower = v.u & 0xFFFFu, upper = v.u >> 16;
+    const uint32_t round = (lower > 0x8000u) || ((lower == 0x8000u) && (upper & 1u));
+    return (uint16_t)(upper + round);
+}
+int orc_gemm_bf16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N, int K,
+                  int lda, int ldb, int ldc, int transpose_b, float alpha, float beta) {
+    if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return -1;
+    for (int m = 0; m < M; ++m) {
+        for (int n = 0; n < N; ++n) {
+            float sum = 0.0f;
+            for (int k = 0; k < K; ++k) {
+                const uint16_t av = A[(size_t)m * lda + k];
+                const uint16_t bv = transpose_b ? B[(size_t)n * ldb + k] : B[(size_t)k * ldb + n];
+                sum += gemm_bf16_to_f32(av) * gemm_bf16_to_f32(bv);
+            }
+            const size_t idx = (size_t)m * ldc + n;
+            const float prev = (beta == 0.0f) ? 0.0f : gemm_bf16_to_f32(C[idx]);
+            C[idx] = gemm_f32_to_bf16(alpha * sum + beta * prev);
+        }
+    }
+    return 0;
+}
+
 int orc_gemm_f16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N, int K,
                  int lda, int ldb, int ldc, int transpose_b, float alpha, float beta, int ref_narrowing) {
     if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return -1;

@@ -1,4 +1,4 @@
-// Dense fp16 GEMM on the sm_100a tensor cores: C[M,N] = alpha * A[M,K] . op(B) + beta * C, fp16
+// Dense fp16 / bf16 GEMM on the sm_100a tensor cores: C[M,N] = alpha * A[M,K] . op(B) + beta * C, 16-bit
 // storage, fp32 accumulation - the case of tc_gemm that the fused-norm callers and a prefill of
 // dequantised weights use (include/tensorcore/gemm.h:16-58; arithmetic lib/ops/gemm_cpu.cpp:544-568,
 // which adds the products in k order; here the tensor core's order, same fp32 accumulation).
@@ -26,6 +26,7 @@
 #include "sm100_prims.cuh"
 
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 namespace tcb {
@@ -46,6 +47,7 @@ struct GemmParams {
     int M, N, K, ldc;
     float alpha, beta;
     int b_kmajor;      // B was given transposed ([N][K])
+    int bf16;          // operands and result are bfloat16 (else binary16)
 };
 
 struct GemmBars {
@@ -125,7 +127,9 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = idesc_f16_f32(kBM, BN) | (p.b_kmajor ? 0u : (1u << 16));   // bit 16: B is MN-major
+            // bit 16: B is MN-major; bits 7-9 and 10-12: operand formats (0 binary16, 1 bfloat16)
+            const uint32_t idesc = idesc_f16_f32(kBM, BN) | (p.b_kmajor ? 0u : (1u << 16)) |
+                                   (p.bf16 ? ((1u << 7) | (1u << 10)) : 0u);
             int used = 0, it = 0;
             for (int t = blockIdx.x; t < n_tiles && !failed; t += gridDim.x, ++it) {
                 const int acc = it & 1;
@@ -193,9 +197,14 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
                         uint32_t h[8];
 #pragma unroll
                         for (int e = 0; e < 8; ++e) {
-                            const __half2 h2 = __floats2half2_rn(p.alpha * __uint_as_float(v[2 * e]),
-                                                                 p.alpha * __uint_as_float(v[2 * e + 1]));
-                            h[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                            const float f0 = p.alpha * __uint_as_float(v[2 * e]), f1 = p.alpha * __uint_as_float(v[2 * e + 1]);
+                            if (p.bf16) {
+                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(f0, f1);
+                                h[e] = *reinterpret_cast<const uint32_t*>(&b2);
+                            } else {
+                                const __half2 h2 = __floats2half2_rn(f0, f1);
+                                h[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                            }
                         }
                         reinterpret_cast<uint4*>(crow)[0] = make_uint4(h[0], h[1], h[2], h[3]);
                         reinterpret_cast<uint4*>(crow)[1] = make_uint4(h[4], h[5], h[6], h[7]);
@@ -204,8 +213,14 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
                         for (int e = 0; e < 16; ++e) {
                             if (n0 + c0 + e >= p.N) break;
                             float f = p.alpha * __uint_as_float(v[e]);
-                            if (p.beta != 0.f) f += p.beta * __half2float(crow[e]);
-                            crow[e] = __float2half_rn(f);
+                            if (p.bf16) {
+                                __nv_bfloat16* cb = reinterpret_cast<__nv_bfloat16*>(crow);
+                                if (p.beta != 0.f) f += p.beta * __bfloat162float(cb[e]);
+                                cb[e] = __float2bfloat16_rn(f);
+                            } else {
+                                if (p.beta != 0.f) f += p.beta * __half2float(crow[e]);
+                                crow[e] = __float2half_rn(f);
+                            }
                         }
                     }
                 }
@@ -279,7 +294,8 @@ cudaError_t init_gemm_tc_kernel(int smem_optin) {
 // cudaErrorNotSupported when the operands are outside what the tiled copies can describe: the leading
 // dimensions must be multiples of 8 elements and the bases 16-byte aligned.
 cudaError_t launch_gemm_f16_tc(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                               bool transpose_b, float alpha, float beta, const LaunchEnv& env, cudaStream_t stream) {
+                               bool transpose_b, float alpha, float beta, const LaunchEnv& env, cudaStream_t stream,
+                               bool bf16) {
     if (M <= 0 || N <= 0 || K <= 0 || lda % 8 || ldb % 8) return cudaErrorNotSupported;
     if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(B) & 15u)) return cudaErrorNotSupported;
     GemmParams p{};
@@ -288,6 +304,7 @@ cudaError_t launch_gemm_f16_tc(const void* A, const void* B, void* C, int M, int
     p.M = M; p.N = N; p.K = K; p.ldc = ldc;
     p.alpha = alpha; p.beta = beta;
     p.b_kmajor = transpose_b ? 1 : 0;
+    p.bf16 = bf16 ? 1 : 0;
     // 256-wide tiles halve the re-reads of A and the number of MMA instructions; measured faster than 128-wide
     // ones whenever N fills them (4096^3: 1119 against 769 TFLOP/s; 512 x 11008 x 4096: 629 against 523).
     const long sms = env.sm_count > 0 ? env.sm_count : 148;

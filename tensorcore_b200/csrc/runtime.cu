@@ -1631,9 +1631,9 @@ extern "C" tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* d, const tc_
                                const tc_buffer* B, tc_buffer* C) {
     if (!ctx) return TC_ERR_NOT_INITIALIZED;
     if (!d || !A || !B || !C || d->M <= 0 || d->N <= 0 || d->K <= 0) return TC_ERR_INVALID_ARG;
-    if (d->a_dtype != TC_DTYPE_F16 || d->b_dtype != TC_DTYPE_F16 || d->c_dtype != TC_DTYPE_F16 ||
-        d->accum_dtype != TC_DTYPE_F32)
-        return TC_ERR_UNSUPPORTED_DTYPE;
+    const bool f16 = d->a_dtype == TC_DTYPE_F16 && d->b_dtype == TC_DTYPE_F16 && d->c_dtype == TC_DTYPE_F16;
+    const bool bf16 = d->a_dtype == TC_DTYPE_BF16 && d->b_dtype == TC_DTYPE_BF16 && d->c_dtype == TC_DTYPE_BF16;
+    if ((!f16 && !bf16) || d->accum_dtype != TC_DTYPE_F32) return TC_ERR_UNSUPPORTED_DTYPE;
     if (d->transpose_a) return TC_ERR_UNSUPPORTED_FAMILY;
     const bool tb = d->transpose_b;
     // defaults as in lib/ops/gemm_cpu.cpp (effective_ldb): N for B as given, K for B transposed
@@ -1647,14 +1647,14 @@ extern "C" tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* d, const tc_
     bool unsupported = false;
     // A handful of rows (a decode step) takes the row kernel, which adds in the reference's k order;
     // anything larger the tensor cores, when the tiled copies can describe the operands.
-    const bool few_rows = d->M <= 4 && !tb;
+    const bool few_rows = d->M <= 4 && !tb && f16;
     const char* used = few_rows ? "gemm_f16_rows_sm100" : "gemm_f16_tcgen05_sm100";
     const tc_status_t st = run_step_op(ctx, "tc_gemm", used, io, 4, [&](cudaStream_t s) {
         cudaError_t e = cudaErrorNotSupported;
         if (!few_rows)
             e = tcb::launch_gemm_f16_tc(A->dptr, B->dptr, C->dptr, d->M, d->N, d->K, lda, ldb, ldc, tb, d->alpha, d->beta,
-                                        make_env(ctx, false), s);
-        if (e == cudaErrorNotSupported && !tb) {
+                                        make_env(ctx, false), s, bf16);
+        if (e == cudaErrorNotSupported && !tb && f16) {
             used = "gemm_f16_rows_sm100";
             e = tcb::launch_gemm_f16_rows(A->dptr, B->dptr, C->dptr, d->M, d->N, d->K, lda, ldb, ldc, d->alpha, d->beta, s);
         }

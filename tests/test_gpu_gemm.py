@@ -86,3 +86,26 @@ def test_argument_checks(tc, ctx):
     with pytest.raises(tc.TensorcoreError) as e:
         tc.gemm(ctx, a, a, a, 128, 64, 64)          # A would need 128 x 64 halves
     assert e.value.status != tc.TC_OK
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 64), (200, 264, 520), (3, 512, 1024), (512, 1024, 2048)])
+@pytest.mark.parametrize("tb", [False, True])
+def test_bfloat16_gemm_matches_oracle(tc, ctx, oracle, shape, tb):
+    """bfloat16 operands and result, fp32 accumulation: always the tensor-core kernel.  A bfloat16 result
+    has 8 significant bits: one last-place flip is 3.9e-3 of that element, so the bar is 2e-3 scaled RMS."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + N * 3 + K * 5 + int(tb))
+    A = oracle.to_bf16_bits(rng.standard_normal((M, K)))
+    B = oracle.to_bf16_bits(rng.standard_normal((N, K) if tb else (K, N)) * 0.05)
+    C0 = oracle.to_bf16_bits(rng.standard_normal((M, N)))
+    for alpha, beta in ((1.0, 0.0), (0.75, 0.5)):
+        a, b, c = ctx.buffer_from_array(A), ctx.buffer_from_array(B), ctx.buffer_from_array(C0)
+        tc.gemm(ctx, a, b, c, M, N, K, dtype="bf16", transpose_b=tb, alpha=alpha, beta=beta)
+        assert tc.cuda_last_kernel_name() == "gemm_f16_tcgen05_sm100"
+        got = oracle.from_bf16_bits(c.to_numpy((M, N), np.uint16))
+        want = oracle.from_bf16_bits(oracle.gemm_bf16(A, B, tb, alpha, beta, C0))
+        assert np.isfinite(got).all()
+        assert oracle.scaled_rms(got, want) <= 2e-3, (alpha, beta)
+        for x in (a, b, c):
+            x.close()
+    assert tc.take_device_error(ctx) == 0

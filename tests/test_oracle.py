@@ -222,6 +222,27 @@ def test_gemm_against_reference_backend_when_built(oracle):
     assert differing <= total // 200          # ties and lost carries are rare
 
 
+def test_gemm_bf16_against_reference_backend_when_built(oracle):
+    """The bfloat16 case of the same loop (conversions lib/ops/gemm_cpu.cpp:217-230): bit for bit."""
+    if not oracle.ref_available():
+        pytest.skip("oracle/_ref not built (no reference checkout on this machine)")
+    R = oracle.RefLib()
+    rng = np.random.default_rng(34)
+    for (M, N, K) in ((3, 8, 16), (17, 40, 136)):
+        A = oracle.to_bf16_bits(rng.standard_normal((M, K)))
+        B = oracle.to_bf16_bits(rng.standard_normal((K, N)))
+        C0 = oracle.to_bf16_bits(rng.standard_normal((M, N)))
+        for tb in (False, True):
+            Bx = np.ascontiguousarray(B.T) if tb else B
+            for alpha, beta in ((1.0, 0.0), (0.5, 1.5)):
+                a = oracle.gemm_bf16(A, Bx, tb, alpha, beta, C0)
+                b = R.gemm_f16(A, Bx, tb, alpha, beta, C0, dtype=1).view(np.uint16)
+                assert np.array_equal(a, b), (M, N, K, tb, alpha, beta)
+    # the bit helpers agree with a widening round trip
+    x = rng.standard_normal(1000).astype(np.float32)
+    assert np.array_equal(oracle.to_bf16_bits(oracle.from_bf16_bits(oracle.to_bf16_bits(x))), oracle.to_bf16_bits(x))
+
+
 def _attention_cases(g):
     return sorted(k[:-2] for k in g.files if k.endswith("_Q"))
 

@@ -303,13 +303,13 @@ tc_status_t tc_swiglu_forward(tc_context* ctx, const tc_buffer* gate, const tc_b
                               int n);
 
 /* include/tensorcore/gemm.h:16-58 (arithmetic: lib/ops/gemm_cpu.cpp:544-568).  Here: binary16 or
- * bfloat16 operands and result (all three the same) with fp32 accumulation, row-major, B as given
- * ([K,N]) or transposed ([N,K]), alpha, beta and leading dimensions - on the tensor cores (tcgen05)
+ * bfloat16 operands and result (all three the same) with fp32 accumulation, row-major, A and B as
+ * given ([M,K], [K,N]) or transposed ([K,M], [N,K]), alpha, beta and leading dimensions - on the tensor cores (tcgen05)
  * when lda and ldb are multiples of 8 elements and A and B are 16-byte aligned; binary16 with up to
  * four rows of A (a decode step: what tests/test_fused_norm_gemv.c compares the fused operations
  * against) or untransposed operands outside that take a row kernel that adds in the reference's k
  * order.  The result is narrowed with round-to-nearest-even.  Every other descriptor answers
- * TC_ERR_UNSUPPORTED_DTYPE (dtypes) or TC_ERR_UNSUPPORTED_FAMILY (transpose_a, bfloat16 operands
+ * TC_ERR_UNSUPPORTED_DTYPE (dtypes) or TC_ERR_UNSUPPORTED_FAMILY (bfloat16 or transposed operands
  * the tiled copies cannot describe). */
 typedef struct {
     int32_t M, N, K;
@@ -320,6 +320,9 @@ typedef struct {
 } tc_gemm_desc;
 tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* desc, const tc_buffer* A, const tc_buffer* B,
                     tc_buffer* C);
+/* include/tensorcore/gemm.h:52-58; runs at once, like the recorded forms of the other step operations. */
+tc_status_t tc_gemm_async(tc_context* ctx, const tc_gemm_desc* desc, const tc_buffer* A, const tc_buffer* B,
+                          tc_buffer* C, tc_stream* stream);
 
 /* include/tensorcore/attention.h:24-69 (arithmetic: lib/ops/attention_cpu.cpp:131-277).  fp16 Q
  * [batch, heads, seq_q, head_dim], K and V [batch, kv_heads, seq_kv, head_dim], O like Q, optional

@@ -154,18 +154,19 @@ def fused_rmsnorm_gemv(X_f16, gamma_f16, W_f16, eps=1e-5) -> np.ndarray:
     return Y.view(np.float16)
 
 
-def gemm_f16(A_f16, B_f16, transpose_b=False, alpha=1.0, beta=0.0, C_f16=None, ref_narrowing=False) -> np.ndarray:
+def gemm_f16(A_f16, B_f16, transpose_b=False, alpha=1.0, beta=0.0, C_f16=None, ref_narrowing=False,
+             transpose_a=False) -> np.ndarray:
     """alpha * A . op(B) + beta * C in the reference's order (lib/ops/gemm_cpu.cpp:544-568), stored with
     IEEE round-to-nearest-even or, ref_narrowing, with the reference GEMM's own narrowing (:142-160)."""
     A = np.ascontiguousarray(A_f16).view(np.uint16)
     B = np.ascontiguousarray(B_f16).view(np.uint16)
-    M, K = A.shape
+    K, M = A.shape if transpose_a else A.shape[::-1]
     N = B.shape[0] if transpose_b else B.shape[1]
     C = (np.zeros((M, N), dtype=np.uint16) if C_f16 is None
          else np.ascontiguousarray(C_f16).view(np.uint16).copy())
-    _call(lib().orc_gemm_f16, _p(A), _p(B), _p(C), c_int(M), c_int(N), c_int(K), c_int(K),
-          c_int(B.shape[1]), c_int(N), c_int(1 if transpose_b else 0), c_float(alpha), c_float(beta),
-          c_int(1 if ref_narrowing else 0))
+    _call(lib().orc_gemm_f16, _p(A), _p(B), _p(C), c_int(M), c_int(N), c_int(K), c_int(A.shape[1]),
+          c_int(B.shape[1]), c_int(N), c_int(1 if transpose_a else 0), c_int(1 if transpose_b else 0),
+          c_float(alpha), c_float(beta), c_int(1 if ref_narrowing else 0))
     return C.view(np.float16)
 
 
@@ -179,16 +180,17 @@ def from_bf16_bits(b: np.ndarray) -> np.ndarray:
     return (np.ascontiguousarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 
-def gemm_bf16(A_bits, B_bits, transpose_b=False, alpha=1.0, beta=0.0, C_bits=None) -> np.ndarray:
+def gemm_bf16(A_bits, B_bits, transpose_b=False, alpha=1.0, beta=0.0, C_bits=None, transpose_a=False) -> np.ndarray:
     """The bfloat16 case of gemm_f16 (lib/ops/gemm_cpu.cpp:544-568, conversions :217-230); operands and
     result are bfloat16 bit patterns (uint16)."""
     A = np.ascontiguousarray(A_bits, dtype=np.uint16)
     B = np.ascontiguousarray(B_bits, dtype=np.uint16)
-    M, K = A.shape
+    K, M = A.shape if transpose_a else A.shape[::-1]
     N = B.shape[0] if transpose_b else B.shape[1]
     C = np.zeros((M, N), dtype=np.uint16) if C_bits is None else np.ascontiguousarray(C_bits, dtype=np.uint16).copy()
-    _call(lib().orc_gemm_bf16, _p(A), _p(B), _p(C), c_int(M), c_int(N), c_int(K), c_int(K),
-          c_int(B.shape[1]), c_int(N), c_int(1 if transpose_b else 0), c_float(alpha), c_float(beta))
+    _call(lib().orc_gemm_bf16, _p(A), _p(B), _p(C), c_int(M), c_int(N), c_int(K), c_int(A.shape[1]),
+          c_int(B.shape[1]), c_int(N), c_int(1 if transpose_a else 0), c_int(1 if transpose_b else 0),
+          c_float(alpha), c_float(beta))
     return C
 
 
@@ -351,7 +353,8 @@ class RefLib:
         self._free(hw, hq)
         return out
 
-    def gemm_f16(self, A_f16, B_f16, transpose_b=False, alpha=1.0, beta=0.0, C_f16=None, dtype=0) -> np.ndarray:
+    def gemm_f16(self, A_f16, B_f16, transpose_b=False, alpha=1.0, beta=0.0, C_f16=None, dtype=0,
+                 transpose_a=False) -> np.ndarray:
         """tc_gemm of the reference's CPU backend (include/tensorcore/gemm.h:16-50), fp16 in and out."""
         class Desc(ctypes.Structure):
             _fields_ = [("M", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32), ("a", c_int), ("b", c_int),
@@ -359,13 +362,13 @@ class RefLib:
                         ("beta", c_float), ("lda", ctypes.c_int32), ("ldb", ctypes.c_int32), ("ldc", ctypes.c_int32)]
         A = np.ascontiguousarray(A_f16).view(np.uint16)
         B = np.ascontiguousarray(B_f16).view(np.uint16)
-        M, K = A.shape
+        K, M = A.shape if transpose_a else A.shape[::-1]
         N = B.shape[0] if transpose_b else B.shape[1]
         C = np.zeros((M, N), dtype=np.uint16) if C_f16 is None else np.ascontiguousarray(C_f16).view(np.uint16)
         ha, _, _ = self._buf(A)
         hb, _, _ = self._buf(B)
         hc, pc, nc = self._buf(C)
-        d = Desc(M, N, K, dtype, dtype, dtype, 2, False, bool(transpose_b), float(alpha), float(beta), 0, 0, 0)   # F16 = 0, BF16 = 1, F32 = 2
+        d = Desc(M, N, K, dtype, dtype, dtype, 2, bool(transpose_a), bool(transpose_b), float(alpha), float(beta), 0, 0, 0)   # F16 = 0, BF16 = 1, F32 = 2
         self.L.tc_gemm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
         st = self.L.tc_gemm(self.ctx, ctypes.byref(d), ha, hb, hc)
         assert st == 0, st

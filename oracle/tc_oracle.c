@@ -305,7 +305,7 @@ static uint16_t gemm_ref_f32_to_f16(float x) {
     return (uint16_t)(sign | ((uint32_t)exp << 10) | ((mant >> 13) + round));
 }
 
-/* lib/ops/gemm_cpu.cpp:544-568 (the binary16 case): row-major A [M,K] (lda), B [K,N] or, transposed,
+/* lib/ops/gemm_cpu.cpp:544-568 (the binary16 case): row-major A [M,K] or, transposed, [K,M] (lda), B [K,N] or, transposed,
  * [N,K] (ldb), C [M,N] (ldc); the products are added in k order in fp32;
  * C = fp16(alpha * sum + beta * C), C not read when beta is 0.  ref_narrowing: 0 = IEEE
  * round-to-nearest-even, 1 = the reference GEMM's own narrowing (see above). */
@@ -322,13 +322,13 @@ static uint16_t gemm_f32_to_bf16(float f) {
     return (uint16_t)(upper + round);
 }
 int orc_gemm_bf16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N, int K,
-                  int lda, int ldb, int ldc, int transpose_b, float alpha, float beta) {
+                  int lda, int ldb, int ldc, int transpose_a, int transpose_b, float alpha, float beta) {
     if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return -1;
     for (int m = 0; m < M; ++m) {
         for (int n = 0; n < N; ++n) {
             float sum = 0.0f;
             for (int k = 0; k < K; ++k) {
-                const uint16_t av = A[(size_t)m * lda + k];
+                const uint16_t av = transpose_a ? A[(size_t)k * lda + m] : A[(size_t)m * lda + k];
                 const uint16_t bv = transpose_b ? B[(size_t)n * ldb + k] : B[(size_t)k * ldb + n];
                 sum += gemm_bf16_to_f32(av) * gemm_bf16_to_f32(bv);
             }
@@ -341,13 +341,13 @@ int orc_gemm_bf16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int 
 }
 
 int orc_gemm_f16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N, int K,
-                 int lda, int ldb, int ldc, int transpose_b, float alpha, float beta, int ref_narrowing) {
+                 int lda, int ldb, int ldc, int transpose_a, int transpose_b, float alpha, float beta, int ref_narrowing) {
     if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return -1;
     for (int m = 0; m < M; ++m) {
         for (int n = 0; n < N; ++n) {
             float sum = 0.0f;
             for (int k = 0; k < K; ++k) {
-                const uint16_t av = A[(size_t)m * lda + k];
+                const uint16_t av = transpose_a ? A[(size_t)k * lda + m] : A[(size_t)m * lda + k];
                 const uint16_t bv = transpose_b ? B[(size_t)n * ldb + k] : B[(size_t)k * ldb + n];
                 sum += orc_f16_to_f32(av) * orc_f16_to_f32(bv);
             }

@@ -60,10 +60,10 @@ int orc_fused_rmsnorm_gemv(const uint16_t* X, const uint16_t* gamma, const uint1
                            uint16_t* Y, int M, int N, int K, float eps);
 /* lib/ops/gemm_cpu.cpp:544-568, fp16 storage and fp32 accumulation in k order. */
 int orc_gemm_f16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N, int K,
-                 int lda, int ldb, int ldc, int transpose_b, float alpha, float beta, int ref_narrowing);
+                 int lda, int ldb, int ldc, int transpose_a, int transpose_b, float alpha, float beta, int ref_narrowing);
 /* The bfloat16 case (conversions lib/ops/gemm_cpu.cpp:217-230); operands as raw 16-bit patterns. */
 int orc_gemm_bf16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N, int K,
-                  int lda, int ldb, int ldc, int transpose_b, float alpha, float beta);
+                  int lda, int ldb, int ldc, int transpose_a, int transpose_b, float alpha, float beta);
 /* lib/ops/training_cpu.cpp:858-935. */
 int orc_fused_layernorm_gemv(const uint16_t* X, const uint16_t* gamma, const uint16_t* beta,
                              const uint16_t* W, uint16_t* Y, int M, int N, int K, float eps);

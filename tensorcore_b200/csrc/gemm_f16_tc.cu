@@ -12,7 +12,8 @@
 //       - A ([M][K]) and a transposed B ([N][K]) are K-major: a box of 64 k x 128 (or BN) rows;
 //         8-row groups 1024 bytes apart, a K step of 16 elements 32 bytes further along the row.
 //       - B as given ([K][N], N contiguous) is MN-major: boxes of 64 n x 64 k, one per 64 columns,
-//         8192 bytes apart; 8 k are 1024 bytes, a K step of 16 is 2048 bytes.
+//         8192 bytes apart; 8 k are 1024 bytes, a K step of 16 is 2048 bytes.  A transposed
+//         ([K][M]) is loaded the same way.
 //     (Which of the descriptor's two strides is which was settled on the device: for the swizzled
 //     MN-major form the first is the stride along N, the second the one along K; for the K-major
 //     form the second is the stride between 8-row groups and the first is not used.)
@@ -47,6 +48,7 @@ struct GemmParams {
     int M, N, K, ldc;
     float alpha, beta;
     int b_kmajor;      // B was given transposed ([N][K])
+    int a_mnmajor;     // A was given transposed ([K][M])
     int bf16;          // operands and result are bfloat16 (else binary16)
 };
 
@@ -108,7 +110,12 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
                     const uint32_t par = static_cast<uint32_t>(issued / kStages) & 1u;
                     if (!bar_wait(&bars->empty[s], par ^ 1u, abort_flag)) { failed = true; break; }
                     bar_expect_tx(&bars->full[s], kAStage + kBStage);
-                    tensor_load_2d(a_ring + s * kAStage, &amap, ks * kBK, m0, &bars->full[s]);
+                    if (p.a_mnmajor) {       // [K][M]: two boxes of 64 m x 64 k, like B as given
+                        tensor_load_2d(a_ring + s * kAStage, &amap, m0, ks * kBK, &bars->full[s]);
+                        tensor_load_2d(a_ring + s * kAStage + 8192, &amap, m0 + 64, ks * kBK, &bars->full[s]);
+                    } else {
+                        tensor_load_2d(a_ring + s * kAStage, &amap, ks * kBK, m0, &bars->full[s]);
+                    }
                     if (p.b_kmajor) {
                         tensor_load_2d(b_ring + s * kBStage, &bmap, ks * kBK, n0, &bars->full[s]);
                     } else {
@@ -128,7 +135,7 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
     } else if (warp == 1) {
         if (lane == 0) {
             // bit 16: B is MN-major; bits 7-9 and 10-12: operand formats (0 binary16, 1 bfloat16)
-            const uint32_t idesc = idesc_f16_f32(kBM, BN) | (p.b_kmajor ? 0u : (1u << 16)) |
+            const uint32_t idesc = idesc_f16_f32(kBM, BN) | (p.b_kmajor ? 0u : (1u << 16)) | (p.a_mnmajor ? (1u << 15) : 0u) |
                                    (p.bf16 ? ((1u << 7) | (1u << 10)) : 0u);
             int used = 0, it = 0;
             for (int t = blockIdx.x; t < n_tiles && !failed; t += gridDim.x, ++it) {
@@ -145,7 +152,8 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
                     const uint32_t a_addr = s_u32(a_ring + s * kAStage), b_addr = s_u32(b_ring + s * kBStage);
 #pragma unroll
                     for (int j = 0; j < kBK / 16; ++j) {
-                        const uint64_t adesc = smem_desc(a_addr + j * 32, 16u, 1024u, kSwizzle128);
+                        const uint64_t adesc = p.a_mnmajor ? smem_desc(a_addr + j * 2048, 8192u, 1024u, kSwizzle128)
+                                                           : smem_desc(a_addr + j * 32, 16u, 1024u, kSwizzle128);
                         const uint64_t bdesc = p.b_kmajor ? smem_desc(b_addr + j * 32, 16u, 1024u, kSwizzle128)
                                                           : smem_desc(b_addr + j * 2048, 8192u, 1024u, kSwizzle128);
                         mma_f16_ss(d_tmem, adesc, bdesc, idesc, (ks > 0 || j > 0) ? 1u : 0u);
@@ -267,11 +275,14 @@ bool encode_rows_sw128(CUtensorMap* map, const void* base, uint64_t rows, uint64
 template <int BN>
 cudaError_t launch_tile(const GemmParams& p, const void* A, const void* B, int lda, int ldb, bool transpose_b,
                         const LaunchEnv& env, cudaStream_t stream) {
+    const bool transpose_a = p.a_mnmajor != 0;
     const int smem = kGemmBarBytes + kStages * (kAStage + BN * kBK * 2);
     if (smem > env.smem_optin) return cudaErrorNotSupported;
     CUtensorMap amap, bmap;
-    if (!encode_rows_sw128(&amap, A, static_cast<uint64_t>(p.M), static_cast<uint64_t>(p.K), static_cast<uint64_t>(lda), kBM))
-        return cudaErrorNotSupported;
+    const bool oka = transpose_a
+        ? encode_rows_sw128(&amap, A, static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.M), static_cast<uint64_t>(lda), kBK)
+        : encode_rows_sw128(&amap, A, static_cast<uint64_t>(p.M), static_cast<uint64_t>(p.K), static_cast<uint64_t>(lda), kBM);
+    if (!oka) return cudaErrorNotSupported;
     const bool okb = transpose_b
         ? encode_rows_sw128(&bmap, B, static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.K), static_cast<uint64_t>(ldb), BN)
         : encode_rows_sw128(&bmap, B, static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.N), static_cast<uint64_t>(ldb), kBK);
@@ -295,7 +306,7 @@ cudaError_t init_gemm_tc_kernel(int smem_optin) {
 // dimensions must be multiples of 8 elements and the bases 16-byte aligned.
 cudaError_t launch_gemm_f16_tc(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                                bool transpose_b, float alpha, float beta, const LaunchEnv& env, cudaStream_t stream,
-                               bool bf16) {
+                               bool bf16, bool transpose_a) {
     if (M <= 0 || N <= 0 || K <= 0 || lda % 8 || ldb % 8) return cudaErrorNotSupported;
     if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(B) & 15u)) return cudaErrorNotSupported;
     GemmParams p{};
@@ -305,6 +316,7 @@ cudaError_t launch_gemm_f16_tc(const void* A, const void* B, void* C, int M, int
     p.alpha = alpha; p.beta = beta;
     p.b_kmajor = transpose_b ? 1 : 0;
     p.bf16 = bf16 ? 1 : 0;
+    p.a_mnmajor = transpose_a ? 1 : 0;
     // 256-wide tiles halve the re-reads of A and the number of MMA instructions; measured faster than 128-wide
     // ones whenever N fills them (4096^3: 1119 against 769 TFLOP/s; 512 x 11008 x 4096: 629 against 523).
     const long sms = env.sm_count > 0 ? env.sm_count : 148;

@@ -234,7 +234,7 @@ cudaError_t launch_gemm_f16_rows(const void* A, const void* B, void* C, int M, i
 cudaError_t init_gemm_tc_kernel(int smem_optin);
 cudaError_t launch_gemm_f16_tc(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                                bool transpose_b, float alpha, float beta, const LaunchEnv& env, cudaStream_t stream,
-                               bool bf16 = false);
+                               bool bf16 = false, bool transpose_a = false);
 
 // --- attention forward for decode (attention.cu); fp16 data, fp32 softmax ----------------------------
 // Floats of scratch the launch needs, and into how many key chunks it will cut a row (1 = no scratch).

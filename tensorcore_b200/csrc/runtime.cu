@@ -1634,12 +1634,12 @@ extern "C" tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* d, const tc_
     const bool f16 = d->a_dtype == TC_DTYPE_F16 && d->b_dtype == TC_DTYPE_F16 && d->c_dtype == TC_DTYPE_F16;
     const bool bf16 = d->a_dtype == TC_DTYPE_BF16 && d->b_dtype == TC_DTYPE_BF16 && d->c_dtype == TC_DTYPE_BF16;
     if ((!f16 && !bf16) || d->accum_dtype != TC_DTYPE_F32) return TC_ERR_UNSUPPORTED_DTYPE;
-    if (d->transpose_a) return TC_ERR_UNSUPPORTED_FAMILY;
+    const bool ta = d->transpose_a;
     const bool tb = d->transpose_b;
     // defaults as in lib/ops/gemm_cpu.cpp (effective_ldb): N for B as given, K for B transposed
-    const int lda = d->lda ? d->lda : d->K, ldb = d->ldb ? d->ldb : (tb ? d->K : d->N), ldc = d->ldc ? d->ldc : d->N;
-    if (lda < d->K || ldb < (tb ? d->K : d->N) || ldc < d->N) return TC_ERR_INVALID_ARG;
-    const size_t ab = (static_cast<size_t>(d->M - 1) * lda + d->K) * 2;
+    const int lda = d->lda ? d->lda : (ta ? d->M : d->K), ldb = d->ldb ? d->ldb : (tb ? d->K : d->N), ldc = d->ldc ? d->ldc : d->N;
+    if (lda < (ta ? d->M : d->K) || ldb < (tb ? d->K : d->N) || ldc < d->N) return TC_ERR_INVALID_ARG;
+    const size_t ab = ta ? (static_cast<size_t>(d->K - 1) * lda + d->M) * 2 : (static_cast<size_t>(d->M - 1) * lda + d->K) * 2;
     const size_t bb = tb ? (static_cast<size_t>(d->N - 1) * ldb + d->K) * 2 : (static_cast<size_t>(d->K - 1) * ldb + d->N) * 2;
     const size_t cb = (static_cast<size_t>(d->M - 1) * ldc + d->N) * 2;
     // beta != 0 reads C as well
@@ -1647,14 +1647,14 @@ extern "C" tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* d, const tc_
     bool unsupported = false;
     // A handful of rows (a decode step) takes the row kernel, which adds in the reference's k order;
     // anything larger the tensor cores, when the tiled copies can describe the operands.
-    const bool few_rows = d->M <= 4 && !tb && f16;
+    const bool few_rows = d->M <= 4 && !ta && !tb && f16;
     const char* used = few_rows ? "gemm_f16_rows_sm100" : "gemm_f16_tcgen05_sm100";
     const tc_status_t st = run_step_op(ctx, "tc_gemm", used, io, 4, [&](cudaStream_t s) {
         cudaError_t e = cudaErrorNotSupported;
         if (!few_rows)
             e = tcb::launch_gemm_f16_tc(A->dptr, B->dptr, C->dptr, d->M, d->N, d->K, lda, ldb, ldc, tb, d->alpha, d->beta,
-                                        make_env(ctx, false), s, bf16);
-        if (e == cudaErrorNotSupported && !tb && f16) {
+                                        make_env(ctx, false), s, bf16, ta);
+        if (e == cudaErrorNotSupported && !ta && !tb && f16) {
             used = "gemm_f16_rows_sm100";
             e = tcb::launch_gemm_f16_rows(A->dptr, B->dptr, C->dptr, d->M, d->N, d->K, lda, ldb, ldc, d->alpha, d->beta, s);
         }
@@ -1663,6 +1663,13 @@ extern "C" tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* d, const tc_
     });
     t_last_kernel = used;
     return unsupported ? TC_ERR_UNSUPPORTED_FAMILY : st;
+}
+
+// include/tensorcore/gemm.h:52-58.  The recorded form runs at once (as the reference's CPU backend does).
+extern "C" tc_status_t tc_gemm_async(tc_context* ctx, const tc_gemm_desc* d, const tc_buffer* A,
+                                     const tc_buffer* B, tc_buffer* C, tc_stream* stream) {
+    if (!stream) return TC_ERR_INVALID_ARG;
+    return tc_gemm(ctx, d, A, B, C);
 }
 
 // ---------------------------------------------------------------------------------------

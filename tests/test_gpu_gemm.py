@@ -78,8 +78,8 @@ def test_argument_checks(tc, ctx):
         tc.gemm(ctx, a, a, a, 64, 64, 64, dtype="f32", accum="f32")
     assert e.value.status == tc.TC_ERR_UNSUPPORTED_DTYPE
     with pytest.raises(tc.TensorcoreError) as e:
-        tc.gemm(ctx, a, a, a, 64, 64, 64, transpose_a=True)
-    assert e.value.status == tc.TC_ERR_UNSUPPORTED_FAMILY
+        tc.gemm(ctx, a, a, a, 64, 64, 64, transpose_a=True, lda=60)      # a leading dimension the tiled copies cannot take
+    assert e.value.status in (tc.TC_ERR_UNSUPPORTED_FAMILY, tc.TC_ERR_INVALID_ARG)
     with pytest.raises(tc.TensorcoreError) as e:
         tc.gemm(ctx, a, a, a, 64, 64, 64, lda=32)
     assert e.value.status == tc.TC_ERR_INVALID_ARG
@@ -108,4 +108,33 @@ def test_bfloat16_gemm_matches_oracle(tc, ctx, oracle, shape, tb):
         assert oracle.scaled_rms(got, want) <= 2e-3, (alpha, beta)
         for x in (a, b, c):
             x.close()
+    assert tc.take_device_error(ctx) == 0
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (200, 264, 520), (8, 512, 1024)])
+@pytest.mark.parametrize("tb", [False, True])
+def test_transposed_a_matches_oracle(tc, ctx, oracle, shape, tb):
+    """A given as [K][M] (transpose_a), with B either way, and through tc_gemm_async."""
+    M, N, K = shape
+    rng = np.random.default_rng(M * 11 + N + K + int(tb))
+    At = rng.standard_normal((K, M)).astype(np.float16)
+    B = (rng.standard_normal((N, K) if tb else (K, N)) * 0.05).astype(np.float16)
+    a, b = ctx.buffer_from_array(At), ctx.buffer_from_array(B)
+    c = ctx.buffer(M * N * 2)
+    tc.gemm(ctx, a, b, c, M, N, K, transpose_a=True, transpose_b=tb)
+    assert tc.cuda_last_kernel_name() == "gemm_f16_tcgen05_sm100"
+    got = c.to_numpy((M, N), np.float16)
+    want = oracle.gemm_f16(At, B, tb, transpose_a=True)
+    assert oracle.scaled_rms(got, want) <= TOL
+    # the recorded form runs at once and gives the same bytes
+    import ctypes
+    st = ctx.stream()
+    d = tc.TCGemmDesc(M, N, K, 0, 0, 0, 2, True, bool(tb), 1.0, 0.0, 0, 0, 0)
+    c2 = ctx.buffer(M * N * 2)
+    L = tc.lib()
+    L.tc_gemm_async.argtypes = [ctypes.c_void_p] * 6
+    assert L.tc_gemm_async(ctx.handle, ctypes.byref(d), a.handle, b.handle, c2.handle, st.handle) == 0
+    assert L.tc_gemm_async(ctx.handle, ctypes.byref(d), a.handle, b.handle, c2.handle, None) == tc.TC_ERR_INVALID_ARG
+    st.sync()
+    assert np.array_equal(c2.to_numpy((M, N), np.uint16), got.view(np.uint16))
     assert tc.take_device_error(ctx) == 0

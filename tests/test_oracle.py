@@ -220,6 +220,14 @@ def test_gemm_against_reference_backend_when_built(oracle):
                 differing += int(np.count_nonzero(ieee.view(np.uint16) != b.view(np.uint16)))
                 total += ieee.size
     assert differing <= total // 200          # ties and lost carries are rare
+    # A given transposed ([K][M])
+    A = rng.standard_normal((40, 9)).astype(np.float16)
+    B = rng.standard_normal((40, 16)).astype(np.float16)
+    for tb in (False, True):
+        Bx = np.ascontiguousarray(B.T) if tb else B
+        a = oracle.gemm_f16(A, Bx, tb, 1.0, 0.0, None, True, transpose_a=True)
+        b = R.gemm_f16(A, Bx, tb, 1.0, 0.0, None, 0, True)
+        assert np.array_equal(a.view(np.uint16), b.view(np.uint16))
 
 
 def test_gemm_bf16_against_reference_backend_when_built(oracle):

@@ -320,6 +320,16 @@ typedef struct {
 } tc_gemm_desc;
 tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* desc, const tc_buffer* A, const tc_buffer* B,
                     tc_buffer* C);
+/* include/tensorcore/gemm.h:59-72: `batch` products of one shape, consecutive matrices stride_* elements
+ * apart (one launch per product).  batch <= 0 -> TC_ERR_INVALID_ARG; batch > 1 with a stride that is
+ * not positive or shorter than a matrix -> TC_ERR_INVALID_SHAPE (lib/ops/gemm_cpu.cpp:775-795). */
+typedef struct {
+    tc_gemm_desc base;
+    int32_t batch;
+    int64_t stride_a, stride_b, stride_c;
+} tc_gemm_batched_desc;
+tc_status_t tc_gemm_batched(tc_context* ctx, const tc_gemm_batched_desc* desc, const tc_buffer* A,
+                            const tc_buffer* B, tc_buffer* C);
 /* include/tensorcore/gemm.h:52-58; runs at once, like the recorded forms of the other step operations. */
 tc_status_t tc_gemm_async(tc_context* ctx, const tc_gemm_desc* desc, const tc_buffer* A, const tc_buffer* B,
                           tc_buffer* C, tc_stream* stream);

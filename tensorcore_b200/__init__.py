@@ -491,6 +491,20 @@ def gemm(ctx, A, B, C, M, N, K, dtype="f16", accum="f32", transpose_a=False, tra
     _check(lib().tc_gemm(_h(ctx), byref(d), _h(A), _h(B), _h(C)))
 
 
+class TCGemmBatchedDesc(Structure):   # tc_gemm_batched_desc
+    _fields_ = [("base", TCGemmDesc), ("batch", ctypes.c_int32), ("stride_a", ctypes.c_int64),
+                ("stride_b", ctypes.c_int64), ("stride_c", ctypes.c_int64)]
+
+
+def gemm_batched(ctx, A, B, C, M, N, K, batch, stride_a, stride_b, stride_c, dtype="f16", accum="f32",
+                 transpose_a=False, transpose_b=False, alpha=1.0, beta=0.0, lda=0, ldb=0, ldc=0) -> None:
+    """`batch` products of one shape, consecutive matrices stride_* elements apart (tc_gemm_batched)."""
+    d = TCGemmBatchedDesc(TCGemmDesc(int(M), int(N), int(K), _dtype(dtype), _dtype(dtype), _dtype(dtype), _dtype(accum),
+                                     bool(transpose_a), bool(transpose_b), float(alpha), float(beta), int(lda), int(ldb),
+                                     int(ldc)), int(batch), int(stride_a), int(stride_b), int(stride_c))
+    _check(lib().tc_gemm_batched(_h(ctx), byref(d), _h(A), _h(B), _h(C)))
+
+
 class TCAttentionDesc(Structure):     # tc_attention_desc
     _fields_ = [("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("seq_q", ctypes.c_int32),
                 ("seq_kv", ctypes.c_int32), ("head_dim", ctypes.c_int32), ("io_dtype", c_int),

@@ -1627,21 +1627,31 @@ extern "C" tc_status_t tc_attention_forward_async(tc_context* ctx, const tc_atte
     return tc_attention_forward(ctx, d, Q, K, V, O, LSE);
 }
 
-extern "C" tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* d, const tc_buffer* A,
-                               const tc_buffer* B, tc_buffer* C) {
+// tc_gemm and tc_gemm_batched (include/tensorcore/gemm.h:45-72; checks as in lib/ops/gemm_cpu.cpp:768-810):
+// `batch` products of the same shape, the matrices of consecutive products stride_* elements apart.
+static tc_status_t gemm_impl(tc_context* ctx, const tc_gemm_desc* d, const tc_buffer* A, const tc_buffer* B,
+                             tc_buffer* C, int batch, long long stride_a, long long stride_b, long long stride_c,
+                             const char* opname) {
     if (!ctx) return TC_ERR_NOT_INITIALIZED;
-    if (!d || !A || !B || !C || d->M <= 0 || d->N <= 0 || d->K <= 0) return TC_ERR_INVALID_ARG;
+    if (!d || !A || !B || !C || d->M <= 0 || d->N <= 0 || d->K <= 0 || batch <= 0) return TC_ERR_INVALID_ARG;
     const bool f16 = d->a_dtype == TC_DTYPE_F16 && d->b_dtype == TC_DTYPE_F16 && d->c_dtype == TC_DTYPE_F16;
     const bool bf16 = d->a_dtype == TC_DTYPE_BF16 && d->b_dtype == TC_DTYPE_BF16 && d->c_dtype == TC_DTYPE_BF16;
     if ((!f16 && !bf16) || d->accum_dtype != TC_DTYPE_F32) return TC_ERR_UNSUPPORTED_DTYPE;
+    if (batch > 1 && (stride_a <= 0 || stride_b <= 0 || stride_c <= 0)) return TC_ERR_INVALID_SHAPE;
     const bool ta = d->transpose_a;
     const bool tb = d->transpose_b;
     // defaults as in lib/ops/gemm_cpu.cpp (effective_ldb): N for B as given, K for B transposed
     const int lda = d->lda ? d->lda : (ta ? d->M : d->K), ldb = d->ldb ? d->ldb : (tb ? d->K : d->N), ldc = d->ldc ? d->ldc : d->N;
     if (lda < (ta ? d->M : d->K) || ldb < (tb ? d->K : d->N) || ldc < d->N) return TC_ERR_INVALID_ARG;
-    const size_t ab = ta ? (static_cast<size_t>(d->K - 1) * lda + d->M) * 2 : (static_cast<size_t>(d->M - 1) * lda + d->K) * 2;
-    const size_t bb = tb ? (static_cast<size_t>(d->N - 1) * ldb + d->K) * 2 : (static_cast<size_t>(d->K - 1) * ldb + d->N) * 2;
-    const size_t cb = (static_cast<size_t>(d->M - 1) * ldc + d->N) * 2;
+    const size_t a1 = ta ? static_cast<size_t>(d->K - 1) * lda + d->M : static_cast<size_t>(d->M - 1) * lda + d->K;
+    const size_t b1 = tb ? static_cast<size_t>(d->N - 1) * ldb + d->K : static_cast<size_t>(d->K - 1) * ldb + d->N;
+    const size_t c1 = static_cast<size_t>(d->M - 1) * ldc + d->N;
+    if (batch > 1 && (static_cast<size_t>(stride_a) < a1 || static_cast<size_t>(stride_b) < b1 || static_cast<size_t>(stride_c) < c1))
+        return TC_ERR_INVALID_SHAPE;
+    const size_t nb1 = static_cast<size_t>(batch - 1);
+    const size_t ab = (nb1 * static_cast<size_t>(batch > 1 ? stride_a : 0) + a1) * 2;
+    const size_t bb = (nb1 * static_cast<size_t>(batch > 1 ? stride_b : 0) + b1) * 2;
+    const size_t cb = (nb1 * static_cast<size_t>(batch > 1 ? stride_c : 0) + c1) * 2;
     // beta != 0 reads C as well
     StepIo io[] = {{mut(A), ab, false}, {mut(B), bb, false}, {C, cb, false}, {C, cb, true}};
     bool unsupported = false;
@@ -1649,20 +1659,41 @@ extern "C" tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* d, const tc_
     // anything larger the tensor cores, when the tiled copies can describe the operands.
     const bool few_rows = d->M <= 4 && !ta && !tb && f16;
     const char* used = few_rows ? "gemm_f16_rows_sm100" : "gemm_f16_tcgen05_sm100";
-    const tc_status_t st = run_step_op(ctx, "tc_gemm", used, io, 4, [&](cudaStream_t s) {
-        cudaError_t e = cudaErrorNotSupported;
-        if (!few_rows)
-            e = tcb::launch_gemm_f16_tc(A->dptr, B->dptr, C->dptr, d->M, d->N, d->K, lda, ldb, ldc, tb, d->alpha, d->beta,
-                                        make_env(ctx, false), s, bf16, ta);
-        if (e == cudaErrorNotSupported && !ta && !tb && f16) {
-            used = "gemm_f16_rows_sm100";
-            e = tcb::launch_gemm_f16_rows(A->dptr, B->dptr, C->dptr, d->M, d->N, d->K, lda, ldb, ldc, d->alpha, d->beta, s);
+    int launched = 0;
+    const tc_status_t st = run_step_op(ctx, opname, used, io, 4, [&](cudaStream_t s) {
+        for (int i = 0; i < batch; ++i) {
+            const uint8_t* pa = static_cast<const uint8_t*>(A->dptr) + static_cast<size_t>(i) * (batch > 1 ? stride_a : 0) * 2;
+            const uint8_t* pb = static_cast<const uint8_t*>(B->dptr) + static_cast<size_t>(i) * (batch > 1 ? stride_b : 0) * 2;
+            uint8_t* pc = static_cast<uint8_t*>(C->dptr) + static_cast<size_t>(i) * (batch > 1 ? stride_c : 0) * 2;
+            cudaError_t e = cudaErrorNotSupported;
+            if (!few_rows)
+                e = tcb::launch_gemm_f16_tc(pa, pb, pc, d->M, d->N, d->K, lda, ldb, ldc, tb, d->alpha, d->beta,
+                                            make_env(ctx, false), s, bf16, ta);
+            if (e == cudaErrorNotSupported && !ta && !tb && f16) {
+                used = "gemm_f16_rows_sm100";
+                e = tcb::launch_gemm_f16_rows(pa, pb, pc, d->M, d->N, d->K, lda, ldb, ldc, d->alpha, d->beta, s);
+            }
+            if (e == cudaErrorNotSupported) { unsupported = true; return cudaSuccess; }
+            if (e != cudaSuccess) return e;
+            ++launched;
         }
-        if (e == cudaErrorNotSupported) { unsupported = true; return cudaSuccess; }
-        return e;
+        return cudaSuccess;
     });
+    if (launched > 1) g_launches.fetch_add(static_cast<uint64_t>(launched - 1));
     t_last_kernel = used;
     return unsupported ? TC_ERR_UNSUPPORTED_FAMILY : st;
+}
+
+extern "C" tc_status_t tc_gemm(tc_context* ctx, const tc_gemm_desc* d, const tc_buffer* A,
+                               const tc_buffer* B, tc_buffer* C) {
+    return gemm_impl(ctx, d, A, B, C, 1, 0, 0, 0, "tc_gemm");
+}
+
+extern "C" tc_status_t tc_gemm_batched(tc_context* ctx, const tc_gemm_batched_desc* bd, const tc_buffer* A,
+                                       const tc_buffer* B, tc_buffer* C) {
+    if (!ctx) return TC_ERR_NOT_INITIALIZED;
+    if (!bd) return TC_ERR_INVALID_ARG;
+    return gemm_impl(ctx, &bd->base, A, B, C, bd->batch, bd->stride_a, bd->stride_b, bd->stride_c, "tc_gemm_batched");
 }
 
 // include/tensorcore/gemm.h:52-58.  The recorded form runs at once (as the reference's CPU backend does).

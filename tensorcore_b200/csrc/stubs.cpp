@@ -29,7 +29,6 @@ TCB_EXPORT int tc_diloco_apply_outer(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_diloco_finalize(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_diloco_init(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_diloco_step(void) { return TCB_UNSUPPORTED; }
-TCB_EXPORT int tc_gemm_batched(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_hip_device_at(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_hip_device_info_get(void) { return TCB_UNSUPPORTED; }
 TCB_EXPORT int tc_hip_init(void) { return TCB_UNSUPPORTED; }

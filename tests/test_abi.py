@@ -97,7 +97,7 @@ def test_no_device_means_failure_not_fallback(tc):
 
 def test_stubs_report_unsupported(tc):
     L = tc.lib()
-    for name in ("tc_gemm_batched", "tc_attention_backward", "tc_rmsnorm_backward", "tc_adamw_step"):
+    for name in ("tc_attention_backward", "tc_rmsnorm_backward", "tc_adamw_step", "tc_conv2d_forward"):
         fn = getattr(L, name)
         fn.restype = ctypes.c_int
         assert fn() == tc.TC_ERR_UNSUPPORTED_FAMILY
@@ -107,6 +107,9 @@ def test_stubs_report_unsupported(tc):
     assert L.tc_swiglu_forward(None, None, None, None, 8) == tc.TC_ERR_NOT_INITIALIZED
     assert L.tc_rope_forward(None, None, None, None, 1, 1, 1, 2) == tc.TC_ERR_NOT_INITIALIZED
     assert L.tc_attention_forward(None, None, None, None, None, None, None) == tc.TC_ERR_NOT_INITIALIZED
+    assert L.tc_gemm(None, None, None, None, None) == tc.TC_ERR_NOT_INITIALIZED
+    assert L.tc_gemm_batched(None, None, None, None, None) == tc.TC_ERR_NOT_INITIALIZED
+    assert L.tc_gemm_async(None, None, None, None, None, None) == tc.TC_ERR_INVALID_ARG      # NULL stream first
     assert L.tc_dist_init(None, 0, 1, 0, None, None) == tc.TC_ERR_NOT_INITIALIZED
     assert L.tc_allreduce(None, None, 0, 2, 0) == tc.TC_ERR_INVALID_ARG and L.tc_barrier(None) == tc.TC_ERR_INVALID_ARG
     assert L.tc_dist_world_size(None) == 0

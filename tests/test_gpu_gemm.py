@@ -138,3 +138,33 @@ def test_transposed_a_matches_oracle(tc, ctx, oracle, shape, tb):
     st.sync()
     assert np.array_equal(c2.to_numpy((M, N), np.uint16), got.view(np.uint16))
     assert tc.take_device_error(ctx) == 0
+
+
+def test_batched_gemm_matches_oracle_per_product(tc, ctx, oracle):
+    """tc_gemm_batched: products of one shape at element strides, B transposed in half of the cases."""
+    rng = np.random.default_rng(77)
+    M, N, K, batch = 136, 264, 320, 3
+    sa, sb, sc = M * K + 64, K * N + 128, M * N + 8
+    A = rng.standard_normal(batch * sa).astype(np.float16)
+    C0 = np.zeros(batch * sc, dtype=np.float16)
+    for tb in (False, True):
+        Bf = (rng.standard_normal(batch * sb) * 0.05).astype(np.float16)
+        a, b, c = ctx.buffer_from_array(A), ctx.buffer_from_array(Bf), ctx.buffer_from_array(C0)
+        tc.gemm_batched(ctx, a, b, c, M, N, K, batch, sa, sb, sc, transpose_b=tb)
+        assert tc.cuda_last_kernel_name() == "gemm_f16_tcgen05_sm100"
+        got = c.to_numpy((batch * sc,), np.float16)
+        for i in range(batch):
+            Ai = A[i * sa:i * sa + M * K].reshape(M, K)
+            Bi = Bf[i * sb:i * sb + K * N].reshape((N, K) if tb else (K, N))
+            want = oracle.gemm_f16(Ai, Bi, tb)
+            assert oracle.scaled_rms(got[i * sc:i * sc + M * N].reshape(M, N), want) <= TOL, (tb, i)
+            assert not got[i * sc + M * N:(i + 1) * sc].any()          # the gap between results stays untouched
+        for x in (a, b, c):
+            x.close()
+    a = ctx.buffer(1 << 20)
+    with pytest.raises(tc.TensorcoreError) as e:
+        tc.gemm_batched(ctx, a, a, a, 64, 64, 64, 0, 4096, 4096, 4096)
+    assert e.value.status == tc.TC_ERR_INVALID_ARG
+    with pytest.raises(tc.TensorcoreError) as e:
+        tc.gemm_batched(ctx, a, a, a, 64, 64, 64, 2, 100, 4096, 4096)       # stride shorter than a matrix
+    assert e.value.status == tc.TC_ERR_INVALID_SHAPE

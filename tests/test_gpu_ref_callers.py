@@ -129,13 +129,34 @@ info = tc.gguf_loaded_tensor_quantized_matrix_info(t)
 tc.gemv_quantized(ctx, bx, t["buffer"], by, "q4_0", M, N, K); tc.buffer_read(by, Y)
 assert np.abs(Y.astype(np.float32) - ref).max() < 2e-2
 tc.gguf_loaded_model_free(ctx, model); tc.gguf_close(g)
+# dense GEMM (fp16 and bf16 storage), its recorded and batched forms
+Mg, Ng, Kg = 136, 264, 320
+Ag = rng.standard_normal((Mg, Kg)).astype(np.float16)
+Bg = (rng.standard_normal((Kg, Ng)) * 0.05).astype(np.float16)
+ba, bb, bc = (tc.buffer_alloc(ctx, n) for n in (Ag.nbytes, Bg.nbytes, Mg * Ng * 2))
+tc.buffer_write(ba, Ag); tc.buffer_write(bb, Bg)
+Cg = np.zeros((Mg, Ng), np.float16)
+tc.gemm(ctx, ba, bb, bc, Mg, Ng, Kg); tc.buffer_read(bc, Cg)
+refg = Ag.astype(np.float32) @ Bg.astype(np.float32)
+assert np.abs(Cg.astype(np.float32) - refg).max() < 2e-2, np.abs(Cg.astype(np.float32) - refg).max()
+assert tc.last_backend_name() == "cuda"
+st = tc.stream_create(ctx)
+tc.gemm_async(ctx, ba, bb, bc, Mg, Ng, Kg, st, alpha=0.5); tc.stream_sync(st); tc.stream_destroy(ctx, st)
+tc.buffer_read(bc, Cg)
+assert np.abs(Cg.astype(np.float32) - 0.5 * refg).max() < 2e-2
+A2 = np.stack([Ag, -Ag]); B2 = np.stack([Bg, Bg])
+ba2, bb2, bc2 = (tc.buffer_alloc(ctx, n) for n in (A2.nbytes, B2.nbytes, 2 * Mg * Ng * 2))
+tc.buffer_write(ba2, A2); tc.buffer_write(bb2, B2)
+C2 = np.zeros((2, Mg, Ng), np.float16)
+tc.gemm_batched(ctx, ba2, bb2, bc2, 2, Mg, Ng, Kg); tc.buffer_read(bc2, C2)
+assert np.abs(C2[0].astype(np.float32) - refg).max() < 2e-2 and np.abs(C2[1].astype(np.float32) + refg).max() < 2e-2
 print("binding ok", info)
 """
 
 
 def test_unchanged_reference_binding_drives_the_path(tc, tmp_path):
-    """Quantise, GEMV (sync and recorded), fused RMSNorm GEMV, dense fused GEMV and the GGUF
-    loader, called through the reference's own ctypes binding (python/tensorcore/__init__.py, not
+    """Quantise, GEMV (sync and recorded), fused RMSNorm GEMV, dense fused GEMV, the GGUF loader
+    and the dense GEMM (plain, recorded, batched), called through the reference's own ctypes binding (python/tensorcore/__init__.py, not
     modified) with TENSORCORE_LIB pointing at this library - the operations that
     python/tests/test_basic.py:981-1026, 690-717 and 1040-1190 cover."""
     if not os.path.isdir(REF_PY):

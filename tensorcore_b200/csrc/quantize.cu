@@ -93,50 +93,49 @@ __global__ void __launch_bounds__(kQThreads) quantize_kernel(const uint4* __rest
 
 // Blocks back to fp16, [N][K] row-major: (q - 8) * d for Q4_0, q * d for Q8_0, one rounding each (the
 // product of an integer of at most 8 bits and an fp16 has at most 19 significant bits).  A thread
-// per block.  For the prefill-sized path of the quantized GEMV (many activation rows), which
-// multiplies the result on the tensor cores.
+// per eight weights: it reads the block's scale and eight bytes of quants (blocks are 2-byte
+// aligned: four 16-bit loads) and writes one 16-byte piece, so a warp writes 512 contiguous bytes.
+// For the prefill-sized path of the quantized GEMV (many activation rows), which multiplies the
+// result on the tensor cores.
 __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ Wq, __half* __restrict__ W,
-                                                         long long blocks, int q8) {
-    const long long b = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (b >= blocks) return;
-    __half* out = W + b * 32;
-    uint32_t packed[16];
-    if (q8) {
-        const uint8_t* src = Wq + b * 34;
-        const float d = __half2float(*reinterpret_cast<const __half*>(src));
-        const int8_t* q = reinterpret_cast<const int8_t*>(src + 2);
+                                                         long long pieces, int q8) {
+    const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= pieces) return;
+    const long long b = t >> 2;
+    const int q = static_cast<int>(t & 3);
+    const uint8_t* blk = Wq + b * (q8 ? 34 : 18);
+    const float d = __half2float(*reinterpret_cast<const __half*>(blk));
+    // Q8_0: elements 8q .. 8q+7 are bytes 8q .. 8q+7.  Q4_0: elements 0-15 are the low nibbles of bytes
+    // 0-15, elements 16-31 the high nibbles: piece q takes bytes 8 (q & 1) .. + 7, high nibbles for q >= 2.
+    const uint16_t* src = reinterpret_cast<const uint16_t*>(blk + 2 + (q8 ? 8 * q : 8 * (q & 1)));
+    uint32_t packed[4];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const __half2 h = __floats2half2_rn(static_cast<float>(q[2 * i]) * d, static_cast<float>(q[2 * i + 1]) * d);
-            packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t two = src[i];
+        float f0, f1;
+        if (q8) {
+            f0 = static_cast<float>(static_cast<int8_t>(two & 0xffu));
+            f1 = static_cast<float>(static_cast<int8_t>(two >> 8));
+        } else {
+            const int sh = (q >> 1) * 4;
+            f0 = static_cast<float>(static_cast<int>((two >> sh) & 15u) - 8);
+            f1 = static_cast<float>(static_cast<int>((two >> (8 + sh)) & 15u) - 8);
         }
-    } else {
-        const uint8_t* src = Wq + b * 18;
-        const float d = __half2float(*reinterpret_cast<const __half*>(src));
-        const uint8_t* q = src + 2;
-        // element i is the low nibble of byte i, element i + 16 the high nibble
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int b0 = q[2 * i], b1 = q[2 * i + 1];
-            const __half2 lo = __floats2half2_rn(static_cast<float>((b0 & 15) - 8) * d, static_cast<float>((b1 & 15) - 8) * d);
-            const __half2 hi = __floats2half2_rn(static_cast<float>((b0 >> 4) - 8) * d, static_cast<float>((b1 >> 4) - 8) * d);
-            packed[i] = *reinterpret_cast<const uint32_t*>(&lo);
-            packed[8 + i] = *reinterpret_cast<const uint32_t*>(&hi);
-        }
+        const __half2 h = __floats2half2_rn(f0 * d, f1 * d);
+        packed[i] = *reinterpret_cast<const uint32_t*>(&h);
     }
-    uint4* o4 = reinterpret_cast<uint4*>(out);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) o4[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+    reinterpret_cast<uint4*>(W)[t] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
 }
 
 cudaError_t launch_dequantize(const void* W_quant, void* W_f16, int fmt, int N, int K, cudaStream_t stream) {
     if ((fmt != FMT_Q4_0 && fmt != FMT_Q8_0) || N <= 0 || K <= 0 || K % 32) return cudaErrorNotSupported;
     if (reinterpret_cast<uintptr_t>(W_f16) & 15u) return cudaErrorNotSupported;
-    const long long blocks = static_cast<long long>(N) * (K / 32);
-    const long long grid = (blocks + 255) / 256;
+    if (reinterpret_cast<uintptr_t>(W_quant) & 1u) return cudaErrorNotSupported;
+    const long long pieces = static_cast<long long>(N) * (K / 32) * 4;
+    const long long grid = (pieces + 255) / 256;
     if (grid > 0x7fffffffLL) return cudaErrorNotSupported;
     dequantize_kernel<<<static_cast<unsigned>(grid), 256, 0, stream>>>(static_cast<const uint8_t*>(W_quant),
-                                                                      static_cast<__half*>(W_f16), blocks, fmt == FMT_Q8_0);
+                                                                      static_cast<__half*>(W_f16), pieces, fmt == FMT_Q8_0);
     return cudaGetLastError();
 }
 

@@ -99,7 +99,29 @@ def main() -> None:
         att[name + "_slopes"], att[name + "_cfg"] = sl, np.array([int(causal), window], np.int32)
         att[name + "_O"], att[name + "_LSE"] = Oa.view(np.uint16), La
     np.savez_compressed(os.path.join(OUT, "attention.npz"), **att)
+    gemm_fixture(R)
     print("wrote", sorted(os.listdir(OUT)))
+
+
+def gemm_fixture(R) -> None:
+    """tc_gemm of the reference's CPU backend: fp16 and bf16 storage, either operand transposed, alpha and
+    beta.  Its own generator so that the other fixtures keep their random streams."""
+    rng = np.random.default_rng(0x6E44)
+    out = {}
+    for name, M, N, K, dt in (("f16_small", 5, 24, 72, 0), ("f16_mid", 33, 40, 256, 0), ("bf16_mid", 17, 40, 136, 1)):
+        conv = (lambda a: a.astype(np.float16).view(np.uint16)) if dt == 0 else O.to_bf16_bits
+        A, B, C0 = conv(rng.standard_normal((M, K))), conv(rng.standard_normal((K, N))), conv(rng.standard_normal((M, N)))
+        out[name + "_A"], out[name + "_B"], out[name + "_C0"] = A, B, C0
+        out[name + "_dtype"] = np.array([dt], np.int32)
+        for ta in (0, 1):
+            for tb in (0, 1):
+                for tag, alpha, beta in (("plain", 1.0, 0.0), ("ab", 0.5, 1.5)):
+                    Ax = np.ascontiguousarray(A.T) if ta else A
+                    Bx = np.ascontiguousarray(B.T) if tb else B
+                    view = (lambda a: a.view(np.float16)) if dt == 0 else (lambda a: a)
+                    Y = R.gemm_f16(view(Ax), view(Bx), bool(tb), alpha, beta, view(C0), dtype=dt, transpose_a=bool(ta))
+                    out[f"{name}_Y_{ta}{tb}_{tag}"] = np.ascontiguousarray(Y).view(np.uint16)
+    np.savez_compressed(os.path.join(OUT, "gemm.npz"), **out)
 
 
 if __name__ == "__main__":

@@ -168,3 +168,37 @@ def test_batched_gemm_matches_oracle_per_product(tc, ctx, oracle):
     with pytest.raises(tc.TensorcoreError) as e:
         tc.gemm_batched(ctx, a, a, a, 64, 64, 64, 2, 100, 4096, 4096)       # stride shorter than a matrix
     assert e.value.status == tc.TC_ERR_INVALID_SHAPE
+
+
+def test_gemm_against_reference_golden_vectors(tc, ctx, oracle):
+    """The reference's own CPU results (tests/golden/gemm.npz): fp16 within the 3e-4 bar (its narrowing
+    differs from IEEE on ties and on a carry out of the mantissa, a handful of elements), bf16 within 2e-3."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "gemm.npz"))
+    for name in sorted({k.rsplit("_A", 1)[0] for k in g.files if k.endswith("_A")}):
+        A, B, C0, dt = g[name + "_A"], g[name + "_B"], g[name + "_C0"], int(g[name + "_dtype"][0])
+        M, K = A.shape
+        N = B.shape[1]
+        widen = (lambda a: a.view(np.float16).astype(np.float32)) if dt == 0 else oracle.from_bf16_bits
+        for ta in (0, 1):
+            for tb in (0, 1):
+                for tag, alpha, beta in (("plain", 1.0, 0.0), ("ab", 0.5, 1.5)):
+                    Ax = np.ascontiguousarray(A.T) if ta else A
+                    Bx = np.ascontiguousarray(B.T) if tb else B
+                    a, b, c = ctx.buffer_from_array(Ax), ctx.buffer_from_array(Bx), ctx.buffer_from_array(C0)
+                    try:
+                        tc.gemm(ctx, a, b, c, M, N, K, dtype="f16" if dt == 0 else "bf16", transpose_a=bool(ta),
+                                transpose_b=bool(tb), alpha=alpha, beta=beta)
+                    except tc.TensorcoreError as e:
+                        # operands the tiled copies cannot describe (a leading dimension that is not a multiple of 8)
+                        assert e.status == tc.TC_ERR_UNSUPPORTED_FAMILY and (ta or tb or dt == 1), (name, ta, tb)
+                        continue
+                    got = widen(c.to_numpy((M, N), np.uint16))
+                    want = widen(g[f"{name}_Y_{ta}{tb}_{tag}"])
+                    bar = 3e-4 if dt == 0 else 2e-3
+                    # the reference's fp16 narrowing can lose a carry (a factor of two on that element): compare robustly
+                    close = np.abs(got - want) <= 0.02 * np.maximum(1.0, np.abs(want))
+                    assert close.mean() >= 0.995, (name, ta, tb, tag)
+                    assert oracle.scaled_rms(got[close], want[close]) <= bar, (name, ta, tb, tag)
+                    for x in (a, b, c):
+                        x.close()

@@ -230,6 +230,28 @@ def test_gemm_against_reference_backend_when_built(oracle):
         assert np.array_equal(a.view(np.uint16), b.view(np.uint16))
 
 
+def test_gemm_matches_reference_golden_vectors(oracle):
+    """tests/golden/gemm.npz holds outputs of the reference's CPU tc_gemm (fp16 with that file's own
+    narrowing, bf16), either operand transposed, with alpha and beta: the oracle reproduces every byte."""
+    g = np.load(os.path.join(GOLDEN, "gemm.npz"))
+    names = sorted({k.rsplit("_A", 1)[0] for k in g.files if k.endswith("_A")})
+    assert len(names) == 3
+    for name in names:
+        A, B, C0, dt = g[name + "_A"], g[name + "_B"], g[name + "_C0"], int(g[name + "_dtype"][0])
+        for ta in (0, 1):
+            for tb in (0, 1):
+                for tag, alpha, beta in (("plain", 1.0, 0.0), ("ab", 0.5, 1.5)):
+                    Ax = np.ascontiguousarray(A.T) if ta else A
+                    Bx = np.ascontiguousarray(B.T) if tb else B
+                    want = g[f"{name}_Y_{ta}{tb}_{tag}"]
+                    if dt == 0:
+                        got = oracle.gemm_f16(Ax.view(np.float16), Bx.view(np.float16), bool(tb), alpha, beta,
+                                              C0.view(np.float16), True, bool(ta)).view(np.uint16)
+                    else:
+                        got = oracle.gemm_bf16(Ax, Bx, bool(tb), alpha, beta, C0, bool(ta))
+                    assert np.array_equal(got, want), (name, ta, tb, tag)
+
+
 def test_gemm_bf16_against_reference_backend_when_built(oracle):
     """The bfloat16 case of the same loop (conversions lib/ops/gemm_cpu.cpp:217-230): bit for bit."""
     if not oracle.ref_available():

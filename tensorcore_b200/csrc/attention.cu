@@ -61,6 +61,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 // per CTA.
 template <int DC, int G>
 __global__ void __launch_bounds__(kAttnWarps * 32) attention_decode_kernel(const AttnParams p) {
+    // the merge kernel that follows may be set up now; it waits for this grid before it reads anything
+    asm volatile("griddepcontrol.launch_dependents;");
     constexpr int kPer = DC ? DC / 32 : kAttnMaxD / 32;      // output elements per lane
     __shared__ float q_s[G][kAttnMaxD];
     __shared__ float o_s[kAttnWarps][G][kAttnMaxD];
@@ -246,6 +248,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_decode_kernel(const
 // keys: 99.5 -> 83.9 us); the four-head instance was slower that way (233 registers, two CTAs).
 template <int G>
 __global__ void __launch_bounds__(kAttnWarps * 32, G == 1 ? 5 : (G == 2 ? 4 : 1)) attention_decode128_kernel(const AttnParams p) {
+    asm volatile("griddepcontrol.launch_dependents;");
     constexpr int D = 128;
     __shared__ float o_s[kAttnWarps][G][D];
     __shared__ float m_s[kAttnWarps][G], l_s[kAttnWarps][G];
@@ -419,6 +422,9 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const AttnParams p
     __shared__ float red_s[4];
     const int row = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int D = p.D, chunks = p.chunks;
+    // launched with programmatic stream serialisation: the grid that wrote the chunks is complete,
+    // and its writes visible, once this returns (without that launch attribute it returns at once)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const float* base = p.part + static_cast<size_t>(row) * chunks * (D + 2);
     float mc = -INFINITY, lc = 0.f;
     if (tid < chunks) {
@@ -517,8 +523,16 @@ cudaError_t launch_attention_forward(const void* Q, const void* K, const void* V
     if (e != cudaSuccess) return e;
     if (launches) *launches += 1;
     if (chunks > 1) {
-        attention_merge_kernel<<<rows, 128, 0, stream>>>(p);
-        e = cudaGetLastError();
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(rows));
+        cfg.blockDim = dim3(128);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, attention_merge_kernel, p);
         if (e == cudaSuccess && launches) *launches += 1;
     }
     return e;

@@ -212,6 +212,9 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
     const uint32_t raw_base = s_u32(smem + p.off_raw);
     const uint32_t x_base = s_u32(smem + p.off_x);
 
+    // The next kernel on the stream may start its own prologue and weight copies now; what it
+    // reads of this kernel's output it reads behind its own dependency wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (tid == kProducerWarp * 32) prefetch_tensormap(&wmap);
     if (tid == 0) {
         for (int i = 0; i < kRawStages; ++i) {
@@ -261,6 +264,10 @@ gemv_q4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap) {
         xs.set(set, kXStages);
         slot.set(2 * set, kASlots);
         XRegs xr;
+        // Activations and outputs belong to the stream's order: wait for the kernel before this one
+        // here, with the weight copies (which no kernel of a decode step writes) already in flight.
+        // These warps also write the outputs.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         if (set < ng) x_load(p, g0 + set, tl, nb, xr);
         for (int i = set; i < ng && !failed; i += kSets) {
             // Activations of this stage: loaded a stage ago, now permuted into shared memory.
@@ -540,13 +547,18 @@ cudaError_t launch_gemv_q4_tc(const GemvQArgs& a, const LaunchEnv& env, cudaStre
     cfg.blockDim = dim3(kTcThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = split;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (env.pdl) {
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 2;
+    }
     if (name) *name = "q4_0_gemv_tcgen05_sm100";
     return cudaLaunchKernelEx(&cfg, gemv_q4_tc_kernel, p, wmap);
 }

@@ -27,6 +27,9 @@ __global__ void __launch_bounds__(256) norm_forward_kernel(const __half* X, cons
                                                            const __half* beta, __half* Y, float* mean_out,
                                                            float* rstd_out, int D, float eps) {
     __shared__ double scratch[8];
+    // A kernel launched behind this one with programmatic serialization (the batched GEMV that
+    // reads the normalised rows) may begin its prologue and weight copies while the rows are made.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int n = blockIdx.x;
     const __half* xr = X + static_cast<size_t>(n) * D;
     __half* yr = Y + static_cast<size_t>(n) * D;

@@ -37,7 +37,6 @@ cudaError_t launch_gemv_q4_tc(const GemvQArgs& a, const LaunchEnv& env, cudaStre
 cudaError_t init_decode_kernel(int smem_optin);
 namespace {
 
-constexpr int kTcMinBatch = 5;   // smallest M the tcgen05 kernel takes by default (measured: faster from M = 5 on every decode shape)
 
 // ---------------------------------------------------------------------------------------
 // The streaming kernel.
@@ -606,7 +605,7 @@ cudaError_t launch_gemv_q(const GemvQArgs& a, const LaunchEnv& env, cudaStream_t
     // Batched decode: the tcgen05 kernel reads the weights once for up to 32 activation rows.
     // It rounds dequantised weights to fp16, which only the fp16-activation bound allows.
     const bool want_tc = env.variant == VARIANT_TC ||
-                         (env.variant == VARIANT_AUTO && a.M >= kTcMinBatch);
+                         (env.variant == VARIANT_AUTO && batched_tc_rows(a.M, a.N, a.K));
     // The fused RMSNorm form takes it too, behind a pass that normalises the rows into the stream's
     // scratch as fp16 (one more rounding, inside the same bound).
     const size_t slab_rows = a.M < 32 ? a.M : 32;

@@ -34,7 +34,7 @@ struct GemvQArgs {
     int fmt = 0, M = 0, N = 0, K = 0;
     bool x_f32 = false, y_f32 = false;
     float eps = 0.f;
-    // scratch of the stream the call runs on, for the batched fused form (M >= 5, fp16): room for
+    // scratch of the stream the call runs on, for the batched fused form (batched_tc_rows, fp16): room for
     // min(M, 32) normalised rows of K halves and as many floats; without it that form takes the
     // integer dot-product kernels, four rows per pass
     void* norm_scratch = nullptr;
@@ -48,6 +48,14 @@ struct GemvQArgs {
 // Measured on 14336 x 4096: Q4_0 64 rows 63 us on the batched kernel, 96 rows 88 us this way (flat up to
 // 128 rows); Q8_0, which has no batched tensor-core kernel, 64 rows 465 us against about 100 us.
 inline int gemm_min_rows(int fmt) { return fmt == 0 ? 96 : 40; }
+// Whether a Q4_0 call with fp16 activations of M rows goes to the batched tcgen05 kernel by default.
+// Five rows or more always; four rows where the matrix is large enough that two passes' worth of
+// integer dot products cost more than the tensor-core kernel's fixed part (measured back to back on
+// a stream, M = 4: 14336 x 4096 21.3 -> 17.8 us, 4096 x 14336 28.6 -> 20.9, 8192 x 8192 23.4 -> 18.7,
+// 28672 x 8192 59.2 -> 51.5, 1024 x 8192 14.1 -> 10.7, 32000 x 4096 32.0 -> 28.8; 4096 x 4096 stays
+// on the dot-product kernel, 9.6 against 11.0 us; at three rows the two are level or the
+// dot-product kernel wins).
+inline bool batched_tc_rows(int M, int N, int K) { return M >= 5 || (M == 4 && (K >= 8192 || N > 4096)); }
 
 struct DenseNormGemvArgs {
     const void* X = nullptr;      // [M,K] fp16

@@ -238,7 +238,7 @@ bool dequant_gemm_wanted(const tcb::GemvQArgs& a) {
 size_t norm_scratch_need(const tcb::GemvQArgs& a) {
     if (!a.gamma || a.x_f32) return 0;
     if (dequant_gemm_wanted(a)) return static_cast<size_t>(a.M) * a.K * 2 + static_cast<size_t>(a.M) * 4;
-    if (a.fmt != 0 || a.M < 5 || a.K % 256 != 0) return 0;
+    if (a.fmt != 0 || !tcb::batched_tc_rows(a.M, a.N, a.K) || a.K % 256 != 0) return 0;
     const size_t rows = a.M < 32 ? a.M : 32;
     return rows * static_cast<size_t>(a.K) * 2 + rows * 4;
 }

@@ -354,8 +354,8 @@ class FusedBackend(CudaBackend):
 
 class BatchedStep:
     """One decode step for `batch` rows on the shard a TPDecoder already holds: one kernel per
-    projection on a torch stream with fp16 activations (five rows or more take the tensor-core
-    kernel), the partial sums of the K-split projections all-reduced in fp32 by NCCL and rounded
+    projection on a torch stream with fp16 activations (five rows or more, four on large shards, take the
+    tensor-core kernel), the partial sums of the K-split projections all-reduced in fp32 by NCCL and rounded
     to fp16 for the next projection, the per-rank logits gathered as [rank][row][vocab / ranks].
     The step is captured once into a CUDA graph (eager launches if the capture is refused)."""
 

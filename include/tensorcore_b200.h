@@ -152,7 +152,7 @@ tc_status_t tc_quantize_weights(tc_context* ctx, const tc_buffer* W_fp16, tc_buf
 /* Y[M,N] = X[M,K] . W^T, X and Y binary16, fp32 accumulation (quantized_cpu.cpp:164-230).
  * By the number of rows M: one to four rows stream the blocks with integer dot products (a
  * recorded list of one-row Q4_0 calls becomes one persistent launch); five rows or more of Q4_0
- * (four, when K >= 8192 or N > 4096) take the tcgen05 kernel that dequantises into tensor memory; from 96 rows (Q4_0) or 40 rows
+ * (four, when K >= 8192 or N > 4096) take the tcgen05 kernel that dequantises into tensor memory; from 96 rows (Q4_0) or 13 rows
  * (Q8_0) the weights are dequantised once into scratch owned by the stream (N * K halves, at most
  * 1.5 GB, else the previous kinds) and multiplied as a dense GEMM on the tensor cores.  The two
  * tensor-core kinds round the dequantised weights to binary16 (inside the 2e-3 bound of binary16

@@ -45,9 +45,13 @@ struct GemvQArgs {
     void* dequant_scratch = nullptr;
     size_t dequant_scratch_bytes = 0;
 };
-// Measured on 14336 x 4096: Q4_0 64 rows 63 us on the batched kernel, 96 rows 88 us this way (flat up to
-// 128 rows); Q8_0, which has no batched tensor-core kernel, 64 rows 465 us against about 100 us.
-inline int gemm_min_rows(int fmt) { return fmt == 0 ? 96 : 40; }
+// Measured back to back on a stream over rotating weight copies.  Q4_0 14336 x 4096: the batched
+// kernel takes 32 rows a pass, 64 rows 44 us, 80 rows 63 us, against 64 us this way whatever the row
+// count.  Q8_0 has no batched tensor-core kernel and streams the blocks once per 4 rows: 14336 x 4096
+// 8 / 12 / 16 / 32 rows 53 / 80 / 105 / 210 us against 66 - 78 us this way; 4096 x 4096 24 / 35 / 46 /
+// 90 against 31; 28672 x 8192 155 / 232 / 308 / 615 against 243 - on every shape measured the fourth
+// pass (13 rows) is where this way wins.
+inline int gemm_min_rows(int fmt) { return fmt == 0 ? 96 : 13; }
 // Whether a Q4_0 call with fp16 activations of M rows goes to the batched tcgen05 kernel by default.
 // Five rows or more always; four rows where the matrix is large enough that two passes' worth of
 // integer dot products cost more than the tensor-core kernel's fixed part (measured back to back on

@@ -105,7 +105,7 @@ def test_batched_agrees_with_the_streaming_kernel(tc, ctx, oracle, split_env):
 
 
 def test_domain(tc, ctx, oracle, split_env):
-    """fp32 activations, Q8_0, small M and K % 256 != 0 stay off it; the fused RMSNorm form takes it
+    """fp32 activations, Q8_0 (up to 12 rows), small M and K % 256 != 0 stay off the tensor cores; the fused RMSNorm form takes it
     behind a normalisation pass."""
     rng = np.random.default_rng(3)
     N, K, M = 256, 512, 16
@@ -120,8 +120,10 @@ def test_domain(tc, ctx, oracle, split_env):
         names["f32"] = tc.cuda_last_kernel_name()
         ctx.fused_rmsnorm_gemv_quantized(x16, g16, w4, y, 0, M, N, K, 1e-5)
         names["fused"] = tc.cuda_last_kernel_name()
-        ctx.gemv_quantized(x16, w8, y, 1, M, N, K)
+        ctx.gemv_quantized(x16, w8, y, 1, 12, N, K)
         names["q8"] = tc.cuda_last_kernel_name()
+        ctx.gemv_quantized(x16, w8, y, 1, M, N, K)      # 13 rows or more: dequantised once, then the GEMM
+        assert tc.cuda_last_kernel_name() == "q8_0_dequant_gemm_tcgen05_sm100"
         ctx.gemv_quantized(x16, w4, y, 0, 4, N, K)
         names["m4"] = tc.cuda_last_kernel_name()
         ctx.gemv_quantized(x16, w4, y, 0, M, N, K)
@@ -157,10 +159,11 @@ def test_fused_rmsnorm_batched_matches_oracle(tc, ctx, oracle, M, N, K):
         s.close()
 
 
-@pytest.mark.parametrize("fmt", [0, 1])
-@pytest.mark.parametrize("shape", [(1024, 512, 128), (520, 1056, 200), (4096, 4096, 512)])
+@pytest.mark.parametrize("fmt,shape", [(0, (1024, 512, 128)), (0, (520, 1056, 200)), (0, (4096, 4096, 512)),
+                                       (1, (1024, 512, 128)), (1, (520, 1056, 200)), (1, (4096, 4096, 512)),
+                                       (1, (1024, 2048, 13)), (1, (4096, 4096, 32))])
 def test_prefill_sized_calls_dequantise_once_and_use_the_gemm(tc, ctx, oracle, fmt, shape):
-    """96 activation rows or more with fp16 results: the weights are dequantised once to fp16 in the
+    """96 activation rows or more (Q4_0; Q8_0, which has no batched kernel, from 13) with fp16 results: the weights are dequantised once to fp16 in the
     stream's scratch and multiplied on the tensor cores (Q4_0 and Q8_0, plain and fused RMSNorm);
     same bar as the batched kernel, against the fp64 dequantise-and-dot."""
     N, K, M = shape

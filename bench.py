@@ -393,6 +393,8 @@ def gemv_cases(ctx, quick: bool = False) -> list[dict]:
         quant_case(f"config 2: fused RMSNorm + Q8_0 11008x4096, {xd} x", 1, 1, 11008, 4096, xd, xd, True, it)
     for M in (1, 4, 8, 16, 32):
         quant_case(f"config 4: Q4_0 14336x4096, M={M}, fp16 x -> fp32 y", 0, M, 14336, 4096, "f16", "f32", False, it // 2)
+    quant_case("config 2 batched: Q8_0 11008x4096, M=16, fp16 x -> fp16 y (weights dequantised once, then the tcgen05 "
+               "GEMM)", 1, 16, 11008, 4096, "f16", "f16", False, 20)
     for fmt, tag in ((0, "Q4_0"), (1, "Q8_0")):
         quant_case(f"prefill block: {tag} 14336x4096, M=512, fp16 x -> fp16 y (weights dequantised once, then the "
                    "tcgen05 GEMM)", fmt, 512, 14336, 4096, "f16", "f16", False, 20)

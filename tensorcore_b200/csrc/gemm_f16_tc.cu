@@ -36,7 +36,7 @@ namespace {
 using namespace sm100;
 
 constexpr int kBM = 128, kBK = 64;
-constexpr int kStages = 4;
+constexpr int kMaxStages = 12;   // the ring is as deep as shared memory allows, up to this
 constexpr int kAStage = kBM * kBK * 2;
 constexpr int kGemmThreads = 6 * 32;          // producer, MMA issuer, four epilogue warps
 constexpr int kGemmBarBytes = 1024;
@@ -50,11 +50,18 @@ struct GemmParams {
     int b_kmajor;      // B was given transposed ([N][K])
     int a_mnmajor;     // A was given transposed ([K][M])
     int bf16;          // operands and result are bfloat16 (else binary16)
+    // Bytes one stage's copy of A delivers.  With fewer than 128 rows of A (given row-major) the box
+    // holds only the rows there are, rounded up to the 8-row swizzle atom: the tile's other rows stay
+    // whatever shared memory held, and feed accumulator rows that the epilogue never stores.
+    uint32_t a_tx;
+    uint32_t a_stage;  // bytes between the stages of the A ring (a_tx rounded to the 1024-byte swizzle atom)
+    int stages;        // ring depth: a stage's copy takes about 1.4 us to land, so a call that streams B
+                       // with few rows of A needs many stages in flight to use the memory system
 };
 
 struct GemmBars {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t acc_full[2];     // MMA issuer -> epilogue warps, per accumulator
     uint64_t acc_empty[2];    // epilogue warps -> MMA issuer
     uint64_t drain;
@@ -76,7 +83,9 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
     GemmBars* bars = reinterpret_cast<GemmBars*>(smem);
     volatile int* abort_flag = &bars->abort_flag;
     uint8_t* a_ring = smem + kGemmBarBytes;
-    uint8_t* b_ring = a_ring + kStages * kAStage;
+    const int stages = p.stages;
+    const uint32_t a_stage = p.a_stage;
+    uint8_t* b_ring = a_ring + stages * a_stage;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ksteps = (p.K + kBK - 1) / kBK;
     // Tiles of C, numbered column-block-major (the CTAs running at the same time share a block of B's
@@ -85,7 +94,7 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
     const int n_tiles = tiles_m * tiles_n;
 
     if (tid == 0) {
-        for (int i = 0; i < kStages; ++i) { bar_init(&bars->full[i], 1); bar_init(&bars->empty[i], 1); }
+        for (int i = 0; i < stages; ++i) { bar_init(&bars->full[i], 1); bar_init(&bars->empty[i], 1); }
         for (int i = 0; i < 2; ++i) { bar_init(&bars->acc_full[i], 1); bar_init(&bars->acc_empty[i], 4); }
         bar_init(&bars->drain, 1);
         bars->abort_flag = 0;
@@ -102,19 +111,18 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
 
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
+            int issued = 0, s = 0;
+            uint32_t par = 0;
             for (int t = blockIdx.x; t < n_tiles && !failed; t += gridDim.x) {
                 const int m0 = (t % tiles_m) * kBM, n0 = (t / tiles_m) * BN;
-                for (int ks = 0; ks < ksteps; ++ks, ++issued) {
-                    const int s = issued % kStages;
-                    const uint32_t par = static_cast<uint32_t>(issued / kStages) & 1u;
+                for (int ks = 0; ks < ksteps; ++ks, ++issued, s = (s + 1 == stages ? 0 : s + 1), par ^= (s == 0 ? 1u : 0u)) {
                     if (!bar_wait(&bars->empty[s], par ^ 1u, abort_flag)) { failed = true; break; }
-                    bar_expect_tx(&bars->full[s], kAStage + kBStage);
+                    bar_expect_tx(&bars->full[s], p.a_tx + kBStage);
                     if (p.a_mnmajor) {       // [K][M]: two boxes of 64 m x 64 k, like B as given
-                        tensor_load_2d(a_ring + s * kAStage, &amap, m0, ks * kBK, &bars->full[s]);
-                        tensor_load_2d(a_ring + s * kAStage + 8192, &amap, m0 + 64, ks * kBK, &bars->full[s]);
+                        tensor_load_2d(a_ring + s * a_stage, &amap, m0, ks * kBK, &bars->full[s]);
+                        tensor_load_2d(a_ring + s * a_stage + 8192, &amap, m0 + 64, ks * kBK, &bars->full[s]);
                     } else {
-                        tensor_load_2d(a_ring + s * kAStage, &amap, ks * kBK, m0, &bars->full[s]);
+                        tensor_load_2d(a_ring + s * a_stage, &amap, ks * kBK, m0, &bars->full[s]);
                     }
                     if (p.b_kmajor) {
                         tensor_load_2d(b_ring + s * kBStage, &bmap, ks * kBK, n0, &bars->full[s]);
@@ -127,9 +135,9 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
             }
             if (failed || *abort_flag) {
                 // Let copies already in flight land before the CTA's shared memory is released.
-                const int first = issued > kStages ? issued - kStages : 0;
+                const int first = issued > stages ? issued - stages : 0;
                 for (int c = first; c < issued; ++c)
-                    bar_wait(&bars->full[c % kStages], static_cast<uint32_t>(c / kStages) & 1u, nullptr, 100000000LL);
+                    bar_wait(&bars->full[c % stages], static_cast<uint32_t>(c / stages) & 1u, nullptr, 100000000LL);
             }
         }
     } else if (warp == 1) {
@@ -137,19 +145,18 @@ gemm_f16_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
             // bit 16: B is MN-major; bits 7-9 and 10-12: operand formats (0 binary16, 1 bfloat16)
             const uint32_t idesc = idesc_f16_f32(kBM, BN) | (p.b_kmajor ? 0u : (1u << 16)) | (p.a_mnmajor ? (1u << 15) : 0u) |
                                    (p.bf16 ? ((1u << 7) | (1u << 10)) : 0u);
-            int used = 0, it = 0;
+            int it = 0, s = 0;
+            uint32_t par = 0;
             for (int t = blockIdx.x; t < n_tiles && !failed; t += gridDim.x, ++it) {
                 const int acc = it & 1;
                 // the accumulator's previous tile (two tiles ago) has been read out
                 if (!bar_wait(&bars->acc_empty[acc], (static_cast<uint32_t>(it >> 1) & 1u) ^ 1u, abort_flag)) { failed = true; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                for (int ks = 0; ks < ksteps; ++ks, ++used) {
-                    const int s = used % kStages;
-                    const uint32_t par = static_cast<uint32_t>(used / kStages) & 1u;
+                for (int ks = 0; ks < ksteps; ++ks, s = (s + 1 == stages ? 0 : s + 1), par ^= (s == 0 ? 1u : 0u)) {
                     if (!bar_wait(&bars->full[s], par, abort_flag)) { failed = true; break; }
                     tc_fence_after_sync();
-                    const uint32_t a_addr = s_u32(a_ring + s * kAStage), b_addr = s_u32(b_ring + s * kBStage);
+                    const uint32_t a_addr = s_u32(a_ring + s * a_stage), b_addr = s_u32(b_ring + s * kBStage);
 #pragma unroll
                     for (int j = 0; j < kBK / 16; ++j) {
                         const uint64_t adesc = p.a_mnmajor ? smem_desc(a_addr + j * 2048, 8192u, 1024u, kSwizzle128)
@@ -276,12 +283,22 @@ template <int BN>
 cudaError_t launch_tile(const GemmParams& p, const void* A, const void* B, int lda, int ldb, bool transpose_b,
                         const LaunchEnv& env, cudaStream_t stream) {
     const bool transpose_a = p.a_mnmajor != 0;
-    const int smem = kGemmBarBytes + kStages * (kAStage + BN * kBK * 2);
-    if (smem > env.smem_optin) return cudaErrorNotSupported;
     CUtensorMap amap, bmap;
+    // A decode batch or a short prefill block has far fewer than 128 rows: copying only those (2 KB
+    // instead of 16 KB a stage at 16 rows) leaves the SM's copy bandwidth to B, which is what such a
+    // call streams.
+    const int a_rows = (!transpose_a && p.M < kBM) ? ((p.M + 7) & ~7) : kBM;
+    GemmParams q = p;
+    q.a_tx = transpose_a ? static_cast<uint32_t>(kAStage) : static_cast<uint32_t>(a_rows) * kBK * 2u;
+    q.a_stage = q.a_tx;     // a multiple of 1024: a_rows is a multiple of 8 rows of 128 bytes
+    const int stage_bytes = static_cast<int>(q.a_stage) + BN * kBK * 2;
+    q.stages = (env.smem_optin - kGemmBarBytes) / stage_bytes;
+    if (q.stages > kMaxStages) q.stages = kMaxStages;
+    if (q.stages < 2) return cudaErrorNotSupported;
+    const int smem = kGemmBarBytes + q.stages * stage_bytes;
     const bool oka = transpose_a
         ? encode_rows_sw128(&amap, A, static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.M), static_cast<uint64_t>(lda), kBK)
-        : encode_rows_sw128(&amap, A, static_cast<uint64_t>(p.M), static_cast<uint64_t>(p.K), static_cast<uint64_t>(lda), kBM);
+        : encode_rows_sw128(&amap, A, static_cast<uint64_t>(p.M), static_cast<uint64_t>(p.K), static_cast<uint64_t>(lda), a_rows);
     if (!oka) return cudaErrorNotSupported;
     const bool okb = transpose_b
         ? encode_rows_sw128(&bmap, B, static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.K), static_cast<uint64_t>(ldb), BN)
@@ -290,7 +307,7 @@ cudaError_t launch_tile(const GemmParams& p, const void* A, const void* B, int l
     const long tiles = static_cast<long>((p.N + BN - 1) / BN) * ((p.M + kBM - 1) / kBM);
     const long sms = env.sm_count > 0 ? env.sm_count : 148;
     const dim3 grid(static_cast<unsigned>(tiles < sms ? tiles : sms));     // one CTA per SM walks the tiles
-    gemm_f16_tc_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(p, amap, bmap);
+    gemm_f16_tc_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(q, amap, bmap);
     return cudaGetLastError();
 }
 
